@@ -1,0 +1,34 @@
+// Arguments shared by the paged attention kernels (plain and tensor-core) and by the
+// merge of split partial results.
+#pragma once
+#include <stdint.h>
+
+struct AttnParams {
+  const void* q;            // [T, H * hd]
+  const void* k_cache;      // this layer's pages: [page][kv_head][page_tokens][hd]
+  const void* v_cache;
+  void* out;                // [T, H * hd]
+  float* part_o;            // [split_rows, H, max_splits, hd] unnormalised partial sums
+  float* part_ml;           // [split_rows, H, max_splits, 2] running maximum and sum
+  const int32_t* q_start;   // [R] first batch row of the request
+  const int32_t* q_len;     // [R] its rows in this step
+  const int32_t* seq_len;   // [R] its context after this step
+  const int32_t* block_table;  // [R, bt_stride] page of logical block i, -1: given back
+  const int32_t* work;      // [num_work, 4]: request (-1: idle), row tile, split, number of splits
+  const int32_t* tok_split_row;  // [T] row of the token in the partial buffers, or -1
+  int bt_stride, num_heads, num_kv_heads, page_tokens;
+  int window;               // 0: all keys; W: keys p-W+1..p
+  int split_keys;           // keys per split, a multiple of the key tile
+  int max_splits;
+  int tile_rows;            // packed rows (query row x head of the group) per row tile
+  float scale;
+};
+
+struct AttnMergeParams {
+  const float* part_o;
+  const float* part_ml;
+  void* out;
+  const int32_t* split_tokens;   // [split_rows] batch row of each split row
+  const int32_t* split_counts;   // [split_rows] number of splits (<= 1: nothing to merge)
+  int num_heads, head_dim, max_splits;
+};

@@ -1,0 +1,241 @@
+// Paged causal attention on the CUDA cores, float32 arithmetic throughout.
+//
+// One kernel serves prompt portions, single decoded tokens and any mix of them: a request
+// brings q_len rows whose positions are seq_len - q_len ... seq_len - 1, and a row at
+// position p reads keys 0..p (or p-W+1..p under a window) from the pages its block table
+// names.  The rows of a request are packed with the query heads that share one key/value
+// head (row-major: packed = row * group + head_in_group), so the group's keys are read
+// once.  Long key ranges of short requests are cut into splits of a fixed number of keys;
+// the partial results are merged by attn_merge_kernel.  Split boundaries depend on the
+// request's own lengths only, never on what else is in the batch.
+//
+// It is the float32 path's attention and the checker for the tensor-core kernel.  It
+// stands where the reference runs paged_mha_kernel.cu:363-550 (decode) and
+// paged_mha_prefill_kernel.cu:120-237,368-520 (prompt portions): s_j = (q.k_j) * scale,
+// online softmax with running maximum and sum, o = acc / l.
+//
+// Compile with -DPBE_HEAD_DIM=<multiple of 16>.
+#include "attention_params.cuh"
+#include "common.cuh"
+
+using namespace pbe;
+
+#ifndef PBE_HEAD_DIM
+#error "PBE_HEAD_DIM must be defined"
+#endif
+
+namespace {
+constexpr int HD = PBE_HEAD_DIM;
+constexpr int BM = 16;       // packed rows per block
+constexpr int BN = 32;       // keys per tile, one per lane
+constexpr int NWARPS = 4;
+constexpr int ROWS_PER_WARP = BM / NWARPS;
+constexpr int DPL = (HD + 31) / 32;   // output dims per lane
+
+template <typename T>
+__global__ void __launch_bounds__(NWARPS * 32)
+attn_simple_kernel(AttnParams p) {
+  extern __shared__ float smem[];
+  float* Qs = smem;                       // [BM][HD]
+  float* Ks = Qs + BM * HD;               // [BN][HD + 1]
+  float* Vs = Ks + BN * (HD + 1);         // [BN][HD]
+
+  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  const int r = work[0];
+  if (r < 0) return;
+  const int m_tile = work[1], split = work[2], nsplit = work[3];
+  const int kvh = blockIdx.y;
+  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+  const int n_packed = nq * G;
+  const int pr0 = m_tile * BM;
+  if (pr0 >= n_packed) return;
+  const int row_lo = pr0 / G;
+  const int last_pr = min(n_packed, pr0 + BM) - 1;
+  const int row_hi = last_pr / G;
+  const int pos0 = sl - nq;
+  const int hi_key = pos0 + row_hi + 1;
+  const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
+  int k_begin = lo_key, k_end = hi_key;
+  if (nsplit > 1) {
+    // split boundaries are absolute multiples of split_keys, counted from the first split
+    // that the request's first row can see; they are the same for every row tile
+    const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int s0 = lo_req / p.split_keys;
+    k_begin = max(lo_key, (s0 + split) * p.split_keys);
+    k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* q = (const T*)p.q;
+  const T* kc = (const T*)p.k_cache;
+  const T* vc = (const T*)p.v_cache;
+  const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
+
+  for (int idx = threadIdx.x; idx < BM * HD; idx += blockDim.x) {
+    const int i = idx / HD, d = idx - i * HD;
+    const int pr = pr0 + i;
+    float v = 0.f;
+    if (pr < n_packed) {
+      const int row = pr / G, hg = pr - row * G;
+      v = to_float(q[((size_t)(qs + row) * H + kvh * G + hg) * HD + d]);
+    }
+    Qs[idx] = v;
+  }
+
+  float m_run[ROWS_PER_WARP], l_run[ROWS_PER_WARP], acc[ROWS_PER_WARP][DPL];
+#pragma unroll
+  for (int j = 0; j < ROWS_PER_WARP; ++j) {
+    m_run[j] = -INFINITY;
+    l_run[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[j][i] = 0.f;
+  }
+
+  const int tile0 = (k_begin / BN) * BN;
+  for (int ts = tile0; ts < k_end; ts += BN) {
+    __syncthreads();   // previous tile fully consumed (and Qs written, first time)
+    for (int j = warp; j < BN; j += NWARPS) {
+      const int key = ts + j;
+      const T* krow = nullptr;
+      const T* vrow = nullptr;
+      if (key >= k_begin && key < k_end) {
+        const int page = bt[key / P];
+        if (page >= 0) {
+          const size_t base = (((size_t)page * KV + kvh) * P + (key % P)) * HD;
+          krow = kc + base;
+          vrow = vc + base;
+        }
+      }
+      for (int d = lane; d < HD; d += 32) {
+        Ks[j * (HD + 1) + d] = krow ? to_float(krow[d]) : 0.f;
+        Vs[j * HD + d] = vrow ? to_float(vrow[d]) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < ROWS_PER_WARP; ++j) {
+      const int i = warp + j * NWARPS;
+      const int pr = pr0 + i;
+      if (pr >= n_packed) continue;
+      const int row = pr / G;
+      const int pos = pos0 + row;
+      const int key = ts + lane;
+      const int row_lo_key = p.window > 0 ? pos - p.window + 1 : 0;
+      const bool visible = key >= k_begin && key < k_end && key <= pos && key >= row_lo_key;
+      float s = 0.f;
+      const float* qrow = Qs + i * HD;
+      const float* krow = Ks + lane * (HD + 1);
+#pragma unroll 8
+      for (int d = 0; d < HD; ++d) s = fmaf(qrow[d], krow[d], s);
+      s = visible ? s * p.scale : -INFINITY;
+      const float m_new = fmaxf(m_run[j], warp_max(s));
+      if (m_new == -INFINITY) continue;     // nothing visible so far
+      const float pj = visible ? expf(s - m_new) : 0.f;
+      const float alpha = expf(m_run[j] - m_new);   // exp(-inf) = 0 on the first visible tile
+      l_run[j] = l_run[j] * alpha + warp_sum(pj);
+      m_run[j] = m_new;
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) acc[j][ii] *= alpha;
+      for (int kk = 0; kk < BN; ++kk) {
+        const float pk = __shfl_sync(0xffffffffu, pj, kk);
+#pragma unroll
+        for (int ii = 0; ii < DPL; ++ii) {
+          const int d = lane + ii * 32;
+          if (d < HD) acc[j][ii] = fmaf(pk, Vs[kk * HD + d], acc[j][ii]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < ROWS_PER_WARP; ++j) {
+    const int i = warp + j * NWARPS;
+    const int pr = pr0 + i;
+    if (pr >= n_packed) continue;
+    const int row = pr / G, hg = pr - row * G;
+    const int head = kvh * G + hg;
+    const int t = qs + row;
+    if (nsplit <= 1) {
+      T* o = (T*)p.out + ((size_t)t * H + head) * HD;
+      const float inv = l_run[j] > 0.f ? 1.0f / l_run[j] : 0.f;
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) {
+        const int d = lane + ii * 32;
+        if (d < HD) o[d] = from_float<T>(acc[j][ii] * inv);
+      }
+    } else {
+      const int srow = p.tok_split_row[t];
+      const size_t base = ((size_t)srow * H + head) * p.max_splits + split;
+      float* po = p.part_o + base * HD;
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) {
+        const int d = lane + ii * 32;
+        if (d < HD) po[d] = acc[j][ii];
+      }
+      if (lane == 0) {
+        p.part_ml[base * 2] = m_run[j];
+        p.part_ml[base * 2 + 1] = l_run[j];
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void attn_merge_kernel(AttnMergeParams p) {
+  const int srow = blockIdx.x, head = blockIdx.y;
+  const int n = p.split_counts[srow];
+  if (n <= 1) return;
+  const int t = p.split_tokens[srow];
+  const size_t base = ((size_t)srow * p.num_heads + head) * p.max_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < n; ++s) m = fmaxf(m, p.part_ml[(base + s) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < n; ++s) {
+    const float ms = p.part_ml[(base + s) * 2];
+    if (ms != -INFINITY) l += p.part_ml[(base + s) * 2 + 1] * expf(ms - m);
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  T* o = (T*)p.out + ((size_t)t * p.num_heads + head) * p.head_dim;
+  for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n; ++s) {
+      const float ms = p.part_ml[(base + s) * 2];
+      if (ms != -INFINITY) a += p.part_o[(base + s) * p.head_dim + d] * expf(ms - m);
+    }
+    o[d] = from_float<T>(a * inv);
+  }
+}
+}  // namespace
+
+PBE_EXPORT int pbe_attn_simple_tile_rows() { return BM; }
+PBE_EXPORT int pbe_attn_simple_key_tile() { return BN; }
+PBE_EXPORT int pbe_attn_simple_head_dim() { return HD; }
+
+PBE_EXPORT int pbe_attn_simple(const AttnParams* params, int num_work, int dtype,
+                               cudaStream_t stream) {
+  if (num_work <= 0) return 0;
+  AttnParams p = *params;
+  if (p.num_heads % p.num_kv_heads != 0 || p.tile_rows != BM || p.split_keys % BN != 0)
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * (BM * HD + BN * (HD + 1) + BN * HD);
+  dim3 grid(num_work, p.num_kv_heads);
+  if (dtype == PBE_F32) {
+    cudaFuncSetAttribute(attn_simple_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_simple_kernel<float><<<grid, NWARPS * 32, smem, stream>>>(p);
+  } else {
+    cudaFuncSetAttribute(attn_simple_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_simple_kernel<__nv_bfloat16><<<grid, NWARPS * 32, smem, stream>>>(p);
+  }
+  return launch_status();
+}
+
+PBE_EXPORT int pbe_attn_merge(const AttnMergeParams* params, int split_rows, int dtype,
+                              cudaStream_t stream) {
+  if (split_rows <= 0) return 0;
+  AttnMergeParams p = *params;
+  dim3 grid(split_rows, p.num_heads);
+  const int threads = p.head_dim >= 128 ? 128 : 64;
+  if (dtype == PBE_F32) attn_merge_kernel<float><<<grid, threads, 0, stream>>>(p);
+  else attn_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(p);
+  return launch_status();
+}

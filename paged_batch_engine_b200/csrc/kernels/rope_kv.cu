@@ -1,0 +1,108 @@
+// Bias add, rotary position encoding of q and k, and the write of k and v into the paged
+// cache, in one pass over the fused QKV projection.
+//
+// Replaces four launches of the reference: add_bias_kernel.cu:7-18 (x3),
+// rope_kernel.cu:149-215 and scatter_kv_kernel.cu:99-126.  The angle pos * freq_i, its
+// sine and cosine, the bias sum and the rotation are float32; each value is rounded once.
+//
+// Cache layout of one layer: [page][kv_head][page_tokens][head_dim] for K and the same
+// for V, so that the keys of one (page, head) are one contiguous tile.
+#include "common.cuh"
+
+using namespace pbe;
+
+struct RopeKvParams {
+  const void* qkv;        // [T, (H + 2*KV) * hd]
+  const float* bias;      // [(H + 2*KV) * hd] or null
+  void* q_out;            // [T, H * hd]
+  void* k_cache;          // this layer's K pages, or null (a layer that reads another layer's cache)
+  void* v_cache;
+  const int32_t* positions;   // [T]
+  const int32_t* slots;       // [T]: page * page_tokens + offset, or < 0: do not write
+  const float* inv_freq;      // [rotary_dim / 2], or null: no rotation
+  int num_tokens, num_heads, num_kv_heads, head_dim, rotary_dim, page_tokens;
+  int interleaved;            // 0: pairs (i, i + rotary_dim/2); 1: pairs (2i, 2i+1)
+};
+
+template <typename T>
+__global__ void rope_kv_kernel(RopeKvParams p) {
+  const int t = blockIdx.x;
+  const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
+  const int row_width = (H + 2 * KV) * hd;
+  const T* in = (const T*)p.qkv + (size_t)t * row_width;
+  const float pos = (float)p.positions[t];
+  const int slot = p.slots ? p.slots[t] : -1;
+  const bool write_kv = p.k_cache != nullptr && slot >= 0;
+  const int page = write_kv ? slot / p.page_tokens : 0;
+  const int off = write_kv ? slot - page * p.page_tokens : 0;
+  const int half = p.rotary_dim / 2;
+  const int rot_heads = H + KV;                       // q heads then k heads are rotated
+  // work items: for rotated heads, one per pair inside rotary_dim and one per element outside it
+  const int per_head = half + (hd - p.rotary_dim);
+  const int n_rot_items = rot_heads * per_head;
+  const int n_v_items = KV * hd;
+  for (int item = threadIdx.x; item < n_rot_items + n_v_items; item += blockDim.x) {
+    if (item < n_rot_items) {
+      const int head = item / per_head;
+      const int j = item - head * per_head;
+      const int base = head * hd;
+      T* dst;
+      if (head < H) {
+        dst = (T*)p.q_out + (size_t)t * H * hd + (size_t)head * hd;
+      } else {
+        if (!write_kv) continue;
+        const int kvh = head - H;
+        dst = (T*)p.k_cache + (((size_t)page * KV + kvh) * p.page_tokens + off) * hd;
+      }
+      if (j < half) {
+        const int i0 = p.interleaved ? 2 * j : j;
+        const int i1 = p.interleaved ? 2 * j + 1 : j + half;
+        float a = to_float(in[base + i0]);
+        float b = to_float(in[base + i1]);
+        if (p.bias) { a += p.bias[base + i0]; b += p.bias[base + i1]; }
+        if (p.inv_freq) {
+          const float angle = pos * p.inv_freq[j];
+          float s, c;
+          sincosf(angle, &s, &c);
+          const float ra = a * c - b * s;
+          const float rb = b * c + a * s;
+          a = ra; b = rb;
+        }
+        dst[i0] = from_float<T>(a);
+        dst[i1] = from_float<T>(b);
+      } else {
+        const int i = p.rotary_dim + (j - half);
+        float a = to_float(in[base + i]);
+        if (p.bias) a += p.bias[base + i];
+        dst[i] = from_float<T>(a);
+      }
+    } else {
+      if (!write_kv) continue;
+      const int e = item - n_rot_items;
+      const int kvh = e / hd, i = e - kvh * hd;
+      const int col = (H + KV) * hd + e;
+      float a = to_float(in[col]);
+      if (p.bias) a += p.bias[col];
+      T* dst = (T*)p.v_cache + (((size_t)page * KV + kvh) * p.page_tokens + off) * hd;
+      dst[i] = from_float<T>(a);
+    }
+  }
+}
+
+PBE_EXPORT int pbe_rope_kv_write(const void* qkv, const float* bias, void* q_out, void* k_cache,
+                                 void* v_cache, const int32_t* positions, const int32_t* slots,
+                                 const float* inv_freq, int num_tokens, int num_heads,
+                                 int num_kv_heads, int head_dim, int rotary_dim, int page_tokens,
+                                 int interleaved, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+  RopeKvParams p{qkv, bias, q_out, k_cache, v_cache, positions, slots, inv_freq, num_tokens,
+                 num_heads, num_kv_heads, head_dim, rotary_dim, page_tokens, interleaved};
+  const int items = (num_heads + num_kv_heads) * (rotary_dim / 2 + head_dim - rotary_dim) +
+                    num_kv_heads * head_dim;
+  int threads = 128;
+  while (threads < 512 && threads * 4 < items) threads *= 2;
+  if (dtype == PBE_F32) rope_kv_kernel<float><<<num_tokens, threads, 0, stream>>>(p);
+  else rope_kv_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(p);
+  return launch_status();
+}

@@ -1,0 +1,338 @@
+"""Python faces of the CUDA entry points: each takes torch tensors on a CUDA device,
+checks what the kernel assumes, and launches on the current stream.
+
+There is no CPU path and no library stand-in for any of these: a tensor that is not on
+a CUDA device is an error, and so is a failed build of the kernel library.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("this engine runs on CUDA devices only: got a tensor on " + str(t.device))
+
+
+def _need_contiguous(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernel operands must be contiguous")
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+_sigs_done = set()
+
+
+def _fn(lib_name, fn_name, argtypes, defines=None):
+    lib = load_library(lib_name, defines)
+    fn = getattr(lib, fn_name)
+    key = (id(lib), fn_name)
+    if key not in _sigs_done:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _sigs_done.add(key)
+    return fn
+
+
+# ------------------------------------------------------------------ elementwise
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] as float32.  ids: int32 [T]."""
+    _need_cuda(out, table, ids)
+    _need_contiguous(out, table, ids)
+    if out.dtype != torch.float32 or ids.dtype != torch.int32:
+        raise KernelError("embedding writes float32 rows from int32 ids")
+    T, d = out.shape
+    if table.shape[1] != d or ids.numel() != T:
+        raise KernelError("embedding: shapes do not agree")
+    fn = _fn("elementwise", "pbe_embedding",
+             [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(out), _ptr(table), _dtype_code(table), _ptr(ids), T, d, table.shape[0], _stream()),
+           "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
+                out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += delta (float32, in place) and out = rmsnorm(residual) * gain.
+
+    With ``rows`` (int32 [n]) output row i is made from batch row rows[i] and the residual
+    is not written."""
+    _need_cuda(residual, delta, gain, out, rows)
+    _need_contiguous(residual, delta, gain, out, rows)
+    if residual.dtype != torch.float32 or gain.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: the residual stream and the gain are float32")
+    d = residual.shape[-1]
+    n = out.shape[0] if out.dim() == 2 else 1
+    if gain.numel() != d or out.shape[-1] != d or (delta is not None and delta.shape != residual.shape):
+        raise KernelError("add_rmsnorm: shapes do not agree")
+    if rows is None and n != residual.shape[0]:
+        raise KernelError("add_rmsnorm: output rows do not match the batch")
+    if rows is not None and (rows.dtype != torch.int32 or rows.numel() != n):
+        raise KernelError("add_rmsnorm: rows must be int32, one per output row")
+    if d * 4 > 200 * 1024:
+        raise KernelError(f"add_rmsnorm: a row of {d} floats does not fit in shared memory")
+    fn = _fn("elementwise", "pbe_add_rmsnorm",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
+              c_void_p])
+    _check(fn(_ptr(residual), _ptr(delta), _dtype_code(delta) if delta is not None else F32,
+              _ptr(gain), _ptr(out), _dtype_code(out), _ptr(rows), n, d, float(eps), _stream()),
+           "add_rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c]."""
+    _need_cuda(gate_up, out)
+    _need_contiguous(gate_up, out)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("silu_mul: shapes or dtypes do not agree")
+    fn = _fn("elementwise", "pbe_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gate_up), _ptr(out), _dtype_code(out), rows, two_i // 2, _stream()), "silu_mul")
+    return out
+
+
+# ------------------------------------------------------------------ rope + cache write
+def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                  k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                  positions: torch.Tensor, slots: Optional[torch.Tensor],
+                  inv_freq: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                  head_dim: int, rotary_dim: int, page_tokens: int, interleaved: bool = False):
+    """q_out = rope(q + b); cache[slot] = rope(k + b), v + b.  k_cache / v_cache are one
+    layer's pages [page, kv_head, page_tokens, head_dim]; None: nothing is written."""
+    _need_cuda(qkv, bias, q_out, k_cache, v_cache, positions, slots, inv_freq)
+    _need_contiguous(qkv, bias, q_out, k_cache, v_cache, positions, slots, inv_freq)
+    T = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width or q_out.shape != (T, num_heads * head_dim) or q_out.dtype != qkv.dtype:
+        raise KernelError("rope_kv_write: shapes or dtypes do not agree")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != width):
+        raise KernelError("rope_kv_write: bias must be float32 of the fused width")
+    if positions.dtype != torch.int32 or positions.numel() != T:
+        raise KernelError("rope_kv_write: positions must be int32 [T]")
+    if k_cache is not None:
+        if slots is None or slots.dtype != torch.int32 or slots.numel() != T:
+            raise KernelError("rope_kv_write: slots must be int32 [T]")
+        for c in (k_cache, v_cache):
+            if c is None or c.dtype != qkv.dtype or tuple(c.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
+                raise KernelError("rope_kv_write: cache pages must be [page, kv_head, page_tokens, head_dim] "
+                                  "in the activations' dtype")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
+    fn = _fn("rope_kv", "pbe_rope_kv_write",
+             [c_void_p] * 8 + [c_int] * 8 + [c_void_p])
+    _check(fn(_ptr(qkv), _ptr(bias), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(positions),
+              _ptr(slots), _ptr(inv_freq), T, num_heads, num_kv_heads, head_dim,
+              rotary_dim if inv_freq is not None else 0, page_tokens, 1 if interleaved else 0,
+              _dtype_code(qkv), _stream()), "rope_kv_write")
+    return q_out
+
+
+# ------------------------------------------------------------------ matrix products
+def sgemm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor):
+    """out = x @ w.T (+ bias) in true float32 arithmetic; w float32 [N, K]."""
+    _need_cuda(x, w, bias, out)
+    _need_contiguous(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.dtype != torch.float32 or w.shape[1] != K or out.shape != (M, N):
+        raise KernelError("sgemm_nt: shapes or dtypes do not agree")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("sgemm_nt: bias must be float32 [N]")
+    fn = _fn("sgemm", "pbe_sgemm_nt",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_void_p])
+    _check(fn(_ptr(x), _dtype_code(x), _ptr(w), _ptr(bias), _ptr(out), _dtype_code(out), M, N, K, K, N,
+              _stream()), "sgemm_nt")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x w^T (+ b).  A float32 weight takes the true-float32 kernel of this package; a
+    bfloat16 weight takes the vendor GEMM library with float32 accumulation, as the
+    reference does for every projection (matmul_kernel_batch.cu:39-208)."""
+    _need_cuda(x, w, bias)
+    out_dtype = out_dtype or x.dtype
+    if w.dtype == torch.float32:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+        return sgemm_nt(x, w, bias, out)
+    if x.dtype != torch.bfloat16:
+        raise KernelError("a bfloat16 weight takes bfloat16 activations")
+    if out_dtype == torch.float32:
+        y = torch.mm(x, w.t(), out_dtype=torch.float32)
+    else:
+        y = torch.mm(x, w.t())
+    if bias is not None:
+        y += bias.to(y.dtype)
+    return y
+
+
+# ------------------------------------------------------------------ attention
+class AttnParams(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("out", c_void_p),
+                ("part_o", c_void_p), ("part_ml", c_void_p), ("q_start", c_void_p),
+                ("q_len", c_void_p), ("seq_len", c_void_p), ("block_table", c_void_p),
+                ("work", c_void_p), ("tok_split_row", c_void_p),
+                ("bt_stride", c_int), ("num_heads", c_int), ("num_kv_heads", c_int),
+                ("page_tokens", c_int), ("window", c_int), ("split_keys", c_int),
+                ("max_splits", c_int), ("tile_rows", c_int), ("scale", c_float)]
+
+
+class AttnMergeParams(ctypes.Structure):
+    _fields_ = [("part_o", c_void_p), ("part_ml", c_void_p), ("out", c_void_p),
+                ("split_tokens", c_void_p), ("split_counts", c_void_p),
+                ("num_heads", c_int), ("head_dim", c_int), ("max_splits", c_int)]
+
+
+SIMPLE_TILE_ROWS = 16   # packed rows per block of the plain attention kernel
+SIMPLE_KEY_TILE = 32
+
+
+def attention_kernel_config(head_dim: int, dtype: torch.dtype, kind: Optional[str] = None):
+    """(kind, tile_rows, key_tile) of the attention kernel used for a head size and dtype."""
+    if head_dim % 16 != 0 or head_dim <= 0 or head_dim > 256:
+        raise KernelError(f"attention kernels take head sizes 16, 32, ..., 256; got {head_dim}")
+    kind = kind or ("mma" if dtype == torch.bfloat16 and _mma_available() else "simple")
+    if kind == "simple":
+        return "simple", SIMPLE_TILE_ROWS, SIMPLE_KEY_TILE
+    return "mma", MMA_TILE_ROWS, MMA_KEY_TILE
+
+
+MMA_TILE_ROWS = 64
+MMA_KEY_TILE = 64
+
+
+def _mma_available() -> bool:
+    import os
+    from .build import KERNEL_DIR
+    return os.path.isfile(os.path.join(KERNEL_DIR, "attention_mma.cu"))
+
+
+def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale, window,
+                    page_tokens, kind="simple"):
+    """Causal attention of every row of the batch over the paged cache.
+
+    ``meta`` carries the step's device arrays for this (group, head grouping, tile size,
+    window): q_start, q_len, seq_len, block_table [R, stride], work [n, 4], tok_split_row,
+    split_tokens, split_counts, max_splits, split_keys, part_o, part_ml."""
+    _need_cuda(q, k_cache, v_cache, out)
+    _need_contiguous(q, k_cache, v_cache, out)
+    if q.dtype != k_cache.dtype or q.dtype != out.dtype:
+        raise KernelError("attention: q, cache and output must share one dtype")
+    if kind == "mma" and q.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention kernel takes bfloat16")
+    lib = "attention_simple" if kind == "simple" else "attention_mma"
+    defines = {"PBE_HEAD_DIM": int(head_dim)}
+    p = AttnParams(
+        q=q.data_ptr(), k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr(), out=out.data_ptr(),
+        part_o=meta.part_o.data_ptr() if meta.part_o is not None else None,
+        part_ml=meta.part_ml.data_ptr() if meta.part_ml is not None else None,
+        q_start=meta.q_start.data_ptr(), q_len=meta.q_len.data_ptr(), seq_len=meta.seq_len.data_ptr(),
+        block_table=meta.block_table.data_ptr(), work=meta.work.data_ptr(),
+        tok_split_row=meta.tok_split_row.data_ptr(), bt_stride=int(meta.bt_stride),
+        num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
+        window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
+        tile_rows=int(meta.tile_rows), scale=float(scale))
+    fn = _fn(lib, "pbe_attn_" + kind, [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p], defines)
+    _check(fn(ctypes.byref(p), int(meta.num_work), _dtype_code(q), _stream()), "paged_attention")
+    if meta.num_split_rows > 0:
+        mp = AttnMergeParams(part_o=meta.part_o.data_ptr(), part_ml=meta.part_ml.data_ptr(),
+                             out=out.data_ptr(), split_tokens=meta.split_tokens.data_ptr(),
+                             split_counts=meta.split_counts.data_ptr(), num_heads=int(num_heads),
+                             head_dim=int(head_dim), max_splits=int(meta.max_splits))
+        mfn = _fn("attention_simple", "pbe_attn_merge",
+                  [ctypes.POINTER(AttnMergeParams), c_int, c_int, c_void_p], defines)
+        _check(mfn(ctypes.byref(mp), int(meta.num_split_rows), _dtype_code(out), _stream()),
+               "attention merge")
+    return out
+
+
+def attention_libraries(head_dim: int, dtype: torch.dtype):
+    """The (library, defines) pairs a model with this head size needs, for parallel builds."""
+    jobs = [("attention_simple", {"PBE_HEAD_DIM": int(head_dim)})]
+    if dtype == torch.bfloat16 and _mma_available():
+        jobs.append(("attention_mma", {"PBE_HEAD_DIM": int(head_dim)}))
+    return jobs
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy token per row; ties go to the lowest id."""
+    _need_cuda(logits, out)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("argmax takes float32 logits with unit column stride")
+    n, V = logits.shape
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    fn = _fn("sampling", "pbe_argmax", [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), n, V, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, uniform, out=None) -> torch.Tensor:
+    """One token per row with per-row temperature (float32), top_k (int32), top_p (float32)
+    and uniform draw (float32)."""
+    _need_cuda(logits, temperature, top_k, top_p, uniform, out)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample takes float32 logits with unit column stride")
+    n, V = logits.shape
+    for t, dt in ((temperature, torch.float32), (top_k, torch.int32), (top_p, torch.float32),
+                  (uniform, torch.float32)):
+        if t.dtype != dt or t.numel() != n or not t.is_contiguous():
+            raise KernelError("sample: per-row parameters must be contiguous, one per row")
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    fn = _fn("sampling", "pbe_sample", [c_void_p, c_ll, c_int, c_int] + [c_void_p] * 6)
+    _check(fn(_ptr(logits), logits.stride(0), n, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+              _ptr(uniform), _ptr(out), _stream()), "sample")
+    return out
+
+
+def apply_penalty(logits, rows, tokens, penalties):
+    """logits[rows[i], tokens[i]] is divided by penalties[i] when positive, multiplied
+    otherwise; every (row, token) pair appears once."""
+    _need_cuda(logits, rows, tokens, penalties)
+    n = rows.numel()
+    if logits.dtype != torch.float32 or rows.dtype != torch.int32 or tokens.dtype != torch.int32 \
+            or penalties.dtype != torch.float32 or tokens.numel() != n or penalties.numel() != n:
+        raise KernelError("apply_penalty: wrong dtypes or sizes")
+    fn = _fn("sampling", "pbe_apply_penalty", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), logits.shape[1], _ptr(rows), _ptr(tokens),
+              _ptr(penalties), n, _stream()), "apply_penalty")
+    return logits

@@ -1,0 +1,266 @@
+"""One step's batch as device arrays.
+
+A step is a list of (request, its next tokens, the places whose logits are wanted).  The
+rows of all requests are laid end to end; a row's position is the request's context
+length before the step plus its offset.  This module turns that list into the integer
+arrays the kernels read (positions, cache slots, block tables, request extents, and the
+attention work lists), packs them into one pinned host buffer and copies them with one
+transfer.
+
+The reference builds the same kind of metadata in ``MixedBatchBuilder``
+(infMain/source/serving/mixed_batch_builder.cpp:100-223: token_ids, positions, seq_lens,
+block_tables padded with -1, logits_indices) and expands it per row in
+``build_row_attention_metadata`` (infMain/source/model/qwen2_batch.cpp:304-469).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+
+SPLIT_KEYS = 256          # keys per split of a short request's long key range
+MAX_SPLIT_TILES = 4       # requests with more row tiles than this are never split
+
+
+@dataclass
+class StepEntry:
+    handle: int                 # the cache manager's request handle
+    tokens: Sequence[int]       # the request's next tokens
+    want: Sequence[int] = ()    # offsets among these tokens whose logits are wanted
+
+
+@dataclass
+class GroupArrays:
+    block_table: torch.Tensor   # int32 [R, stride]
+    bt_stride: int
+    slots: torch.Tensor         # int32 [T]
+
+
+@dataclass
+class AttentionWork:
+    """Device arrays of one attention work list (see ``build_attention_work``)."""
+    q_start: torch.Tensor
+    q_len: torch.Tensor
+    seq_len: torch.Tensor
+    block_table: torch.Tensor
+    bt_stride: int
+    work: torch.Tensor
+    num_work: int
+    tok_split_row: torch.Tensor
+    split_tokens: Optional[torch.Tensor]
+    split_counts: Optional[torch.Tensor]
+    num_split_rows: int
+    max_splits: int
+    split_keys: int
+    tile_rows: int
+    part_o: Optional[torch.Tensor] = None
+    part_ml: Optional[torch.Tensor] = None
+
+
+def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.ndarray,
+                          group_size: int, tile_rows: int, window: Optional[int],
+                          split_keys: int = SPLIT_KEYS, force_split: bool = False,
+                          fixed_splits: int = 0):
+    """Host arrays of an attention work list.
+
+    Each request's rows are packed with the ``group_size`` query heads of a key/value head
+    (packed = row * group_size + head) and cut into tiles of ``tile_rows``.  A request with
+    few tiles and a long key range is also cut along its keys into splits of
+    ``split_keys``, at absolute multiples of ``split_keys``; the number of splits follows
+    from the request's own lengths only.  Returns (work [n,4], tok_split_row [T],
+    split_tokens, split_counts, max_splits).  ``force_split`` lists every row as a split
+    row and ``fixed_splits`` pads every request to that many work items (idle ones carry
+    request -1), which gives a work list of fixed size for a captured graph.
+    """
+    R = len(q_len)
+    q_len = q_len.astype(np.int64)
+    seq_len = seq_len.astype(np.int64)
+    packed = q_len * group_size
+    m_tiles = (packed + tile_rows - 1) // tile_rows
+    pos0 = seq_len - q_len
+    lo_req = np.maximum(0, pos0 - window + 1) if window else np.zeros(R, dtype=np.int64)
+    span_splits = (seq_len + split_keys - 1) // split_keys - lo_req // split_keys
+    can_split = (m_tiles <= MAX_SPLIT_TILES) & (span_splits > 1)
+    n_splits = np.where(can_split, span_splits, 1)
+    if fixed_splits:
+        if (n_splits > fixed_splits).any() or (m_tiles != 1).any():
+            raise ValueError("a fixed-size work list needs one row tile per request and "
+                             "no more splits than its capacity")
+        per_req = np.full(R, fixed_splits, dtype=np.int64)
+    else:
+        per_req = m_tiles * n_splits
+    total = int(per_req.sum())
+    req = np.repeat(np.arange(R, dtype=np.int64), per_req)
+    first = np.cumsum(per_req) - per_req
+    local = np.arange(total, dtype=np.int64) - np.repeat(first, per_req)
+    ns = n_splits[req]
+    work = np.empty((total, 4), dtype=np.int32)
+    if fixed_splits:
+        idle = local >= ns
+        work[:, 0] = np.where(idle, -1, req)
+        work[:, 1] = 0
+        work[:, 2] = np.where(idle, 0, local)
+    else:
+        work[:, 0] = req
+        work[:, 1] = local // ns
+        work[:, 2] = local % ns
+    work[:, 3] = ns
+    T = int(q_len.sum())
+    tok_split_row = np.full(T, -1, dtype=np.int32)
+    is_split = (n_splits > 1) | force_split
+    split_req = np.nonzero(is_split)[0]
+    if len(split_req):
+        rows_per = q_len[split_req]
+        n_rows = int(rows_per.sum())
+        sfirst = np.cumsum(rows_per) - rows_per
+        rreq = np.repeat(split_req, rows_per)
+        off = np.arange(n_rows, dtype=np.int64) - np.repeat(sfirst, rows_per)
+        split_tokens = (q_start[rreq] + off).astype(np.int32)
+        split_counts = n_splits[rreq].astype(np.int32)
+        tok_split_row[split_tokens] = np.arange(n_rows, dtype=np.int32)
+    else:
+        split_tokens = np.zeros(0, dtype=np.int32)
+        split_counts = np.zeros(0, dtype=np.int32)
+    max_splits = int(fixed_splits or (n_splits.max() if R else 1))
+    return work, tok_split_row, split_tokens, split_counts, max_splits
+
+
+class _Packer:
+    """Collects int32 arrays into one buffer; hands out views after a single copy."""
+
+    def __init__(self):
+        self.parts: List[np.ndarray] = []
+        self.offsets: List[Tuple[int, Tuple[int, ...]]] = []
+        self.total = 0
+
+    def add(self, a: np.ndarray) -> int:
+        a = np.ascontiguousarray(a, dtype=np.int32)
+        idx = len(self.parts)
+        self.parts.append(a)
+        self.offsets.append((self.total, a.shape))
+        self.total += (a.size + 3) // 4 * 4      # keep every array 16-byte aligned
+        return idx
+
+    def upload(self, device, pinned: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+        n = max(self.total, 4)
+        if pinned is None or pinned.numel() < n:
+            pinned = torch.empty(n, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        host = pinned.numpy()
+        for a, (o, _) in zip(self.parts, self.offsets):
+            host[o:o + a.size] = a.reshape(-1)
+        if out is None or out.numel() < n:
+            out = torch.empty(n, dtype=torch.int32, device=device)
+        out[:n].copy_(pinned[:n], non_blocking=True)
+        self.device_buffer = out
+        self.pinned = pinned
+        return out
+
+    def view(self, idx: int) -> torch.Tensor:
+        o, shape = self.offsets[idx]
+        n = int(np.prod(shape)) if len(shape) else 1
+        return self.device_buffer[o:o + n].view(shape)
+
+
+class StepContext:
+    """Everything the parts read about the step besides their input rows."""
+
+    def __init__(self, manager: CacheManager, entries: Sequence[StepEntry], device, work_keys,
+                 vocab_size: Optional[int] = None, min_bt_stride: int = 1):
+        self.manager = manager
+        self.page_tokens = manager.page_tokens
+        self.device = device
+        P = self.page_tokens
+        R = len(entries)
+        if R == 0:
+            raise ValueError("a step needs at least one entry")
+        q_len = np.array([len(e.tokens) for e in entries], dtype=np.int64)
+        if (q_len <= 0).any():
+            raise ValueError("every entry of a step brings at least one token")
+        ctx_before = np.array([manager.context_len(e.handle) for e in entries], dtype=np.int64)
+        for e, n, c in zip(entries, q_len, ctx_before):
+            if manager.reserved_len(e.handle) < c + n:
+                raise ValueError("a step's tokens must be backed by pages before it runs "
+                                 "(reserve them with the cache manager)")
+        seq_len = ctx_before + q_len
+        q_start = np.cumsum(q_len) - q_len
+        T = int(q_len.sum())
+        self.num_tokens, self.num_requests = T, R
+        self.q_len_host, self.seq_len_host, self.q_start_host = q_len, seq_len, q_start
+        self.context_before_host = ctx_before
+        self.state_slots_host = np.array([manager.state_slot(e.handle) for e in entries], dtype=np.int64)
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if vocab_size is not None and ((tokens < 0) | (tokens >= vocab_size)).any():
+            bad = tokens[(tokens < 0) | (tokens >= vocab_size)][0]
+            raise ValueError(f"token id {int(bad)} is outside the vocabulary of {vocab_size}")
+        req_of_tok = np.repeat(np.arange(R), q_len)
+        offs = np.arange(T) - q_start[req_of_tok]
+        positions = ctx_before[req_of_tok] + offs
+        want_rows = []
+        for r, e in enumerate(entries):
+            for w in e.want:
+                if not (0 <= int(w) < q_len[r]):
+                    raise ValueError(f"wanted place {w} is outside the entry's {int(q_len[r])} tokens")
+                want_rows.append(int(q_start[r]) + int(w))
+        self.num_wanted = len(want_rows)
+
+        pk = _Packer()
+        i_tokens, i_pos = pk.add(tokens), pk.add(positions)
+        i_qs, i_ql, i_sl = pk.add(q_start), pk.add(q_len), pk.add(seq_len)
+        i_want = pk.add(np.array(want_rows, dtype=np.int64))
+        i_state = pk.add(self.state_slots_host)
+        i_groups = []
+        for g in range(len(manager.groups)):
+            tables = [manager.block_table(e.handle, g) for e in entries]
+            stride = max(min_bt_stride, max(len(t) for t in tables))
+            bt = np.full((R, stride), -1, dtype=np.int32)
+            for r, t in enumerate(tables):
+                bt[r, :len(t)] = t
+            blk = positions // P
+            page = bt[req_of_tok, blk]
+            if (page < 0).any():
+                raise ValueError("a token of this step lies in a page that is not held")
+            slots = page.astype(np.int64) * P + positions % P
+            i_groups.append((pk.add(bt), stride, pk.add(slots)))
+        i_work = {}
+        self._work_host = {}
+        for key in work_keys:
+            group, gsize, tile_rows, window = key
+            work, tsr, st, sc, max_splits = attention_work_arrays(q_len, seq_len, q_start, gsize,
+                                                                  tile_rows, window)
+            i_work[key] = (pk.add(work), len(work), pk.add(tsr), pk.add(st), pk.add(sc), len(st),
+                           max_splits)
+        pk.upload(device)
+        self._packer = pk
+        self.token_ids = pk.view(i_tokens)
+        self.positions = pk.view(i_pos)
+        self.q_start, self.q_len, self.seq_len = pk.view(i_qs), pk.view(i_ql), pk.view(i_sl)
+        self.want_rows = pk.view(i_want)
+        self.state_slots = pk.view(i_state)
+        self._groups = [GroupArrays(pk.view(ib), stride, pk.view(isl)) for ib, stride, isl in i_groups]
+        self._work: Dict[tuple, AttentionWork] = {}
+        for key, (iw, nw, itsr, ist, isc, ns, max_splits) in i_work.items():
+            g = self._groups[key[0]]
+            self._work[key] = AttentionWork(
+                q_start=self.q_start, q_len=self.q_len, seq_len=self.seq_len,
+                block_table=g.block_table, bt_stride=g.bt_stride, work=pk.view(iw), num_work=nw,
+                tok_split_row=pk.view(itsr), split_tokens=pk.view(ist) if ns else None,
+                split_counts=pk.view(isc) if ns else None, num_split_rows=ns, max_splits=max_splits,
+                split_keys=SPLIT_KEYS, tile_rows=key[2])
+
+    def group(self, g: int) -> GroupArrays:
+        return self._groups[g]
+
+    def attention_work(self, group: int, group_size: int, tile_rows: int, window, num_heads: int,
+                       head_dim: int) -> AttentionWork:
+        w = self._work[(group, group_size, tile_rows, window)]
+        if w.num_split_rows and (w.part_o is None or w.part_o.shape[1] != num_heads
+                                 or w.part_o.shape[3] != head_dim):
+            w.part_o = torch.empty((w.num_split_rows, num_heads, w.max_splits, head_dim),
+                                   dtype=torch.float32, device=self.device)
+            w.part_ml = torch.empty((w.num_split_rows, num_heads, w.max_splits, 2),
+                                    dtype=torch.float32, device=self.device)
+        return w

@@ -1,0 +1,98 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config.specs import PartSpec
+from ..csrc import ops
+from ..weights.loader import ParamSpec
+from .base import KVNeed, Mixer, build_part, register_part
+
+
+class GQAttention(Mixer):
+    """q, k, v = x W^T (+ b) as one fused product; position encoding on q and k; k and v
+    written to the cache; causal attention of every row over its request's pages (all
+    keys, or the last ``window``); output projection.
+
+    Reference: infMain/source/model/qwen2_batch.cpp:604-750 (three products, three bias
+    launches, rope, scatter, decode and prefill attention kernels, output product).
+    Checkpoint tensors: {q,k,v}_proj.weight [heads*head_dim, hidden] (+ .bias),
+    o_proj.weight [hidden, heads*head_dim] (+ .bias when o_bias)."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 dtype, device, qkv_bias: bool = True, o_bias: bool = False,
+                 scale: Optional[float] = None, window: Optional[int] = None,
+                 position: Optional[PartSpec] = None, kernel: Optional[str] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.qkv_bias, self.o_bias = head_dim, qkv_bias, o_bias
+        self.scale = float(scale) if scale is not None else head_dim ** -0.5
+        self.window = int(window) if window else None
+        self.dtype, self.device = dtype, device
+        self.position = build_part("position", position, dtype, device) if position is not None \
+            else build_part("position", PartSpec("none"), dtype, device)
+        self.kernel_kind, self.tile_rows, self.key_tile = ops.attention_kernel_config(head_dim, dtype, kernel)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    # ---- what it keeps
+    def cache_need(self):
+        return KVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def work_keys(self):
+        return [(self.num_heads // self.num_kv_heads, self.tile_rows, self.window)]
+
+    def kernel_libraries(self, dtype):
+        return [("elementwise", None), ("rope_kv", None), ("sgemm", None)] + \
+            ops.attention_libraries(self.head_dim, dtype)
+
+    # ---- tensors
+    def param_specs(self, prefix):
+        q_out, kv_out = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        specs = [ParamSpec(prefix + "q_proj.weight", (q_out, self.hidden_size)),
+                 ParamSpec(prefix + "k_proj.weight", (kv_out, self.hidden_size)),
+                 ParamSpec(prefix + "v_proj.weight", (kv_out, self.hidden_size)),
+                 ParamSpec(prefix + "o_proj.weight", (self.hidden_size, q_out))]
+        if self.qkv_bias:
+            specs += [ParamSpec(prefix + "q_proj.bias", (q_out,)),
+                      ParamSpec(prefix + "k_proj.bias", (kv_out,)),
+                      ParamSpec(prefix + "v_proj.bias", (kv_out,))]
+        if self.o_bias:
+            specs.append(ParamSpec(prefix + "o_proj.bias", (self.hidden_size,)))
+        return specs
+
+    def load(self, tensors, prefix):
+        ws = [tensors.pop(prefix + f"{n}_proj.weight") for n in "qkv"]
+        if len({w.dtype for w in ws}) != 1:
+            ws = [w.to(torch.float32) for w in ws]
+        self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        del ws
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors.pop(prefix + f"{n}_proj.bias").to(torch.float32)
+                                    for n in "qkv"]).contiguous()
+        self.w_o = tensors.pop(prefix + "o_proj.weight").contiguous()
+        if self.o_bias:
+            self.b_o = tensors.pop(prefix + "o_proj.bias").to(torch.float32).contiguous()
+
+    # ---- compute
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = ops.linear(x, self.w_qkv, None, out_dtype=self.dtype)
+        q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
+        inv_freq, rotary_dim, interleaved = self.position.kernel_args()
+        group = ctx.group(cache.group)
+        k_pages, v_pages = cache.k, cache.v
+        ops.rope_kv_write(qkv, self.b_qkv, q, k_pages if cache.writes else None,
+                          v_pages if cache.writes else None, ctx.positions, group.slots, inv_freq,
+                          H, KV, hd, rotary_dim, ctx.page_tokens, interleaved)
+        out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
+        meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
+        ops.paged_attention(q, k_pages, v_pages, out, meta, H, KV, hd, self.scale, self.window,
+                            ctx.page_tokens, kind=self.kernel_kind)
+        return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
+
+
+register_part("mixer", "attention", GQAttention, replace=True)

@@ -1,0 +1,122 @@
+"""Interfaces of the parts a decoder is assembled from, and the registry that maps a
+``PartSpec.kind`` to its class.
+
+A part is constructed from its constants alone (sizes, eps, theta, window ...): it never
+sees a model configuration and does not know which architecture it serves.  It states
+which tensors it needs (``param_specs``), takes them (``load``) and computes
+(``forward`` / ``add_norm``).  A new kind of part is added by subclassing one of these
+classes and calling ``register_part``; nothing else in the package has to change.
+
+Interfaces
+----------
+Norm:       ``add_norm(residual, delta, rows=None) -> normed``: residual += delta (float32,
+            in place), then the normalised rows in the run dtype.
+PositionEncoding: ``kernel_args() -> (inv_freq | None, rotary_dim, interleaved)`` for the
+            mixer that applies it, or ``apply(q, k, positions)`` for one that brings its own code.
+Mixer:      ``cache_need() -> KVNeed | StateNeed | None`` (what it keeps between steps) and
+            ``forward(x, ctx, cache) -> y`` over all rows of the step.
+FeedForward: ``forward(x, ctx) -> y``.
+Block:      ``forward(residual, delta, ctx, cache) -> (residual, delta)``: the arrangement
+            of norms, mixer and feed-forward; ``delta`` is the not-yet-added output of the
+            previous part, so that the add is fused with the next norm.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.specs import ConfigError, PartSpec
+from ..weights.loader import ParamSpec
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Keys and values in pages: geometry and lifetime of one cache layer."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A fixed-size state per request (one row per request slot)."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    def param_specs(self, prefix: str) -> List[ParamSpec]:
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
+        pass
+
+    def kernel_libraries(self, dtype: torch.dtype):
+        """(library, defines) pairs this part will launch, so they can be built together."""
+        return []
+
+
+class Norm(Part):
+    def add_norm(self, residual, delta, rows=None, out_dtype=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def kernel_args(self):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def work_keys(self):
+        """Attention work lists this mixer needs from the step: (heads per kv head,
+        tile rows, window) triples."""
+        return []
+
+    def forward(self, x, ctx, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, residual, delta, ctx, cache):
+        raise NotImplementedError
+
+
+_PARTS: Dict[Tuple[str, str], Callable[..., Part]] = {}
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+
+
+def register_part(category: str, kind: str, factory: Callable[..., Part], replace: bool = False):
+    if category not in CATEGORIES:
+        raise ConfigError(f"unknown part category {category!r}; one of {CATEGORIES}")
+    if (category, kind) in _PARTS and not replace:
+        raise ConfigError(f"{category} part {kind!r} is already registered")
+    _PARTS[(category, kind)] = factory
+
+
+def build_block(spec, dtype: torch.dtype, device) -> Block:
+    """A block from its ``BlockSpec``; ``spec.kind`` names the arrangement."""
+    key = ("block", spec.kind)
+    if key not in _PARTS:
+        known = sorted(k for c, k in _PARTS if c == "block")
+        raise ConfigError(f"no block arrangement {spec.kind!r}; known: {', '.join(known)}")
+    return _PARTS[key](spec=spec, dtype=dtype, device=device)
+
+
+def build_part(category: str, spec: PartSpec, dtype: torch.dtype, device) -> Part:
+    key = (category, spec.kind)
+    if key not in _PARTS:
+        known = sorted(k for c, k in _PARTS if c == category)
+        raise ConfigError(f"no {category} part of kind {spec.kind!r}; known: {', '.join(known)}")
+    return _PARTS[key](dtype=dtype, device=device, **spec.args)

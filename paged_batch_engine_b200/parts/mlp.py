@@ -1,0 +1,47 @@
+"""Dense gated feed-forward."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import ParamSpec
+from .base import FeedForward, register_part
+
+
+class SwiGLU(FeedForward):
+    """m = (silu(x W_gate^T) * (x W_up^T)) W_down^T, no biases; gate and up are one fused
+    product.  Reference: infMain/source/model/qwen2_batch.cpp:762-777 and
+    swiglu_kernel.cu:6-25 (g * 1/(1+exp(-g)) * u in float32).
+    Checkpoint tensors: gate_proj.weight, up_proj.weight [inter, hidden]; down_proj.weight
+    [hidden, inter]."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype, device):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.dtype, self.device = dtype, device
+        self.w_gate_up = self.w_down = None
+
+    def kernel_libraries(self, dtype):
+        return [("elementwise", None), ("sgemm", None)]
+
+    def param_specs(self, prefix):
+        i, h = self.intermediate_size, self.hidden_size
+        return [ParamSpec(prefix + "gate_proj.weight", (i, h)),
+                ParamSpec(prefix + "up_proj.weight", (i, h)),
+                ParamSpec(prefix + "down_proj.weight", (h, i))]
+
+    def load(self, tensors, prefix):
+        g, u = tensors.pop(prefix + "gate_proj.weight"), tensors.pop(prefix + "up_proj.weight")
+        if g.dtype != u.dtype:
+            g, u = g.to(torch.float32), u.to(torch.float32)
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        del g, u
+        self.w_down = tensors.pop(prefix + "down_proj.weight").contiguous()
+
+    def forward(self, x, ctx):
+        gu = ops.linear(x, self.w_gate_up, None, out_dtype=self.dtype)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
+        ops.silu_mul(gu, act)
+        return ops.linear(act, self.w_down, None, out_dtype=self.dtype)
+
+
+register_part("feed_forward", "swiglu", SwiGLU, replace=True)
