@@ -58,7 +58,7 @@ def load_config(path_or_dict):
         path = path_or_dict
         if os.path.isdir(path):
             path = os.path.join(path, "config.json")
-        if not os.path.isfile(path):
+        if not os.path.exists(path) or os.path.isdir(path):
             raise ConfigError(f"no config.json at {path}")
         with open(path, "r", encoding="utf-8") as f:
             try:

@@ -219,11 +219,20 @@ PBE_EXPORT int pbe_attn_simple(const AttnParams* params, int num_work, int dtype
     return (int)cudaErrorInvalidValue;
   const size_t smem = sizeof(float) * (BM * HD + BN * (HD + 1) + BN * HD);
   dim3 grid(num_work, p.num_kv_heads);
+  // the shared-memory opt-in is set once per process and kernel, outside any stream capture
+  // that a later launch may be part of
+  static bool opted[2] = {false, false};
   if (dtype == PBE_F32) {
-    cudaFuncSetAttribute(attn_simple_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!opted[0]) {
+      cudaFuncSetAttribute(attn_simple_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      opted[0] = true;
+    }
     attn_simple_kernel<float><<<grid, NWARPS * 32, smem, stream>>>(p);
   } else {
-    cudaFuncSetAttribute(attn_simple_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!opted[1]) {
+      cudaFuncSetAttribute(attn_simple_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      opted[1] = true;
+    }
     attn_simple_kernel<__nv_bfloat16><<<grid, NWARPS * 32, smem, stream>>>(p);
   }
   return launch_status();

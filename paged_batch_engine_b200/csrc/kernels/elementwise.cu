@@ -78,9 +78,12 @@ PBE_EXPORT int pbe_add_rmsnorm(float* residual, const void* delta, int delta_dty
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
 #define LAUNCH(TD, TO)                                                                          \
   do {                                                                                          \
-    if (smem > 48 * 1024)                                                                       \
+    static size_t opted = 48 * 1024;                                                            \
+    if (smem > opted) {                                                                         \
       cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                           (int)smem);                                                          \
+                           200 * 1024);                                                         \
+      opted = 200 * 1024;                                                                       \
+    }                                                                                           \
     add_rmsnorm_kernel<TD, TO><<<num_rows, threads, smem, stream>>>(                            \
         residual, (const TD*)delta, gain, (TO*)out, row_index, d, eps);                         \
   } while (0)

@@ -50,9 +50,20 @@ def _need_contiguous(*tensors):
             raise KernelError("kernel operands must be contiguous")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches of this package issued from Python so far (a captured graph's
+    launches count once, at capture)."""
+    return _launches
+
+
 def _check(code: int, what: str):
+    global _launches
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
+    _launches += 1
 
 
 _sigs_done = set()

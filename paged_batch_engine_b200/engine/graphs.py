@@ -1,0 +1,205 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every request brings exactly one token has the same launches every time;
+only the integers the kernels read change.  Such steps are captured once per (batch
+bucket, key-split bucket) with all integer arrays living in one persistent device buffer
+at fixed offsets, and replayed after a single host-to-device copy of that buffer.  Rows
+beyond the live requests are padding: they write nothing to the cache, carry idle
+attention work items, and their logits are dropped.
+
+Split boundaries and the number of splits per request are the same as in eager steps (they
+follow from the request's own length), so a captured step returns what an eager step
+would.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .batch import (SPLIT_KEYS, AttentionWork, GroupArrays, StepContext, StepEntry,
+                    attention_work_arrays)
+
+
+def _bucket(n: int, cap: Optional[int] = None) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b if cap is None else min(b, max(cap, n))
+
+
+class DecodeStepContext(StepContext):
+    """A StepContext whose arrays are fixed views of one persistent buffer."""
+
+    def __init__(self, manager, device, work_keys, batch: int, splits: int, bt_strides: Sequence[int]):
+        self.manager, self.device = manager, device
+        self.page_tokens = manager.page_tokens
+        self.batch, self.splits = batch, splits
+        self.num_tokens = self.num_requests = self.num_wanted = batch
+        self.work_keys = list(work_keys)
+        B, S = batch, splits
+        off = 0
+        lay: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
+
+        def place(name, shape):
+            nonlocal off
+            n = int(np.prod(shape))
+            lay[name] = (off, tuple(shape))
+            off += (n + 3) // 4 * 4
+        for name in ("tokens", "positions", "q_start", "q_len", "seq_len", "want", "state"):
+            place(name, (B,))
+        for g, stride in enumerate(bt_strides):
+            place(f"bt{g}", (B, stride))
+            place(f"slots{g}", (B,))
+        for i, _ in enumerate(self.work_keys):
+            place(f"work{i}", (B * S, 4))
+            place(f"tsr{i}", (B,))
+            place(f"st{i}", (B,))
+            place(f"sc{i}", (B,))
+        self._layout, self._size = lay, off
+        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
+        self._host_np = self.host.numpy()
+        self.dev = torch.zeros(off, dtype=torch.int32, device=device)
+
+        def view(name):
+            o, shape = lay[name]
+            return self.dev[o:o + int(np.prod(shape))].view(shape)
+        self.token_ids, self.positions = view("tokens"), view("positions")
+        self.q_start, self.q_len, self.seq_len = view("q_start"), view("q_len"), view("seq_len")
+        self.want_rows, self.state_slots = view("want"), view("state")
+        self._groups = [GroupArrays(view(f"bt{g}"), stride, view(f"slots{g}"))
+                        for g, stride in enumerate(bt_strides)]
+        self._work = {}
+        for i, key in enumerate(self.work_keys):
+            grp = self._groups[key[0]]
+            self._work[key] = AttentionWork(
+                q_start=self.q_start, q_len=self.q_len, seq_len=self.seq_len,
+                block_table=grp.block_table, bt_stride=grp.bt_stride, work=view(f"work{i}"),
+                num_work=B * S, tok_split_row=view(f"tsr{i}"), split_tokens=view(f"st{i}"),
+                split_counts=view(f"sc{i}"), num_split_rows=B, max_splits=S, split_keys=SPLIT_KEYS,
+                tile_rows=key[2])
+
+    def _h(self, name):
+        o, shape = self._layout[name]
+        return self._host_np[o:o + int(np.prod(shape))].reshape(shape)
+
+    def fill(self, entries: Sequence[StepEntry], vocab_size: int) -> None:
+        m, B, S, P = self.manager, self.batch, self.splits, self.page_tokens
+        R = len(entries)
+        ctx_before = np.fromiter((m.context_len(e.handle) for e in entries), dtype=np.int64, count=R)
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+        if ((tokens < 0) | (tokens >= vocab_size)).any():
+            raise ValueError("a token id is outside the vocabulary")
+        self.q_len_host = np.ones(R, dtype=np.int64)
+        self.seq_len_host = ctx_before + 1
+        self.q_start_host = np.arange(R, dtype=np.int64)
+        self.context_before_host = ctx_before
+        self.state_slots_host = np.fromiter((m.state_slot(e.handle) for e in entries), dtype=np.int64, count=R)
+        t = self._h("tokens"); t[:] = 0; t[:R] = tokens
+        p = self._h("positions"); p[:] = 0; p[:R] = ctx_before
+        self._h("q_start")[:] = np.arange(B)
+        q = self._h("q_len"); q[:] = 0; q[:R] = 1
+        s = self._h("seq_len"); s[:] = 0; s[:R] = ctx_before + 1
+        self._h("want")[:] = np.arange(B)
+        st = self._h("state"); st[:] = 0; st[:R] = self.state_slots_host
+        for g in range(len(m.groups)):
+            bt = self._h(f"bt{g}")
+            bt[:] = -1
+            for r, e in enumerate(entries):
+                table = m.block_table(e.handle, g)
+                bt[r, :len(table)] = table
+            page = bt[np.arange(R), ctx_before // P]
+            if (page < 0).any():
+                raise ValueError("a token of this step lies in a page that is not held")
+            sl = self._h(f"slots{g}"); sl[:] = -1
+            sl[:R] = page.astype(np.int64) * P + ctx_before % P
+        for i, key in enumerate(self.work_keys):
+            _, gsize, tile_rows, window = key
+            work, tsr, stoks, scnt, _ = attention_work_arrays(
+                self.q_len_host, self.seq_len_host, self.q_start_host, gsize, tile_rows, window,
+                force_split=True, fixed_splits=S)
+            w = self._h(f"work{i}"); w[:] = -1; w[:R * S] = work
+            a = self._h(f"tsr{i}"); a[:] = np.arange(B)
+            a = self._h(f"st{i}"); a[:] = np.arange(B)
+            a = self._h(f"sc{i}"); a[:] = 0; a[:R] = scnt
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def attention_work(self, group, group_size, tile_rows, window, num_heads, head_dim):
+        w = self._work[(group, group_size, tile_rows, window)]
+        if w.part_o is None:
+            w.part_o = torch.empty((self.batch, num_heads, self.splits, head_dim), dtype=torch.float32,
+                                   device=self.device)
+            w.part_ml = torch.empty((self.batch, num_heads, self.splits, 2), dtype=torch.float32,
+                                    device=self.device)
+        return w
+
+
+class DecodeGraphs:
+    """Captured decode steps of one runner, keyed by (batch bucket, split bucket)."""
+
+    def __init__(self, runner, max_context: int):
+        self.runner = runner
+        self.max_context = int(max_context)
+        self.graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, DecodeStepContext, torch.Tensor]] = {}
+        self.replays = 0
+        self.launches_per_replay = 0      # this package's kernels inside one captured step
+        self.last_h2d_bytes = 0           # size of the integer buffer copied before a replay
+
+    def eligible(self, entries: Sequence[StepEntry]) -> bool:
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return False
+        if self.runner.storage.state:      # a mixer with state of its own runs host logic per step
+            return False
+        # one row tile per request is what a fixed work list holds
+        return all(gsize <= tile_rows for _, gsize, tile_rows, _ in self.runner._work_keys)
+
+    def _splits_needed(self, entries) -> int:
+        m = self.runner.cache
+        longest = max(m.context_len(e.handle) for e in entries) + 1
+        worst = 1
+        for _, _, _, window in self.runner._work_keys:
+            lo = max(0, longest - 1 - window + 1) if window else 0
+            worst = max(worst, (longest + SPLIT_KEYS - 1) // SPLIT_KEYS - lo // SPLIT_KEYS)
+        return worst
+
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        runner = self.runner
+        R = len(entries)
+        B = _bucket(R)
+        S = _bucket(self._splits_needed(entries))
+        key = (B, S)
+        if key not in self.graphs:
+            self.graphs[key] = self._capture(B, S, entries)
+        graph, ctx, logits = self.graphs[key]
+        ctx.fill(entries, runner.model.spec.vocab_size)
+        self.last_h2d_bytes = ctx._size * 4
+        graph.replay()
+        self.replays += 1
+        return logits[:R]
+
+    def _capture(self, B: int, S: int, entries):
+        runner = self.runner
+        P = runner.cache.page_tokens
+        need = max(len(runner.cache.block_table(e.handle, g)) for e in entries
+                   for g in range(len(runner.cache.groups))) if runner.cache.groups else 1
+        cap = max((self.max_context + P - 1) // P, need, 1)
+        strides = [cap for _ in runner.cache.groups]
+        ctx = DecodeStepContext(runner.cache, runner.device, runner._work_keys, B, S, strides)
+        ctx.fill(entries, runner.model.spec.vocab_size)
+        # Warm up on a side stream (library handles, lazy kernel loading), then capture.  The
+        # warm-up and the capture write this step's keys and values to the slots the step
+        # will write anyway, so the cache is not disturbed.
+        side = torch.cuda.Stream(device=runner.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            runner.model.forward(ctx, runner.storage)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        from ..csrc import ops
+        before = ops.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = runner.model.forward(ctx, runner.storage)
+        self.launches_per_replay = ops.launch_count() - before
+        return graph, ctx, logits

@@ -60,7 +60,7 @@ def build_model(config, dtype, device) -> DecoderModel:
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_tokens: int = 16, num_pages=None,
                  max_requests: int = 256, max_cache_tokens: Optional[int] = None, lifo: bool = False,
-                 poison: bool = False):
+                 poison: bool = False, max_context: Optional[int] = None):
         self.model = model
         self.device = model.device
         if num_pages is None:
@@ -72,6 +72,11 @@ class ModelRunner:
         self.cache = self.storage.manager
         self._work_keys = model.work_keys(self.storage)
         self.steps_run = 0
+        self.graphs = None
+        if self.device.type == "cuda":
+            from .graphs import DecodeGraphs
+            cap = self.cache.capacity_tokens()
+            self.graphs = DecodeGraphs(self, min(max_context or model.spec.max_position, cap))
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -99,11 +104,16 @@ class ModelRunner:
         return cls(model, **kw)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], commit: bool = True) -> torch.Tensor:
-        ctx = StepContext(self.cache, entries, self.device, self._work_keys,
-                          vocab_size=self.model.spec.vocab_size)
-        ctx.entries = entries
-        logits = self.model.forward(ctx, self.storage)
+    def step(self, entries: Sequence[StepEntry], commit: bool = True,
+             decode_graph: bool = False) -> torch.Tensor:
+        """Runs the entries as one batch; float32 logits [wanted, vocab] on the device.
+        ``decode_graph``: replay a captured CUDA graph when every entry is a single token."""
+        if decode_graph and self.graphs is not None and self.graphs.eligible(entries):
+            logits = self.graphs.run(entries)
+        else:
+            ctx = StepContext(self.cache, entries, self.device, self._work_keys,
+                              vocab_size=self.model.spec.vocab_size)
+            logits = self.model.forward(ctx, self.storage)
         if commit:
             for e in entries:
                 self.cache.commit(e.handle, len(e.tokens))

@@ -255,7 +255,7 @@ def sample_row(logits: Sequence[float], temperature: float = 0.0, top_k: int = 0
     Reference: infMain/source/model/qwen2.cpp:104-203.
     """
     n = len(logits)
-    vals = [float(torch.tensor(x, dtype=torch.float32)) for x in logits]
+    vals = torch.as_tensor(logits, dtype=torch.float32).tolist()   # float32 values, as the row holds
     greedy = temperature <= 0.0 and top_k <= 0 and top_p >= 1.0 and repetition_penalty == 1.0
     if greedy:
         best, best_val = 0, vals[0]
@@ -269,13 +269,15 @@ def sample_row(logits: Sequence[float], temperature: float = 0.0, top_k: int = 0
             if 0 <= i < n:
                 x = vals[i]
                 x = x / repetition_penalty if x > 0.0 else x * repetition_penalty
-                vals[i] = float(torch.tensor(x, dtype=torch.float32))
+                vals[i] = torch.tensor(x, dtype=torch.float32).item()
     cands = sorted(range(n), key=lambda i: (-vals[i], i))
     k = min(top_k, n) if top_k > 0 else n
     cands = cands[:k]
     t = max(1e-6, float(temperature))
     mx = vals[cands[0]]
-    probs = {i: math.exp(float(torch.tensor(vals[i] - mx, dtype=torch.float32)) / t) for i in cands}
+    diffs = (torch.tensor([vals[i] for i in cands], dtype=torch.float32)
+             - torch.tensor(mx, dtype=torch.float32)).tolist()       # float32 subtraction
+    probs = {i: math.exp(d / t) for i, d in zip(cands, diffs)}
     denom = sum(probs[i] for i in cands)
     if not (denom > 0.0) or not math.isfinite(denom):
         return cands[0]
@@ -306,7 +308,7 @@ def sample_cdf_interval(logits: Sequence[float], token: int, temperature: float,
     mass), or None if the token is not among the kept candidates.  Lets a test state
     how far a uniform draw lies from a decision boundary."""
     n = len(logits)
-    vals = [float(torch.tensor(x, dtype=torch.float32)) for x in logits]
+    vals = torch.as_tensor(logits, dtype=torch.float32).tolist()
     cands = sorted(range(n), key=lambda i: (-vals[i], i))
     k = min(top_k, n) if top_k > 0 else n
     cands = cands[:k]

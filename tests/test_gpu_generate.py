@@ -1,0 +1,155 @@
+"""Generation through the Python entry point and the command line: greedy tokens equal
+the plain implementation's; sampled tokens equal the reference's sampling algorithm on
+plain logits; captured decode graphs, few pages (preemption and recomputation) and
+batching do not change the tokens."""
+import json
+import os
+import subprocess
+
+import pytest
+import torch
+
+from tests.helpers import TINY, load_plain
+from tests.plain import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+
+def prompts_for(vocab, lens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab - 8, (n,), generator=g).tolist() for n in lens]
+
+
+def engine(folder, dtype, page, **kw):
+    from paged_batch_engine_b200 import Engine
+    kw.setdefault("num_pages", 64)
+    kw.setdefault("max_num_batched_tokens", 32)
+    kw.setdefault("prefill_chunk_cap", 16)
+    return Engine(folder, dtype=dtype, page_size=page, **kw)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_equals_plain(tiny_folders, name):
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY[name]
+    folder = tiny_folders[name]
+    pcfg, w = load_plain(folder)
+    prompts = prompts_for(cfg["vocab_size"], [5, 17, 33] if name == "A" else [1, 9, 40, 71])
+    eng = engine(folder, "float32", page)
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=8, ignore_eos=True))
+    for p, r in zip(prompts, res):
+        assert r.output_tokens == plain.greedy_generate(pcfg, w, p, 8), (name, len(p))
+        assert r.finish_reason == "length" and r.prompt_tokens == p
+    assert eng.runner.graphs.replays > 0                  # decode steps went through captured graphs
+    assert eng.runner.cache.num_live_requests == 0
+    # the same without graphs, and one prompt at a time
+    eng2 = engine(folder, "float32", page, use_cuda_graphs=False)
+    for p, r in zip(prompts, res):
+        assert eng2.generate([p], SamplingParams(max_new_tokens=8, ignore_eos=True))[0].output_tokens == r.output_tokens
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_bfloat16_greedy_tokens_are_plain_argmax_up_to_rounding(tiny_folders, name):
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY[name]
+    folder = tiny_folders[name]
+    pcfg, w = load_plain(folder)
+    prompts = prompts_for(cfg["vocab_size"], [9, 40], seed=3)
+    res = engine(folder, "bfloat16", page).generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
+    for p, r in zip(prompts, res):
+        seq = p + r.output_tokens
+        logits = plain.forward_logits(pcfg, w, seq[:-1])
+        for i, tok in enumerate(r.output_tokens):
+            row = logits[len(p) - 1 + i]
+            assert row.max() - row[tok] <= 0.04 * logits.abs().max(), (name, i)
+
+
+def test_temperature_sampling_follows_the_reference_algorithm(tiny_folders):
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["B"]
+    folder = tiny_folders["B"]
+    pcfg, w = load_plain(folder)
+    prompts = prompts_for(cfg["vocab_size"], [1, 9, 40, 71], seed=1)
+    params = [SamplingParams(max_new_tokens=12, temperature=0.8, seed=100 + i, ignore_eos=True)
+              for i in range(len(prompts))]
+    params[2] = SamplingParams(max_new_tokens=12, temperature=1.1, top_k=20, top_p=0.9, seed=5,
+                               repetition_penalty=1.3, ignore_eos=True)
+    eng = engine(folder, "float32", page)
+    res = eng.generate(prompts, params)
+    again = engine(folder, "float32", page, max_num_batched_tokens=7, prefill_chunk_cap=5,
+                   use_cuda_graphs=False).generate(prompts[::-1], params[::-1])[::-1]
+    for p, sp, r, r2 in zip(prompts, params, res, again):
+        assert r.output_tokens == r2.output_tokens          # batch order and portions do not matter
+        seq = p + r.output_tokens
+        logits = plain.forward_logits(pcfg, w, seq[:-1])
+        for i, tok in enumerate(r.output_tokens):
+            row = logits[len(p) - 1 + i].tolist()
+            u = plain.request_sample_uniform(sp.seed, i)
+            want = plain.sample_row(row, sp.temperature, sp.top_k, sp.top_p, sp.repetition_penalty,
+                                    seen_tokens=seq[:len(p) + i], uniform=u)
+            if tok != want:     # only when the draw sits on a boundary of the CDF
+                pen = list(row)
+                if sp.repetition_penalty != 1.0:
+                    for t in set(seq[:len(p) + i]):
+                        pen[t] = pen[t] / sp.repetition_penalty if pen[t] > 0 else pen[t] * sp.repetition_penalty
+                iv = plain.sample_cdf_interval(pen, tok, sp.temperature, sp.top_k, sp.top_p)
+                assert iv is not None and iv[0] - 1e-4 <= u <= iv[1] + 1e-4, (i, tok, want)
+    assert any(len(set(r.output_tokens)) > 3 for r in res)     # it really sampled
+
+
+def test_few_pages_preempt_and_recompute_without_changing_tokens(tiny_folders):
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    prompts = prompts_for(cfg["vocab_size"], [20, 25, 30, 18], seed=7)
+    sp = SamplingParams(max_new_tokens=40, ignore_eos=True)
+    roomy = engine(folder, "float32", page, num_pages=64).generate(prompts, sp)
+    tight_engine = engine(folder, "float32", page, num_pages=9)     # 144 tokens for 4 x (up to 70)
+    tight = tight_engine.generate(prompts, sp)
+    assert tight_engine.scheduler.metrics["preemptions"] > 0
+    assert any(r.preemptions for r in tight)
+    for a, b in zip(roomy, tight):
+        assert a.output_tokens == b.output_tokens and b.finish_reason == "length"
+    tight_engine.runner.cache.check_invariants()
+    assert tight_engine.runner.cache.num_free_pages() == 9
+
+
+def test_eos_stops_generation(tiny_folders):
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    pcfg, w = load_plain(folder)
+    p = prompts_for(cfg["vocab_size"], [12], seed=11)[0]
+    free = plain.greedy_generate(pcfg, w, p, 10)
+    eos = free[4]
+    first = free.index(eos)
+    eng = engine(folder, "float32", page)
+    eng.scheduler.eos = {eos}
+    r = eng.generate([p], SamplingParams(max_new_tokens=10))[0]
+    assert r.output_tokens == free[:first] and r.finish_reason == "stop"
+    r = eng.generate([p], SamplingParams(max_new_tokens=10, ignore_eos=True))[0]
+    assert r.output_tokens == free
+
+
+def test_command_line(tiny_folders, tmp_path):
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    pcfg, w = load_plain(folder)
+    prompts = prompts_for(cfg["vocab_size"], [6, 11], seed=2)
+    cmd = [os.path.join(ROOT, "bin", "pbe-qwen"), folder, "--dtype", "float32", "--max-new-tokens=5",
+           "--ignore-eos", "--kv-cache-blocks-per-layer=32", "--step-profile"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    outs = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert [o["output_ids"] for o in outs] == [plain.greedy_generate(pcfg, w, p, 5) for p in prompts]
+    assert "steps:10" in proc.stdout and "steps/s:" in proc.stdout and "STEP_PROFILE" in proc.stdout
+    # the random-weights mode writes a folder the engine can load
+    cfgfile = tmp_path / "c.json"
+    cfgfile.write_text(json.dumps(TINY["B"][0]))
+    out = tmp_path / "rand"
+    proc = subprocess.run([os.path.join(ROOT, "bin", "pbe-qwen"), "--write-random-model", str(out),
+                           "--config", str(cfgfile), "--weights-seed", "4"], capture_output=True, text=True)
+    assert proc.returncode == 0 and sorted(os.listdir(out)) == ["config.json", "model.safetensors"]

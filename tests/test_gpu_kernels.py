@@ -1,0 +1,373 @@
+"""Each CUDA kernel alone against its plain float32 reference, at sizes other than the
+engine's tiny models: widths and vocabularies that are no power of two, head sizes in
+steps of 16, several head groupings, page sizes, windows and key splits.  Where random
+data would hide a fault (one far key among hundreds, a window's edge, a page's edge) the
+inputs are made so that one key dominates and the output must be that key's value."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from paged_batch_engine_b200.csrc import ops as o
+    return o
+
+
+def bf16_round(t):
+    return t.to(torch.bfloat16).float()
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d,vocab", [(88, 517), (3584, 1003)])
+def test_embedding(dtype, d, vocab):
+    torch.manual_seed(0)
+    table = torch.randn(vocab, d).to(dtype)
+    ids = torch.randint(0, vocab, (37,), dtype=torch.int32)
+    ids[0], ids[1] = 0, vocab - 1
+    out = torch.empty(37, d, dtype=torch.float32, device=DEV)
+    ops().embedding(out, table.to(DEV), ids.to(DEV))
+    assert torch.equal(out.cpu(), plain.embedding(ids.tolist(), table.float()))
+
+
+# ------------------------------------------------------------------ residual add + rmsnorm
+@pytest.mark.parametrize("d", [64, 88, 1000, 3584, 5120])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(d, out_dtype):
+    torch.manual_seed(d)
+    T, eps = 13, 3e-6
+    res = torch.randn(T, d) * 3
+    delta = (torch.randn(T, d) * 2).to(out_dtype)
+    gain = 1 + 0.1 * torch.randn(d)
+    r = res.clone().to(DEV)
+    out = torch.empty(T, d, dtype=out_dtype, device=DEV)
+    ops().add_rmsnorm(r, delta.to(DEV), gain.to(DEV), out, eps)
+    x = res + delta.float()
+    want = plain.rmsnorm(x, gain, eps)
+    assert torch.equal(r.cpu(), x)                          # the sum is exact float32
+    tol = 1e-5 if out_dtype == torch.float32 else 0.0
+    if out_dtype == torch.float32:
+        assert (out.cpu() - want).abs().max() <= 1e-5 * want.abs().max()
+    else:
+        assert (out.float().cpu() - want).abs().max() <= 2 ** -8 * want.abs().max()
+    # no delta: the residual is only normalised
+    r2 = res.clone().to(DEV)
+    out2 = torch.empty(T, d, dtype=out_dtype, device=DEV)
+    ops().add_rmsnorm(r2, None, gain.to(DEV), out2, eps)
+    assert torch.equal(r2.cpu(), res)
+    assert (out2.float().cpu() - plain.rmsnorm(res, gain, eps)).abs().max() <= 2 ** -8 * want.abs().max()
+    # wanted rows only: the residual stays as it was
+    rows = torch.tensor([12, 0, 5], dtype=torch.int32)
+    r3 = res.clone().to(DEV)
+    out3 = torch.empty(3, d, dtype=out_dtype, device=DEV)
+    ops().add_rmsnorm(r3, delta.to(DEV), gain.to(DEV), out3, eps, rows=rows.to(DEV))
+    assert torch.equal(r3.cpu(), res)
+    assert torch.equal(out3.cpu(), out.cpu()[rows.long()])
+
+
+# ------------------------------------------------------------------ silu * up
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,inter", [(1, 208), (19, 18944), (300, 37)])
+def test_silu_mul(dtype, rows, inter):
+    torch.manual_seed(1)
+    gu = (torch.randn(rows, 2 * inter) * 3).to(dtype)
+    out = torch.empty(rows, inter, dtype=dtype, device=DEV)
+    ops().silu_mul(gu.to(DEV), out)
+    want = plain.swiglu(gu.float()[:, :inter], gu.float()[:, inter:])
+    if dtype == torch.float32:
+        assert (out.cpu() - want).abs().max() <= 1e-5
+    else:
+        assert (out.float().cpu() - want).abs().max() <= 2 ** -8 * want.abs().max()
+
+
+# ------------------------------------------------------------------ rope + bias + cache write
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,hd,rot,inter", [(4, 2, 16, 16, False), (6, 3, 48, 48, False),
+                                               (28, 4, 128, 128, False), (5, 1, 32, 16, False),
+                                               (3, 3, 32, 32, True)])
+def test_rope_bias_cache_write(dtype, H, KV, hd, rot, inter):
+    torch.manual_seed(2)
+    T, P, pages, theta = 11, 8, 9, 50000.0
+    width = (H + 2 * KV) * hd
+    qkv = torch.randn(T, width).to(dtype)
+    bias = torch.randn(width) * 0.5
+    pos = torch.tensor([0, 1, 2, 3, 700, 701, 9, 4095, 64, 65, 66], dtype=torch.int32)
+    slots = torch.randperm(pages * P)[:T].to(torch.int32)
+    slots[3] = -1                                            # a row that must not be written
+    inv = plain.rope_inv_freq(rot, theta)
+    kc = torch.full((pages, KV, P, hd), 7.0, dtype=dtype, device=DEV)
+    vc = torch.full((pages, KV, P, hd), 7.0, dtype=dtype, device=DEV)
+    q = torch.empty(T, H * hd, dtype=dtype, device=DEV)
+    ops().rope_kv_write(qkv.to(DEV), bias.to(DEV), q, kc, vc, pos.to(DEV), slots.to(DEV), inv.to(DEV),
+                        H, KV, hd, rot, P, interleaved=inter)
+    x = qkv.float() + bias
+    qf = x[:, :H * hd].view(T, H, hd)
+    kf = x[:, H * hd:(H + KV) * hd].view(T, KV, hd)
+    vf = x[:, (H + KV) * hd:].view(T, KV, hd)
+    rope = plain.rope_interleaved if inter else plain.rope_rotate_half
+
+    def rotate(t):
+        return torch.cat([rope(t[..., :rot], pos, theta), t[..., rot:]], dim=-1)
+    want_q, want_k = rotate(qf), rotate(kf)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -7
+    scale = want_q.abs().max()
+    assert (q.float().cpu().view(T, H, hd) - want_q).abs().max() <= tol * scale
+    kc, vc = kc.float().cpu(), vc.float().cpu()
+    touched = torch.zeros(pages, P, dtype=torch.bool)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        page, off = s // P, s % P
+        touched[page, off] = True
+        assert (kc[page, :, off] - want_k[t]).abs().max() <= tol * scale
+        assert (vc[page, :, off] - vf[t]).abs().max() <= tol * scale
+    untouched = ~touched
+    assert (kc.permute(0, 2, 1, 3)[untouched] == 7.0).all()          # nothing else was written
+    assert (vc.permute(0, 2, 1, 3)[untouched] == 7.0).all()
+    # a layer that reads another layer's cache writes nothing
+    kc2 = torch.full((pages, KV, P, hd), 7.0, dtype=dtype, device=DEV)
+    ops().rope_kv_write(qkv.to(DEV), bias.to(DEV), q, None, None, pos.to(DEV), None, inv.to(DEV),
+                        H, KV, hd, rot, P, interleaved=inter)
+    assert (kc2 == 7.0).all()
+
+
+# ------------------------------------------------------------------ float32 GEMM
+@pytest.mark.parametrize("M,N,K", [(1, 33, 50), (7, 64, 64), (130, 517, 88), (65, 100, 1003)])
+def test_sgemm_true_float32(M, N, K):
+    torch.manual_seed(3)
+    x, w, b = torch.randn(M, K), torch.randn(N, K), torch.randn(N)
+    out = torch.empty(M, N, device=DEV)
+    ops().sgemm_nt(x.to(DEV), w.to(DEV), b.to(DEV), out)
+    want = (x.double() @ w.double().t() + b.double())
+    err = (out.cpu().double() - want).abs().max().item()
+    assert err <= 2e-6 * math.sqrt(K) * 4          # float32 accumulation; TF32 would be ~1e-3
+    # bfloat16 storage in and out, float32 arithmetic
+    xb = x.to(torch.bfloat16)
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops().sgemm_nt(xb.to(DEV), w.to(DEV), None, outb)
+    wantb = xb.double() @ w.double().t()
+    assert (outb.cpu().double() - wantb).abs().max() <= 2 ** -8 * wantb.abs().max()
+
+
+def test_sgemm_rows_do_not_depend_on_the_batch():
+    torch.manual_seed(4)
+    x, w = torch.randn(150, 333, device=DEV), torch.randn(77, 333, device=DEV)
+    full = torch.empty(150, 77, device=DEV)
+    ops().sgemm_nt(x, w, None, full)
+    for lo, hi in [(0, 1), (3, 10), (64, 129), (149, 150)]:
+        part = torch.empty(hi - lo, 77, device=DEV)
+        ops().sgemm_nt(x[lo:hi].contiguous(), w, None, part)
+        assert torch.equal(part, full[lo:hi])       # same summation order: bitwise equal
+
+
+# ------------------------------------------------------------------ paged attention
+class AttnCase:
+    """Requests with a context already in the cache and q_len new rows each; pages handed
+    out in a scrambled order; K and V written by indexing."""
+
+    def __init__(self, H, KV, hd, P, window, reqs, dtype, seed=0, kind="simple", num_pages=None):
+        from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+        from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
+        o = ops()
+        g = torch.Generator().manual_seed(seed)
+        self.H, self.KV, self.hd, self.P, self.window, self.dtype, self.kind = H, KV, hd, P, window, dtype, kind
+        kind_, tile_rows, _ = o.attention_kernel_config(hd, dtype, kind)
+        total_pages = num_pages or sum((c + n + P - 1) // P for c, n in reqs) + 3
+        m = CacheManager([KVGroupSpec((0,), KV, hd, window)], P, total_pages, max_requests=16, lifo=True)
+        # scramble the free list: take all pages and give them back in random order
+        tmp = m.add_request()
+        m.reserve(tmp, total_pages * P)
+        order = torch.randperm(total_pages, generator=g).tolist()
+        pages = list(m.block_table(tmp))
+        m._lookup(tmp).tables[0] = [pages[i] for i in order]
+        m.free(tmp)
+        self.k_pages = torch.full((total_pages, KV, P, hd), float("nan"), dtype=dtype, device=DEV)
+        self.v_pages = torch.full((total_pages, KV, P, hd), float("nan"), dtype=dtype, device=DEV)
+        self.seqs, entries = [], []
+        for ctx_len, n in reqs:
+            h = m.add_request()
+            L = ctx_len + n
+            assert m.reserve(h, L)
+            k = torch.randn(L, KV, hd, generator=g).to(dtype)
+            v = torch.randn(L, KV, hd, generator=g).to(dtype)
+            q = torch.randn(L, H, hd, generator=g).to(dtype)
+            self.seqs.append((q, k, v, ctx_len, n, h))
+            entries.append(StepEntry(h, [0] * n))
+        self.manager = m
+        self._entries = entries
+        self.tile_rows = tile_rows
+
+    def write_cache(self):
+        m, P = self.manager, self.P
+        for q, k, v, ctx_len, n, h in self.seqs:
+            table = m.block_table(h)
+            for p in range(ctx_len + n):
+                self.k_pages[table[p // P], :, p % P] = k[p].to(DEV)
+                self.v_pages[table[p // P], :, p % P] = v[p].to(DEV)
+
+    def run(self):
+        from paged_batch_engine_b200.engine.batch import StepContext
+        o = ops()
+        m = self.manager
+        for q, k, v, ctx_len, n, h in self.seqs:
+            m.commit(h, ctx_len)
+        G = self.H // self.KV
+        key = (0, G, self.tile_rows, self.window)
+        ctx = StepContext(m, self._entries, torch.device(DEV), [key])
+        meta = ctx.attention_work(0, G, self.tile_rows, self.window, self.H, self.hd)
+        qrows = torch.cat([q[c:c + n] for q, k, v, c, n, h in self.seqs]).reshape(-1, self.H * self.hd)
+        out = torch.full_like(qrows, float("nan")).to(DEV)
+        o.paged_attention(qrows.to(DEV).contiguous(), self.k_pages, self.v_pages, out, meta, self.H,
+                          self.KV, self.hd, self.hd ** -0.5, self.window, self.P, kind=self.kind)
+        self.meta = meta
+        return out.float().cpu().view(-1, self.H, self.hd)
+
+    def reference(self):
+        outs = []
+        for q, k, v, ctx_len, n, h in self.seqs:
+            o = plain.causal_attention(q.float(), k.float(), v.float(), self.hd ** -0.5, self.window)
+            outs.append(o[ctx_len:ctx_len + n])
+        return torch.cat(outs)
+
+
+ATTN_SHAPES = [
+    # H, KV, hd, P, window, [(context, new rows)...]
+    (4, 2, 16, 16, None, [(0, 5), (0, 17), (0, 33)]),
+    (6, 1, 32, 8, None, [(40, 1), (0, 9), (71, 1), (3, 40)]),
+    (6, 3, 48, 8, 24, [(0, 50), (30, 1), (23, 2), (100, 7)]),
+    (28, 4, 128, 16, None, [(300, 1), (0, 70), (513, 3)]),
+    (8, 8, 64, 32, None, [(1000, 1), (255, 2), (256, 1), (257, 1)]),
+    (14, 2, 80, 16, 300, [(700, 1), (290, 20), (0, 400)]),
+    (5, 5, 256, 16, None, [(20, 3), (600, 1)]),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", ATTN_SHAPES, ids=lambda s: f"H{s[0]}kv{s[1]}hd{s[2]}P{s[3]}w{s[4]}")
+def test_paged_attention_simple(shape, dtype):
+    H, KV, hd, P, window, reqs = shape
+    case = AttnCase(H, KV, hd, P, window, reqs, dtype, seed=hd)
+    case.write_cache()
+    got, want = case.run(), case.reference()
+    assert not torch.isnan(got).any()
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -7
+    assert (got - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+    if any(c + n > 256 and n * (H // KV) <= 64 for c, n in reqs):
+        assert case.meta.num_split_rows > 0 and case.meta.max_splits > 1   # the split path ran
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_one_key_stands_out(dtype):
+    """One key among many gets a large score: the output row must be that key's value.
+    The special key sits at a page's first and last slot, at a split's edge, at the
+    window's first and last key, and just outside the window (then it must NOT win)."""
+    H, KV, hd, P = 4, 2, 32, 16
+    L = 1030
+    for window, specials in [(None, [0, 15, 16, 255, 256, 511, 512, 1023, 1024, 1029]),
+                             (100, [1029, 930, 929])]:
+        for j in specials:
+            case = AttnCase(H, KV, hd, P, window, [(L - 1, 1)], dtype, seed=j)
+            q, k, v, c, n, h = case.seqs[0]
+            k.mul_(0.05)
+            q[L - 1] = 0
+            q[L - 1, :, 0] = 40.0
+            k[j, :, 0] = 40.0                      # score 1600/sqrt(32) above all others
+            case.write_cache()
+            got = case.run()[0]
+            visible = window is None or j > (L - 1) - window
+            for head in range(H):
+                is_special = torch.allclose(got[head], v[j, head // 2].float(), atol=2e-2)
+                assert is_special == visible, (window, j, head)
+            assert (got - case.reference()[0]).abs().max() <= (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+def test_attention_ignores_stale_data_in_reused_and_foreign_pages():
+    """Pages beyond a request's length and pages of other requests hold NaN or huge
+    values: the result must not change."""
+    H, KV, hd, P = 6, 3, 48, 8
+    case = AttnCase(H, KV, hd, P, None, [(13, 4), (0, 6)], torch.float32, seed=5)
+    case.k_pages.fill_(1e30)
+    case.v_pages.fill_(float("nan"))
+    case.write_cache()
+    got, want = case.run(), case.reference()
+    assert not torch.isnan(got).any() and (got - want).abs().max() <= 2e-5
+
+
+# ------------------------------------------------------------------ sampling
+def test_argmax_ties_go_to_the_lowest_id():
+    torch.manual_seed(6)
+    logits = torch.randn(5, 151937)
+    logits[0, 77] = logits[0, 150000] = 50.0
+    logits[1, 151936] = 60.0
+    logits[2, 0] = 60.0
+    logits[3] = 1.25
+    out = ops().argmax(logits.to(DEV)).cpu().tolist()
+    assert out == [77, 151936, 0, 0, int(torch.argmax(logits[4]))]
+    # a view with a row stride (logits of a wider buffer)
+    wide = torch.randn(4, 1000, device=DEV)
+    assert ops().argmax(wide[:, :517]).cpu().tolist() == torch.argmax(wide[:, :517], dim=1).cpu().tolist()
+
+
+@pytest.mark.parametrize("vocab", [517, 32003])
+def test_sampler_matches_the_reference_algorithm(vocab):
+    rng = np.random.default_rng(vocab)
+    rows = []
+    cases = [(0.8, 0, 1.0), (1.0, 40, 1.0), (0.7, 0, 0.9), (1.3, 50, 0.5), (0.0, 5, 1.0), (1.0, 1, 1.0),
+             (0.5, 0, 0.01), (2.0, 0, 1.0), (0.0, 0, 1.0), (1.0, 200, 0.95)]
+    us = [0.0, 0.03, 0.31, 0.5, 0.77, 0.93, 0.99999]
+    logits = torch.tensor(rng.normal(0, 2.0, size=(len(cases) * len(us), vocab)), dtype=torch.float32)
+    logits[:, 11] = logits[:, 400]                 # exact ties inside every row
+    logits[3, :] = logits[3, :].round()            # many ties
+    t, k, p, u = [], [], [], []
+    for c in cases:
+        for x in us:
+            t.append(c[0]); k.append(c[1]); p.append(c[2]); u.append(x)
+    got = ops().sample(logits.to(DEV), torch.tensor(t, dtype=torch.float32, device=DEV),
+                       torch.tensor(k, dtype=torch.int32, device=DEV),
+                       torch.tensor(p, dtype=torch.float32, device=DEV),
+                       torch.tensor(u, dtype=torch.float32, device=DEV)).cpu().tolist()
+    mismatches = 0
+    for i, tok in enumerate(got):
+        want = plain.sample_row(logits[i].tolist(), t[i], k[i], p[i], uniform=u[i])
+        if tok == want:
+            continue
+        # the only admissible difference: the draw sits within 1e-5 of a boundary of the CDF
+        iv = plain.sample_cdf_interval(logits[i].tolist(), tok, t[i], k[i], p[i])
+        assert iv is not None, (i, tok, want)
+        assert iv[0] - 1e-5 <= u[i] <= iv[1] + 1e-5, (i, tok, want, iv, u[i])
+        mismatches += 1
+    assert mismatches <= 2
+
+
+def test_sampler_does_not_depend_on_the_batch_and_follows_the_distribution():
+    torch.manual_seed(8)
+    V, n = 1003, 4000
+    row = torch.randn(V) * 1.5
+    u = torch.rand(n)
+    logits = row.expand(n, V).contiguous().to(DEV)
+    args = (torch.full((n,), 0.9, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+            torch.ones(n, device=DEV))
+    got = ops().sample(logits, *args, u.to(DEV)).cpu()
+    one = ops().sample(logits[:1].contiguous(), args[0][:1], args[1][:1], args[2][:1], u[:1].to(DEV)).cpu()
+    assert one[0] == got[0]
+    probs = torch.softmax(row.double() / 0.9, dim=0)
+    top = torch.argsort(probs, descending=True)[:5]
+    freq = torch.bincount(got.long(), minlength=V).double() / n
+    for tkn in top.tolist():
+        assert abs(freq[tkn] - probs[tkn]) < 4 * math.sqrt(probs[tkn] * (1 - probs[tkn]) / n) + 1e-3
+
+
+def test_repetition_penalty():
+    logits = torch.tensor([[1.0, -2.0, 4.0, 0.5], [3.0, 3.0, -1.0, 2.0]], device=DEV)
+    ops().apply_penalty(logits, torch.tensor([0, 0, 1], dtype=torch.int32, device=DEV),
+                        torch.tensor([1, 2, 0], dtype=torch.int32, device=DEV),
+                        torch.tensor([2.0, 2.0, 1.5], device=DEV))
+    assert logits.cpu().tolist() == [[1.0, -4.0, 2.0, 0.5], [2.0, 3.0, -1.0, 2.0]]

@@ -1,0 +1,264 @@
+"""Each part of a layer alone against the plain functions, and the framework's openness:
+a toy mixer with state of its own, a toy architecture whose run order names a block twice
+and lets a layer read another layer's cache, all defined here and registered without a
+change to the package's files."""
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import pytest
+import torch
+
+from tests.plain import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ctx(manager, entries, work_keys):
+    from paged_batch_engine_b200.engine.batch import StepContext
+    return StepContext(manager, entries, torch.device(DEV), work_keys)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_and_feed_forward_parts(dtype):
+    from paged_batch_engine_b200.config import PartSpec
+    from paged_batch_engine_b200.parts import build_part
+    torch.manual_seed(0)
+    d, inter, T = 88, 208, 9
+    norm = build_part("norm", PartSpec("rmsnorm", dict(size=d, eps=3e-6)), dtype, DEV)
+    assert [p.name for p in norm.param_specs("x.")] == ["x.weight"]
+    gain = 1 + 0.1 * torch.randn(d)
+    norm.load({"x.weight": gain.to(DEV)}, "x.")
+    res = torch.randn(T, d)
+    r = res.clone().to(DEV)
+    y = norm.add_norm(r, None)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    assert (y.float().cpu() - plain.rmsnorm(res, gain, 3e-6)).abs().max() <= tol * 4
+
+    ffn = build_part("feed_forward", PartSpec("swiglu", dict(hidden_size=d, intermediate_size=inter)), dtype, DEV)
+    w = {"m.gate_proj.weight": torch.randn(inter, d) * 0.1, "m.up_proj.weight": torch.randn(inter, d) * 0.1,
+         "m.down_proj.weight": torch.randn(d, inter) * 0.1}
+    w = {k: v.to(dtype) for k, v in w.items()}
+    assert sorted(p.name for p in ffn.param_specs("m.")) == sorted(w)
+    ffn.load({k: v.to(DEV) for k, v in w.items()}, "m.")
+    x = torch.randn(T, d).to(dtype)
+    got = ffn.forward(x.to(DEV), None).float().cpu()
+    want = plain.feed_forward(x.float(), {k: v.float() for k, v in w.items()}, "m.")
+    assert (got - want).abs().max() <= (1e-5 if dtype == torch.float32 else 0.03) * max(1.0, want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 10])
+def test_attention_part_whole_and_in_portions(dtype, window):
+    from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+    from paged_batch_engine_b200.cache.storage import CacheStorage
+    from paged_batch_engine_b200.config import PartSpec
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    from paged_batch_engine_b200.parts import build_part
+    torch.manual_seed(1)
+    d, H, KV, hd, T, P = 72, 6, 2, 32, 45, 8
+    spec = PartSpec("attention", dict(hidden_size=d, num_heads=H, num_kv_heads=KV, head_dim=hd,
+                                      window=window, qkv_bias=True, o_bias=False,
+                                      position=PartSpec("rope", dict(theta=777.0, head_dim=hd))))
+    attn = build_part("mixer", spec, dtype, DEV)
+    cfg = dict(num_attention_heads=H, num_key_value_heads=KV, head_dim=hd, hidden_size=d, rope_theta=777.0)
+    w = {}
+    for p in attn.param_specs("a."):
+        w[p.name] = (torch.randn(p.shape) * (0.4 if "q_proj.w" in p.name or "k_proj.w" in p.name else 0.15)).to(
+            dtype if len(p.shape) > 1 else torch.float32)
+    attn.load({k: v.to(DEV) for k, v in w.items()}, "a.")
+    x = torch.randn(T, d).to(dtype)
+    want = plain.attention_block(x.float(), torch.arange(T), {k: v.float() for k, v in w.items()}, "a.", cfg, window)
+    storage = CacheStorage([attn.cache_need()], P, 16, 4, dtype, torch.device(DEV), poison=True)
+    keys = [(0,) + k for k in attn.work_keys()]
+    for cuts in ([T], [7, 2, 16, 1, 19]):
+        h = storage.manager.add_request()
+        outs, i = [], 0
+        for n in cuts:
+            assert storage.manager.reserve(h, n)
+            ctx = _ctx(storage.manager, [StepEntry(h, [0] * n)], keys)
+            outs.append(attn.forward(x[i:i + n].to(DEV).contiguous(), ctx, storage.layer(0)).float().cpu())
+            storage.manager.commit(h, n)
+            i += n
+        storage.manager.free(h)
+        got = torch.cat(outs)
+        tol = 2e-5 if dtype == torch.float32 else 0.03
+        assert (got - want).abs().max() <= tol * max(1.0, want.abs().max()), cuts
+
+
+# ------------------------------------------------------------------ toy parts, defined in the test
+def _toy_decay():
+    return 0.75
+
+
+def make_toy_mixer_class():
+    from paged_batch_engine_b200.parts import Mixer, StateNeed
+    from paged_batch_engine_b200.weights import ParamSpec
+
+    class ToyStateMixer(Mixer):
+        """y_t = s_t with s_t = decay * s_{t-1} + x_t * w: a mixer with a fixed-size state per
+        request, no pages.  The state lives in the request's slot between steps."""
+
+        def __init__(self, hidden_size, dtype, device, decay=0.5):
+            self.d, self.decay, self.dtype, self.device = hidden_size, decay, dtype, device
+            self.w = None
+
+        def cache_need(self):
+            return StateNeed((self.d,), torch.float32)
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "mix", (self.d,))]
+
+        def load(self, tensors, prefix):
+            self.w = tensors.pop(prefix + "mix").float()
+
+        def forward(self, x, ctx, cache):
+            y = torch.empty_like(x)
+            for r in range(ctx.num_requests):
+                lo, n = int(ctx.q_start_host[r]), int(ctx.q_len_host[r])
+                slot = int(ctx.state_slots_host[r])
+                s = cache.state[slot]
+                if ctx.context_before_host[r] == 0:
+                    s.zero_()                      # a new request starts from an empty state
+                for t in range(lo, lo + n):
+                    s.mul_(self.decay).add_(x[t].float() * self.w)
+                    y[t] = s.to(x.dtype)
+            return y
+
+    return ToyStateMixer
+
+
+def plain_toy_model(cfg, w, tokens):
+    """The toy architecture, whole sequence, plain: see ToyConfig.model_spec below."""
+    x = plain.embedding(tokens, w["emb"])
+    pos = torch.arange(len(tokens))
+    acfg = dict(num_attention_heads=cfg["heads"], num_key_value_heads=cfg["kv"], head_dim=cfg["hd"],
+                hidden_size=cfg["d"], rope_theta=cfg["theta"])
+
+    def attn_layer(x, p, kv_from=None):
+        h = plain.rmsnorm(x, w[p + "n1.weight"], cfg["eps"])
+        ww = dict(w)
+        if kv_from is not None:        # reads the keys and values another layer computed
+            T, H, KV, hd = len(tokens), cfg["heads"], cfg["kv"], cfg["hd"]
+            q = plain.linear(h, w[p + "at.q_proj.weight"], w[p + "at.q_proj.bias"]).view(T, H, hd)
+            q = plain.rope_rotate_half(q, pos, cfg["theta"])
+            o = plain.causal_attention(q, kv_from[0], kv_from[1], hd ** -0.5)
+            a = plain.linear(o.reshape(T, H * hd), w[p + "at.o_proj.weight"])
+            kv = kv_from
+        else:
+            T, H, KV, hd = len(tokens), cfg["heads"], cfg["kv"], cfg["hd"]
+            k = plain.rope_rotate_half(plain.linear(h, w[p + "at.k_proj.weight"], w[p + "at.k_proj.bias"]).view(T, KV, hd), pos, cfg["theta"])
+            v = plain.linear(h, w[p + "at.v_proj.weight"], w[p + "at.v_proj.bias"]).view(T, KV, hd)
+            a = plain.attention_block(h, pos, ww, p + "at.", acfg, None)
+            kv = (k, v)
+        x = x + a
+        f = plain.rmsnorm(x, w[p + "n2.weight"], cfg["eps"])
+        return x + plain.feed_forward(f, w, p + "ff."), kv
+
+    def toy_layer(x, p):
+        h = plain.rmsnorm(x, w[p + "n1.weight"], cfg["eps"])
+        s = torch.zeros(cfg["d"])
+        out = []
+        for t in range(len(tokens)):
+            s = _toy_decay() * s + h[t] * w[p + "tm.mix"]
+            out.append(s.clone())
+        x = x + torch.stack(out)
+        f = plain.rmsnorm(x, w[p + "n2.weight"], cfg["eps"])
+        return x + plain.feed_forward(f, w, p + "ff.")
+
+    x, kv0 = attn_layer(x, "L0.")            # block 0, cache layer 0
+    x = toy_layer(x, "L1.")                  # block 1, state in cache layer 1
+    x, _ = attn_layer(x, "L2.", kv_from=kv0)  # block 2 reads cache layer 0, writes nothing
+    x = toy_layer(x, "L1.")                  # block 1 again, with a state of its own (cache layer 2)
+    x = plain.rmsnorm(x, w["fn.weight"], cfg["eps"])
+    return plain.linear(x, w["head"])
+
+
+def test_toy_architecture_registers_builds_and_steps():
+    from paged_batch_engine_b200.config import (BlockSpec, ModelSpec, PartSpec, RunStep, load_config,
+                                                register_architecture)
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    from paged_batch_engine_b200.engine.runner import ModelRunner, build_model
+    from paged_batch_engine_b200.parts import register_part
+    from paged_batch_engine_b200.weights import random_state_dict
+
+    register_part("mixer", "toy_state", make_toy_mixer_class(), replace=True)
+
+    @dataclass
+    class ToyConfig:
+        d: int = 40
+        heads: int = 4
+        kv: int = 2
+        hd: int = 16
+        inter: int = 56
+        vocab: int = 97
+        eps: float = 2e-5
+        theta: float = 300.0
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+        def model_spec(self):
+            norm = PartSpec("rmsnorm", dict(size=self.d, eps=self.eps))
+            ffn = PartSpec("swiglu", dict(hidden_size=self.d, intermediate_size=self.inter))
+            attn = PartSpec("attention", dict(hidden_size=self.d, num_heads=self.heads, num_kv_heads=self.kv,
+                                              head_dim=self.hd, position=PartSpec("rope", dict(theta=self.theta, head_dim=self.hd))))
+            toy = PartSpec("toy_state", dict(hidden_size=self.d, decay=_toy_decay()))
+            names = dict(norm_mixer="n1.", norm_feed_forward="n2.", feed_forward="ff.")
+            blocks = (BlockSpec("prenorm", attn, ffn, norm, norm, "L0.", dict(names, mixer="at.")),
+                      BlockSpec("prenorm", toy, ffn, norm, norm, "L1.", dict(names, mixer="tm.")),
+                      BlockSpec("prenorm", attn, ffn, norm, norm, "L2.", dict(names, mixer="at.")))
+            run = (RunStep(0, 0), RunStep(1, 1), RunStep(2, 0, writes_cache=False), RunStep(1, 2))
+            return ModelSpec("ToyForCausalLM", self.d, self.vocab, blocks, run, norm, "emb", "fn.", "head", 512)
+
+    register_architecture("ToyForCausalLM", ToyConfig, replace=True)
+    arch, cfg = load_config({"architectures": ["ToyForCausalLM"], "vocab": 97})
+    assert arch.name == "ToyForCausalLM"
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 0.05)):
+        model = build_model(cfg, dtype, torch.device(DEV))
+        assert [type(n).__name__ for n in model.cache_needs] == ["KVNeed", "StateNeed", "StateNeed"]
+        sd = random_state_dict(model.param_specs(), seed=3, dtype=torch.float32)
+        for k in sd:
+            if "q_proj.weight" in k or "k_proj.weight" in k:
+                sd[k] = sd[k] * 10
+            if k.endswith("mix"):
+                sd[k] = torch.linspace(0.5, 1.5, 40)
+        if dtype == torch.bfloat16:
+            sd = {k: (v.to(torch.bfloat16) if v.dim() > 1 else v) for k, v in sd.items()}
+        model.build_kernels()
+        model.load({k: v.to(DEV) for k, v in sd.items()})
+        runner = ModelRunner(model, page_tokens=8, num_pages=12, max_requests=3)
+        toks = {"a": torch.randint(0, 97, (37,), generator=torch.Generator().manual_seed(1)).tolist(),
+                "b": torch.randint(0, 97, (20,), generator=torch.Generator().manual_seed(2)).tolist()}
+        want = {k: plain_toy_model(cfg.__dict__, {n: t.float() for n, t in sd.items()}, v) for k, v in toks.items()}
+        # whole, then interleaved portions of both requests with single tokens at the end
+        for plan in ([("a", 37)], [("b", 20)],
+                     [("a", 5), ("b", 3), ("a", 2), ("b", 16), ("a", 29), ("b", 1), ("a", 1)]):
+            handles, done, got = {}, {}, {}
+            i = 0
+            while i < len(plan):
+                batch = [plan[i]]
+                if i + 1 < len(plan) and plan[i + 1][0] != plan[i][0] and len(plan) > 2:
+                    batch.append(plan[i + 1])
+                i += len(batch)
+                entries = []
+                for rid, n in batch:
+                    if rid not in handles:
+                        handles[rid] = runner.cache.add_request()
+                        done[rid] = 0
+                    assert runner.cache.reserve(handles[rid], n)
+                    entries.append(StepEntry(handles[rid], toks[rid][done[rid]:done[rid] + n], list(range(n))))
+                logits = runner.step(entries).float().cpu()
+                j = 0
+                for rid, n in batch:
+                    got.setdefault(rid, []).append(logits[j:j + n])
+                    j += n
+                    done[rid] += n
+            for rid in handles:
+                runner.cache.free(handles[rid])
+                out = torch.cat(got[rid])
+                assert out.shape == want[rid][:len(out)].shape
+                err = (out - want[rid][:len(out)]).abs().max().item()
+                assert err <= tol * max(1.0, want[rid].abs().max().item()), (dtype, plan, rid, err)

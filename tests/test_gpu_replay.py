@@ -1,0 +1,191 @@
+"""The engine against the plain implementation under every way of cutting and batching:
+whole requests; most of a request in one step and its last 32 tokens one by one; portions
+of changing size down to two tokens; up to four live requests mixed, with so few pages
+that pages are used again; long decoding; the first tokens of a sequence.  In float32 and
+in bfloat16, on three tiny configurations that differ in every size and option."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import replay_util as ru
+from tests.helpers import TINY, load_plain
+from tests.plain import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+# Stated tolerances on max |logit - plain logit| over all wanted rows.
+#  float32: the engine and the plain implementation differ in summation order only.
+#  bfloat16: activations between kernels are rounded to 8 bits of mantissa; the bound is
+#  relative to the largest logit of the model.
+TOL_F32 = 2e-5
+TOL_BF16_REL = 0.04
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71], "C": [3, 26, 58, 90]}
+
+
+def requests_for(name, vocab, extra=()):
+    g = torch.Generator().manual_seed(sum(map(ord, name)))
+    lens = LENGTHS[name] + list(extra)
+    return {f"{name}{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(lens)}
+
+
+_plain_cache = {}
+
+
+def plain_logits(folder, reqs):
+    cfg, w = load_plain(folder)
+    out = {}
+    for rid, toks in reqs.items():
+        key = (folder, tuple(toks))
+        if key not in _plain_cache:
+            _plain_cache[key] = plain.forward_logits(cfg, w, toks)
+        out[rid] = _plain_cache[key]
+    return out
+
+
+def make_runner(folder, dtype, page, pool_tokens, **kw):
+    from paged_batch_engine_b200.engine.runner import ModelRunner
+    return ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_tokens=page,
+                                   max_cache_tokens=pool_tokens, max_requests=8, poison=True, **kw)
+
+
+def check(got, want, dtype, label):
+    worst, where, scale = ru.max_error(got, want)
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16_REL * scale
+    print(f"\n[replay] {label} {dtype}: max|dlogit| = {worst:.3e} at {where}, max|logit| = {scale:.3f}, tol = {tol:.3e}")
+    assert worst <= tol, (label, dtype, worst, where, "first beyond tolerance:", ru.first_wrong(got, want, tol))
+    n_rows = sum(len(v) for v in got.values())
+    assert n_rows == sum(len(v) for v in want.values() if True) or n_rows > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_schedules_agree_with_plain(tiny_folders, name, dtype):
+    cfg, _, page, _ = TINY[name]
+    folder = tiny_folders[name]
+    reqs = requests_for(name, cfg["vocab_size"])
+    want = plain_logits(folder, reqs)
+    longest = max(len(t) for t in reqs.values())
+    runner = make_runner(folder, dtype, page, pool_tokens=((longest + 63) // 64) * 64)
+    for label, recs in (("whole", ru.whole(reqs)), ("tail32", ru.tail_decoded(reqs)),
+                        ("portions", ru.portions(reqs))):
+        got = ru.run_records(runner, recs)
+        assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in reqs.items()}
+        check(got, want, dtype, f"{name}/{label}")
+        runner.cache.check_invariants()
+        assert runner.cache.num_live_requests == 0
+    # pages were handed out again and again from a pool that holds one request
+    assert runner.cache.pools[0].allocations > runner.cache.pools[0].num_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_batches_with_page_reuse(tiny_folders, name, dtype):
+    cfg, _, page, _ = TINY[name]
+    folder = tiny_folders[name]
+    reqs = requests_for(name, cfg["vocab_size"], extra=(12, 47, 29, 64, 2, 65, 31, 80, 16, 55))
+    want = plain_logits(folder, reqs)
+    for seed in (0, 1):
+        recs = ru.mixed(reqs, max_live=4, seed=seed)
+        pool = ru.pool_tokens_needed(recs)        # the smallest pool the trace may be given
+        runner = make_runner(folder, dtype, page, pool_tokens=pool, lifo=bool(seed))
+        assert max(len(r["entries"]) for r in recs) >= 3
+        assert any(len(e["tokens"]) > 1 for r in recs for e in r["entries"]) and \
+            any(len(e["tokens"]) == 1 and len(r["entries"]) > 1 for r in recs for e in r["entries"])
+        got = ru.run_records(runner, recs)
+        check(got, want, dtype, f"{name}/mixed{seed}")
+        pool0 = runner.cache.pools[0]
+        assert pool0.allocations > pool0.num_pages or max(pool0.generation) >= 2   # pages were used again
+        runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding_and_first_tokens(tiny_folders, name, dtype):
+    """A request decoded one token at a time from its first token to beyond the first
+    key split (256 keys) and, for C, far beyond the window; and requests of one and two
+    tokens."""
+    cfg, _, page, _ = TINY[name]
+    folder = tiny_folders[name]
+    g = torch.Generator().manual_seed(99)
+    reqs = {"long": torch.randint(0, cfg["vocab_size"], (300,), generator=g).tolist(),
+            "one": [7], "two": [3, 5]}
+    want = plain_logits(folder, reqs)
+    runner = make_runner(folder, dtype, page, pool_tokens=320 + 128)
+    recs = ru.tail_decoded({"long": reqs["long"]}, tail=299) + [
+        {"step": 1000, "entries": [{"id": "one", "tokens": [7], "want": [0]},
+                                   {"id": "two", "tokens": [3, 5], "want": [0, 1]}], "end": ["one", "two"]}]
+    got = ru.run_records(runner, recs)
+    check(got, want, dtype, f"{name}/long-decode")
+    if name == "C":   # the windowed group gave pages back while the full group kept them
+        full_g = [i for i, s in enumerate(runner.cache.groups) if s.window is None][0]
+        win_g = [i for i, s in enumerate(runner.cache.groups) if s.window is not None][0]
+        assert runner.cache.pools[win_g].allocations == runner.cache.pools[full_g].allocations
+        assert runner.cache.num_free_pages(win_g) == runner.cache.pools[win_g].num_pages
+
+
+def test_schedules_do_not_change_float32_logits_beyond_rounding(tiny_folders):
+    """Whole, portions and mixed runs of the same requests agree with each other far more
+    closely than with the plain implementation's summation order."""
+    cfg, _, page, _ = TINY["B"]
+    reqs = requests_for("B", cfg["vocab_size"])
+    runner = make_runner(tiny_folders["B"], "float32", page, pool_tokens=512)
+    a = ru.run_records(runner, ru.whole(reqs))
+    b = ru.run_records(runner, ru.portions(reqs))
+    c = ru.run_records(runner, ru.mixed(reqs, seed=3))
+    for other in (b, c):
+        worst = max((a[r][p] - other[r][p]).abs().max().item() for r in a for p in a[r])
+        assert worst <= 2e-5
+
+
+def test_trace_run_program(tiny_folders, tmp_path):
+    """The program itself, as a user calls it: steps on standard input, <step>.f32 files,
+    a ``done`` line after every step, exit code 0."""
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    reqs = requests_for("A", cfg["vocab_size"])
+    want = plain_logits(folder, reqs)
+    recs = ru.mixed(reqs, max_live=4, seed=5)
+    for r in recs:                       # also steps that want nothing, and partial wants
+        if r["step"] % 3 == 1:
+            for e in r["entries"]:
+                e["want"] = e["want"][-1:]
+    recs[2]["entries"][0]["want"] = []
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                               "--out", str(out), "--max-tokens", "256"],
+                              input="".join(json.dumps(r) + "\n" for r in recs), capture_output=True,
+                              text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {r['step']}" for r in recs]
+        progress, worst, scale = {}, 0.0, 0.0
+        for r in recs:
+            n_want = sum(len(e["want"]) for e in r["entries"])
+            path = out / f"{r['step']}.f32"
+            if n_want == 0:
+                assert not path.exists()
+            else:
+                rows = np.fromfile(path, dtype="<f4").reshape(n_want, cfg["vocab_size"])
+                i = 0
+                for e in r["entries"]:
+                    base = progress.get(e["id"], 0)
+                    for w in e["want"]:
+                        ref = want[e["id"]][base + w]
+                        worst = max(worst, float(np.abs(rows[i] - ref.numpy()).max()))
+                        scale = max(scale, float(ref.abs().max()))
+                        i += 1
+            for e in r["entries"]:
+                progress[e["id"]] = progress.get(e["id"], 0) + len(e["tokens"])
+        assert worst <= (TOL_F32 if dtype == "float32" else TOL_BF16_REL * scale), (dtype, worst)
+    # a pool that is too small is an error, not a wrong result
+    proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                           "--out", str(tmp_path / "small"), "--max-tokens", "16"],
+                          input=json.dumps(ru.whole(reqs)[3]) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode != 0 and "cannot hold" in proc.stderr

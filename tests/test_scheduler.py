@@ -1,0 +1,193 @@
+"""The scheduler's decisions with scripted sampled tokens and no model (no GPU), in the
+manner of the reference's scheduler test (test/test_scheduler_radix_cache.cpp:50-135):
+token budget, portion caps, decode first, admission order, finishing, and what happens
+when pages run out (preempt and recompute; fail what can never run)."""
+import pytest
+
+from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+from paged_batch_engine_b200.engine.scheduler import Scheduler, SchedulerConfig
+from paged_batch_engine_b200.sampling.params import SamplingParams, request_sample_uniform
+
+
+def make(pages=64, page=4, **cfg):
+    m = CacheManager([KVGroupSpec((0, 1), 2, 16)], page, pages, max_requests=cfg.pop("slots", 16))
+    defaults = dict(max_num_seqs=8, max_num_batched_tokens=16, prefill_chunk_cap=8)
+    defaults.update(cfg)
+    return m, Scheduler(SchedulerConfig(**defaults), m, eos_token_ids=[99])
+
+
+def drive(s, token_fn=lambda req: 7, max_steps=500):
+    """Runs steps with a scripted sampler; returns the list of per-step entry summaries."""
+    log = []
+    for _ in range(max_steps):
+        if not s.has_active_requests():
+            break
+        out = s.schedule_step()
+        log.append([(e.request.request_id, len(e.tokens), e.samples) for e in out.entries])
+        s.process_outputs(out, [token_fn(e.request) for e in out.entries if e.samples])
+        s.cache.check_invariants()
+    assert not s.has_active_requests()
+    return log
+
+
+def test_prompt_is_cut_under_budget_and_cap_then_decoded():
+    m, s = make()
+    r = s.add_request(list(range(1, 21)), SamplingParams(max_new_tokens=3))
+    log = drive(s)
+    assert log[:3] == [[(0, 8, False)], [(0, 8, False)], [(0, 4, True)]]      # cap 8, last portion samples
+    assert log[3:] == [[(0, 1, True)], [(0, 1, True)]]
+    assert r.outputs == [7, 7, 7] and r.finish_reason == "length" and r.status == "finished"
+    assert m.num_live_requests == 0 and m.num_free_pages() == 64
+
+
+def test_decodes_first_then_running_prompts_then_new_requests():
+    m, s = make(max_num_batched_tokens=10, prefill_chunk_cap=6)
+    a = s.add_request([1] * 3, SamplingParams(max_new_tokens=50))
+    drive_one = lambda: s.process_outputs(o, [7] * sum(e.samples for e in o.entries))
+    o = s.schedule_step(); drive_one()                       # a's prompt; a now decodes
+    b = s.add_request([2] * 14, SamplingParams(max_new_tokens=2))
+    c = s.add_request([3] * 5, SamplingParams(max_new_tokens=2))
+    o = s.schedule_step()
+    assert [(e.request.request_id, len(e.tokens)) for e in o.entries] == [(0, 1), (1, 6), (2, 3)]
+    assert o.num_decode == 1 and o.total_tokens == 10        # the budget is used up exactly
+    drive_one()
+    o = s.schedule_step()
+    # decode row first, then the running prompts in order, each within cap and budget
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in o.entries] == \
+        [(0, 1, True), (1, 6, False), (2, 2, True)]
+    drive_one()
+    o = s.schedule_step()
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in o.entries] == \
+        [(0, 1, True), (2, 1, True), (1, 2, True)]
+
+
+def test_max_num_seqs_and_fifo_admission():
+    m, s = make(max_num_seqs=2)
+    reqs = [s.add_request([5] * 4, SamplingParams(max_new_tokens=2)) for _ in range(4)]
+    o = s.schedule_step()
+    assert [e.request.request_id for e in o.entries] == [0, 1]
+    s.process_outputs(o, [7, 7])
+    log = drive(s)
+    order = [r.request_id for r in s.pop_finished()]
+    assert order == [0, 1, 2, 3]
+
+
+def test_eos_min_new_tokens_and_ignore_eos():
+    m, s = make()
+    a = s.add_request([1, 2], SamplingParams(max_new_tokens=10))
+    b = s.add_request([1, 2], SamplingParams(max_new_tokens=10, min_new_tokens=3))
+    c = s.add_request([1, 2], SamplingParams(max_new_tokens=4, ignore_eos=True))
+    drive(s, token_fn=lambda r: 99)
+    assert a.outputs == [] and a.finish_reason == "stop" and a.generated == 1    # EOS is not part of the output
+    assert b.finish_reason == "stop" and b.generated == 4 and b.outputs == [99, 99, 99]
+    assert c.finish_reason == "length" and c.outputs == [99] * 4
+
+
+def test_portion_is_cut_to_the_free_pages():
+    m, s = make(pages=5, page=4, max_num_batched_tokens=64, prefill_chunk_cap=64)
+    a = s.add_request([1] * 9, SamplingParams(max_new_tokens=2))      # 3 pages
+    o = s.schedule_step(); s.process_outputs(o, [7])
+    b = s.add_request([2] * 13, SamplingParams(max_new_tokens=1))     # needs 4 pages, 2 are free
+    o = s.schedule_step()
+    assert [(e.request.request_id, len(e.tokens)) for e in o.entries] == [(0, 1), (1, 8)]
+    s.process_outputs(o, [7])                                         # a finishes, pages come back
+    o = s.schedule_step()
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in o.entries] == [(1, 5, True)]
+
+
+def test_decode_without_a_page_is_preempted_and_recomputed():
+    m, s = make(pages=4, page=4, max_num_batched_tokens=64, prefill_chunk_cap=64)
+    a = s.add_request([1] * 7, SamplingParams(max_new_tokens=8))
+    b = s.add_request([2] * 7, SamplingParams(max_new_tokens=3))
+    seen = []
+    for _ in range(200):
+        if not s.has_active_requests():
+            break
+        o = s.schedule_step()
+        seen.append(([(e.request.request_id, len(e.tokens), e.samples) for e in o.entries], list(o.preempted)))
+        s.process_outputs(o, [40 + e.request.generated for e in o.entries if e.samples])
+        m.check_invariants()
+    assert not s.has_active_requests()
+    assert s.metrics["preemptions"] >= 1 and any(p for _, p in seen)
+    victim = a if a.preemptions else b
+    # the preempted request came back with its prompt and outputs as one portion to recompute
+    assert any(n > 7 for entries, _ in seen for rid, n, _ in entries if rid == victim.request_id)
+    # every request still received exactly its tokens, in order, despite the recomputation
+    assert a.outputs == [40 + i for i in range(8)] and b.outputs == [40 + i for i in range(3)]
+    assert a.finish_reason == b.finish_reason == "length"
+    assert m.num_free_pages() == 4 and m.num_live_requests == 0
+
+
+def test_preempted_request_waits_until_its_whole_context_fits():
+    m, s = make(pages=12, page=4, max_num_batched_tokens=64, prefill_chunk_cap=64)
+    a = s.add_request([1] * 10, SamplingParams(max_new_tokens=30))
+    b = s.add_request([2] * 10, SamplingParams(max_new_tokens=30))
+    running_when_admitted = []
+    for _ in range(400):
+        if not s.has_active_requests():
+            break
+        o = s.schedule_step()
+        for e in o.entries:
+            if e.request.preemptions and len(e.tokens) > 1 and e.request.computed == 0:
+                # admitted again: room for all its tokens plus the next one was free
+                need = (e.request.target + 1 + 3) // 4
+                running_when_admitted.append(need)
+        s.process_outputs(o, [7] * sum(e.samples for e in o.entries))
+    assert not s.has_active_requests()
+    assert s.metrics["preemptions"] >= 1 and running_when_admitted
+    assert len(a.outputs) == 30 and len(b.outputs) == 30
+    assert a.status == b.status == "finished" and m.num_free_pages() == 12
+
+
+def test_requests_that_can_never_run_fail_instead_of_waiting():
+    m, s = make(pages=3, page=4)
+    too_long = s.add_request([1] * 13)
+    assert too_long.status == "failed" and too_long.finish_reason == "prompt_exceeds_kv_capacity"
+    empty = s.add_request([])
+    assert empty.status == "failed"
+    # fits alone but grows beyond the pool while decoding: preempted, then can never come back
+    r = s.add_request([1] * 10, SamplingParams(max_new_tokens=20))
+    drive(s)
+    assert r.status == "failed" and r.finish_reason == "preempted_recompute_exceeds_kv_capacity"
+    assert r.outputs == [7] * 3                     # 10 + 2 fed tokens filled the 12 slots
+    assert m.num_free_pages() == 3 and m.num_live_requests == 0
+    assert [x.request_id for x in s.pop_finished()] == [0, 1, 2]
+
+
+def test_stalled_prompts_do_not_deadlock():
+    m, s = make(pages=4, page=4, max_num_seqs=2, max_num_batched_tokens=12, prefill_chunk_cap=6)
+    a = s.add_request([1] * 12, SamplingParams(max_new_tokens=1))
+    b = s.add_request([2] * 12, SamplingParams(max_new_tokens=1))
+    drive(s)
+    assert sorted([a.status, b.status]) == ["failed", "finished"]
+    assert "prefill_stalled_kv_exhausted" in (a.finish_reason, b.finish_reason)
+    assert m.num_free_pages() == 4
+
+
+def test_no_request_slot_left_waits():
+    m, s = make(slots=1)
+    a = s.add_request([1] * 3, SamplingParams(max_new_tokens=2))
+    b = s.add_request([1] * 3, SamplingParams(max_new_tokens=2))
+    log = drive(s)
+    assert all(len(step) == 1 for step in log) and a.outputs == b.outputs == [7, 7]
+
+
+def test_long_prompt_threshold_and_cancel():
+    m, s = make(long_prefill_token_threshold=3, prefill_chunk_cap=8)
+    a = s.add_request([1] * 10, SamplingParams(max_new_tokens=1))
+    o = s.schedule_step()
+    assert len(o.entries[0].tokens) == 3
+    s.process_outputs(o, [])
+    s.cancel(a)
+    assert a.finish_reason == "cancelled" and m.num_free_pages() == 64 and not s.has_active_requests()
+
+
+def test_uniform_draws_depend_on_seed_and_counter_only():
+    """test/test_request_progress.cpp:7-52: reorder and retry do not consume random state."""
+    a = [request_sample_uniform(11, c) for c in range(5)]
+    assert a == [request_sample_uniform(11, c) for c in range(5)]
+    assert a != [request_sample_uniform(12, c) for c in range(5)]
+    assert all(0.0 <= u < 1.0 for u in a) and len(set(a)) == 5
+    p = SamplingParams(temperature=-1, top_p=7, top_k=-3, max_new_tokens=0, min_new_tokens=9).normalized()
+    assert (p.temperature, p.top_p, p.top_k, p.max_new_tokens, p.min_new_tokens) == (0.0, 1.0, 0, 1, 1)
+    assert p.is_greedy and not SamplingParams(top_k=5).is_greedy
