@@ -1,0 +1,385 @@
+// Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16, float32
+// accumulation), flash style: scores, softmax statistics and the output accumulator never
+// leave the registers, keys and values stream from the pages through shared memory with
+// cp.async double buffering.
+//
+// Work decomposition is the one of attention_simple.cu and the two kernels are
+// interchangeable: a request's rows are packed with the query heads that share a key/value
+// head, cut into tiles of 64 packed rows, and short requests with long key ranges are cut
+// along the keys into splits that attn_merge_kernel (attention_simple.cu) combines.
+//
+// Two compute modes, chosen per block from the number of packed rows in its tile:
+//  * rows mode (more than 16 packed rows: prompt portions): warp w owns rows 16w..16w+15
+//    and visits all 64 keys of every key tile.
+//  * keys mode (at most 16 packed rows: decoded tokens): all four warps own the same 16
+//    rows and warp w visits keys 16w..16w+15 of every key tile with statistics of its own;
+//    the four partial results are merged through shared memory at the end.  The block still
+//    streams each key tile once, with all of its threads.
+//
+// Softmax statistics are float32; exponentials are exp2f with log2(e) folded into the
+// score scale.  Compile with -DPBE_HEAD_DIM=<multiple of 16, at most 256>.
+#include <cuda_bf16.h>
+
+#include "attention_params.cuh"
+#include "common.cuh"
+
+using namespace pbe;
+
+#ifndef PBE_HEAD_DIM
+#error "PBE_HEAD_DIM must be defined"
+#endif
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int HD = PBE_HEAD_DIM;
+constexpr int BM = 64;            // packed rows per block
+constexpr int BN = 64;            // keys per tile
+constexpr int NTHREADS = 128;
+constexpr int LDS = HD + 8;       // shared row stride in elements: ldmatrix without bank conflicts
+constexpr int CPR = HD / 8;       // 16-byte chunks per row
+constexpr int KSTEPS = HD / 16;   // k-steps of Q.K^T
+constexpr int ONT = HD / 8;       // 8-wide output tiles of P.V
+static_assert(HD % 16 == 0 && HD <= 256, "head size must be a multiple of 16, at most 256");
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;      // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct RowInfo {      // the two rows of this thread's accumulator fragment
+  int pos[2];         // absolute position of the row's query (-1: no such row)
+  int lo[2];          // first visible key
+};
+
+// One key tile for one warp: NKT 8-key score tiles starting at key `key0` (absolute) which
+// sit at row `krow0` of the shared K and V tiles.  Updates m, l (log2 domain) and o.
+template <int NKT>
+__device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
+                                             const bf16* __restrict__ Vs, int krow0, int key0,
+                                             int k_begin, int k_end, const RowInfo& ri, float scale_log2,
+                                             float (&m)[2], float (&l)[2], float (&o)[ONT][4], int lane) {
+  float s[NKT][4];
+#pragma unroll
+  for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
+  // S = Q K^T
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    unsigned a[4];
+    ldmatrix_x4(a, Qw + (lane & 15) * LDS + ks * 16 + 8 * (lane >> 4));
+#pragma unroll
+    for (int np = 0; np < NKT / 2; ++np) {
+      unsigned b[4];
+      const int krow = krow0 + np * 16 + (lane & 7) + 8 * (lane >> 4);
+      ldmatrix_x4(b, Ks + krow * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+      mma_bf16(s[2 * np], a, b[0], b[1]);
+      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+  // scale, mask, running maximum
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = c >> 1;
+      const int key = key0 + nt * 8 + (lane & 3) * 2 + (c & 1);
+      const bool vis = key >= k_begin && key < k_end && key <= ri.pos[r] && key >= ri.lo[r];
+      const float v = vis ? s[nt][c] * scale_log2 : -INFINITY;
+      s[nt][c] = v;
+      mx[r] = fmaxf(mx[r], v);
+    }
+  float alpha[2], m_use[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(m[r], mx[r]);
+    m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;   // nothing visible yet: keep exp2 finite
+    alpha[r] = exp2f(m[r] - m_use[r]);               // m = -inf gives 0, and o is 0 then
+    m[r] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = c >> 1;
+      const float p = exp2f(s[nt][c] - m_use[r]);    // masked: exp2(-inf) = 0
+      s[nt][c] = p;
+      sum[r] += p;
+    }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+    l[r] = l[r] * alpha[r] + sum[r];
+  }
+#pragma unroll
+  for (int nt = 0; nt < ONT; ++nt) {
+    o[nt][0] *= alpha[0];
+    o[nt][1] *= alpha[0];
+    o[nt][2] *= alpha[1];
+    o[nt][3] *= alpha[1];
+  }
+  // O += P V
+#pragma unroll
+  for (int kk = 0; kk < NKT / 2; ++kk) {
+    unsigned a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    const int vrow = krow0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+    for (int dp = 0; dp < ONT / 2; ++dp) {
+      unsigned b[4];
+      ldmatrix_x4_trans(b, Vs + vrow * LDS + dp * 16 + 8 * (lane >> 4));
+      mma_bf16(o[2 * dp], a, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NTHREADS)
+attn_mma_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [BM][LDS]
+  bf16* Ks = Qs + BM * LDS;                            // [2][BN][LDS]
+  bf16* Vs = Ks + 2 * BN * LDS;                        // [2][BN][LDS]
+
+  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  const int r = work[0];
+  if (r < 0) return;
+  const int m_tile = work[1], split = work[2], nsplit = work[3];
+  const int kvh = blockIdx.y;
+  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+  const int n_packed = nq * G;
+  const int pr0 = m_tile * BM;
+  if (pr0 >= n_packed) return;
+  const int rows_here = min(BM, n_packed - pr0);
+  const int row_lo = pr0 / G;
+  const int row_hi = (pr0 + rows_here - 1) / G;
+  const int pos0 = sl - nq;
+  const int hi_key = pos0 + row_hi + 1;
+  const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
+  int k_begin = lo_key, k_end = hi_key;
+  if (nsplit > 1) {
+    const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int s0 = lo_req / p.split_keys;
+    k_begin = max(lo_key, (s0 + split) * p.split_keys);
+    k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+  }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bf16* q = (const bf16*)p.q;
+  const bf16* kc = (const bf16*)p.k_cache;
+  const bf16* vc = (const bf16*)p.v_cache;
+  const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
+  const bool keys_mode = rows_here <= 16;
+
+  // Q tile -> shared (rows beyond the request are zeros)
+  for (int c = tid; c < BM * CPR; c += NTHREADS) {
+    const int i = c / CPR, col = c - i * CPR;
+    const int pr = pr0 + i;
+    const bool valid = pr < n_packed;
+    const int row = valid ? pr / G : 0, hg = valid ? pr - row * G : 0;
+    cp_async16(Qs + i * LDS + col * 8, q + ((size_t)(qs + row) * H + kvh * G + hg) * HD + col * 8, valid);
+  }
+  auto load_tile = [&](int ts, int buf) {
+    bf16* kd = Ks + buf * BN * LDS;
+    bf16* vd = Vs + buf * BN * LDS;
+    for (int c = tid; c < BN * CPR; c += NTHREADS) {
+      const int j = c / CPR, col = c - j * CPR;
+      const int key = ts + j;
+      bool valid = key >= k_begin && key < k_end;
+      size_t off = 0;
+      if (valid) {
+        const int blk = key / P;
+        const int page = bt[blk];
+        valid = page >= 0;
+        if (valid) off = (((size_t)page * KV + kvh) * P + (key - blk * P)) * HD + col * 8;
+      }
+      cp_async16(kd + j * LDS + col * 8, kc + off, valid);
+      cp_async16(vd + j * LDS + col * 8, vc + off, valid);
+    }
+  };
+
+  const int tile0 = (k_begin / BN) * BN;
+  const int n_tiles = k_end > tile0 ? (k_end - tile0 + BN - 1) / BN : 0;
+  if (n_tiles > 0) load_tile(tile0, 0);
+  cp_async_commit();
+
+  // rows of this thread's fragments
+  RowInfo ri;
+  const int frag_row0 = (keys_mode ? 0 : warp * 16) + (lane >> 2);
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int pr = pr0 + frag_row0 + rr * 8;
+    if (pr < n_packed) {
+      ri.pos[rr] = pos0 + pr / G;
+      ri.lo[rr] = p.window > 0 ? ri.pos[rr] - p.window + 1 : 0;
+    } else {
+      ri.pos[rr] = -1;     // no key is visible to a row that does not exist
+      ri.lo[rr] = 0;
+    }
+  }
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[ONT][4];
+#pragma unroll
+  for (int nt = 0; nt < ONT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
+  const bf16* Qw = Qs + (keys_mode ? 0 : warp * 16) * LDS;
+  const bool warp_has_rows = keys_mode || (warp * 16 < rows_here);
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int ts = tile0 + t * BN;
+    if (t + 1 < n_tiles) load_tile(ts + BN, (t + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();          // tile t (and Q) have landed
+    __syncthreads();
+    const bf16* kt = Ks + (t & 1) * BN * LDS;
+    const bf16* vt = Vs + (t & 1) * BN * LDS;
+    if (keys_mode) {
+      process_tile<2>(Qw, kt, vt, warp * 16, ts + warp * 16, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+    } else if (warp_has_rows) {
+      process_tile<8>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+    }
+    __syncthreads();             // everyone is done with buffer t & 1 before it is refilled
+  }
+  cp_async_wait<0>();
+
+  const float LN2 = 0.6931471805599453f;
+  if (keys_mode) {
+    // merge the four warps' partial results: reuse the K/V buffers as float scratch
+    __syncthreads();
+    float* sc_o = reinterpret_cast<float*>(Ks);          // [4][16][HD]
+    float* sc_ml = sc_o + 4 * 16 * HD;                   // [4][16][2]
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int row = (lane >> 2) + rr * 8;
+#pragma unroll
+      for (int nt = 0; nt < ONT; ++nt) {
+        float2 v = make_float2(o[nt][rr * 2], o[nt][rr * 2 + 1]);
+        *reinterpret_cast<float2*>(sc_o + ((warp * 16 + row) * HD) + nt * 8 + (lane & 3) * 2) = v;
+      }
+      if ((lane & 3) == 0) {
+        sc_ml[(warp * 16 + row) * 2] = m[rr];
+        sc_ml[(warp * 16 + row) * 2 + 1] = l[rr];
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_here * HD; idx += NTHREADS) {
+      const int row = idx / HD, d = idx - row * HD;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sc_ml[(w * 16 + row) * 2]);
+      float ll = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = sc_ml[(w * 16 + row) * 2];
+        if (mw != -INFINITY) {
+          const float f = exp2f(mw - mm);
+          ll += sc_ml[(w * 16 + row) * 2 + 1] * f;
+          acc += sc_o[(w * 16 + row) * HD + d] * f;
+        }
+      }
+      const int pr = pr0 + row;
+      const int qrow = pr / G, hg = pr - qrow * G;
+      const int head = kvh * G + hg;
+      const int tok = qs + qrow;
+      if (nsplit <= 1) {
+        ((bf16*)p.out)[((size_t)tok * H + head) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      } else {
+        const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
+        p.part_o[base * HD + d] = acc;
+        if (d == 0) {
+          p.part_ml[base * 2] = mm == -INFINITY ? -INFINITY : mm * LN2;   // natural-log domain for the merge
+          p.part_ml[base * 2 + 1] = ll;
+        }
+      }
+    }
+    return;
+  }
+
+  if (!warp_has_rows) return;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int pr = pr0 + warp * 16 + (lane >> 2) + rr * 8;
+    if (pr >= n_packed) continue;
+    const int qrow = pr / G, hg = pr - qrow * G;
+    const int head = kvh * G + hg;
+    const int tok = qs + qrow;
+    if (nsplit <= 1) {
+      const float inv = l[rr] > 0.f ? 1.0f / l[rr] : 0.f;
+      bf16* dst = (bf16*)p.out + ((size_t)tok * H + head) * HD + (lane & 3) * 2;
+#pragma unroll
+      for (int nt = 0; nt < ONT; ++nt) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
+            __floats2bfloat162_rn(o[nt][rr * 2] * inv, o[nt][rr * 2 + 1] * inv);
+      }
+    } else {
+      const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
+      float* dst = p.part_o + base * HD + (lane & 3) * 2;
+#pragma unroll
+      for (int nt = 0; nt < ONT; ++nt)
+        *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][rr * 2], o[nt][rr * 2 + 1]);
+      if ((lane & 3) == 0) {
+        p.part_ml[base * 2] = m[rr] == -INFINITY ? -INFINITY : m[rr] * LN2;
+        p.part_ml[base * 2 + 1] = l[rr];
+      }
+    }
+  }
+}
+}  // namespace
+
+PBE_EXPORT int pbe_attn_mma_tile_rows() { return BM; }
+PBE_EXPORT int pbe_attn_mma_head_dim() { return HD; }
+
+PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, cudaStream_t stream) {
+  if (num_work <= 0) return 0;
+  AttnParams p = *params;
+  if (dtype != PBE_BF16 || p.num_heads % p.num_kv_heads != 0 || p.tile_rows != BM ||
+      p.split_keys % BN != 0)
+    return (int)cudaErrorInvalidValue;
+  size_t smem = sizeof(bf16) * (size_t)(BM + 4 * BN) * LDS;
+  const size_t merge = sizeof(float) * (4 * 16 * HD + 4 * 16 * 2);   // keys-mode scratch lives in K/V
+  if (merge > sizeof(bf16) * (size_t)4 * BN * LDS) return (int)cudaErrorInvalidValue;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  dim3 grid(num_work, p.num_kv_heads);
+  attn_mma_kernel<<<grid, NTHREADS, smem, stream>>>(p);
+  return launch_status();
+}

@@ -250,22 +250,25 @@ ATTN_SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+KINDS = [("simple", torch.float32), ("simple", torch.bfloat16), ("mma", torch.bfloat16)]
+
+
+@pytest.mark.parametrize("kind,dtype", KINDS, ids=lambda v: str(v).replace("torch.", ""))
 @pytest.mark.parametrize("shape", ATTN_SHAPES, ids=lambda s: f"H{s[0]}kv{s[1]}hd{s[2]}P{s[3]}w{s[4]}")
-def test_paged_attention_simple(shape, dtype):
+def test_paged_attention(shape, kind, dtype):
     H, KV, hd, P, window, reqs = shape
-    case = AttnCase(H, KV, hd, P, window, reqs, dtype, seed=hd)
+    case = AttnCase(H, KV, hd, P, window, reqs, dtype, seed=hd, kind=kind)
     case.write_cache()
     got, want = case.run(), case.reference()
     assert not torch.isnan(got).any()
     tol = 2e-5 if dtype == torch.float32 else 2 ** -7
     assert (got - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
-    if any(c + n > 256 and n * (H // KV) <= 64 for c, n in reqs):
+    if any(c + n > 256 and n * (H // KV) <= 4 * case.tile_rows for c, n in reqs):
         assert case.meta.num_split_rows > 0 and case.meta.max_splits > 1   # the split path ran
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_one_key_stands_out(dtype):
+@pytest.mark.parametrize("kind,dtype", KINDS, ids=lambda v: str(v).replace("torch.", ""))
+def test_attention_one_key_stands_out(kind, dtype):
     """One key among many gets a large score: the output row must be that key's value.
     The special key sits at a page's first and last slot, at a split's edge, at the
     window's first and last key, and just outside the window (then it must NOT win)."""
@@ -274,7 +277,7 @@ def test_attention_one_key_stands_out(dtype):
     for window, specials in [(None, [0, 15, 16, 255, 256, 511, 512, 1023, 1024, 1029]),
                              (100, [1029, 930, 929])]:
         for j in specials:
-            case = AttnCase(H, KV, hd, P, window, [(L - 1, 1)], dtype, seed=j)
+            case = AttnCase(H, KV, hd, P, window, [(L - 1, 1)], dtype, seed=j, kind=kind)
             q, k, v, c, n, h = case.seqs[0]
             k.mul_(0.05)
             q[L - 1] = 0
@@ -289,16 +292,28 @@ def test_attention_one_key_stands_out(dtype):
             assert (got - case.reference()[0]).abs().max() <= (2e-5 if dtype == torch.float32 else 2e-2)
 
 
+def test_attention_mma_prompt_tiles_and_mixed_batch():
+    """Long prompt portions (many row tiles, rows mode) beside decoded tokens (keys mode) in
+    one launch, with the 7-heads-per-kv-head grouping of the 7B shape."""
+    case = AttnCase(28, 4, 128, 16, None, [(0, 200), (777, 1), (130, 90), (2047, 1), (64, 5)],
+                    torch.bfloat16, seed=3, kind="mma")
+    case.write_cache()
+    got, want = case.run(), case.reference()
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
+
+
 def test_attention_ignores_stale_data_in_reused_and_foreign_pages():
     """Pages beyond a request's length and pages of other requests hold NaN or huge
     values: the result must not change."""
     H, KV, hd, P = 6, 3, 48, 8
-    case = AttnCase(H, KV, hd, P, None, [(13, 4), (0, 6)], torch.float32, seed=5)
-    case.k_pages.fill_(1e30)
-    case.v_pages.fill_(float("nan"))
-    case.write_cache()
-    got, want = case.run(), case.reference()
-    assert not torch.isnan(got).any() and (got - want).abs().max() <= 2e-5
+    for kind, dtype, tol in (("simple", torch.float32, 2e-5), ("mma", torch.bfloat16, 2e-2)):
+        case = AttnCase(H, KV, hd, P, None, [(13, 4), (0, 6)], dtype, seed=5, kind=kind)
+        case.k_pages.fill_(1e30)
+        case.v_pages.fill_(float("nan"))
+        case.write_cache()
+        got, want = case.run(), case.reference()
+        assert not torch.isnan(got).any() and (got - want).abs().max() <= tol
 
 
 # ------------------------------------------------------------------ sampling
