@@ -35,6 +35,29 @@ PBE_EXPORT int pbe_embedding(float* out, const void* table, int table_dtype, con
   return launch_status();
 }
 
+// four consecutive elements, 16-byte aligned for float and 8-byte aligned for bfloat16
+__device__ __forceinline__ void load4(const float* p, float (&a)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&a)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  a[0] = __low2float(lo); a[1] = __high2float(lo); a[2] = __low2float(hi); a[3] = __high2float(hi);
+}
+__device__ __forceinline__ void store4(float* p, const float (&a)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(a[0], a[1], a[2], a[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&a)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a[0], a[1]);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(a[2], a[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&lo);
+  raw.y = *reinterpret_cast<unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 // One block per output row.  row_index == nullptr: row r of the batch, the sum is written
 // back to `residual`.  Otherwise output row r is made from batch row row_index[r] and the
@@ -50,8 +73,35 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   float* res = residual + (size_t)src * d;
   const TD* dl = delta ? delta + (size_t)src * d : nullptr;
   TO* o = out + (size_t)r * d;
-  extern __shared__ float row[];  // d floats: the summed row
+  extern __shared__ __align__(16) float row[];  // d floats: the summed row
   float ss = 0.f;
+  const bool write_back = (row_index == nullptr) && (dl != nullptr);
+  if ((d & 3) == 0) {
+    // four elements a thread: 16-byte loads of the residual, 8- or 16-byte loads of the delta
+    const float4* res4 = reinterpret_cast<const float4*>(res);
+    float4* row4 = reinterpret_cast<float4*>(row);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+      float4 v = res4[i];
+      if (dl) {
+        float a[4];
+        load4(dl + 4 * i, a);
+        v.x += a[0]; v.y += a[1]; v.z += a[2]; v.w += a[3];
+      }
+      row4[i] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = rsqrtf(total / (float)d + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+      const float4 v = row4[i];
+      const float4 g = g4[i];
+      if (write_back) reinterpret_cast<float4*>(res)[i] = v;
+      const float y[4] = {(g.x * v.x) * scale, (g.y * v.y) * scale, (g.z * v.z) * scale, (g.w * v.w) * scale};
+      store4(o + 4 * i, y);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = res[i];
     if (dl) v += to_float(dl[i]);
@@ -60,7 +110,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   }
   const float total = block_sum(ss, red);
   const float scale = rsqrtf(total / (float)d + eps);
-  const bool write_back = (row_index == nullptr) && (dl != nullptr);
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float v = row[i];
     if (write_back) res[i] = v;
@@ -111,11 +160,43 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   }
 }
 
+// the same, four columns a thread (inter a multiple of 4)
+template <typename T>
+__global__ void silu_mul_vec4_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
+                                     size_t total4) {
+  const int q = inter / 4;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / q;
+    const int c = (int)(idx - r * q) * 4;
+    float g[4], u[4], y[4];
+    load4(in + r * 2 * inter + c, g);
+    load4(in + r * 2 * inter + inter + c, u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float sg = 1.0f / (1.0f + expf(-g[i]));
+      y[i] = (g[i] * sg) * u[i];
+    }
+    store4(out + r * inter + c, y);
+  }
+}
+
 PBE_EXPORT int pbe_silu_mul(const void* in, void* out, int dtype, int rows, int inter,
                             cudaStream_t stream) {
   const size_t total = (size_t)rows * inter;
   if (total == 0) return 0;
   const int threads = 256;
+  if ((inter & 3) == 0) {
+    const size_t total4 = total / 4;
+    size_t nb = (total4 + threads - 1) / threads;
+    if (nb > 148 * 32) nb = 148 * 32;
+    if (dtype == PBE_F32)
+      silu_mul_vec4_kernel<float><<<(int)nb, threads, 0, stream>>>((const float*)in, (float*)out, inter, total4);
+    else
+      silu_mul_vec4_kernel<__nv_bfloat16><<<(int)nb, threads, 0, stream>>>(
+          (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total4);
+    return launch_status();
+  }
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == PBE_F32)

@@ -89,6 +89,96 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
 }
 
+// bfloat16, full rotate-half encoding, head size a multiple of 16: eight elements a thread
+// with 16-byte loads and stores; the sines and cosines of the token's position are
+// computed once per block and shared by all heads.
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&a)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    a[2 * i] = __low2float(v);
+    a[2 * i + 1] = __high2float(v);
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&a)[8]) {
+  unsigned w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+    w[i] = *reinterpret_cast<unsigned*>(&v);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__global__ void rope_kv_vec_kernel(RopeKvParams p) {
+  extern __shared__ float trig[];            // cos[half], sin[half]
+  typedef __nv_bfloat16 T;
+  const int t = blockIdx.x;
+  const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
+  const int half = hd / 2, half8 = half / 8, hd8 = hd / 8;
+  float* cs = trig;
+  float* sn = trig + half;
+  const float pos = (float)p.positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * p.inv_freq[i], &sn[i], &cs[i]);
+  __syncthreads();
+  const int row_width = (H + 2 * KV) * hd;
+  const T* in = (const T*)p.qkv + (size_t)t * row_width;
+  const int slot = p.slots ? p.slots[t] : -1;
+  const bool write_kv = p.k_cache != nullptr && slot >= 0;
+  const int page = write_kv ? slot / p.page_tokens : 0;
+  const int off = write_kv ? slot - page * p.page_tokens : 0;
+  const int n_rot = (H + KV) * half8;
+  const int n_v = KV * hd8;
+  for (int item = threadIdx.x; item < n_rot + n_v; item += blockDim.x) {
+    if (item < n_rot) {
+      const int head = item / half8;
+      const int j = (item - head * half8) * 8;
+      const int base = head * hd;
+      T* dst;
+      if (head < H) {
+        dst = (T*)p.q_out + (size_t)t * H * hd + (size_t)head * hd;
+      } else {
+        if (!write_kv) continue;
+        dst = (T*)p.k_cache + (((size_t)page * KV + (head - H)) * p.page_tokens + off) * hd;
+      }
+      float a[8], b[8];
+      load8(in + base + j, a);
+      load8(in + base + j + half, b);
+      if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          a[e] += p.bias[base + j + e];
+          b[e] += p.bias[base + j + half + e];
+        }
+      }
+      float ra[8], rb[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cs[j + e], s = sn[j + e];
+        ra[e] = a[e] * c - b[e] * s;
+        rb[e] = b[e] * c + a[e] * s;
+      }
+      store8(dst + j, ra);
+      store8(dst + j + half, rb);
+    } else {
+      if (!write_kv) continue;
+      const int e8 = item - n_rot;
+      const int kvh = e8 / hd8, i = (e8 - kvh * hd8) * 8;
+      const int col = (H + KV) * hd + kvh * hd + i;
+      float a[8];
+      load8(in + col, a);
+      if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += p.bias[col + e];
+      }
+      T* dst = (T*)p.v_cache + (((size_t)page * KV + kvh) * p.page_tokens + off) * hd;
+      store8(dst + i, a);
+    }
+  }
+}
+
 PBE_EXPORT int pbe_rope_kv_write(const void* qkv, const float* bias, void* q_out, void* k_cache,
                                  void* v_cache, const int32_t* positions, const int32_t* slots,
                                  const float* inv_freq, int num_tokens, int num_heads,
@@ -100,6 +190,14 @@ PBE_EXPORT int pbe_rope_kv_write(const void* qkv, const float* bias, void* q_out
                  num_heads, num_kv_heads, head_dim, rotary_dim, page_tokens, interleaved};
   const int items = (num_heads + num_kv_heads) * (rotary_dim / 2 + head_dim - rotary_dim) +
                     num_kv_heads * head_dim;
+  if (dtype == PBE_BF16 && !interleaved && inv_freq != nullptr && rotary_dim == head_dim &&
+      head_dim % 16 == 0) {
+    const int vec_items = (num_heads + num_kv_heads) * (head_dim / 16) + num_kv_heads * (head_dim / 8);
+    int vt = 64;
+    while (vt < 256 && vt < vec_items) vt *= 2;
+    rope_kv_vec_kernel<<<num_tokens, vt, head_dim * sizeof(float), stream>>>(p);
+    return launch_status();
+  }
   int threads = 128;
   while (threads < 512 && threads * 4 < items) threads *= 2;
   if (dtype == PBE_F32) rope_kv_kernel<float><<<num_tokens, threads, 0, stream>>>(p);

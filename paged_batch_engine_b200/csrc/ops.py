@@ -193,6 +193,39 @@ def sgemm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
     return out
 
 
+SKINNY_MAX_ROWS = 16     # batches of at most this many rows take the weight-streaming kernel; 0: never
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None, swiglu: bool = False) -> torch.Tensor:
+    """y = x w^T (+ b) for at most 16 rows, bfloat16 operands, weights streamed once.
+    ``swiglu``: w is [gate; up] stacked and y = silu(x gate^T) * (x up^T), [M, N/2]."""
+    _need_cuda(x, w, bias)
+    _need_contiguous(x, w, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError("gemm_skinny takes bfloat16 x [M, K] and w [N, K]")
+    if M > 16 or K % 8 != 0:
+        raise KernelError(f"gemm_skinny takes at most 16 rows and K a multiple of 8 (got M={M}, K={K})")
+    if swiglu and (N % 2 or bias is not None):
+        raise KernelError("gemm_skinny: the SwiGLU epilogue needs an even N and no bias")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_skinny: bias must be float32 [N]")
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    fn = _fn("gemm_skinny", "pbe_gemm_skinny",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _dtype_code(out), M, N, K, 1 if swiglu else 0,
+              _stream()), "gemm_skinny")
+    return out
+
+
+def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (0 < x.shape[0] <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.shape[1] % 8 == 0)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y = x w^T (+ b).  A float32 weight takes the true-float32 kernel of this package; a
@@ -205,6 +238,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return sgemm_nt(x, w, bias, out)
     if x.dtype != torch.bfloat16:
         raise KernelError("a bfloat16 weight takes bfloat16 activations")
+    if skinny_applies(x, w):
+        return gemm_skinny(x, w, bias, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(x, w.t(), out_dtype=torch.float32)
     else:

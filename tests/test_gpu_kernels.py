@@ -386,3 +386,34 @@ def test_repetition_penalty():
                         torch.tensor([1, 2, 0], dtype=torch.int32, device=DEV),
                         torch.tensor([2.0, 2.0, 1.5], device=DEV))
     assert logits.cpu().tolist() == [[1.0, -4.0, 2.0, 0.5], [2.0, 3.0, -1.0, 2.0]]
+
+
+# ------------------------------------------------------------------ weight-streaming GEMM for few rows
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(64, 64), (1000, 88), (517, 192), (4608, 3584), (320, 2368)])
+def test_gemm_skinny(M, N, K):
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N)
+    want = x.double() @ w.double().t()
+    scale = want.abs().max().item()
+    got = ops().gemm_skinny(x.to(DEV), w.to(DEV), None, torch.float32).cpu().double()
+    assert (got - want).abs().max().item() <= 1e-5 * scale * math.sqrt(K) / 8 + 1e-6   # float32 accumulation
+    gotb = ops().gemm_skinny(x.to(DEV), w.to(DEV), b.to(DEV), torch.bfloat16).float().cpu().double()
+    assert (gotb - (want + b.double())).abs().max().item() <= 2 ** -8 * (scale + b.abs().max().item())
+    if N % 2 == 0:
+        act = ops().gemm_skinny(x.to(DEV), w.to(DEV), None, torch.float32, swiglu=True).cpu()
+        ref = plain.swiglu(want[:, :N // 2].float(), want[:, N // 2:].float())
+        assert act.shape == (M, N // 2)
+        assert (act - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
+
+
+def test_gemm_skinny_rows_do_not_depend_on_the_batch():
+    torch.manual_seed(5)
+    x = torch.randn(16, 3584).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(1003, 3584) * 0.05).to(torch.bfloat16).to(DEV)
+    full = ops().gemm_skinny(x, w, None, torch.float32)
+    for lo, hi in [(0, 1), (3, 8), (7, 16), (15, 16)]:
+        part = ops().gemm_skinny(x[lo:hi].contiguous(), w, None, torch.float32)
+        assert torch.equal(part, full[lo:hi])
