@@ -22,6 +22,7 @@
 
 #include "attention_params.cuh"
 #include "common.cuh"
+#include "pdl.cuh"
 
 using namespace pbe;
 
@@ -175,16 +176,23 @@ attn_mma_kernel(AttnParams p) {
   bf16* Ks = Qs + BM * LDS;                            // [2][BN][LDS]
   bf16* Vs = Ks + 2 * BN * LDS;                        // [2][BN][LDS]
 
+  pdl_wait();
   const int32_t* work = p.work + (size_t)blockIdx.x * 4;
   const int r = work[0];
-  if (r < 0) return;
+  if (r < 0) {
+    pdl_launch_dependents();
+    return;
+  }
   const int m_tile = work[1], split = work[2], nsplit = work[3];
   const int kvh = blockIdx.y;
   const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
   const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
   const int pr0 = m_tile * BM;
-  if (pr0 >= n_packed) return;
+  if (pr0 >= n_packed) {
+    pdl_launch_dependents();
+    return;
+  }
   const int rows_here = min(BM, n_packed - pr0);
   const int row_lo = pr0 / G;
   const int row_hi = (pr0 + rows_here - 1) / G;
@@ -277,6 +285,7 @@ attn_mma_kernel(AttnParams p) {
     __syncthreads();             // everyone is done with buffer t & 1 before it is refilled
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();      // the keys and values are read: the next kernel may start launching
 
   const float LN2 = 0.6931471805599453f;
   if (keys_mode) {
@@ -380,6 +389,6 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
     opted = true;
   }
   dim3 grid(num_work, p.num_kv_heads);
-  attn_mma_kernel<<<grid, NTHREADS, smem, stream>>>(p);
+  launch_k(attn_mma_kernel, grid, NTHREADS, smem, stream, p);
   return launch_status();
 }

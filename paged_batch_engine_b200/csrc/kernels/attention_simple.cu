@@ -17,6 +17,7 @@
 // Compile with -DPBE_HEAD_DIM=<multiple of 16>.
 #include "attention_params.cuh"
 #include "common.cuh"
+#include "pdl.cuh"
 
 using namespace pbe;
 
@@ -40,6 +41,8 @@ attn_simple_kernel(AttnParams p) {
   float* Ks = Qs + BM * HD;               // [BN][HD + 1]
   float* Vs = Ks + BN * (HD + 1);         // [BN][HD]
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int32_t* work = p.work + (size_t)blockIdx.x * 4;
   const int r = work[0];
   if (r < 0) return;
@@ -182,6 +185,8 @@ attn_simple_kernel(AttnParams p) {
 
 template <typename T>
 __global__ void attn_merge_kernel(AttnMergeParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int srow = blockIdx.x, head = blockIdx.y;
   const int n = p.split_counts[srow];
   if (n <= 1) return;
@@ -227,13 +232,13 @@ PBE_EXPORT int pbe_attn_simple(const AttnParams* params, int num_work, int dtype
       cudaFuncSetAttribute(attn_simple_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       opted[0] = true;
     }
-    attn_simple_kernel<float><<<grid, NWARPS * 32, smem, stream>>>(p);
+    launch_k(attn_simple_kernel<float>, grid, NWARPS * 32, smem, stream, p);
   } else {
     if (!opted[1]) {
       cudaFuncSetAttribute(attn_simple_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       opted[1] = true;
     }
-    attn_simple_kernel<__nv_bfloat16><<<grid, NWARPS * 32, smem, stream>>>(p);
+    launch_k(attn_simple_kernel<__nv_bfloat16>, grid, NWARPS * 32, smem, stream, p);
   }
   return launch_status();
 }
@@ -244,7 +249,7 @@ PBE_EXPORT int pbe_attn_merge(const AttnMergeParams* params, int split_rows, int
   AttnMergeParams p = *params;
   dim3 grid(split_rows, p.num_heads);
   const int threads = p.head_dim >= 128 ? 128 : 64;
-  if (dtype == PBE_F32) attn_merge_kernel<float><<<grid, threads, 0, stream>>>(p);
-  else attn_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(p);
+  if (dtype == PBE_F32) launch_k(attn_merge_kernel<float>, grid, threads, 0, stream, p);
+  else launch_k(attn_merge_kernel<__nv_bfloat16>, grid, threads, 0, stream, p);
   return launch_status();
 }

@@ -5,6 +5,7 @@
 // swiglu_kernel.cu:6-25.  The residual stream is float32 in every run mode; statistics,
 // the sum and the products are float32 and each result is rounded once on store.
 #include "common.cuh"
+#include "pdl.cuh"
 
 using namespace pbe;
 
@@ -12,6 +13,8 @@ using namespace pbe;
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int32_t* __restrict__ ids, int d, int vocab) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * d;
@@ -28,10 +31,10 @@ PBE_EXPORT int pbe_embedding(float* out, const void* table, int table_dtype, con
   if (num_tokens <= 0) return 0;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == PBE_F32)
-    embedding_kernel<float><<<num_tokens, threads, 0, stream>>>(out, (const float*)table, ids, d, vocab);
+    launch_k(embedding_kernel<float>, num_tokens, threads, 0, stream, out, (const float*)table, ids, d, vocab);
   else
-    embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
-        out, (const __nv_bfloat16*)table, ids, d, vocab);
+    launch_k(embedding_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, out,
+             (const __nv_bfloat16*)table, ids, d, vocab);
   return launch_status();
 }
 
@@ -68,6 +71,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    const float* __restrict__ gain, TO* __restrict__ out,
                                    const int32_t* __restrict__ row_index, int d, float eps) {
   __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   const int src = row_index ? row_index[r] : r;
   float* res = residual + (size_t)src * d;
@@ -133,8 +138,8 @@ PBE_EXPORT int pbe_add_rmsnorm(float* residual, const void* delta, int delta_dty
                            200 * 1024);                                                         \
       opted = 200 * 1024;                                                                       \
     }                                                                                           \
-    add_rmsnorm_kernel<TD, TO><<<num_rows, threads, smem, stream>>>(                            \
-        residual, (const TD*)delta, gain, (TO*)out, row_index, d, eps);                         \
+    launch_k(add_rmsnorm_kernel<TD, TO>, num_rows, threads, smem, stream, residual,             \
+             (const TD*)delta, gain, (TO*)out, row_index, d, eps);                              \
   } while (0)
   if (delta_dtype == PBE_F32 && out_dtype == PBE_F32) LAUNCH(float, float);
   else if (delta_dtype == PBE_BF16 && out_dtype == PBE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -149,6 +154,8 @@ PBE_EXPORT int pbe_add_rmsnorm(float* residual, const void* delta, int delta_dty
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
                                 size_t total) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / inter;
@@ -164,6 +171,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
 template <typename T>
 __global__ void silu_mul_vec4_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
                                      size_t total4) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int q = inter / 4;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -191,18 +200,18 @@ PBE_EXPORT int pbe_silu_mul(const void* in, void* out, int dtype, int rows, int 
     size_t nb = (total4 + threads - 1) / threads;
     if (nb > 148 * 32) nb = 148 * 32;
     if (dtype == PBE_F32)
-      silu_mul_vec4_kernel<float><<<(int)nb, threads, 0, stream>>>((const float*)in, (float*)out, inter, total4);
+      launch_k(silu_mul_vec4_kernel<float>, (int)nb, threads, 0, stream, (const float*)in, (float*)out, inter, total4);
     else
-      silu_mul_vec4_kernel<__nv_bfloat16><<<(int)nb, threads, 0, stream>>>(
-          (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total4);
+      launch_k(silu_mul_vec4_kernel<__nv_bfloat16>, (int)nb, threads, 0, stream, (const __nv_bfloat16*)in,
+               (__nv_bfloat16*)out, inter, total4);
     return launch_status();
   }
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == PBE_F32)
-    silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)in, (float*)out, inter, total);
+    launch_k(silu_mul_kernel<float>, (int)blocks, threads, 0, stream, (const float*)in, (float*)out, inter, total);
   else
-    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total);
+    launch_k(silu_mul_kernel<__nv_bfloat16>, (int)blocks, threads, 0, stream, (const __nv_bfloat16*)in,
+             (__nv_bfloat16*)out, inter, total);
   return launch_status();
 }

@@ -6,7 +6,8 @@
 // activations the B operand (16 k by 8 batch rows).  A thread reads 16 contiguous bytes of
 // a weight row per 32 k (8 lanes x 4 chunks cover 16 rows x 64 bytes, fully coalesced) and
 // uses them for two mma steps; the activations are read with the same permutation of k, so
-// no shuffle or shared-memory staging of the weights is needed.  Each block has 8 warps
+// no shuffle is needed; the chunks travel through a per-thread cp.async ring in shared
+// memory, which keeps many loads in flight without a barrier.  Each block has 8 warps
 // arranged as WN weight-row tiles by WK slices of K; the slices are summed through shared
 // memory in a fixed order.  The arrangement follows from N alone, so an output element is
 // the same sum whatever the batch is.
@@ -20,13 +21,13 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "pdl.cuh"
 
 using namespace pbe;
 
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int WARPS = 8;
-constexpr int UNROLL = 8;      // k32 blocks in flight per thread
 
 struct SkinnyParams {
   const bf16* X;      // [M, K]
@@ -38,12 +39,6 @@ struct SkinnyParams {
   int tiles;          // 16-row tiles (plain: ceil(N/16); SwiGLU: ceil((N/2)/8))
 };
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
   asm volatile(
@@ -53,11 +48,38 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async16_cg(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;      // 0: zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16_ca(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+// "memory": the shared-memory reads that follow must not be moved above the wait
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <int NT> struct Stages { static constexpr int value = NT == 1 ? 8 : 6; };
+
 // NT: batch tiles of 8 rows (M <= 8 * NT).  WN x WK = 8 warps.  SWIGLU: see above.  TY: output type.
+//
+// Every thread owns a ring of STAGES slots in shared memory, one slot per block of 32 k:
+// its two 16-byte weight chunks and its NT activation chunks.  cp.async fills the slots
+// STAGES-1 blocks ahead; a thread only ever reads the slots it filled itself, so the main
+// loop needs no barrier.  The first STAGES-1 weight blocks are requested before the
+// programmatic dependency on the previous kernel is awaited: weights do not depend on it.
 template <int NT, int WN, int WK, bool SWIGLU, typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(SkinnyParams p) {
   static_assert(WN * WK == WARPS, "8 warps per block");
+  constexpr int STAGES = Stages<NT>::value;
+  constexpr int SLOT = 2 + NT;                       // 16-byte chunks per thread and stage
+  extern __shared__ __align__(16) uint4 ring[];      // [WARPS][STAGES][SLOT][32]
   __shared__ float red[WK][WN][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wn = warp % WN, wk = warp / WN;
@@ -90,36 +112,59 @@ gemm_skinny_kernel(SkinnyParams p) {
   const int kblocks = (K + 31) / 32;
   const int per = (kblocks + WK - 1) / WK;
   const int kb0 = wk * per, kb1 = min(kblocks, kb0 + per);
+  uint4* my = ring + (size_t)warp * STAGES * SLOT * 32 + lane;
+
+  auto issue_w = [&](int blk, int s) {
+    const int k = blk * 32 + c4 * 8;
+    const bool ok = blk < kb1 && k < K;              // K is a multiple of 8: whole chunks only
+    cp_async16_cg(my + (s * SLOT + 0) * 32, ok && wa ? (const void*)(wa + k) : (const void*)p.W, ok && wa);
+    cp_async16_cg(my + (s * SLOT + 1) * 32, ok && wb ? (const void*)(wb + k) : (const void*)p.W, ok && wb);
+  };
+  auto issue_x = [&](int blk, int s) {
+    const int k = blk * 32 + c4 * 8;
+    const bool ok = blk < kb1 && k < K;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+      cp_async16_ca(my + (s * SLOT + 2 + nt) * 32, ok && xr[nt] ? (const void*)(xr[nt] + k) : (const void*)p.W,
+                    ok && xr[nt]);
+  };
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue_w(kb0 + s, s);
+  cp_async_commit();
+  pdl_wait();                                        // from here on the activations are valid
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    issue_x(kb0 + s, s);
+    cp_async_commit();
+  }
 
   float acc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
 
-  for (int kb = kb0; kb < kb1; kb += UNROLL) {
-    uint4 a[UNROLL], b[UNROLL], x[UNROLL][NT];
+  int s_use = 0, s_fill = STAGES - 1;
+  for (int blk = kb0; blk < kb1; ++blk) {
+    issue_w(blk + STAGES - 1, s_fill);
+    issue_x(blk + STAGES - 1, s_fill);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();                     // block `blk` has landed
+    const uint4 a = my[(s_use * SLOT + 0) * 32];
+    const uint4 b = my[(s_use * SLOT + 1) * 32];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int k = (kb + u) * 32 + c4 * 8;
-      const bool ok = (kb + u) < kb1 && k < K;       // K is a multiple of 8: whole chunks only
-      a[u] = (ok && wa) ? ld_stream(wa + k) : zero;
-      b[u] = (ok && wb) ? ld_stream(wb + k) : zero;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-        x[u][nt] = (ok && xr[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint4 x = my[(s_use * SLOT + 2 + nt) * 32];
+      // the 8 elements of a chunk serve two k16 steps: (0,1 | 2,3) and (4,5 | 6,7)
+      mma_bf16(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
+      mma_bf16(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
     }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        // the 8 elements of a chunk serve two k16 steps: (0,1 | 2,3) and (4,5 | 6,7)
-        mma_bf16(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x[u][nt].x, x[u][nt].y);
-        mma_bf16(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x[u][nt].z, x[u][nt].w);
-      }
-    }
+    s_use = s_use + 1 == STAGES ? 0 : s_use + 1;
+    s_fill = s_fill + 1 == STAGES ? 0 : s_fill + 1;
   }
+  cp_async_wait<0>();
+  pdl_launch_dependents();                           // the weights are read: the next kernel may launch
 
   // sum the K slices in a fixed order
   if (WK > 1) {
@@ -168,17 +213,25 @@ gemm_skinny_kernel(SkinnyParams p) {
   }
 }
 
+template <int NT, int WN, int WK, bool SWIGLU, typename TY>
+int launch_cfg(const SkinnyParams& p, int blocks, cudaStream_t stream) {
+  constexpr size_t smem = sizeof(uint4) * WARPS * Stages<NT>::value * (2 + NT) * 32;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(gemm_skinny_kernel<NT, WN, WK, SWIGLU, TY>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  launch_k(gemm_skinny_kernel<NT, WN, WK, SWIGLU, TY>, blocks, WARPS * 32, smem, stream, p);
+  return launch_status();
+}
+
 template <int NT, bool SWIGLU, typename TY>
 int launch(const SkinnyParams& p, cudaStream_t stream) {
   const int tiles = p.tiles;
-  if (tiles >= 148 * 8) {
-    gemm_skinny_kernel<NT, 4, 2, SWIGLU, TY><<<(tiles + 3) / 4, WARPS * 32, 0, stream>>>(p);
-  } else if (tiles >= 148 * 4) {
-    gemm_skinny_kernel<NT, 2, 4, SWIGLU, TY><<<(tiles + 1) / 2, WARPS * 32, 0, stream>>>(p);
-  } else {
-    gemm_skinny_kernel<NT, 1, 8, SWIGLU, TY><<<tiles, WARPS * 32, 0, stream>>>(p);
-  }
-  return launch_status();
+  if (tiles >= 148 * 8) return launch_cfg<NT, 4, 2, SWIGLU, TY>(p, (tiles + 3) / 4, stream);
+  if (tiles >= 148 * 4) return launch_cfg<NT, 2, 4, SWIGLU, TY>(p, (tiles + 1) / 2, stream);
+  return launch_cfg<NT, 1, 8, SWIGLU, TY>(p, tiles, stream);
 }
 }  // namespace
 

@@ -8,6 +8,7 @@
 // Cache layout of one layer: [page][kv_head][page_tokens][head_dim] for K and the same
 // for V, so that the keys of one (page, head) are one contiguous tile.
 #include "common.cuh"
+#include "pdl.cuh"
 
 using namespace pbe;
 
@@ -26,6 +27,8 @@ struct RopeKvParams {
 
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
   const int row_width = (H + 2 * KV) * hd;
@@ -115,6 +118,8 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&a)[8]) {
 __global__ void rope_kv_vec_kernel(RopeKvParams p) {
   extern __shared__ float trig[];            // cos[half], sin[half]
   typedef __nv_bfloat16 T;
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
   const int half = hd / 2, half8 = half / 8, hd8 = hd / 8;
@@ -195,12 +200,12 @@ PBE_EXPORT int pbe_rope_kv_write(const void* qkv, const float* bias, void* q_out
     const int vec_items = (num_heads + num_kv_heads) * (head_dim / 16) + num_kv_heads * (head_dim / 8);
     int vt = 64;
     while (vt < 256 && vt < vec_items) vt *= 2;
-    rope_kv_vec_kernel<<<num_tokens, vt, head_dim * sizeof(float), stream>>>(p);
+    launch_k(rope_kv_vec_kernel, num_tokens, vt, head_dim * sizeof(float), stream, p);
     return launch_status();
   }
   int threads = 128;
   while (threads < 512 && threads * 4 < items) threads *= 2;
-  if (dtype == PBE_F32) rope_kv_kernel<float><<<num_tokens, threads, 0, stream>>>(p);
-  else rope_kv_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(p);
+  if (dtype == PBE_F32) launch_k(rope_kv_kernel<float>, num_tokens, threads, 0, stream, p);
+  else launch_k(rope_kv_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, p);
   return launch_status();
 }

@@ -15,6 +15,7 @@
 // 64-bit fixed point (2^-40 units), so sums are exact, order-independent and the result
 // is the same whatever else is in the batch.
 #include "common.cuh"
+#include "pdl.cuh"
 
 using namespace pbe;
 
@@ -207,6 +208,8 @@ __device__ void block_argmax(const float* row, int V, Shared& sh, float* out_max
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, size_t ld, int V, int32_t* __restrict__ out) {
   __shared__ Shared sh;
+  pdl_wait();
+  pdl_launch_dependents();
   float mx;
   int idx;
   block_argmax(logits + (size_t)blockIdx.x * ld, V, sh, &mx, &idx);
@@ -278,7 +281,7 @@ __global__ void penalty_kernel(float* logits, size_t ld, int V, const int32_t* r
 PBE_EXPORT int pbe_argmax(const float* logits, long long ld, int num_rows, int vocab, int32_t* out,
                           cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  argmax_kernel<<<num_rows, THREADS, 0, stream>>>(logits, (size_t)ld, vocab, out);
+  launch_k(argmax_kernel, num_rows, THREADS, 0, stream, logits, (size_t)ld, vocab, out);
   return launch_status();
 }
 
