@@ -40,6 +40,8 @@ constexpr int LDS = HD + 8;       // shared row stride in elements: ldmatrix wit
 constexpr int CPR = HD / 8;       // 16-byte chunks per row
 constexpr int KSTEPS = HD / 16;   // k-steps of Q.K^T
 constexpr int ONT = HD / 8;       // 8-wide output tiles of P.V
+constexpr int MAX_SMEM_PAGES = 1024;
+static_assert((BN * CPR) % NTHREADS == 0, "a key tile is a whole number of 16-byte chunks per thread");
 static_assert(HD % 16 == 0 && HD <= 256, "head size must be a multiple of 16, at most 256");
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -80,7 +82,7 @@ struct RowInfo {      // the two rows of this thread's accumulator fragment
 
 // One key tile for one warp: NKT 8-key score tiles starting at key `key0` (absolute) which
 // sit at row `krow0` of the shared K and V tiles.  Updates m, l (log2 domain) and o.
-template <int NKT>
+template <int NKT, bool MASK>
 __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
                                              const bf16* __restrict__ Vs, int krow0, int key0,
                                              int k_begin, int k_end, const RowInfo& ri, float scale_log2,
@@ -111,9 +113,12 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int r = c >> 1;
-      const int key = key0 + nt * 8 + (lane & 3) * 2 + (c & 1);
-      const bool vis = key >= k_begin && key < k_end && key <= ri.pos[r] && key >= ri.lo[r];
-      const float v = vis ? s[nt][c] * scale_log2 : -INFINITY;
+      float v = s[nt][c] * scale_log2;
+      if (MASK) {
+        const int key = key0 + nt * 8 + (lane & 3) * 2 + (c & 1);
+        const bool vis = key >= k_begin && key < k_end && key <= ri.pos[r] && key >= ri.lo[r];
+        v = vis ? v : -INFINITY;
+      }
       s[nt][c] = v;
       mx[r] = fmaxf(mx[r], v);
     }
@@ -175,6 +180,7 @@ attn_mma_kernel(AttnParams p) {
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [BM][LDS]
   bf16* Ks = Qs + BM * LDS;                            // [2][BN][LDS]
   bf16* Vs = Ks + 2 * BN * LDS;                        // [2][BN][LDS]
+  __shared__ int s_pages[MAX_SMEM_PAGES];
 
   pdl_wait();
   const int32_t* work = p.work + (size_t)blockIdx.x * 4;
@@ -221,17 +227,31 @@ attn_mma_kernel(AttnParams p) {
     const int row = valid ? pr / G : 0, hg = valid ? pr - row * G : 0;
     cp_async16(Qs + i * LDS + col * 8, q + ((size_t)(qs + row) * H + kvh * G + hg) * HD + col * 8, valid);
   }
+  const int tile0 = (k_begin / BN) * BN;
+  const int n_tiles = k_end > tile0 ? (k_end - tile0 + BN - 1) / BN : 0;
+  // The page ids of this block's key range go to shared memory once, so that a tile's
+  // address arithmetic does not wait on a global load per row.  Ranges with more pages
+  // than fit (very long unsplit contexts) read the block table directly.
+  const int blk_first = tile0 / P;
+  const int blk_count = n_tiles > 0 ? (k_end - 1) / P - blk_first + 1 : 0;
+  const bool pages_in_smem = blk_count <= MAX_SMEM_PAGES;
+  if (pages_in_smem) {
+    for (int i = tid; i < blk_count; i += NTHREADS) s_pages[i] = bt[blk_first + i];
+    __syncthreads();
+  }
   auto load_tile = [&](int ts, int buf) {
     bf16* kd = Ks + buf * BN * LDS;
     bf16* vd = Vs + buf * BN * LDS;
-    for (int c = tid; c < BN * CPR; c += NTHREADS) {
+#pragma unroll
+    for (int it = 0; it < (BN * CPR) / NTHREADS; ++it) {
+      const int c = tid + it * NTHREADS;
       const int j = c / CPR, col = c - j * CPR;
       const int key = ts + j;
       bool valid = key >= k_begin && key < k_end;
       size_t off = 0;
       if (valid) {
         const int blk = key / P;
-        const int page = bt[blk];
+        const int page = pages_in_smem ? s_pages[blk - blk_first] : bt[blk];
         valid = page >= 0;
         if (valid) off = (((size_t)page * KV + kvh) * P + (key - blk * P)) * HD + col * 8;
       }
@@ -240,8 +260,6 @@ attn_mma_kernel(AttnParams p) {
     }
   };
 
-  const int tile0 = (k_begin / BN) * BN;
-  const int n_tiles = k_end > tile0 ? (k_end - tile0 + BN - 1) / BN : 0;
   if (n_tiles > 0) load_tile(tile0, 0);
   cp_async_commit();
 
@@ -268,6 +286,15 @@ attn_mma_kernel(AttnParams p) {
     for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
   const bf16* Qw = Qs + (keys_mode ? 0 : warp * 16) * LDS;
   const bool warp_has_rows = keys_mode || (warp * 16 < rows_here);
+  // A key tile needs no mask for this warp when every key in it is visible to every one of
+  // the warp's existing rows: the tile lies inside the block's key range, ends at or before
+  // the earliest row's position and begins at or after the latest row's first visible key.
+  // (Fragment rows beyond the request compute on zeros and are never stored.)
+  const int wrow0 = keys_mode ? 0 : warp * 16;
+  const int wrows = min(16, rows_here - wrow0);                 // <= 0: the warp has no rows
+  const int pos_min = pos0 + (pr0 + wrow0) / G;
+  const int pos_last = pos0 + (pr0 + wrow0 + max(wrows, 1) - 1) / G;
+  const int lo_max = p.window > 0 ? max(0, pos_last - p.window + 1) : 0;
 
   for (int t = 0; t < n_tiles; ++t) {
     const int ts = tile0 + t * BN;
@@ -278,9 +305,18 @@ attn_mma_kernel(AttnParams p) {
     const bf16* kt = Ks + (t & 1) * BN * LDS;
     const bf16* vt = Vs + (t & 1) * BN * LDS;
     if (keys_mode) {
-      process_tile<2>(Qw, kt, vt, warp * 16, ts + warp * 16, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+      const int key0 = ts + warp * 16;
+      const bool interior = key0 >= k_begin && key0 + 16 <= k_end && key0 + 15 <= pos_min && key0 >= lo_max;
+      if (interior)
+        process_tile<2, false>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+      else
+        process_tile<2, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane);
     } else if (warp_has_rows) {
-      process_tile<8>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+      const bool interior = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
+      if (interior)
+        process_tile<8, false>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+      else
+        process_tile<8, true>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
     }
     __syncthreads();             // everyone is done with buffer t & 1 before it is refilled
   }

@@ -18,6 +18,7 @@
 //
 // It stands where the reference calls cublasLt for every projection of a decode step
 // (matmul_kernel_batch.cu:39-208) followed by swiglu_kernel.cu for the activation.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -27,7 +28,7 @@ using namespace pbe;
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int WARPS = 8;
+namespace cg = cooperative_groups;
 
 struct SkinnyParams {
   const bf16* X;      // [M, K]
@@ -66,24 +67,30 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 
 template <int NT> struct Stages { static constexpr int value = NT == 1 ? 8 : 6; };
 
-// NT: batch tiles of 8 rows (M <= 8 * NT).  WN x WK = 8 warps.  SWIGLU: see above.  TY: output type.
+// NT: batch tiles of 8 rows (M <= 8 * NT).  A block has WN x WK warps: WN weight-row tiles by
+// WK slices of K.  CL blocks form a thread-block cluster that shares one set of row tiles
+// and splits K CL * WK ways; block 1 hands its partial sums to block 0 through distributed
+// shared memory.  Small matrices use CL = 2 with four warps a block, so that there are enough
+// blocks to fill every SM evenly while all of them are resident at once.
 //
 // Every thread owns a ring of STAGES slots in shared memory, one slot per block of 32 k:
 // its two 16-byte weight chunks and its NT activation chunks.  cp.async fills the slots
 // STAGES-1 blocks ahead; a thread only ever reads the slots it filled itself, so the main
 // loop needs no barrier.  The first STAGES-1 weight blocks are requested before the
 // programmatic dependency on the previous kernel is awaited: weights do not depend on it.
-template <int NT, int WN, int WK, bool SWIGLU, typename TY>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY>
+__global__ void __launch_bounds__(WN * WK * 32)
 gemm_skinny_kernel(SkinnyParams p) {
-  static_assert(WN * WK == WARPS, "8 warps per block");
   constexpr int STAGES = Stages<NT>::value;
   constexpr int SLOT = 2 + NT;                       // 16-byte chunks per thread and stage
-  extern __shared__ __align__(16) uint4 ring[];      // [WARPS][STAGES][SLOT][32]
+  extern __shared__ __align__(16) uint4 ring[];      // [WN * WK][STAGES][SLOT][32]
   __shared__ float red[WK][WN][NT][32][4];
+  __shared__ float xred[WN][NT][32][4];              // partial sums of the cluster's other block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wn = warp % WN, wk = warp / WN;
-  const int tile = blockIdx.x * WN + wn;
+  int crank = 0;
+  if (CL > 1) crank = (int)cg::this_cluster().block_rank();
+  const int tile = (blockIdx.x / CL) * WN + wn;
   const int g = lane >> 2, c4 = lane & 3;
   const int K = p.K;
   // the two weight rows of this thread's fragments
@@ -110,8 +117,8 @@ gemm_skinny_kernel(SkinnyParams p) {
   }
   // this warp's slice of K, in blocks of 32
   const int kblocks = (K + 31) / 32;
-  const int per = (kblocks + WK - 1) / WK;
-  const int kb0 = wk * per, kb1 = min(kblocks, kb0 + per);
+  const int per = (kblocks + CL * WK - 1) / (CL * WK);
+  const int kb0 = min(kblocks, (crank * WK + wk) * per), kb1 = min(kblocks, kb0 + per);
   uint4* my = ring + (size_t)warp * STAGES * SLOT * 32 + lane;
 
   auto issue_w = [&](int blk, int s) {
@@ -166,24 +173,44 @@ gemm_skinny_kernel(SkinnyParams p) {
   cp_async_wait<0>();
   pdl_launch_dependents();                           // the weights are read: the next kernel may launch
 
-  // sum the K slices in a fixed order
+  // sum the K slices in a fixed order: the warps of a block, then the blocks of a cluster
   if (WK > 1) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int c = 0; c < 4; ++c) red[wk][wn][nt][lane][c] = acc[nt][c];
     __syncthreads();
-    if (wk != 0) return;
+    if (wk == 0) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float s = red[0][wn][nt][lane][c];
+        for (int c = 0; c < 4; ++c) {
+          float s = red[0][wn][nt][lane][c];
 #pragma unroll
-        for (int w = 1; w < WK; ++w) s += red[w][wn][nt][lane][c];
-        acc[nt][c] = s;
-      }
+          for (int w = 1; w < WK; ++w) s += red[w][wn][nt][lane][c];
+          acc[nt][c] = s;
+        }
+    }
   }
+  if (CL > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (crank == 1 && wk == 0) {
+      float* remote = cluster.map_shared_rank(&xred[0][0][0][0], 0);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) remote[((wn * NT + nt) * 32 + lane) * 4 + c] = acc[nt][c];
+    }
+    cluster.sync();
+    if (crank != 0) return;
+    if (wk == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[nt][c] += xred[wn][nt][lane][c];
+    }
+  }
+  if (wk != 0) return;
   if (row_a < 0 && row_b < 0) return;
   TY* Y = (TY*)p.Y;
 #pragma unroll
@@ -213,25 +240,25 @@ gemm_skinny_kernel(SkinnyParams p) {
   }
 }
 
-template <int NT, int WN, int WK, bool SWIGLU, typename TY>
-int launch_cfg(const SkinnyParams& p, int blocks, cudaStream_t stream) {
-  constexpr size_t smem = sizeof(uint4) * WARPS * Stages<NT>::value * (2 + NT) * 32;
+template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY>
+int launch_cfg(const SkinnyParams& p, int row_blocks, cudaStream_t stream) {
+  constexpr size_t smem = sizeof(uint4) * WN * WK * Stages<NT>::value * (2 + NT) * 32;
   static bool opted = false;
   if (!opted) {
-    cudaFuncSetAttribute(gemm_skinny_kernel<NT, WN, WK, SWIGLU, TY>,
+    cudaFuncSetAttribute(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     opted = true;
   }
-  launch_k(gemm_skinny_kernel<NT, WN, WK, SWIGLU, TY>, blocks, WARPS * 32, smem, stream, p);
+  launch_k_cluster(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY>, row_blocks * CL, WN * WK * 32, smem, stream,
+                   CL, p);
   return launch_status();
 }
 
 template <int NT, bool SWIGLU, typename TY>
 int launch(const SkinnyParams& p, cudaStream_t stream) {
   const int tiles = p.tiles;
-  if (tiles >= 148 * 8) return launch_cfg<NT, 4, 2, SWIGLU, TY>(p, (tiles + 3) / 4, stream);
-  if (tiles >= 148 * 4) return launch_cfg<NT, 2, 4, SWIGLU, TY>(p, (tiles + 1) / 2, stream);
-  return launch_cfg<NT, 1, 8, SWIGLU, TY>(p, tiles, stream);
+  if (tiles >= 148 * 8) return launch_cfg<NT, 4, 2, 1, SWIGLU, TY>(p, (tiles + 3) / 4, stream);
+  return launch_cfg<NT, 1, 4, 2, SWIGLU, TY>(p, tiles, stream);
 }
 }  // namespace
 

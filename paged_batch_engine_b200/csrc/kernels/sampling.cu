@@ -14,6 +14,8 @@
 // logit, four bits a pass, with per-thread histograms in registers.  Weights are summed as
 // 64-bit fixed point (2^-40 units), so sums are exact, order-independent and the result
 // is the same whatever else is in the batch.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "pdl.cuh"
 
@@ -216,6 +218,45 @@ argmax_kernel(const float* __restrict__ logits, size_t ld, int V, int32_t* __res
   if (threadIdx.x == 0) out[blockIdx.x] = idx;
 }
 
+// Greedy argmax with one thread-block cluster per row: the eight blocks of a cluster each
+// scan an eighth of the vocabulary, hand their (maximum, lowest index) to block 0 through
+// distributed shared memory, and block 0 picks the winner.  No scratch in global memory and
+// eight times the memory parallelism of one block per row.
+constexpr int ARGMAX_CLUSTER = 8;
+
+__global__ void __cluster_dims__(ARGMAX_CLUSTER, 1, 1) __launch_bounds__(THREADS)
+argmax_cluster_kernel(const float* __restrict__ logits, size_t ld, int V, int32_t* __restrict__ out) {
+  namespace cg = cooperative_groups;
+  __shared__ Shared sh;
+  __shared__ float part_v[ARGMAX_CLUSTER];
+  __shared__ int part_i[ARGMAX_CLUSTER];
+  cg::cluster_group cluster = cg::this_cluster();
+  pdl_wait();
+  pdl_launch_dependents();
+  const int rank = (int)cluster.block_rank();
+  const int row = blockIdx.x / ARGMAX_CLUSTER;
+  const int chunk = ((V + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER + 3) & ~3;
+  const int lo = min(V, rank * chunk), hi = min(V, lo + chunk);
+  float mx = -INFINITY;
+  int idx = 0;
+  if (hi > lo) block_argmax(logits + (size_t)row * ld + lo, hi - lo, sh, &mx, &idx);
+  if (threadIdx.x == 0) {
+    float* pv = cluster.map_shared_rank(part_v, 0);
+    int* pi = cluster.map_shared_rank(part_i, 0);
+    pv[rank] = hi > lo ? mx : -INFINITY;
+    pi[rank] = hi > lo ? lo + idx : 0x7fffffff;
+  }
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    float b = part_v[0];
+    int bi = part_i[0];
+    for (int r = 1; r < ARGMAX_CLUSTER; ++r) {
+      if (part_v[r] > b || (part_v[r] == b && part_i[r] < bi)) { b = part_v[r]; bi = part_i[r]; }
+    }
+    out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, size_t ld, int V,
               const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
@@ -281,7 +322,10 @@ __global__ void penalty_kernel(float* logits, size_t ld, int V, const int32_t* r
 PBE_EXPORT int pbe_argmax(const float* logits, long long ld, int num_rows, int vocab, int32_t* out,
                           cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  launch_k(argmax_kernel, num_rows, THREADS, 0, stream, logits, (size_t)ld, vocab, out);
+  if (vocab >= 8 * THREADS)
+    launch_k(argmax_cluster_kernel, num_rows * ARGMAX_CLUSTER, THREADS, 0, stream, logits, (size_t)ld, vocab, out);
+  else
+    launch_k(argmax_kernel, num_rows, THREADS, 0, stream, logits, (size_t)ld, vocab, out);
   return launch_status();
 }
 
