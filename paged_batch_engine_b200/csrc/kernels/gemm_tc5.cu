@@ -1,0 +1,378 @@
+// Y[M,N] = X[M,K] * W[N,K]^T for many rows (prompt portions) on the fifth-generation tensor
+// cores: tcgen05.mma issued by one thread, operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast), the 128 x 256 float32 accumulator
+// in tensor memory, read back with tcgen05.ld for the epilogue.
+//
+// One block per SM walks over 128 x 256 output tiles.  Warp 0 is the TMA producer, warp 1 owns
+// the tensor memory and issues the MMAs, warps 2-5 are the epilogue (one TMEM lane quarter
+// each); two accumulators alternate so that the epilogue of a tile overlaps the next tile.
+// A four-stage ring of (A 128x64, B 256x64) bf16 tiles is handed over with mbarriers: TMA
+// completes `full`, tcgen05.commit completes `empty` when the MMAs that read a stage are done.
+//
+// Epilogues: plain (bfloat16 or float32 out) and SwiGLU for a stacked [gate; up] weight: the
+// B tile is then gate rows n..n+127 and up rows I+n..I+n+127, so a thread holds gate and up of
+// the same output element and writes silu(gate) * up: the activation costs no extra pass over
+// memory.  It stands where the reference calls cublasLt and then swiglu_kernel.cu.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets *err and the block goes on
+// to its end (wrong numbers, flagged), so that tensor memory is always released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "pdl.cuh"
+
+using namespace pbe;
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NTHREADS = 192;
+constexpr int TMEM_COLS = 512;          // two accumulators of 256 columns
+constexpr long long WAIT_LIMIT = 40LL * 1000 * 1000;   // polls; about a second
+
+struct Tc5Params {
+  void* Y;
+  int M, N_out, K;
+  int ld_y;
+  int swiglu;          // 0: plain; 1: B tile = gate rows and up rows
+  int up_offset;       // row of W where the up rows start (SwiGLU)
+  int y_float;         // 1: float32 output (plain mode only)
+  int tiles_m, tiles_n;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  const uint32_t addr = smem_u32(bar);
+  for (long long i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  if (err) atomicExch(err, 1);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of 8
+// rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+  d |= (uint64_t)1 << 46;                             // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M x N.
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 32 consecutive outputs of one row: 16-byte stores when the row allows it
+template <typename T>
+__device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int valid, bool aligned);
+template <>
+__device__ __forceinline__ void store_row32<bf16>(bf16* dst, const float (&v)[32], int valid, bool aligned) {
+  if (valid >= 32 && aligned) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      unsigned w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[i * 8 + 2 * j], v[i * 8 + 2 * j + 1]);
+        w[j] = *reinterpret_cast<unsigned*>(&h);
+      }
+      reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+    for (int i = 0; i < 32 && i < valid; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], int valid, bool aligned) {
+  if (valid >= 32 && aligned) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    for (int i = 0; i < 32 && i < valid; ++i) dst[i] = v[i];
+  }
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: each block walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// (tiles of one weight column block are neighbours, so blocks running side by side share
+// the weight tile in L2).  Two accumulators of 256 columns alternate in tensor memory: while
+// the epilogue warps drain one, the MMA warp fills the other.
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                Tc5Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  // stage buffers on a 1024-byte boundary (the swizzle atom)
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_smem;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int tiles_m = p.tiles_m, num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);          // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {   // tensor memory: all 512 columns, allocated and later freed by this warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_smem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_smem;
+  pdl_wait();     // the activations come from the previous kernel
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int tile_m = t % tiles_m, tile_n = t / tiles_m;
+        const int m0 = tile_m * BM;
+        const int wrow0 = p.swiglu ? tile_n * 128 : tile_n * BN;
+        const int wrow1 = p.swiglu ? p.up_offset + tile_n * 128 : tile_n * BN + 128;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty_bar[s], ph ^ 1, p.err);
+          if (!ok) break;
+          unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
+          unsigned char* b = a + A_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(a, &map_x, kb * BK, m0, &full_bar[s]);
+          tma_load_2d(b, &map_w, kb * BK, wrow0, &full_bar[s]);
+          tma_load_2d(b + 128 * BK * 2, &map_w, kb * BK, wrow1, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ MMA issuer
+      const uint32_t idesc = make_idesc(BM, BN);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++j) {
+        const int buf = j & 1;
+        ok = mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, p.err);   // the epilogue has drained this accumulator
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full_bar[s], ph, p.err);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = make_desc(a_addr + k * UMMA_K * 2);
+            const uint64_t bdesc = make_desc(b_addr + k * UMMA_K * 2);
+            umma(tmem_d, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
+        }
+        umma_commit(&acc_full[buf]);       // this tile's accumulator is complete
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue warps 2..5
+    const int quarter = warp & 3;          // the TMEM lanes this warp may read
+    int j = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++j) {
+      const int tile_m = t % tiles_m, tile_n = t / tiles_m;
+      const int buf = j & 1;
+      const int row = tile_m * BM + quarter * 32 + lane;
+      mbar_wait(&acc_full[buf], (j >> 1) & 1, p.err);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      if (p.swiglu) {
+        const int n0 = tile_n * 128;
+        bf16* yrow = (bf16*)p.Y + (size_t)row * p.ld_y;
+        const bool aligned = (p.ld_y % 8) == 0;
+        for (int c = 0; c < 4; ++c) {
+          float g[32], u[32];
+          tmem_ld32(lane_addr + c * 32, g);
+          tmem_ld32(lane_addr + 128 + c * 32, u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float sg = 1.0f / (1.0f + expf(-g[i]));
+            g[i] = (g[i] * sg) * u[i];
+          }
+          const int col = n0 + c * 32;
+          if (row < p.M && col < p.N_out) store_row32<bf16>(yrow + col, g, p.N_out - col, aligned);
+        }
+      } else {
+        const int n0 = tile_n * BN;
+        for (int c = 0; c < 8; ++c) {
+          float v[32];
+          tmem_ld32(lane_addr + c * 32, v);
+          const int col = n0 + c * 32;
+          if (row < p.M && col < p.N_out) {
+            if (p.y_float)
+              store_row32<float>((float*)p.Y + (size_t)row * p.ld_y + col, v, p.N_out - col, (p.ld_y % 4) == 0);
+            else
+              store_row32<bf16>((bf16*)p.Y + (size_t)row * p.ld_y + col, v, p.N_out - col, (p.ld_y % 8) == 0);
+          }
+        }
+      }
+      // this warp has read its quarter of the accumulator: hand it back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    pdl_launch_dependents();
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// [rows, K] row-major bfloat16, boxes of 128 rows x 64 columns, 128-byte swizzle, zeros outside
+int make_map(CUtensorMap* map, const void* base, int rows, int K) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {BK, 128};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+// mode 0: Y[M, N] = X W^T; mode 1: W is [gate; up] with N rows in total, Y[M, N/2] = silu(X gate^T) * (X up^T).
+// err: device int, set to 1 if a bounded wait ran out (the result is then invalid).
+PBE_EXPORT int pbe_gemm_tc5(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int mode,
+                            int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) != 0) return (int)cudaErrorInvalidValue;          // TMA: row stride a multiple of 16 bytes
+  if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+  if (mode == 1 && ((N & 1) || y_dtype != PBE_BF16)) return (int)cudaErrorInvalidValue;
+  CUtensorMap map_x, map_w;
+  int rc = make_map(&map_x, X, M, K);
+  if (rc != 0) return rc;
+  rc = make_map(&map_w, W, N, K);
+  if (rc != 0) return rc;
+  Tc5Params p;
+  p.Y = Y;
+  p.M = M;
+  p.K = K;
+  p.swiglu = mode == 1;
+  p.N_out = mode == 1 ? N / 2 : N;
+  p.ld_y = p.N_out;
+  p.up_offset = N / 2;
+  p.y_float = y_dtype == PBE_F32;
+  p.err = err;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  p.tiles_n = mode == 1 ? (p.N_out + 127) / 128 : (N + BN - 1) / BN;
+  p.tiles_m = (M + BM - 1) / BM;
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (num_sms <= 0) num_sms = 148;
+  }
+  const long long total = (long long)p.tiles_m * p.tiles_n;
+  const int blocks = (int)(total < num_sms ? total : num_sms);
+  launch_k(gemm_tc5_kernel, blocks, NTHREADS, smem, stream, map_x, map_w, p);
+  return launch_status();
+}

@@ -221,6 +221,50 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+_tc5_err = {}
+
+
+def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+             swiglu: bool = False, check: bool = False) -> torch.Tensor:
+    """y = x w^T for many rows on the tcgen05 tensor cores (TMA-fed, accumulator in tensor
+    memory).  ``swiglu``: w is [gate; up] stacked and y = silu(x gate^T) * (x up^T), [M, N/2].
+    ``check`` synchronises and raises if a bounded wait inside the kernel ran out."""
+    _need_cuda(x, w)
+    _need_contiguous(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError("gemm_tc5 takes bfloat16 x [M, K] and w [N, K]")
+    if K % 8 != 0:
+        raise KernelError(f"gemm_tc5 needs K to be a multiple of 8 (rows on 16-byte boundaries), got {K}")
+    out_dtype = out_dtype or torch.bfloat16
+    if swiglu and (N % 2 or out_dtype != torch.bfloat16):
+        raise KernelError("gemm_tc5: the SwiGLU epilogue needs an even N and bfloat16 output")
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    err = _tc5_err.get(x.device)
+    if err is None:
+        err = _tc5_err[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    fn = _fn("gemm_tc5", "pbe_gemm_tc5",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _ptr(out), _dtype_code(out), M, N, K, 1 if swiglu else 0, _ptr(err), _stream()),
+           "gemm_tc5")
+    if check and int(err.item()) != 0:
+        err.zero_()
+        raise KernelError("gemm_tc5: a wait inside the kernel ran out; the result is invalid")
+    return out
+
+
+# Projections of many rows: the vendor GEMM library by default (it runs two-SM tiles and is
+# the faster one); PBE_GEMM=tc5 in the environment sends them through gemm_tc5 instead.
+import os as _os
+TC5_MIN_ROWS = 128 if _os.environ.get("PBE_GEMM", "") == "tc5" else 0     # 0: never
+
+
+def tc5_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (TC5_MIN_ROWS > 0 and x.shape[0] >= TC5_MIN_ROWS and x.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0)
+
+
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (0 < x.shape[0] <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and x.shape[1] % 8 == 0)
@@ -240,6 +284,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         raise KernelError("a bfloat16 weight takes bfloat16 activations")
     if skinny_applies(x, w):
         return gemm_skinny(x, w, bias, out_dtype)
+    if tc5_applies(x, w) and bias is None:
+        return gemm_tc5(x, w, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(x, w.t(), out_dtype=torch.float32)
     else:

@@ -21,7 +21,7 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self.w_down = None
 
     def kernel_libraries(self, dtype):
-        return [("elementwise", None), ("sgemm", None), ("gemm_skinny", None)]
+        return [("elementwise", None), ("sgemm", None), ("gemm_skinny", None), ("gemm_tc5", None)]
 
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size
@@ -41,6 +41,9 @@ class SwiGLU(FeedForward):
         if ops.skinny_applies(x, self.w_gate_up):
             # few rows (decode): the activation is the epilogue of the weight-streaming product
             act = ops.gemm_skinny(x, self.w_gate_up, None, self.dtype, swiglu=True)
+            return ops.linear(act, self.w_down, None, out_dtype=self.dtype)
+        if ops.tc5_applies(x, self.w_gate_up):
+            act = ops.gemm_tc5(x, self.w_gate_up, self.dtype, swiglu=True)
             return ops.linear(act, self.w_down, None, out_dtype=self.dtype)
         gu = ops.linear(x, self.w_gate_up, None, out_dtype=self.dtype)
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)

@@ -417,3 +417,24 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch():
     for lo, hi in [(0, 1), (3, 8), (7, 16), (15, 16)]:
         part = ops().gemm_skinny(x[lo:hi].contiguous(), w, None, torch.float32)
         assert torch.equal(part, full[lo:hi])
+
+
+# ------------------------------------------------------------------ tcgen05 GEMM for many rows
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 256, 64), (300, 1000, 200), (2048, 4608, 3584),
+                                   (129, 520, 1000), (640, 3584, 18944)])
+def test_gemm_tc5(M, N, K):
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).to(DEV)
+    want = (x.double() @ w.double().t())
+    scale = want.abs().max().item()
+    got = ops().gemm_tc5(x, w, torch.float32, check=True).double()
+    assert got.shape == (M, N)
+    assert (got - want).abs().max().item() <= 2e-5 * scale * math.sqrt(K) / 8 + 1e-6     # float32 accumulation
+    gotb = ops().gemm_tc5(x, w, torch.bfloat16, check=True).double()
+    assert (gotb - want).abs().max().item() <= 2 ** -8 * scale
+    if N % 2 == 0:
+        act = ops().gemm_tc5(x, w, torch.bfloat16, swiglu=True, check=True).float().cpu()
+        ref = plain.swiglu(want[:, :N // 2].float().cpu(), want[:, N // 2:].float().cpu())
+        assert act.shape == (M, N // 2)
+        assert (act - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
