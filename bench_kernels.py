@@ -1,0 +1,92 @@
+#!/usr/bin/env python3
+"""Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
+each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
+
+    python bench_kernels.py [skinny|attn_decode|attn_prefill|tc5|all] [--once]
+
+Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
+buffer is written between launches, so every launch starts with a cold L2)."""
+import sys
+
+import torch
+
+sys.path.insert(0, __import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+from paged_batch_engine_b200.csrc import ops  # noqa: E402
+
+DEV = "cuda:0"
+ONCE = "--once" in sys.argv
+
+
+def timed(fn, flush, n=5):
+    if ONCE:                     # under a profiler: one launch of each case is enough
+        fn()
+        torch.cuda.synchronize()
+        return float("nan")
+    for _ in range(2):
+        fn()
+    ts = []
+    for _ in range(n):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    return sorted(ts)[len(ts) // 2]
+
+
+def attention_case(reqs, H=28, KV=4, hd=128, P=16):
+    from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+    from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
+    pages = sum((c + n + P - 1) // P for c, n in reqs) + 2
+    m = CacheManager([KVGroupSpec((0,), KV, hd)], P, pages, max_requests=len(reqs))
+    entries = []
+    for c, n in reqs:
+        h = m.add_request()
+        m.reserve(h, c + n)
+        m.commit(h, c)
+        entries.append(StepEntry(h, [0] * n))
+    kind, tile_rows, _ = ops.attention_kernel_config(hd, torch.bfloat16)
+    key = (0, H // KV, tile_rows, None)
+    ctx = StepContext(m, entries, torch.device(DEV), [key])
+    meta = ctx.attention_work(0, H // KV, tile_rows, None, H, hd)
+    T = sum(n for _, n in reqs)
+    q = torch.randn(T, H * hd, device=DEV).to(torch.bfloat16)
+    k = torch.randn(pages, KV, P, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(pages, KV, P, hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    run = lambda: ops.paged_attention(q, k, v, out, meta, H, KV, hd, hd ** -0.5, None, P, kind=kind)
+    return run, sum(c + n for c, n in reqs) * KV * hd * 2 * 2
+
+
+def main():
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    if what in ("skinny", "all"):
+        for name, N, K, sw in (("qkv", 4608, 3584, False), ("gate_up", 37888, 3584, True), ("down", 3584, 18944, False)):
+            w = (torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16)
+            x = torch.randn(8, K, device=DEV).to(torch.bfloat16)
+            t = timed(lambda: ops.gemm_skinny(x, w, None, torch.bfloat16, swiglu=sw), flush)
+            print(f"gemm_skinny {name} M=8: {t * 1e3:.1f} us, {N * K * 2 / t / 1e6:.0f} GB/s")
+    if what in ("attn_decode", "all"):
+        for B in (8, 64):
+            run, kv_bytes = attention_case([(2047, 1)] * B)
+            t = timed(run, flush)
+            print(f"attention decode B={B} ctx 2048: {t * 1e3:.1f} us, {kv_bytes / t / 1e6:.0f} GB/s")
+    if what in ("attn_prefill", "all"):
+        run, _ = attention_case([(0, 2048)])
+        t = timed(run, flush)
+        flops = 2 * 2 * 28 * 128 * (2048 * 2049 // 2)
+        print(f"attention prefill 2048 tokens: {t * 1e3:.1f} us, {flops / t / 1e9:.0f} TFLOP/s")
+    if what in ("tc5", "all"):
+        w = (torch.randn(37888, 3584, device=DEV) * 0.02).to(torch.bfloat16)
+        x = torch.randn(2048, 3584, device=DEV).to(torch.bfloat16)
+        t = timed(lambda: ops.gemm_tc5(x, w, torch.bfloat16, swiglu=True), flush)
+        print(f"gemm_tc5 gate_up+SwiGLU M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
+        t = timed(lambda: torch.mm(x, w.t()), flush)
+        print(f"library GEMM gate_up M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
+
+
+if __name__ == "__main__":
+    main()

@@ -33,15 +33,15 @@ using namespace pbe;
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int HD = PBE_HEAD_DIM;
-constexpr int BM = 64;            // packed rows per block
-constexpr int BN = 64;            // keys per tile
+constexpr int BM = 64;            // packed rows per row tile
+constexpr int BN_KEYS = 64;       // keys per tile, keys mode (16 per warp)
+constexpr int BN_ROWS = 32;       // keys per tile, rows mode: smaller stages, more blocks per SM
 constexpr int NTHREADS = 128;
 constexpr int LDS = HD + 8;       // shared row stride in elements: ldmatrix without bank conflicts
 constexpr int CPR = HD / 8;       // 16-byte chunks per row
 constexpr int KSTEPS = HD / 16;   // k-steps of Q.K^T
 constexpr int ONT = HD / 8;       // 8-wide output tiles of P.V
 constexpr int MAX_SMEM_PAGES = 1024;
-static_assert((BN * CPR) % NTHREADS == 0, "a key tile is a whole number of 16-byte chunks per thread");
 static_assert(HD % 16 == 0 && HD <= 256, "head size must be a multiple of 16, at most 256");
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -174,11 +174,17 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
   }
 }
 
-__global__ void __launch_bounds__(NTHREADS)
+// KEYS = false: rows mode, row tiles of more than 16 packed rows (prompt portions).
+// KEYS = true: keys mode, row tiles of at most 16 packed rows (decoded tokens); only 16 query
+// rows are staged, so that three blocks fit on an SM.  Each instance skips the other's work.
+template <bool KEYS>
+__global__ void __launch_bounds__(NTHREADS, HD <= 128 ? 3 : 1)
 attn_mma_kernel(AttnParams p) {
+  constexpr int QROWS = KEYS ? 16 : BM;
+  constexpr int BN = KEYS ? BN_KEYS : BN_ROWS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [BM][LDS]
-  bf16* Ks = Qs + BM * LDS;                            // [2][BN][LDS]
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [QROWS][LDS]
+  bf16* Ks = Qs + QROWS * LDS;                         // [2][BN][LDS]
   bf16* Vs = Ks + 2 * BN * LDS;                        // [2][BN][LDS]
   __shared__ int s_pages[MAX_SMEM_PAGES];
 
@@ -195,11 +201,11 @@ attn_mma_kernel(AttnParams p) {
   const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
   const int pr0 = m_tile * BM;
-  if (pr0 >= n_packed) {
+  const int rows_here = min(BM, n_packed - pr0);
+  if (rows_here <= 0 || (rows_here <= 16) != KEYS) {   // nothing here, or the other instance's work
     pdl_launch_dependents();
     return;
   }
-  const int rows_here = min(BM, n_packed - pr0);
   const int row_lo = pr0 / G;
   const int row_hi = (pr0 + rows_here - 1) / G;
   const int pos0 = sl - nq;
@@ -217,10 +223,9 @@ attn_mma_kernel(AttnParams p) {
   const bf16* kc = (const bf16*)p.k_cache;
   const bf16* vc = (const bf16*)p.v_cache;
   const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
-  const bool keys_mode = rows_here <= 16;
 
   // Q tile -> shared (rows beyond the request are zeros)
-  for (int c = tid; c < BM * CPR; c += NTHREADS) {
+  for (int c = tid; c < QROWS * CPR; c += NTHREADS) {
     const int i = c / CPR, col = c - i * CPR;
     const int pr = pr0 + i;
     const bool valid = pr < n_packed;
@@ -243,8 +248,9 @@ attn_mma_kernel(AttnParams p) {
     bf16* kd = Ks + buf * BN * LDS;
     bf16* vd = Vs + buf * BN * LDS;
 #pragma unroll
-    for (int it = 0; it < (BN * CPR) / NTHREADS; ++it) {
+    for (int it = 0; it < (BN * CPR + NTHREADS - 1) / NTHREADS; ++it) {
       const int c = tid + it * NTHREADS;
+      if ((BN * CPR) % NTHREADS != 0 && c >= BN * CPR) break;
       const int j = c / CPR, col = c - j * CPR;
       const int key = ts + j;
       bool valid = key >= k_begin && key < k_end;
@@ -265,7 +271,7 @@ attn_mma_kernel(AttnParams p) {
 
   // rows of this thread's fragments
   RowInfo ri;
-  const int frag_row0 = (keys_mode ? 0 : warp * 16) + (lane >> 2);
+  const int frag_row0 = (KEYS ? 0 : warp * 16) + (lane >> 2);
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     const int pr = pr0 + frag_row0 + rr * 8;
@@ -284,13 +290,13 @@ attn_mma_kernel(AttnParams p) {
   for (int nt = 0; nt < ONT; ++nt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
-  const bf16* Qw = Qs + (keys_mode ? 0 : warp * 16) * LDS;
-  const bool warp_has_rows = keys_mode || (warp * 16 < rows_here);
+  const bf16* Qw = Qs + (KEYS ? 0 : warp * 16) * LDS;
+  const bool warp_has_rows = KEYS || (warp * 16 < rows_here);
   // A key tile needs no mask for this warp when every key in it is visible to every one of
   // the warp's existing rows: the tile lies inside the block's key range, ends at or before
   // the earliest row's position and begins at or after the latest row's first visible key.
   // (Fragment rows beyond the request compute on zeros and are never stored.)
-  const int wrow0 = keys_mode ? 0 : warp * 16;
+  const int wrow0 = KEYS ? 0 : warp * 16;
   const int wrows = min(16, rows_here - wrow0);                 // <= 0: the warp has no rows
   const int pos_min = pos0 + (pr0 + wrow0) / G;
   const int pos_last = pos0 + (pr0 + wrow0 + max(wrows, 1) - 1) / G;
@@ -304,7 +310,7 @@ attn_mma_kernel(AttnParams p) {
     __syncthreads();
     const bf16* kt = Ks + (t & 1) * BN * LDS;
     const bf16* vt = Vs + (t & 1) * BN * LDS;
-    if (keys_mode) {
+    if (KEYS) {
       const int key0 = ts + warp * 16;
       const bool interior = key0 >= k_begin && key0 + 16 <= k_end && key0 + 15 <= pos_min && key0 >= lo_max;
       if (interior)
@@ -314,9 +320,9 @@ attn_mma_kernel(AttnParams p) {
     } else if (warp_has_rows) {
       const bool interior = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
       if (interior)
-        process_tile<8, false>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+        process_tile<BN / 8, false>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
       else
-        process_tile<8, true>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+        process_tile<BN / 8, true>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
     }
     __syncthreads();             // everyone is done with buffer t & 1 before it is refilled
   }
@@ -324,7 +330,7 @@ attn_mma_kernel(AttnParams p) {
   pdl_launch_dependents();      // the keys and values are read: the next kernel may start launching
 
   const float LN2 = 0.6931471805599453f;
-  if (keys_mode) {
+  if (KEYS) {
     // merge the four warps' partial results: reuse the K/V buffers as float scratch
     __syncthreads();
     float* sc_o = reinterpret_cast<float*>(Ks);          // [4][16][HD]
@@ -410,21 +416,27 @@ attn_mma_kernel(AttnParams p) {
 PBE_EXPORT int pbe_attn_mma_tile_rows() { return BM; }
 PBE_EXPORT int pbe_attn_mma_head_dim() { return HD; }
 
+// params->kinds: bit 0: some row tile has at most 16 packed rows (keys mode), bit 1: some has
+// more (rows mode); 0: unknown, both instances run.
 PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, cudaStream_t stream) {
   if (num_work <= 0) return 0;
   AttnParams p = *params;
   if (dtype != PBE_BF16 || p.num_heads % p.num_kv_heads != 0 || p.tile_rows != BM ||
-      p.split_keys % BN != 0)
+      p.split_keys % BN_KEYS != 0)
     return (int)cudaErrorInvalidValue;
-  size_t smem = sizeof(bf16) * (size_t)(BM + 4 * BN) * LDS;
+  const size_t smem_rows = sizeof(bf16) * (size_t)(BM + 4 * BN_ROWS) * LDS;
+  const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
   const size_t merge = sizeof(float) * (4 * 16 * HD + 4 * 16 * 2);   // keys-mode scratch lives in K/V
-  if (merge > sizeof(bf16) * (size_t)4 * BN * LDS) return (int)cudaErrorInvalidValue;
+  if (merge > sizeof(bf16) * (size_t)4 * BN_KEYS * LDS) return (int)cudaErrorInvalidValue;
   static bool opted = false;
   if (!opted) {
-    cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
+    cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
     opted = true;
   }
   dim3 grid(num_work, p.num_kv_heads);
-  launch_k(attn_mma_kernel, grid, NTHREADS, smem, stream, p);
+  const int kinds = p.kinds == 0 ? 3 : p.kinds;
+  if (kinds & 2) launch_k(attn_mma_kernel<false>, grid, NTHREADS, smem_rows, stream, p);
+  if (kinds & 1) launch_k(attn_mma_kernel<true>, grid, NTHREADS, smem_keys, stream, p);
   return launch_status();
 }

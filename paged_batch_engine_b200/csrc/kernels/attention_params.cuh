@@ -22,6 +22,7 @@ struct AttnParams {
   int max_splits;
   int tile_rows;            // packed rows (query row x head of the group) per row tile
   float scale;
+  int kinds;                // tensor-core kernel: bit 0 small row tiles present, bit 1 large ones; 0: unknown
 };
 
 struct AttnMergeParams {

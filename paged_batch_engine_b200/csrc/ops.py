@@ -303,7 +303,7 @@ class AttnParams(ctypes.Structure):
                 ("work", c_void_p), ("tok_split_row", c_void_p),
                 ("bt_stride", c_int), ("num_heads", c_int), ("num_kv_heads", c_int),
                 ("page_tokens", c_int), ("window", c_int), ("split_keys", c_int),
-                ("max_splits", c_int), ("tile_rows", c_int), ("scale", c_float)]
+                ("max_splits", c_int), ("tile_rows", c_int), ("scale", c_float), ("kinds", c_int)]
 
 
 class AttnMergeParams(ctypes.Structure):
@@ -360,7 +360,7 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
         tok_split_row=meta.tok_split_row.data_ptr(), bt_stride=int(meta.bt_stride),
         num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
         window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
-        tile_rows=int(meta.tile_rows), scale=float(scale))
+        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=int(getattr(meta, "kinds", 0)))
     fn = _fn(lib, "pbe_attn_" + kind, [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p], defines)
     _check(fn(ctypes.byref(p), int(meta.num_work), _dtype_code(q), _stream()), "paged_attention")
     if meta.num_split_rows > 0:

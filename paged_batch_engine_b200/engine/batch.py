@@ -59,6 +59,7 @@ class AttentionWork:
     tile_rows: int
     part_o: Optional[torch.Tensor] = None
     part_ml: Optional[torch.Tensor] = None
+    kinds: int = 0                  # bit 0: row tiles of at most 16 packed rows exist, bit 1: larger ones
 
 
 def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.ndarray,
@@ -127,6 +128,18 @@ def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.nd
         split_counts = np.zeros(0, dtype=np.int32)
     max_splits = int(fixed_splits or (n_splits.max() if R else 1))
     return work, tok_split_row, split_tokens, split_counts, max_splits
+
+
+def work_kinds(work: np.ndarray, q_len: np.ndarray, group_size: int, tile_rows: int) -> int:
+    """Which instances of the tensor-core attention kernel have work: bit 0 for row tiles of
+    at most 16 packed rows (decoded tokens, tails), bit 1 for larger ones."""
+    live = work[:, 0] >= 0
+    if not live.any():
+        return 0
+    req = work[live, 0].astype(np.int64)
+    rows = np.minimum(tile_rows, q_len[req].astype(np.int64) * group_size - work[live, 1].astype(np.int64) * tile_rows)
+    small = rows <= 16
+    return (1 if small.any() else 0) | (2 if (~small).any() else 0)
 
 
 class _Packer:
@@ -232,7 +245,7 @@ class StepContext:
             work, tsr, st, sc, max_splits = attention_work_arrays(q_len, seq_len, q_start, gsize,
                                                                   tile_rows, window)
             i_work[key] = (pk.add(work), len(work), pk.add(tsr), pk.add(st), pk.add(sc), len(st),
-                           max_splits)
+                           max_splits, work_kinds(work, q_len, gsize, tile_rows))
         pk.upload(device)
         self._packer = pk
         self.token_ids = pk.view(i_tokens)
@@ -242,14 +255,14 @@ class StepContext:
         self.state_slots = pk.view(i_state)
         self._groups = [GroupArrays(pk.view(ib), stride, pk.view(isl)) for ib, stride, isl in i_groups]
         self._work: Dict[tuple, AttentionWork] = {}
-        for key, (iw, nw, itsr, ist, isc, ns, max_splits) in i_work.items():
+        for key, (iw, nw, itsr, ist, isc, ns, max_splits, kinds) in i_work.items():
             g = self._groups[key[0]]
             self._work[key] = AttentionWork(
                 q_start=self.q_start, q_len=self.q_len, seq_len=self.seq_len,
                 block_table=g.block_table, bt_stride=g.bt_stride, work=pk.view(iw), num_work=nw,
                 tok_split_row=pk.view(itsr), split_tokens=pk.view(ist) if ns else None,
                 split_counts=pk.view(isc) if ns else None, num_split_rows=ns, max_splits=max_splits,
-                split_keys=SPLIT_KEYS, tile_rows=key[2])
+                split_keys=SPLIT_KEYS, tile_rows=key[2], kinds=kinds)
 
     def group(self, g: int) -> GroupArrays:
         return self._groups[g]

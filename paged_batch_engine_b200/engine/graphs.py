@@ -78,7 +78,7 @@ class DecodeStepContext(StepContext):
                 block_table=grp.block_table, bt_stride=grp.bt_stride, work=view(f"work{i}"),
                 num_work=B * S, tok_split_row=view(f"tsr{i}"), split_tokens=view(f"st{i}"),
                 split_counts=view(f"sc{i}"), num_split_rows=B, max_splits=S, split_keys=SPLIT_KEYS,
-                tile_rows=key[2])
+                tile_rows=key[2], kinds=1 if key[1] <= 16 else 2)
 
     def _h(self, name):
         o, shape = self._layout[name]
