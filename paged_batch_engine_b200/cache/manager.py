@@ -209,6 +209,11 @@ class CacheManager:
         if n_tokens < 0:
             raise CacheError(f"cannot reserve {n_tokens} tokens")
         req = self._lookup(handle)
+        # the usual decode step: the token still fits in the last page of every group
+        room = req.reserved + n_tokens
+        if all(room <= len(t) * self.page_tokens for t in req.tables):
+            req.reserved = room
+            return True
         need = self.pages_needed(handle, n_tokens)
         if any(n > p.num_free for n, p in zip(need, self.pools)):
             return False

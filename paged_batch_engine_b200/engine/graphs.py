@@ -60,6 +60,12 @@ class DecodeStepContext(StepContext):
         self._layout, self._size = lay, off
         self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
         self._host_np = self.host.numpy()
+        self._handles: List[int] = []
+        self._known: List[List[int]] = []
+        self._arange = np.arange(B, dtype=np.int64)
+        self._srange = np.arange(S, dtype=np.int64)
+        self._ones = np.ones(B, dtype=np.int64)
+        self.state_slots_host = np.zeros(0, dtype=np.int64)
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
 
         def view(name):
@@ -70,6 +76,11 @@ class DecodeStepContext(StepContext):
         self.want_rows, self.state_slots = view("want"), view("state")
         self._groups = [GroupArrays(view(f"bt{g}"), stride, view(f"slots{g}"))
                         for g, stride in enumerate(bt_strides)]
+        self._h("q_start")[:] = np.arange(B)
+        self._h("want")[:] = np.arange(B)
+        for i, _ in enumerate(self.work_keys):
+            self._h(f"tsr{i}")[:] = np.arange(B)
+            self._h(f"st{i}")[:] = np.arange(B)
         self._work = {}
         for i, key in enumerate(self.work_keys):
             grp = self._groups[key[0]]
@@ -85,44 +96,69 @@ class DecodeStepContext(StepContext):
         return self._host_np[o:o + int(np.prod(shape))].reshape(shape)
 
     def fill(self, entries: Sequence[StepEntry], vocab_size: int) -> None:
+        """Writes this step's integers into the pinned buffer and copies it to the device.
+        Rows keep their block tables between steps: when the same requests come back in the
+        same order (the usual case while decoding), only newly added pages are written."""
         m, B, S, P = self.manager, self.batch, self.splits, self.page_tokens
         R = len(entries)
-        ctx_before = np.fromiter((m.context_len(e.handle) for e in entries), dtype=np.int64, count=R)
+        handles = [e.handle for e in entries]
+        same = handles == self._handles
+        ctx_before = np.fromiter((m.context_len(h) for h in handles), dtype=np.int64, count=R)
         tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
-        if ((tokens < 0) | (tokens >= vocab_size)).any():
+        if tokens.min() < 0 or tokens.max() >= vocab_size:
             raise ValueError("a token id is outside the vocabulary")
-        self.q_len_host = np.ones(R, dtype=np.int64)
-        self.seq_len_host = ctx_before + 1
-        self.q_start_host = np.arange(R, dtype=np.int64)
+        seq_len = ctx_before + 1
+        self.q_len_host = self._ones[:R]
+        self.seq_len_host = seq_len
+        self.q_start_host = self._arange[:R]
         self.context_before_host = ctx_before
-        self.state_slots_host = np.fromiter((m.state_slot(e.handle) for e in entries), dtype=np.int64, count=R)
-        t = self._h("tokens"); t[:] = 0; t[:R] = tokens
-        p = self._h("positions"); p[:] = 0; p[:R] = ctx_before
-        self._h("q_start")[:] = np.arange(B)
-        q = self._h("q_len"); q[:] = 0; q[:R] = 1
-        s = self._h("seq_len"); s[:] = 0; s[:R] = ctx_before + 1
-        self._h("want")[:] = np.arange(B)
-        st = self._h("state"); st[:] = 0; st[:R] = self.state_slots_host
+        self._h("tokens")[:R] = tokens
+        self._h("positions")[:R] = ctx_before
+        self._h("seq_len")[:R] = seq_len
+        if not same:
+            self.state_slots_host = np.fromiter((m.state_slot(h) for h in handles), dtype=np.int64, count=R)
+            self._h("tokens")[R:] = 0
+            self._h("positions")[R:] = 0
+            self._h("seq_len")[R:] = 0
+            q = self._h("q_len"); q[:] = 0; q[:R] = 1
+            st = self._h("state"); st[:] = 0; st[:R] = self.state_slots_host
+            self._known = [[0] * R for _ in m.groups]
+            for g in range(len(m.groups)):
+                self._h(f"bt{g}")[:] = -1
+                self._h(f"slots{g}")[:] = -1
         for g in range(len(m.groups)):
             bt = self._h(f"bt{g}")
-            bt[:] = -1
-            for r, e in enumerate(entries):
-                table = m.block_table(e.handle, g)
-                bt[r, :len(table)] = table
-            page = bt[np.arange(R), ctx_before // P]
-            if (page < 0).any():
+            known = self._known[g]
+            for r, h in enumerate(handles):
+                table = m.block_table(h, g)
+                n = len(table)
+                k = known[r]
+                if n != k or m.groups[g].window is not None:
+                    lo = 0 if m.groups[g].window is not None else k     # a window also takes pages away
+                    bt[r, lo:n] = table[lo:]
+                    known[r] = n
+            page = bt[self._arange[:R], ctx_before // P]
+            if page.min() < 0:
                 raise ValueError("a token of this step lies in a page that is not held")
-            sl = self._h(f"slots{g}"); sl[:] = -1
-            sl[:R] = page.astype(np.int64) * P + ctx_before % P
+            self._h(f"slots{g}")[:R] = page.astype(np.int64) * P + ctx_before % P
         for i, key in enumerate(self.work_keys):
             _, gsize, tile_rows, window = key
-            work, tsr, stoks, scnt, _ = attention_work_arrays(
-                self.q_len_host, self.seq_len_host, self.q_start_host, gsize, tile_rows, window,
-                force_split=True, fixed_splits=S)
-            w = self._h(f"work{i}"); w[:] = -1; w[:R * S] = work
-            a = self._h(f"tsr{i}"); a[:] = np.arange(B)
-            a = self._h(f"st{i}"); a[:] = np.arange(B)
-            a = self._h(f"sc{i}"); a[:] = 0; a[:R] = scnt
+            # one row tile per request; the number of splits follows from its own length
+            lo = np.maximum(0, ctx_before - window + 1) if window else 0
+            ns = (seq_len + SPLIT_KEYS - 1) // SPLIT_KEYS - lo // SPLIT_KEYS
+            if ns.max() > S:
+                raise ValueError("a request needs more key splits than this captured step holds")
+            w = self._h(f"work{i}").reshape(B, S, 4)
+            live = self._srange[None, :] < ns[:, None]                    # [R, S]
+            w[:R, :, 0] = np.where(live, self._arange[:R, None], -1)
+            w[:R, :, 3] = ns[:, None]
+            self._h(f"sc{i}")[:R] = ns
+            if not same:
+                w[R:, :, 0] = -1
+                w[:, :, 1] = 0
+                w[:, :, 2] = self._srange[None, :]
+                self._h(f"sc{i}")[R:] = 0
+        self._handles = handles
         self.dev.copy_(self.host, non_blocking=True)
 
     def attention_work(self, group, group_size, tile_rows, window, num_heads, head_dim):

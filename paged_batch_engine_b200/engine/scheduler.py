@@ -55,6 +55,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.outputs
 
+    def token_slice(self, lo: int, hi: int) -> List[int]:
+        """tokens[lo:hi] without building the whole list (called for every row of every step)."""
+        n = len(self.prompt)
+        if hi <= n:
+            return self.prompt[lo:hi]
+        if lo >= n:
+            return self.outputs[lo - n:hi - n]
+        return self.prompt[lo:] + self.outputs[:hi - n]
+
     @property
     def target(self) -> int:
         """Tokens that must be in the cache before the next token can be sampled."""
@@ -163,7 +172,7 @@ class Scheduler:
                 self._preempt(req, out)
                 continue
             req.scheduled = 1
-            out.entries.append(ScheduledEntry(req, [req.tokens[req.computed]], True))
+            out.entries.append(ScheduledEntry(req, req.token_slice(req.computed, req.computed + 1), True))
             out.num_decode += 1
             budget -= 1
         return budget
@@ -214,7 +223,7 @@ class Scheduler:
         return budget
 
     def _append_prefill(self, req: Request, chunk: int, out: SchedulerOutput) -> None:
-        toks = req.tokens[req.computed:req.computed + chunk]
+        toks = req.token_slice(req.computed, req.computed + chunk)
         req.scheduled = chunk
         out.entries.append(ScheduledEntry(req, toks, req.computed + chunk == req.target))
 
