@@ -82,11 +82,12 @@ struct RowInfo {      // the two rows of this thread's accumulator fragment
 
 // One key tile for one warp: NKT 8-key score tiles starting at key `key0` (absolute) which
 // sit at row `krow0` of the shared K and V tiles.  Updates m, l (log2 domain) and o.
-template <int NKT, bool MASK>
+template <int NKT, bool MASK, bool QREG = false>
 __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
                                              const bf16* __restrict__ Vs, int krow0, int key0,
                                              int k_begin, int k_end, const RowInfo& ri, float scale_log2,
-                                             float (&m)[2], float (&l)[2], float (&o)[ONT][4], int lane) {
+                                             float (&m)[2], float (&l)[2], float (&o)[ONT][4], int lane,
+                                             const unsigned (*qreg)[4] = nullptr) {
   float s[NKT][4];
 #pragma unroll
   for (int nt = 0; nt < NKT; ++nt)
@@ -96,7 +97,12 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
     unsigned a[4];
-    ldmatrix_x4(a, Qw + (lane & 15) * LDS + ks * 16 + 8 * (lane >> 4));
+    if (QREG) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = qreg[ks][i];
+    } else {
+      ldmatrix_x4(a, Qw + (lane & 15) * LDS + ks * 16 + 8 * (lane >> 4));
+    }
 #pragma unroll
     for (int np = 0; np < NKT / 2; ++np) {
       unsigned b[4];
@@ -411,13 +417,185 @@ attn_mma_kernel(AttnParams p) {
     }
   }
 }
+// Decoded tokens (row tiles of at most 16 packed rows), persistent and warp-private: every
+// warp walks over work items (request, row tile, key split, kv head) on its own, streams the
+// item's keys and values in tiles of 16 through a three-stage cp.async ring that only it
+// touches (no block-wide barrier anywhere), keeps the query fragments in registers, and
+// writes the item's result or partial result straight from its accumulator registers.  Two
+// blocks of four warps fit on an SM, each warp with two tiles in flight.
+constexpr int DEC_KEYS = 16;            // keys per tile
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_WARPS = 4;
+
+__global__ void __launch_bounds__(DEC_WARPS * 32, HD <= 128 ? 2 : 1)
+attn_decode_kernel(AttnParams p, int num_work) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * DEC_STAGES * 2 * DEC_KEYS * LDS;
+  pdl_wait();
+  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const bf16* q = (const bf16*)p.q;
+  const bf16* kc = (const bf16*)p.k_cache;
+  const bf16* vc = (const bf16*)p.v_cache;
+  const int total_items = num_work * KV;
+  const int g = lane >> 2, c4 = lane & 3;
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  const float LN2 = 0.6931471805599453f;
+
+  for (int item = blockIdx.x * DEC_WARPS + warp; item < total_items; item += gridDim.x * DEC_WARPS) {
+    const int wk = item / KV, kvh = item - wk * KV;
+    const int32_t* work = p.work + (size_t)wk * 4;
+    const int r = work[0];
+    if (r < 0) continue;
+    const int m_tile = work[1], split = work[2], nsplit = work[3];
+    const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+    const int n_packed = nq * G;
+    const int pr0 = m_tile * BM;
+    const int rows_here = min(BM, n_packed - pr0);
+    if (rows_here <= 0 || rows_here > 16) continue;          // larger tiles belong to the rows-mode kernel
+    const int row_lo = pr0 / G;
+    const int row_hi = (pr0 + rows_here - 1) / G;
+    const int pos0 = sl - nq;
+    const int hi_key = pos0 + row_hi + 1;
+    const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
+    int k_begin = lo_key, k_end = hi_key;
+    if (nsplit > 1) {
+      const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+      const int s0 = lo_req / p.split_keys;
+      k_begin = max(lo_key, (s0 + split) * p.split_keys);
+      k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+    }
+    const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
+
+    // query fragments of the 16 packed rows, straight into the mma A layout
+    unsigned qa[KSTEPS][4];
+    RowInfo ri;
+    {
+      const bf16* qrow[2];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int pr = pr0 + g + rr * 8;
+        if (pr < n_packed) {
+          const int row = pr / G, hg = pr - row * G;
+          qrow[rr] = q + ((size_t)(qs + row) * H + kvh * G + hg) * HD;
+          ri.pos[rr] = pos0 + row;
+          ri.lo[rr] = p.window > 0 ? ri.pos[rr] - p.window + 1 : 0;
+        } else {
+          qrow[rr] = nullptr;
+          ri.pos[rr] = -1;
+          ri.lo[rr] = 0;
+        }
+      }
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const bf16* src = qrow[i & 1];
+          const int col = ks * 16 + c4 * 2 + (i >> 1) * 8;
+          qa[ks][i] = src ? *reinterpret_cast<const unsigned*>(src + col) : 0u;
+        }
+      }
+    }
+    const int pos_min = pos0 + row_lo;
+    const int lo_max = p.window > 0 ? max(0, pos0 + row_hi - p.window + 1) : 0;
+
+    const int tile0 = (k_begin / DEC_KEYS) * DEC_KEYS;
+    const int n_tiles = k_end > tile0 ? (k_end - tile0 + DEC_KEYS - 1) / DEC_KEYS : 0;
+    // page ids: a window of 32 block-table entries in registers, one per lane
+    int win = tile0 / P;
+    int pg = (win + lane) * P < k_end ? bt[win + lane] : -1;
+    auto load_tile = [&](int t, int stage) {
+      const int ts = tile0 + t * DEC_KEYS;
+      const int last_blk = (ts + DEC_KEYS - 1) / P;
+      if (last_blk >= win + 32) {                      // warp-uniform: slide the window
+        win = ts / P;
+        pg = (win + lane) * P < k_end ? bt[win + lane] : -1;
+      }
+      bf16* kd = ring + (size_t)stage * 2 * DEC_KEYS * LDS;
+      bf16* vd = kd + DEC_KEYS * LDS;
+#pragma unroll
+      for (int it = 0; it < (DEC_KEYS * CPR + 31) / 32; ++it) {
+        const int c = lane + it * 32;
+        const int j = (c / CPR) % DEC_KEYS, col = c - (c / CPR) * CPR;
+        const int key = ts + j;
+        const int blk = key / P;
+        const int page = __shfl_sync(0xffffffffu, pg, (blk - win) & 31);
+        const bool valid = c < DEC_KEYS * CPR && key >= k_begin && key < k_end && page >= 0;
+        const size_t off = valid ? (((size_t)page * KV + kvh) * P + (key - blk * P)) * HD + col * 8 : 0;
+        if (c < DEC_KEYS * CPR) {
+          cp_async16(kd + j * LDS + col * 8, kc + off, valid);
+          cp_async16(vd + j * LDS + col * 8, vc + off, valid);
+        }
+      }
+    };
+    __syncwarp();                 // the previous item's reads of the ring are over
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+      if (st < n_tiles) load_tile(st, st);
+      cp_async_commit();
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[ONT][4];
+#pragma unroll
+    for (int nt = 0; nt < ONT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
+    int buf = 0, fill = DEC_STAGES - 1;
+    for (int t = 0; t < n_tiles; ++t) {
+      if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, fill);
+      cp_async_commit();
+      cp_async_wait<DEC_STAGES - 1>();
+      __syncwarp();               // every lane's copies of tile t are visible to the warp
+      const bf16* kt = ring + (size_t)buf * 2 * DEC_KEYS * LDS;
+      const bf16* vt = kt + DEC_KEYS * LDS;
+      const int key0 = tile0 + t * DEC_KEYS;
+      const bool interior = key0 >= k_begin && key0 + DEC_KEYS <= k_end && key0 + DEC_KEYS - 1 <= pos_min &&
+                            key0 >= lo_max;
+      if (interior)
+        process_tile<2, false, true>(nullptr, kt, vt, 0, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane, qa);
+      else
+        process_tile<2, true, true>(nullptr, kt, vt, 0, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane, qa);
+      __syncwarp();               // the stage may be refilled
+      buf = buf + 1 == DEC_STAGES ? 0 : buf + 1;
+      fill = fill + 1 == DEC_STAGES ? 0 : fill + 1;
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int pr = pr0 + g + rr * 8;
+      if (pr >= n_packed) continue;
+      const int qrow = pr / G, hg = pr - qrow * G;
+      const int head = kvh * G + hg;
+      const int tok = qs + qrow;
+      if (nsplit <= 1) {
+        const float inv = l[rr] > 0.f ? 1.0f / l[rr] : 0.f;
+        bf16* dst = (bf16*)p.out + ((size_t)tok * H + head) * HD + c4 * 2;
+#pragma unroll
+        for (int nt = 0; nt < ONT; ++nt)
+          *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
+              __floats2bfloat162_rn(o[nt][rr * 2] * inv, o[nt][rr * 2 + 1] * inv);
+      } else {
+        const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
+        float* dst = p.part_o + base * HD + c4 * 2;
+#pragma unroll
+        for (int nt = 0; nt < ONT; ++nt)
+          *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][rr * 2], o[nt][rr * 2 + 1]);
+        if (c4 == 0) {
+          p.part_ml[base * 2] = m[rr] == -INFINITY ? -INFINITY : m[rr] * LN2;
+          p.part_ml[base * 2 + 1] = l[rr];
+        }
+      }
+    }
+  }
+  pdl_launch_dependents();
+}
 }  // namespace
 
 PBE_EXPORT int pbe_attn_mma_tile_rows() { return BM; }
 PBE_EXPORT int pbe_attn_mma_head_dim() { return HD; }
 
-// params->kinds: bit 0: some row tile has at most 16 packed rows (keys mode), bit 1: some has
-// more (rows mode); 0: unknown, both instances run.
+// params->kinds: bit 0: some row tile has at most 16 packed rows (decoded tokens), bit 1: some
+// has more (prompt portions); neither: unknown, both run.  Bit 2: the step has few requests.
 PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, cudaStream_t stream) {
   if (num_work <= 0) return 0;
   AttnParams p = *params;
@@ -425,18 +603,36 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
       p.split_keys % BN_KEYS != 0)
     return (int)cudaErrorInvalidValue;
   const size_t smem_rows = sizeof(bf16) * (size_t)(BM + 4 * BN_ROWS) * LDS;
-  const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
-  const size_t merge = sizeof(float) * (4 * 16 * HD + 4 * 16 * 2);   // keys-mode scratch lives in K/V
-  if (merge > sizeof(bf16) * (size_t)4 * BN_KEYS * LDS) return (int)cudaErrorInvalidValue;
   static bool opted = false;
   if (!opted) {
     cudaFuncSetAttribute(attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
-    cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
     opted = true;
   }
   dim3 grid(num_work, p.num_kv_heads);
-  const int kinds = p.kinds == 0 ? 3 : p.kinds;
+  const int kinds = (p.kinds & 3) == 0 ? (p.kinds | 3) : p.kinds;
   if (kinds & 2) launch_k(attn_mma_kernel<false>, grid, NTHREADS, smem_rows, stream, p);
-  if (kinds & 1) launch_k(attn_mma_kernel<true>, grid, NTHREADS, smem_keys, stream, p);
+  if ((kinds & 1) && (kinds & 4)) {
+    // few requests: four warps share every key tile, the shortest path through one work item
+    const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
+    static bool opted_keys = false;
+    if (!opted_keys) {
+      cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+      opted_keys = true;
+    }
+    launch_k(attn_mma_kernel<true>, grid, NTHREADS, smem_keys, stream, p);
+  } else if (kinds & 1) {
+    const size_t smem_dec = sizeof(bf16) * (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_KEYS * LDS;
+    static int dec_blocks = 0;
+    if (dec_blocks == 0) {
+      cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      dec_blocks = (sms > 0 ? sms : 148) * (HD <= 128 ? 2 : 1);
+    }
+    const int items = num_work * p.num_kv_heads;
+    const int blocks = min(dec_blocks, (items + DEC_WARPS - 1) / DEC_WARPS);
+    launch_k(attn_decode_kernel, blocks, DEC_WARPS * 32, smem_dec, stream, p, num_work);
+  }
   return launch_status();
 }

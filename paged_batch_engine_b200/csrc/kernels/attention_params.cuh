@@ -22,7 +22,8 @@ struct AttnParams {
   int max_splits;
   int tile_rows;            // packed rows (query row x head of the group) per row tile
   float scale;
-  int kinds;                // tensor-core kernel: bit 0 small row tiles present, bit 1 large ones; 0: unknown
+  int kinds;                // tensor-core kernel: bit 0 small row tiles present, bit 1 large ones (0: unknown);
+                            // bit 2: few requests, small tiles go to the block-cooperative instance
 };
 
 struct AttnMergeParams {

@@ -22,8 +22,20 @@ import torch
 
 from ..cache.manager import CacheManager
 
-SPLIT_KEYS = 256          # keys per split of a short request's long key range
+SPLIT_KEYS = 256          # keys per split of a short request's long key range, many requests
 MAX_SPLIT_TILES = 4       # requests with more row tiles than this are never split
+
+
+def choose_split_keys(num_requests: int) -> int:
+    """Keys per split for a step.  One size for every step: a row's partial sums are then
+    combined in the same order whatever else is in the batch."""
+    return SPLIT_KEYS
+
+
+# Steps with at most this many requests run decoded tokens through the block-cooperative
+# instance of the attention kernel (four warps share each key tile: shortest latency per work
+# item); larger steps through the persistent warp-private instance (most bytes in flight).
+DECODE_BLOCK_MAX_REQUESTS = 16
 
 
 @dataclass
@@ -139,7 +151,10 @@ def work_kinds(work: np.ndarray, q_len: np.ndarray, group_size: int, tile_rows: 
     req = work[live, 0].astype(np.int64)
     rows = np.minimum(tile_rows, q_len[req].astype(np.int64) * group_size - work[live, 1].astype(np.int64) * tile_rows)
     small = rows <= 16
-    return (1 if small.any() else 0) | (2 if (~small).any() else 0)
+    kinds = (1 if small.any() else 0) | (2 if (~small).any() else 0)
+    if len(q_len) <= DECODE_BLOCK_MAX_REQUESTS:
+        kinds |= 4
+    return kinds
 
 
 class _Packer:
@@ -190,6 +205,7 @@ class StepContext:
         R = len(entries)
         if R == 0:
             raise ValueError("a step needs at least one entry")
+        self.split_keys = choose_split_keys(R)
         q_len = np.array([len(e.tokens) for e in entries], dtype=np.int64)
         if (q_len <= 0).any():
             raise ValueError("every entry of a step brings at least one token")
@@ -243,7 +259,7 @@ class StepContext:
         for key in work_keys:
             group, gsize, tile_rows, window = key
             work, tsr, st, sc, max_splits = attention_work_arrays(q_len, seq_len, q_start, gsize,
-                                                                  tile_rows, window)
+                                                                  tile_rows, window, split_keys=self.split_keys)
             i_work[key] = (pk.add(work), len(work), pk.add(tsr), pk.add(st), pk.add(sc), len(st),
                            max_splits, work_kinds(work, q_len, gsize, tile_rows))
         pk.upload(device)
@@ -262,7 +278,7 @@ class StepContext:
                 block_table=g.block_table, bt_stride=g.bt_stride, work=pk.view(iw), num_work=nw,
                 tok_split_row=pk.view(itsr), split_tokens=pk.view(ist) if ns else None,
                 split_counts=pk.view(isc) if ns else None, num_split_rows=ns, max_splits=max_splits,
-                split_keys=SPLIT_KEYS, tile_rows=key[2], kinds=kinds)
+                split_keys=self.split_keys, tile_rows=key[2], kinds=kinds)
 
     def group(self, g: int) -> GroupArrays:
         return self._groups[g]

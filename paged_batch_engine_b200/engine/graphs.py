@@ -18,8 +18,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from .batch import (SPLIT_KEYS, AttentionWork, GroupArrays, StepContext, StepEntry,
-                    attention_work_arrays)
+from .batch import (DECODE_BLOCK_MAX_REQUESTS, AttentionWork, GroupArrays, StepContext, StepEntry,
+                    attention_work_arrays, choose_split_keys)
 
 
 def _bucket(n: int, cap: Optional[int] = None) -> int:
@@ -36,6 +36,7 @@ class DecodeStepContext(StepContext):
         self.manager, self.device = manager, device
         self.page_tokens = manager.page_tokens
         self.batch, self.splits = batch, splits
+        self.split_keys = choose_split_keys(batch)
         self.num_tokens = self.num_requests = self.num_wanted = batch
         self.work_keys = list(work_keys)
         B, S = batch, splits
@@ -88,8 +89,8 @@ class DecodeStepContext(StepContext):
                 q_start=self.q_start, q_len=self.q_len, seq_len=self.seq_len,
                 block_table=grp.block_table, bt_stride=grp.bt_stride, work=view(f"work{i}"),
                 num_work=B * S, tok_split_row=view(f"tsr{i}"), split_tokens=view(f"st{i}"),
-                split_counts=view(f"sc{i}"), num_split_rows=B, max_splits=S, split_keys=SPLIT_KEYS,
-                tile_rows=key[2], kinds=1 if key[1] <= 16 else 2)
+                split_counts=view(f"sc{i}"), num_split_rows=B, max_splits=S, split_keys=self.split_keys,
+                tile_rows=key[2], kinds=(1 if key[1] <= 16 else 2) | (4 if B <= DECODE_BLOCK_MAX_REQUESTS else 0))
 
     def _h(self, name):
         o, shape = self._layout[name]
@@ -145,7 +146,7 @@ class DecodeStepContext(StepContext):
             _, gsize, tile_rows, window = key
             # one row tile per request; the number of splits follows from its own length
             lo = np.maximum(0, ctx_before - window + 1) if window else 0
-            ns = (seq_len + SPLIT_KEYS - 1) // SPLIT_KEYS - lo // SPLIT_KEYS
+            ns = (seq_len + self.split_keys - 1) // self.split_keys - lo // self.split_keys
             if ns.max() > S:
                 raise ValueError("a request needs more key splits than this captured step holds")
             w = self._h(f"work{i}").reshape(B, S, 4)
@@ -190,20 +191,20 @@ class DecodeGraphs:
         # one row tile per request is what a fixed work list holds
         return all(gsize <= tile_rows for _, gsize, tile_rows, _ in self.runner._work_keys)
 
-    def _splits_needed(self, entries) -> int:
+    def _splits_needed(self, entries, split_keys: int) -> int:
         m = self.runner.cache
         longest = max(m.context_len(e.handle) for e in entries) + 1
         worst = 1
         for _, _, _, window in self.runner._work_keys:
             lo = max(0, longest - 1 - window + 1) if window else 0
-            worst = max(worst, (longest + SPLIT_KEYS - 1) // SPLIT_KEYS - lo // SPLIT_KEYS)
+            worst = max(worst, (longest + split_keys - 1) // split_keys - lo // split_keys)
         return worst
 
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         runner = self.runner
         R = len(entries)
         B = _bucket(R)
-        S = _bucket(self._splits_needed(entries))
+        S = _bucket(self._splits_needed(entries, choose_split_keys(B)))
         key = (B, S)
         if key not in self.graphs:
             self.graphs[key] = self._capture(B, S, entries)
