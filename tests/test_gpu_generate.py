@@ -65,6 +65,31 @@ def test_bfloat16_greedy_tokens_are_plain_argmax_up_to_rounding(tiny_folders, na
             assert row.max() - row[tok] <= 0.04 * logits.abs().max(), (name, i)
 
 
+def test_many_requests_at_once(tiny_folders):
+    """Twenty requests decode together (captured steps of 32 rows, the many-requests attention
+    instance); every one must produce what it produces alone."""
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["C"]
+    folder = tiny_folders["C"]
+    prompts = prompts_for(cfg["vocab_size"], [3 + 5 * i for i in range(20)], seed=9)
+    sp = SamplingParams(max_new_tokens=10, ignore_eos=True)
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(folder, dtype, page, num_pages=256, max_num_seqs=32, max_num_batched_tokens=64)
+        together = eng.generate(prompts, sp)
+        assert eng.runner.graphs.replays > 0
+        alone = engine(folder, dtype, page, num_pages=256)
+        pcfg, w = load_plain(folder)
+        for p, r in zip(prompts, together):
+            if dtype == "float32":
+                assert r.output_tokens == alone.generate([p], sp)[0].output_tokens
+            else:
+                seq = p + r.output_tokens
+                logits = plain.forward_logits(pcfg, w, seq[:-1])
+                for i, tok in enumerate(r.output_tokens):
+                    row = logits[len(p) - 1 + i]
+                    assert row.max() - row[tok] <= 0.04 * logits.abs().max()
+
+
 def test_temperature_sampling_follows_the_reference_algorithm(tiny_folders):
     from paged_batch_engine_b200 import SamplingParams
     cfg, _, page, _ = TINY["B"]

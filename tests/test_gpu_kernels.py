@@ -181,7 +181,7 @@ class AttnCase:
         self.H, self.KV, self.hd, self.P, self.window, self.dtype, self.kind = H, KV, hd, P, window, dtype, kind
         kind_, tile_rows, _ = o.attention_kernel_config(hd, dtype, kind)
         total_pages = num_pages or sum((c + n + P - 1) // P for c, n in reqs) + 3
-        m = CacheManager([KVGroupSpec((0,), KV, hd, window)], P, total_pages, max_requests=16, lifo=True)
+        m = CacheManager([KVGroupSpec((0,), KV, hd, window)], P, total_pages, max_requests=64, lifo=True)
         # scramble the free list: take all pages and give them back in random order
         tmp = m.add_request()
         m.reserve(tmp, total_pages * P)
@@ -301,6 +301,36 @@ def test_attention_mma_prompt_tiles_and_mixed_batch():
     got, want = case.run(), case.reference()
     assert not torch.isnan(got).any()
     assert (got - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("H,KV,hd,P,window", [(28, 4, 128, 16, None), (6, 3, 48, 8, 40), (4, 2, 16, 16, None),
+                                               (5, 5, 256, 16, None)])
+def test_attention_mma_many_decoding_requests(H, KV, hd, P, window):
+    """More than 16 requests in a step: decoded tokens go through the persistent warp-private
+    instance (one warp streams a whole key split).  Contexts end on and off tile, split and
+    page edges; a few short prompt portions ride along."""
+    ctxs = [0, 1, 15, 16, 17, 63, 64, 255, 256, 257, 300, 511, 512, 513, 700, 31, 33, 1000, 129, 5]
+    reqs = [(c, 1) for c in ctxs] + [(90, 2), (0, 12)]
+    case = AttnCase(H, KV, hd, P, window, reqs, torch.bfloat16, seed=hd + len(reqs), kind="mma")
+    case.write_cache()
+    got, want = case.run(), case.reference()
+    assert case.meta.kinds & 4 == 0 and case.meta.kinds & 1          # the many-requests path was taken
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
+    # one key stands out at the last position of a long context, for every request at once
+    case2 = AttnCase(H, KV, hd, P, None, [(600 + 7 * i, 1) for i in range(18)], torch.bfloat16, seed=1, kind="mma")
+    for i, (q, k, v, c, n, h) in enumerate(case2.seqs):
+        j = [0, 15, 16, 255, 256, 599][i % 6]
+        k.mul_(0.05)
+        q[c] = 0
+        q[c, :, 0] = 40.0
+        k[j, :, 0] = 40.0
+    case2.write_cache()
+    got2 = case2.run()
+    for i, (q, k, v, c, n, h) in enumerate(case2.seqs):
+        j = [0, 15, 16, 255, 256, 599][i % 6]
+        for head in range(H):
+            assert torch.allclose(got2[i, head], v[j, head // (H // KV)].float(), atol=3e-2), (i, j, head)
 
 
 def test_attention_ignores_stale_data_in_reused_and_foreign_pages():
