@@ -234,7 +234,10 @@ def main():
     pk = peaks()
     page = 16
     max_batch = 64 if not args.no_points else args.batch
-    max_len = args.context + 2 * (steps + warmup) + 64
+    # tokens a request may generate: warm-up and timed steps twice (device-timed, then through
+    # the entry point) plus what it decodes while the later prompts of its batch are still read
+    new_tokens = 2 * (steps + warmup) + 8 + max_batch
+    max_len = args.context + new_tokens + 64
     pool_pages = max_batch * ((max_len + page - 1) // page) + 2 * ((2048 + page - 1) // page)
     engine = Engine(typed, dtype=args.dtype, seed=0, page_size=page, num_pages=pool_pages,
                     max_num_seqs=max(max_batch, args.batch), max_num_batched_tokens=4096,
@@ -245,7 +248,7 @@ def main():
         kv_per_token *= 2
 
     def decode_point(batch, sampler=None):
-        reqs = prepare_decode(engine, batch, args.context, 2 * (steps + warmup) + 8, seed=batch)
+        reqs = prepare_decode(engine, batch, args.context, new_tokens, seed=batch)
         if sampler:
             sampler.active = True
         ms_dev, own = time_decode_device(engine, reqs, steps, warmup)

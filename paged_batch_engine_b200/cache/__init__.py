@@ -1,6 +1,6 @@
-from .manager import NO_PAGE, CacheError, CacheManager, KVGroupSpec, PagePool
+from .manager import NO_PAGE, CacheError, CacheManager, KVGroupSpec, PagePoolView
 
-__all__ = ["NO_PAGE", "CacheError", "CacheManager", "KVGroupSpec", "PagePool", "CacheStorage",
+__all__ = ["NO_PAGE", "CacheError", "CacheManager", "KVGroupSpec", "PagePoolView", "CacheStorage",
            "LayerCache"]
 
 

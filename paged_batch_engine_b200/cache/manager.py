@@ -5,6 +5,10 @@ request's block table per group, how many tokens of a request are reserved and h
 are computed, and which fixed-size state slot a request has.  It owns no device memory
 (``storage.py`` does) and launches nothing, so all of it is tested without a GPU.
 
+The bookkeeping itself is C++ (``csrc/host/cache_manager.cpp``, built with g++ at first
+use and called through ctypes); this module is its Python face and adds nothing but
+argument checking and error messages.
+
 In the reference the same duties are spread over ``base::BlockAllocator`` (one pool per
 layer, FIFO free queue, refcounts, generations: infMain/source/base/block_allocator.cpp:
 205-230, 264-282), ``base::SequenceKVManager`` (per-request page tables, transactional
@@ -19,13 +23,17 @@ gives pages back as soon as the window has passed them.
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
 
 _SLOT_BITS = 20
 _SLOT_MASK = (1 << _SLOT_BITS) - 1
 NO_PAGE = -1
+
+_ERR_STALE, _ERR_FREED_TWICE, _ERR_BAD_ARG, _ERR_CORRUPT = -1, -2, -3, -4
 
 
 class CacheError(RuntimeError):
@@ -41,58 +49,75 @@ class KVGroupSpec:
     window: Optional[int] = None     # None: every key is kept; W: only the last W keys are read
 
 
-class PagePool:
-    """Physical page ids 0..n-1 of one group: a free queue, a reference count and a
-    generation per page.  ``lifo`` takes the page given back last first (pages are then
-    used again at once, which tests want); the default FIFO spreads reuse."""
+_lib = None
 
-    def __init__(self, num_pages: int, lifo: bool = False):
-        if num_pages <= 0:
-            raise CacheError(f"a page pool needs at least one page, got {num_pages}")
-        self.num_pages = int(num_pages)
-        self.lifo = lifo
-        self._free = deque(range(self.num_pages))
-        self._refs = [0] * self.num_pages
-        self.generation = [0] * self.num_pages
-        self.allocations = 0
+
+def _host():
+    global _lib
+    if _lib is None:
+        from ..csrc.build import load_host_library
+        lib = load_host_library("cache_manager")
+        i32, i64, vp = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
+        pi32, pi64 = ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int64)
+        sig = {
+            "pbe_cm_new": (vp, [i32, pi32, i32, pi32, i32, i32]),
+            "pbe_cm_delete": (None, [vp]),
+            "pbe_cm_add_request": (i64, [vp]),
+            "pbe_cm_is_live": (i32, [vp, i64]),
+            "pbe_cm_num_live": (i32, [vp]),
+            "pbe_cm_context_len": (i64, [vp, i64]),
+            "pbe_cm_reserved_len": (i64, [vp, i64]),
+            "pbe_cm_num_free_pages": (i32, [vp, i32]),
+            "pbe_cm_pool_num_pages": (i32, [vp, i32]),
+            "pbe_cm_pool_allocations": (i64, [vp, i32]),
+            "pbe_cm_page_generation": (i32, [vp, i32, i32]),
+            "pbe_cm_page_refcount": (i32, [vp, i32, i32]),
+            "pbe_cm_pages_needed": (i32, [vp, i64, i64, pi32]),
+            "pbe_cm_max_appendable": (i64, [vp, i64]),
+            "pbe_cm_reserve": (i32, [vp, i64, i64]),
+            "pbe_cm_commit": (i32, [vp, i64, i64]),
+            "pbe_cm_truncate": (i32, [vp, i64, i64]),
+            "pbe_cm_free": (i32, [vp, i64]),
+            "pbe_cm_block_table": (i32, [vp, i64, i32, vp, i32]),
+            "pbe_cm_set_free_order": (i32, [vp, i32, vp, i32]),
+            "pbe_cm_check": (i32, [vp, ctypes.c_char_p, i32]),
+            "pbe_cm_decode_fill": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, vp, i32]),
+            "pbe_cm_reserve_many": (None, [vp, i32, vp, i64, vp]),
+            "pbe_cm_commit_many": (i32, [vp, i32, vp, vp]),
+            "pbe_decode_work_fill": (i32, [i32, i32, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, i32]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class PagePoolView:
+    """Read-only view of one group's page pool."""
+
+    def __init__(self, manager: "CacheManager", group: int):
+        self._m, self._g = manager, group
+
+    @property
+    def num_pages(self) -> int:
+        return _host().pbe_cm_pool_num_pages(self._m._h, self._g)
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return _host().pbe_cm_num_free_pages(self._m._h, self._g)
 
-    def allocate(self) -> int:
-        if not self._free:
-            return NO_PAGE
-        page = self._free.pop() if self.lifo else self._free.popleft()
-        if self._refs[page] != 0:
-            raise CacheError(f"page {page} was in the free queue while held {self._refs[page]} times")
-        self._refs[page] = 1
-        self.generation[page] += 1
-        self.allocations += 1
-        return page
+    @property
+    def allocations(self) -> int:
+        return _host().pbe_cm_pool_allocations(self._m._h, self._g)
 
-    def release(self, page: int) -> None:
-        if not (0 <= page < self.num_pages):
-            raise CacheError(f"page id {page} is outside the pool of {self.num_pages}")
-        if self._refs[page] <= 0:
-            raise CacheError(f"page {page} freed twice")
-        self._refs[page] -= 1
-        if self._refs[page] == 0:
-            self._free.append(page)
+    @property
+    def generation(self) -> List[int]:
+        lib = _host()
+        return [lib.pbe_cm_page_generation(self._m._h, self._g, p) for p in range(self.num_pages)]
 
     def refcount(self, page: int) -> int:
-        return self._refs[page]
-
-
-@dataclass
-class _Request:
-    slot: int
-    generation: int
-    reserved: int = 0                 # tokens backed by pages (computed + in flight)
-    computed: int = 0                 # tokens whose keys and values are written
-    tables: List[List[int]] = field(default_factory=list)   # per group: page of logical block i
-    first_live: List[int] = field(default_factory=list)     # per group: first block not yet given back
-    user_id: object = None
+        return _host().pbe_cm_page_refcount(self._m._h, self._g, page)
 
 
 class CacheManager:
@@ -114,92 +139,103 @@ class CacheManager:
         self.page_tokens = int(page_tokens)
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.groups)
+        num_pages = [int(n) for n in num_pages]
         if len(num_pages) != len(self.groups):
             raise CacheError("num_pages needs one entry per group")
-        self.pools = [PagePool(n, lifo=lifo) for n in num_pages]
+        if any(n <= 0 for n in num_pages):
+            raise CacheError(f"a page pool needs at least one page, got {num_pages}")
         self.max_requests = int(max_requests)
         self.state_bytes = int(state_bytes)
-        self._slots: List[Optional[_Request]] = [None] * self.max_requests
-        self._slot_generation = [0] * self.max_requests
-        self._free_slots = deque(range(self.max_requests))
+        n = len(self.groups)
+        windows = (ctypes.c_int * max(n, 1))(*[(-1 if g.window is None else int(g.window)) for g in self.groups])
+        pages = (ctypes.c_int * max(n, 1))(*num_pages)
+        self._h = _host().pbe_cm_new(n, windows, self.page_tokens, pages, self.max_requests, 1 if lifo else 0)
+        if not self._h:
+            raise CacheError("the cache manager could not be created with these sizes")
+        self.pools = [PagePoolView(self, g) for g in range(n)]
+        self._need = (ctypes.c_int * max(n, 1))()
         self.state_slot_assignments = 0
 
-    # ------------------------------------------------------------------ handles
-    def _lookup(self, handle: int) -> _Request:
-        if not isinstance(handle, int) or handle < 0:
-            raise CacheError(f"malformed request handle {handle!r}")
-        slot, gen = handle & _SLOT_MASK, handle >> _SLOT_BITS
-        if slot >= self.max_requests:
-            raise CacheError(f"request handle {handle} names slot {slot} of {self.max_requests}")
-        req = self._slots[slot]
-        if req is None or req.generation != gen:
-            raise CacheError(f"stale request handle {handle} (slot {slot}, generation {gen})")
-        return req
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h and _lib is not None:
+            _lib.pbe_cm_delete(h)
 
-    def is_live(self, handle: int) -> bool:
-        try:
-            self._lookup(handle)
-            return True
-        except CacheError:
-            return False
+    # ------------------------------------------------------------------ errors
+    def _raise(self, code: int, handle=None, what: str = ""):
+        if code == _ERR_STALE:
+            raise CacheError(f"stale or malformed request handle {handle!r}")
+        if code == _ERR_FREED_TWICE:
+            raise CacheError("a page was freed twice or lies outside its pool")
+        if code == _ERR_BAD_ARG:
+            raise CacheError(f"{what or 'bad argument'}")
+        raise CacheError(f"cache manager failure ({code}) {what}")
+
+    def _handle(self, handle) -> int:
+        if not isinstance(handle, int) or isinstance(handle, bool) or handle < 0:
+            raise CacheError(f"malformed request handle {handle!r}")
+        return handle
+
+    # ------------------------------------------------------------------ handles
+    def is_live(self, handle) -> bool:
+        return isinstance(handle, int) and handle >= 0 and bool(_host().pbe_cm_is_live(self._h, handle))
 
     @property
     def num_live_requests(self) -> int:
-        return self.max_requests - len(self._free_slots)
+        return _host().pbe_cm_num_live(self._h)
 
     def add_request(self, user_id=None) -> Optional[int]:
         """A new request with no tokens; None when every request slot is taken."""
-        if not self._free_slots:
+        h = _host().pbe_cm_add_request(self._h)
+        if h < 0:
             return None
-        slot = self._free_slots.popleft()
-        self._slot_generation[slot] += 1
-        gen = self._slot_generation[slot]
-        self._slots[slot] = _Request(slot=slot, generation=gen,
-                                     tables=[[] for _ in self.groups],
-                                     first_live=[0 for _ in self.groups], user_id=user_id)
         self.state_slot_assignments += 1
-        return (gen << _SLOT_BITS) | slot
+        return int(h)
 
     def state_slot(self, handle: int) -> int:
         """Index of the request's fixed-size state (row of the state tensor)."""
-        return self._lookup(handle).slot
+        if not self.is_live(handle):
+            self._raise(_ERR_STALE, handle)
+        return handle & _SLOT_MASK
 
     # ------------------------------------------------------------------ sizes
     def context_len(self, handle: int) -> int:
-        return self._lookup(handle).computed
+        v = _host().pbe_cm_context_len(self._h, self._handle(handle))
+        if v < 0:
+            self._raise(int(v), handle)
+        return int(v)
 
     def reserved_len(self, handle: int) -> int:
-        return self._lookup(handle).reserved
+        v = _host().pbe_cm_reserved_len(self._h, self._handle(handle))
+        if v < 0:
+            self._raise(int(v), handle)
+        return int(v)
 
     def num_free_pages(self, group: int = 0) -> int:
-        return self.pools[group].num_free
-
-    def _blocks_for(self, tokens: int) -> int:
-        return (tokens + self.page_tokens - 1) // self.page_tokens
+        return _host().pbe_cm_num_free_pages(self._h, group)
 
     def pages_needed(self, handle: int, n_tokens: int) -> List[int]:
         """New pages per group that ``reserve(handle, n_tokens)`` would take."""
-        req = self._lookup(handle)
-        target = self._blocks_for(req.reserved + n_tokens)
-        return [max(0, target - len(t)) for t in req.tables]
+        rc = _host().pbe_cm_pages_needed(self._h, self._handle(handle), int(n_tokens), self._need)
+        if rc < 0:
+            self._raise(rc, handle)
+        return [self._need[g] for g in range(len(self.groups))]
 
     def can_reserve(self, handle: int, n_tokens: int) -> bool:
         need = self.pages_needed(handle, n_tokens)
-        return all(n <= p.num_free for n, p in zip(need, self.pools))
+        return all(n <= self.num_free_pages(g) for g, n in enumerate(need))
 
     def max_appendable_tokens(self, handle: int) -> int:
         """How many more tokens fit: room in the last page plus the free pages, the
         smallest over the groups (infMain/source/serving/scheduler.cpp:23-34)."""
-        req = self._lookup(handle)
-        best = None
-        for table, pool in zip(req.tables, self.pools):
-            room = len(table) * self.page_tokens - req.reserved + pool.num_free * self.page_tokens
-            best = room if best is None else min(best, room)
-        return max(0, best) if best is not None else (1 << 30)
+        v = _host().pbe_cm_max_appendable(self._h, self._handle(handle))
+        if v < 0:
+            self._raise(int(v), handle)
+        return int(v)
 
     def capacity_tokens(self) -> int:
         """Tokens one request could hold with every page of the scarcest group."""
-        if not self.pools:
+        if not self.groups:
             return 1 << 30
         return min(p.num_pages for p in self.pools) * self.page_tokens
 
@@ -208,23 +244,29 @@ class CacheManager:
         """Back tokens [reserved, reserved + n) with pages in every group, or change nothing."""
         if n_tokens < 0:
             raise CacheError(f"cannot reserve {n_tokens} tokens")
-        req = self._lookup(handle)
-        # the usual decode step: the token still fits in the last page of every group
-        room = req.reserved + n_tokens
-        if all(room <= len(t) * self.page_tokens for t in req.tables):
-            req.reserved = room
-            return True
-        need = self.pages_needed(handle, n_tokens)
-        if any(n > p.num_free for n, p in zip(need, self.pools)):
-            return False
-        for g, n in enumerate(need):
-            for _ in range(n):
-                page = self.pools[g].allocate()
-                if page == NO_PAGE:   # cannot happen after the check above
-                    raise CacheError("page pool ran dry inside a checked reservation")
-                req.tables[g].append(page)
-        req.reserved += n_tokens
-        return True
+        rc = _host().pbe_cm_reserve(self._h, self._handle(handle), int(n_tokens))
+        if rc < 0:
+            self._raise(rc, handle)
+        return rc == 1
+
+    def reserve_many(self, handles: Sequence[int], n_tokens: int = 1) -> List[bool]:
+        """``reserve`` for several requests in one call (the decode phase of a step)."""
+        R = len(handles)
+        hs = np.asarray(handles, dtype=np.int64)
+        ok = np.empty(R, dtype=np.int32)
+        _host().pbe_cm_reserve_many(self._h, R, hs.ctypes.data, int(n_tokens), ok.ctypes.data)
+        if (ok < 0).any():
+            bad = int(np.nonzero(ok < 0)[0][0])
+            self._raise(int(ok[bad]), handles[bad])
+        return [bool(v) for v in ok]
+
+    def commit_many(self, handles: Sequence[int], n_tokens: Sequence[int]) -> None:
+        """``commit`` for several requests in one call (after a step)."""
+        hs = np.asarray(handles, dtype=np.int64)
+        ns = np.asarray(n_tokens, dtype=np.int64)
+        rc = _host().pbe_cm_commit_many(self._h, len(hs), hs.ctypes.data, ns.ctypes.data)
+        if rc < 0:
+            self._raise(rc, None, "a commit exceeds its reservation")
 
     def commit(self, handle: int, n_tokens: int) -> None:
         """Mark ``n_tokens`` more as computed and give back what a window has passed.
@@ -233,103 +275,90 @@ class CacheManager:
         tokens are written, the next query (position ``computed``) needs nothing below
         ``computed - W + 1``; pages that end at or before it go back to the pool and their
         block-table entries become NO_PAGE."""
-        req = self._lookup(handle)
-        if n_tokens < 0 or req.computed + n_tokens > req.reserved:
-            raise CacheError(
-                f"commit of {n_tokens} tokens exceeds the reservation ({req.computed}+{n_tokens} > {req.reserved})")
-        req.computed += n_tokens
-        for g, spec in enumerate(self.groups):
-            if spec.window is None:
-                continue
-            first_needed = req.computed - spec.window + 1
-            if first_needed <= 0:
-                continue
-            dead_blocks = min(first_needed // self.page_tokens, len(req.tables[g]))
-            for b in range(req.first_live[g], dead_blocks):
-                page = req.tables[g][b]
-                if page != NO_PAGE:
-                    self.pools[g].release(page)
-                    req.tables[g][b] = NO_PAGE
-            req.first_live[g] = max(req.first_live[g], dead_blocks)
+        rc = _host().pbe_cm_commit(self._h, self._handle(handle), int(n_tokens))
+        if rc < 0:
+            self._raise(rc, handle, f"commit of {n_tokens} tokens exceeds the reservation")
 
     def truncate(self, handle: int, n_tokens: int) -> None:
         """Keep only the first ``n_tokens`` tokens (gives back tail pages).  Not allowed
         below what a window has already released."""
-        req = self._lookup(handle)
-        if n_tokens < 0 or n_tokens > req.reserved:
-            raise CacheError(f"cannot truncate to {n_tokens} tokens (reserved {req.reserved})")
-        keep = self._blocks_for(n_tokens)
-        for g, table in enumerate(req.tables):
-            if keep < req.first_live[g]:
-                raise CacheError("cannot truncate below pages a window has already given back")
-            while len(table) > keep:
-                page = table.pop()
-                if page != NO_PAGE:
-                    self.pools[g].release(page)
-        req.reserved = n_tokens
-        req.computed = min(req.computed, n_tokens)
+        rc = _host().pbe_cm_truncate(self._h, self._handle(handle), int(n_tokens))
+        if rc < 0:
+            self._raise(rc, handle, f"cannot truncate to {n_tokens} tokens")
 
     def free(self, handle: int) -> None:
-        req = self._lookup(handle)
-        for g, table in enumerate(req.tables):
-            for page in table:
-                if page != NO_PAGE:
-                    self.pools[g].release(page)
-            table.clear()
-        self._slots[req.slot] = None
-        self._free_slots.append(req.slot)
-
-    def reset(self) -> None:
-        for slot, req in enumerate(self._slots):
-            if req is not None:
-                self.free((req.generation << _SLOT_BITS) | slot)
+        rc = _host().pbe_cm_free(self._h, self._handle(handle))
+        if rc < 0:
+            self._raise(rc, handle)
 
     # ------------------------------------------------------------------ views
     def block_table(self, handle: int, group: int = 0) -> List[int]:
-        return self._lookup(handle).tables[group]
+        lib = _host()
+        n = lib.pbe_cm_block_table(self._h, self._handle(handle), group, None, 0)
+        if n < 0:
+            self._raise(n, handle)
+        out = np.empty(max(n, 1), dtype=np.int32)
+        lib.pbe_cm_block_table(self._h, handle, group, out.ctypes.data, n)
+        return out[:n].tolist()
 
     def slot_of_token(self, handle: int, group: int, position: int) -> int:
         """page * page_tokens + offset of a token (infMain/source/base/sequence_kv_manager.cpp:41-52)."""
-        table = self._lookup(handle).tables[group]
+        table = self.block_table(handle, group)
         page = table[position // self.page_tokens]
         if page == NO_PAGE:
             raise CacheError(f"position {position} lies in a page that was given back")
         return page * self.page_tokens + position % self.page_tokens
 
     def page_generation(self, group: int, page: int) -> int:
-        return self.pools[group].generation[page]
+        return _host().pbe_cm_page_generation(self._h, group, page)
+
+    def set_free_order(self, group: int, pages: Sequence[int]) -> None:
+        """Test hook: the order in which the free pages of a group will be handed out."""
+        arr = np.asarray(list(pages), dtype=np.int32)
+        rc = _host().pbe_cm_set_free_order(self._h, group, arr.ctypes.data, len(arr))
+        if rc < 0:
+            self._raise(rc, None, "the order must list every free page exactly once")
+
+    def decode_fill(self, handles: np.ndarray, ctx_before: np.ndarray, state_slots: np.ndarray,
+                    block_tables: Sequence[np.ndarray], slots: Sequence[np.ndarray], known: np.ndarray,
+                    refresh: bool) -> None:
+        """One decode step's integers for ``handles`` (int64 [R]), written in place: context
+        lengths and state slots (int64 [R]), block-table rows (int32 matrices, only entries
+        beyond ``known`` unless ``refresh``) and cache slots (int32 [R]) per group."""
+        n = len(self.groups)
+        bt_ptrs = (ctypes.c_void_p * max(n, 1))(*[a.ctypes.data for a in block_tables])
+        strides = (ctypes.c_int * max(n, 1))(*[a.strides[0] // 4 for a in block_tables])
+        sl_ptrs = (ctypes.c_void_p * max(n, 1))(*[a.ctypes.data for a in slots])
+        rc = _host().pbe_cm_decode_fill(self._h, len(handles), handles.ctypes.data, ctx_before.ctypes.data,
+                                        state_slots.ctypes.data, ctypes.addressof(bt_ptrs),
+                                        ctypes.addressof(strides), ctypes.addressof(sl_ptrs),
+                                        known.ctypes.data, 1 if refresh else 0)
+        if rc == _ERR_STALE:
+            self._raise(rc, None)
+        if rc < 0:
+            raise ValueError("a token of this step lies in a page that is not held")
 
     # ------------------------------------------------------------------ self check
     def check_invariants(self) -> None:
         """No page lost, held twice or both held and free; counts agree."""
-        for g, pool in enumerate(self.pools):
-            held: Dict[int, int] = {}
-            for req in self._slots:
-                if req is None:
-                    continue
-                for page in req.tables[g]:
-                    if page == NO_PAGE:
-                        continue
-                    held[page] = held.get(page, 0) + 1
-            free = list(pool._free)
-            if len(set(free)) != len(free):
-                raise CacheError(f"group {g}: a page is in the free queue twice")
-            for page, n in held.items():
-                if n != 1:
-                    raise CacheError(f"group {g}: page {page} is held by {n} block tables")
-                if pool.refcount(page) != 1:
-                    raise CacheError(f"group {g}: page {page} is held but its count is {pool.refcount(page)}")
-                if page in set(free):
-                    raise CacheError(f"group {g}: page {page} is both held and free")
-            if len(held) + len(free) != pool.num_pages:
-                raise CacheError(
-                    f"group {g}: {pool.num_pages - len(held) - len(free)} pages are lost "
-                    f"({len(held)} held, {len(free)} free of {pool.num_pages})")
-        for req in self._slots:
-            if req is None:
-                continue
-            if not (0 <= req.computed <= req.reserved):
-                raise CacheError("computed/reserved out of order")
-            for table in req.tables:
-                if len(table) != self._blocks_for(req.reserved):
-                    raise CacheError("a block table does not cover the reservation")
+        buf = ctypes.create_string_buffer(512)
+        if _host().pbe_cm_check(self._h, buf, 512) != 0:
+            raise CacheError(buf.value.decode())
+
+    def reset(self) -> None:
+        raise CacheError("reset is not supported: free the requests you hold")
+
+
+def decode_work_fill(R: int, B: int, S: int, ctx_before: np.ndarray, window: Optional[int], split_keys: int,
+                     work: np.ndarray, split_counts: np.ndarray, positions: Optional[np.ndarray],
+                     seq_len: Optional[np.ndarray], tokens: Optional[np.ndarray],
+                     token_values: Optional[np.ndarray], refresh: bool) -> int:
+    """The attention work list of a captured decode step, written in place by the host library
+    (see ``pbe_decode_work_fill``); returns the largest number of splits."""
+    p = lambda a: a.ctypes.data if a is not None else None
+    rc = _host().pbe_decode_work_fill(R, B, S, ctx_before.ctypes.data, int(window or 0), int(split_keys),
+                                      p(work), p(split_counts), p(positions), p(seq_len), p(tokens),
+                                      p(token_values), R if refresh else B)
+    if rc < 0:
+        raise ValueError("a request needs more key splits than this captured step holds")
+    return rc

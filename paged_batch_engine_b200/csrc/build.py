@@ -158,3 +158,44 @@ def compile_many(jobs: Iterable[Tuple[str, Optional[Dict[str, object]]]], worker
     workers = workers or min(len(jobs), os.cpu_count() or 4) or 1
     with ThreadPoolExecutor(max_workers=workers) as ex:
         return list(ex.map(lambda j: compile_library(j[0], j[1]), jobs))
+
+
+# ------------------------------------------------------------------ host libraries (plain C++)
+HOST_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "host")
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def load_host_library(name: str) -> ctypes.CDLL:
+    """Builds (g++, once) and loads a host-side C++ library of the package: the runtime parts
+    that need no GPU.  Same naming and caching rule as the CUDA libraries."""
+    source = os.path.join(HOST_DIR, name + ".cpp")
+    if not os.path.isfile(source):
+        raise BuildError(f"no host source {source}")
+    h = hashlib.sha256()
+    with open(source, "rb") as f:
+        h.update(f.read())
+    h.update(repr(HOST_FLAGS).encode())
+    out = os.path.join(build_dir(), f"libpbe_host_{name}-{h.hexdigest()[:16]}.so")
+    with _lock:
+        lib = _loaded.get(out)
+        if lib is not None:
+            return lib
+    if not os.path.isfile(out):
+        cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+        if not cxx:
+            raise BuildError("no C++ compiler found (g++): the host runtime of this engine cannot be built")
+        tmp = f"{out}.tmp{os.getpid()}.{threading.get_ident()}"
+        print(f"[pbe] compiling {os.path.basename(out)} ...", file=sys.stderr, flush=True)
+        proc = subprocess.run([cxx] + HOST_FLAGS + ["-o", tmp, source], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True)
+        if proc.returncode != 0:
+            if os.path.exists(tmp):
+                os.remove(tmp)
+            raise BuildError(f"{cxx} failed for {source}:\n{proc.stdout}")
+        os.replace(tmp, out)
+    with _lock:
+        lib = _loaded.get(out)
+        if lib is None:
+            lib = ctypes.CDLL(out)
+            _loaded[out] = lib
+        return lib

@@ -18,6 +18,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..cache.manager import decode_work_fill
 from .batch import (DECODE_BLOCK_MAX_REQUESTS, AttentionWork, GroupArrays, StepContext, StepEntry,
                     attention_work_arrays, choose_split_keys)
 
@@ -61,8 +62,11 @@ class DecodeStepContext(StepContext):
         self._layout, self._size = lay, off
         self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
         self._host_np = self.host.numpy()
+        self._views: Dict[str, np.ndarray] = {}
         self._handles: List[int] = []
-        self._known: List[List[int]] = []
+        self._known = np.zeros((1, 0), dtype=np.int32)
+        self._handles_np = np.zeros(0, dtype=np.int64)
+        self._ctx = np.zeros(0, dtype=np.int64)
         self._arange = np.arange(B, dtype=np.int64)
         self._srange = np.arange(S, dtype=np.int64)
         self._ones = np.ones(B, dtype=np.int64)
@@ -93,8 +97,11 @@ class DecodeStepContext(StepContext):
                 tile_rows=key[2], kinds=(1 if key[1] <= 16 else 2) | (4 if B <= DECODE_BLOCK_MAX_REQUESTS else 0))
 
     def _h(self, name):
-        o, shape = self._layout[name]
-        return self._host_np[o:o + int(np.prod(shape))].reshape(shape)
+        v = self._views.get(name)
+        if v is None:
+            o, shape = self._layout[name]
+            v = self._views[name] = self._host_np[o:o + int(np.prod(shape))].reshape(shape)
+        return v
 
     def fill(self, entries: Sequence[StepEntry], vocab_size: int) -> None:
         """Writes this step's integers into the pinned buffer and copies it to the device.
@@ -104,61 +111,40 @@ class DecodeStepContext(StepContext):
         R = len(entries)
         handles = [e.handle for e in entries]
         same = handles == self._handles
-        ctx_before = np.fromiter((m.context_len(h) for h in handles), dtype=np.int64, count=R)
         tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
         if tokens.min() < 0 or tokens.max() >= vocab_size:
             raise ValueError("a token id is outside the vocabulary")
-        seq_len = ctx_before + 1
-        self.q_len_host = self._ones[:R]
-        self.seq_len_host = seq_len
-        self.q_start_host = self._arange[:R]
-        self.context_before_host = ctx_before
-        self._h("tokens")[:R] = tokens
-        self._h("positions")[:R] = ctx_before
-        self._h("seq_len")[:R] = seq_len
         if not same:
-            self.state_slots_host = np.fromiter((m.state_slot(h) for h in handles), dtype=np.int64, count=R)
-            self._h("tokens")[R:] = 0
-            self._h("positions")[R:] = 0
-            self._h("seq_len")[R:] = 0
-            q = self._h("q_len"); q[:] = 0; q[:R] = 1
-            st = self._h("state"); st[:] = 0; st[:R] = self.state_slots_host
-            self._known = [[0] * R for _ in m.groups]
+            self._handles_np = np.asarray(handles, dtype=np.int64)
+            self._known = np.zeros((max(len(m.groups), 1), R), dtype=np.int32)
+            self._ctx = np.empty(R, dtype=np.int64)
+            self.state_slots_host = np.empty(R, dtype=np.int64)
             for g in range(len(m.groups)):
                 self._h(f"bt{g}")[:] = -1
                 self._h(f"slots{g}")[:] = -1
-        for g in range(len(m.groups)):
-            bt = self._h(f"bt{g}")
-            known = self._known[g]
-            for r, h in enumerate(handles):
-                table = m.block_table(h, g)
-                n = len(table)
-                k = known[r]
-                if n != k or m.groups[g].window is not None:
-                    lo = 0 if m.groups[g].window is not None else k     # a window also takes pages away
-                    bt[r, lo:n] = table[lo:]
-                    known[r] = n
-            page = bt[self._arange[:R], ctx_before // P]
-            if page.min() < 0:
-                raise ValueError("a token of this step lies in a page that is not held")
-            self._h(f"slots{g}")[:R] = page.astype(np.int64) * P + ctx_before % P
+        # context lengths, state slots, new block-table entries and cache slots in one call
+        m.decode_fill(self._handles_np, self._ctx, self.state_slots_host,
+                      [self._h(f"bt{g}") for g in range(len(m.groups))],
+                      [self._h(f"slots{g}") for g in range(len(m.groups))], self._known, refresh=not same)
+        ctx_before = self._ctx
+        self.q_len_host = self._ones[:R]
+        self.seq_len_host = ctx_before + 1
+        self.q_start_host = self._arange[:R]
+        self.context_before_host = ctx_before
+        if not same:
+            q = self._h("q_len"); q[:] = 0; q[:R] = 1
+            st = self._h("state"); st[:] = 0; st[:R] = self.state_slots_host
         for i, key in enumerate(self.work_keys):
-            _, gsize, tile_rows, window = key
-            # one row tile per request; the number of splits follows from its own length
-            lo = np.maximum(0, ctx_before - window + 1) if window else 0
-            ns = (seq_len + self.split_keys - 1) // self.split_keys - lo // self.split_keys
-            if ns.max() > S:
-                raise ValueError("a request needs more key splits than this captured step holds")
-            w = self._h(f"work{i}").reshape(B, S, 4)
-            live = self._srange[None, :] < ns[:, None]                    # [R, S]
-            w[:R, :, 0] = np.where(live, self._arange[:R, None], -1)
-            w[:R, :, 3] = ns[:, None]
-            self._h(f"sc{i}")[:R] = ns
-            if not same:
-                w[R:, :, 0] = -1
-                w[:, :, 1] = 0
-                w[:, :, 2] = self._srange[None, :]
-                self._h(f"sc{i}")[R:] = 0
+            # positions, lengths, tokens (once) and the work list of this key, in the host library
+            first = i == 0
+            decode_work_fill(R, B, S, ctx_before, key[3], self.split_keys, self._h(f"work{i}"),
+                             self._h(f"sc{i}"), self._h("positions") if first else None,
+                             self._h("seq_len") if first else None, self._h("tokens") if first else None,
+                             tokens if first else None, refresh=not same)
+        if not self.work_keys:
+            self._h("tokens")[:R] = tokens
+            self._h("positions")[:R] = ctx_before
+            self._h("seq_len")[:R] = ctx_before + 1
         self._handles = handles
         self.dev.copy_(self.host, non_blocking=True)
 

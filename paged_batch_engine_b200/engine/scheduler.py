@@ -163,12 +163,22 @@ class Scheduler:
         return out
 
     def _schedule_decodes(self, out: SchedulerOutput, budget: int) -> int:
-        for req in self.running:
-            if budget <= 0 or out.num_decode >= self.config.max_num_seqs:
-                break
-            if not req.is_decode:
-                continue
-            if not self.cache.reserve(req.handle, 1):
+        limit = min(budget, self.config.max_num_seqs - out.num_decode)
+        decoding = [r for r in self.running if r.is_decode][:max(limit, 0)]
+        if not decoding:
+            return budget
+        # one call reserves a slot for every decoding request; from the first that finds no
+        # page on, go one by one, because a preemption gives pages back to those after it
+        ok = self.cache.reserve_many([r.handle for r in decoding], 1)
+        first_bad = ok.index(False) if False in ok else len(ok)
+        for i, req in enumerate(decoding):
+            if i < first_bad:
+                got = True
+            elif i == first_bad:
+                got = False
+            else:
+                got = ok[i] or self.cache.reserve(req.handle, 1)
+            if not got:
                 self._preempt(req, out)
                 continue
             req.scheduled = 1
@@ -280,9 +290,10 @@ class Scheduler:
     def process_outputs(self, out: SchedulerOutput, sampled: Sequence[int]) -> None:
         """``sampled``: one token for each entry with ``samples``, in entry order."""
         it = iter(sampled)
+        if out.entries:
+            self.cache.commit_many([e.request.handle for e in out.entries], [len(e.tokens) for e in out.entries])
         for e in out.entries:
             req = e.request
-            self.cache.commit(req.handle, len(e.tokens))
             req.computed += len(e.tokens)
             req.scheduled = 0
             if e.samples:

@@ -6,7 +6,7 @@ import random
 
 import pytest
 
-from paged_batch_engine_b200.cache import NO_PAGE, CacheError, CacheManager, KVGroupSpec, PagePool
+from paged_batch_engine_b200.cache import NO_PAGE, CacheError, CacheManager, KVGroupSpec
 
 
 def full(layers=(0, 1)):
@@ -18,18 +18,23 @@ def windowed(w, layers=(2,)):
 
 
 def test_pool_allocate_release_generation():
-    pool = PagePool(3)
-    a, b, c = pool.allocate(), pool.allocate(), pool.allocate()
-    assert sorted([a, b, c]) == [0, 1, 2] and pool.allocate() == NO_PAGE
-    pool.release(b)
+    m = CacheManager([full((0,))], page_tokens=1, num_pages=3, max_requests=4)
+    pool = m.pools[0]
+    hs = [m.add_request() for _ in range(3)]
+    assert all(m.reserve(h, 1) for h in hs)
+    pages = [m.block_table(h)[0] for h in hs]
+    assert sorted(pages) == [0, 1, 2] and pool.num_free == 0
+    extra = m.add_request()
+    assert not m.reserve(extra, 1)                       # the pool is dry: nothing changes
+    m.free(hs[1])
     assert pool.num_free == 1
-    again = pool.allocate()
-    assert again == b and pool.generation[b] == 2       # used again, with a new generation
+    assert m.reserve(extra, 1)
+    again = m.block_table(extra)[0]
+    assert again == pages[1] and pool.generation[again] == 2       # used again, with a new generation
+    assert pool.refcount(again) == 1 and pool.allocations == 4
     with pytest.raises(CacheError):
-        pool.release(7)
-    pool.release(a)
-    with pytest.raises(CacheError):
-        pool.release(a)                                  # freed twice
+        m.free(hs[1])                                    # freed twice: the handle is stale
+    m.check_invariants()
 
 
 def test_append_across_page_edges_and_slots():

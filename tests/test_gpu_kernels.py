@@ -183,12 +183,7 @@ class AttnCase:
         total_pages = num_pages or sum((c + n + P - 1) // P for c, n in reqs) + 3
         m = CacheManager([KVGroupSpec((0,), KV, hd, window)], P, total_pages, max_requests=64, lifo=True)
         # scramble the free list: take all pages and give them back in random order
-        tmp = m.add_request()
-        m.reserve(tmp, total_pages * P)
-        order = torch.randperm(total_pages, generator=g).tolist()
-        pages = list(m.block_table(tmp))
-        m._lookup(tmp).tables[0] = [pages[i] for i in order]
-        m.free(tmp)
+        m.set_free_order(0, torch.randperm(total_pages, generator=g).tolist())
         self.k_pages = torch.full((total_pages, KV, P, hd), float("nan"), dtype=dtype, device=DEV)
         self.v_pages = torch.full((total_pages, KV, P, hd), float("nan"), dtype=dtype, device=DEV)
         self.seqs, entries = [], []
