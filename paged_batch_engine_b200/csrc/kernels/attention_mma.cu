@@ -33,7 +33,7 @@ using namespace pbe;
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int HD = PBE_HEAD_DIM;
-constexpr int BM = 64;            // packed rows per row tile
+constexpr int BM = HD <= 128 ? 128 : 64;   // packed rows per row tile: 32 per warp (16 for head sizes above 128)
 constexpr int BN_KEYS = 64;       // keys per tile, keys mode (16 per warp)
 constexpr int BN_ROWS = 32;       // keys per tile, rows mode: smaller stages, more blocks per SM
 constexpr int NTHREADS = 128;
@@ -180,11 +180,118 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
   }
 }
 
+// The same for a warp that owns 32 rows (two 16-row fragments): every key and value fragment
+// read from shared memory feeds two MMAs, which halves the shared-memory traffic per flop.
+template <int NKT, bool MASK>
+__device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
+                                                  const bf16* __restrict__ Vs, int key0, int k_begin, int k_end,
+                                                  const RowInfo (&ri)[2], float scale_log2, float (&m)[2][2],
+                                                  float (&l)[2][2], float (&o)[2][ONT][4], int lane) {
+  float s[2][NKT][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[mt][nt][c] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    unsigned a[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+      ldmatrix_x4(a[mt], Qw + (mt * 16 + (lane & 15)) * LDS + ks * 16 + 8 * (lane >> 4));
+#pragma unroll
+    for (int np = 0; np < NKT / 2; ++np) {
+      unsigned b[4];
+      const int krow = np * 16 + (lane & 7) + 8 * (lane >> 4);
+      ldmatrix_x4(b, Ks + krow * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        mma_bf16(s[mt][2 * np], a[mt], b[0], b[1]);
+        mma_bf16(s[mt][2 * np + 1], a[mt], b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = c >> 1;
+        float v = s[mt][nt][c] * scale_log2;
+        if (MASK) {
+          const int key = key0 + nt * 8 + (lane & 3) * 2 + (c & 1);
+          const bool vis = key >= k_begin && key < k_end && key <= ri[mt].pos[r] && key >= ri[mt].lo[r];
+          v = vis ? v : -INFINITY;
+        }
+        s[mt][nt][c] = v;
+        mx[r] = fmaxf(mx[r], v);
+      }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m[mt][r], mx[r]);
+      m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[r] = exp2f(m[mt][r] - m_use[r]);
+      m[mt][r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = c >> 1;
+        const float pv = exp2f(s[mt][nt][c] - m_use[r]);
+        s[mt][nt][c] = pv;
+        sum[r] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+      l[mt][r] = l[mt][r] * alpha[r] + sum[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < ONT; ++nt) {
+      o[mt][nt][0] *= alpha[0];
+      o[mt][nt][1] *= alpha[0];
+      o[mt][nt][2] *= alpha[1];
+      o[mt][nt][3] *= alpha[1];
+    }
+  }
+#pragma unroll
+  for (int kk = 0; kk < NKT / 2; ++kk) {
+    unsigned a[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+      a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+      a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+      a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+    }
+    const int vrow = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+    for (int dp = 0; dp < ONT / 2; ++dp) {
+      unsigned b[4];
+      ldmatrix_x4_trans(b, Vs + vrow * LDS + dp * 16 + 8 * (lane >> 4));
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        mma_bf16(o[mt][2 * dp], a[mt], b[0], b[1]);
+        mma_bf16(o[mt][2 * dp + 1], a[mt], b[2], b[3]);
+      }
+    }
+  }
+}
+
 // KEYS = false: rows mode, row tiles of more than 16 packed rows (prompt portions).
 // KEYS = true: keys mode, row tiles of at most 16 packed rows (decoded tokens); only 16 query
 // rows are staged, so that three blocks fit on an SM.  Each instance skips the other's work.
 template <bool KEYS>
-__global__ void __launch_bounds__(NTHREADS, HD <= 128 ? 3 : 1)
+__global__ void __launch_bounds__(NTHREADS, KEYS ? (HD <= 128 ? 3 : 1) : (HD <= 128 ? 2 : 1))
 attn_mma_kernel(AttnParams p) {
   constexpr int QROWS = KEYS ? 16 : BM;
   constexpr int BN = KEYS ? BN_KEYS : BN_ROWS;
@@ -275,35 +382,45 @@ attn_mma_kernel(AttnParams p) {
   if (n_tiles > 0) load_tile(tile0, 0);
   cp_async_commit();
 
-  // rows of this thread's fragments
-  RowInfo ri;
-  const int frag_row0 = (KEYS ? 0 : warp * 16) + (lane >> 2);
+  // rows of this thread's fragments: one 16-row fragment in keys mode, two in rows mode
+  constexpr int MT = (KEYS || HD > 128) ? 1 : 2;
+  constexpr int WROWS = 16 * MT;                          // rows a warp owns
+  RowInfo ri[MT];
 #pragma unroll
-  for (int rr = 0; rr < 2; ++rr) {
-    const int pr = pr0 + frag_row0 + rr * 8;
-    if (pr < n_packed) {
-      ri.pos[rr] = pos0 + pr / G;
-      ri.lo[rr] = p.window > 0 ? ri.pos[rr] - p.window + 1 : 0;
-    } else {
-      ri.pos[rr] = -1;     // no key is visible to a row that does not exist
-      ri.lo[rr] = 0;
+  for (int mt = 0; mt < MT; ++mt) {
+    const int frag_row0 = (KEYS ? 0 : warp * WROWS) + mt * 16 + (lane >> 2);
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int pr = pr0 + frag_row0 + rr * 8;
+      if (pr < n_packed) {
+        ri[mt].pos[rr] = pos0 + pr / G;
+        ri[mt].lo[rr] = p.window > 0 ? ri[mt].pos[rr] - p.window + 1 : 0;
+      } else {
+        ri[mt].pos[rr] = -1;     // no key is visible to a row that does not exist
+        ri[mt].lo[rr] = 0;
+      }
     }
   }
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[ONT][4];
+  float m[MT][2], l[MT][2];
+  float o[MT][ONT][4];
 #pragma unroll
-  for (int nt = 0; nt < ONT; ++nt)
+  for (int mt = 0; mt < MT; ++mt) {
+    m[mt][0] = m[mt][1] = -INFINITY;
+    l[mt][0] = l[mt][1] = 0.f;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) o[nt][c] = 0.f;
-  const bf16* Qw = Qs + (KEYS ? 0 : warp * 16) * LDS;
-  const bool warp_has_rows = KEYS || (warp * 16 < rows_here);
+    for (int nt = 0; nt < ONT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[mt][nt][c] = 0.f;
+  }
+  const bf16* Qw = Qs + (KEYS ? 0 : warp * WROWS) * LDS;
+  const bool warp_has_rows = KEYS || (warp * WROWS < rows_here);
   // A key tile needs no mask for this warp when every key in it is visible to every one of
   // the warp's existing rows: the tile lies inside the block's key range, ends at or before
   // the earliest row's position and begins at or after the latest row's first visible key.
   // (Fragment rows beyond the request compute on zeros and are never stored.)
-  const int wrow0 = KEYS ? 0 : warp * 16;
-  const int wrows = min(16, rows_here - wrow0);                 // <= 0: the warp has no rows
+  const int wrow0 = KEYS ? 0 : warp * WROWS;
+  const int wrows = min(WROWS, rows_here - wrow0);              // <= 0: the warp has no rows
   const int pos_min = pos0 + (pr0 + wrow0) / G;
   const int pos_last = pos0 + (pr0 + wrow0 + max(wrows, 1) - 1) / G;
   const int lo_max = p.window > 0 ? max(0, pos_last - p.window + 1) : 0;
@@ -316,19 +433,26 @@ attn_mma_kernel(AttnParams p) {
     __syncthreads();
     const bf16* kt = Ks + (t & 1) * BN * LDS;
     const bf16* vt = Vs + (t & 1) * BN * LDS;
-    if (KEYS) {
+    if constexpr (KEYS) {
       const int key0 = ts + warp * 16;
       const bool interior = key0 >= k_begin && key0 + 16 <= k_end && key0 + 15 <= pos_min && key0 >= lo_max;
       if (interior)
-        process_tile<2, false>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+        process_tile<2, false>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
       else
-        process_tile<2, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+        process_tile<2, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
     } else if (warp_has_rows) {
       const bool interior = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
-      if (interior)
-        process_tile<BN / 8, false>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
-      else
-        process_tile<BN / 8, true>(Qw, kt, vt, 0, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+      if constexpr (MT == 2) {
+        if (interior)
+          process_tile_rows<BN / 8, false>(Qw, kt, vt, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+        else
+          process_tile_rows<BN / 8, true>(Qw, kt, vt, ts, k_begin, k_end, ri, scale_log2, m, l, o, lane);
+      } else if constexpr (!KEYS) {
+        if (interior)
+          process_tile<BN / 8, false>(Qw, kt, vt, 0, ts, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
+        else
+          process_tile<BN / 8, true>(Qw, kt, vt, 0, ts, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
+      }
     }
     __syncthreads();             // everyone is done with buffer t & 1 before it is refilled
   }
@@ -336,7 +460,7 @@ attn_mma_kernel(AttnParams p) {
   pdl_launch_dependents();      // the keys and values are read: the next kernel may start launching
 
   const float LN2 = 0.6931471805599453f;
-  if (KEYS) {
+  if constexpr (KEYS) {
     // merge the four warps' partial results: reuse the K/V buffers as float scratch
     __syncthreads();
     float* sc_o = reinterpret_cast<float*>(Ks);          // [4][16][HD]
@@ -346,12 +470,12 @@ attn_mma_kernel(AttnParams p) {
       const int row = (lane >> 2) + rr * 8;
 #pragma unroll
       for (int nt = 0; nt < ONT; ++nt) {
-        float2 v = make_float2(o[nt][rr * 2], o[nt][rr * 2 + 1]);
+        float2 v = make_float2(o[0][nt][rr * 2], o[0][nt][rr * 2 + 1]);
         *reinterpret_cast<float2*>(sc_o + ((warp * 16 + row) * HD) + nt * 8 + (lane & 3) * 2) = v;
       }
       if ((lane & 3) == 0) {
-        sc_ml[(warp * 16 + row) * 2] = m[rr];
-        sc_ml[(warp * 16 + row) * 2 + 1] = l[rr];
+        sc_ml[(warp * 16 + row) * 2] = m[0][rr];
+        sc_ml[(warp * 16 + row) * 2 + 1] = l[0][rr];
       }
     }
     __syncthreads();
@@ -388,35 +512,41 @@ attn_mma_kernel(AttnParams p) {
     return;
   }
 
-  if (!warp_has_rows) return;
+  if constexpr (!KEYS) {
+    if (!warp_has_rows) return;
 #pragma unroll
-  for (int rr = 0; rr < 2; ++rr) {
-    const int pr = pr0 + warp * 16 + (lane >> 2) + rr * 8;
-    if (pr >= n_packed) continue;
-    const int qrow = pr / G, hg = pr - qrow * G;
-    const int head = kvh * G + hg;
-    const int tok = qs + qrow;
-    if (nsplit <= 1) {
-      const float inv = l[rr] > 0.f ? 1.0f / l[rr] : 0.f;
-      bf16* dst = (bf16*)p.out + ((size_t)tok * H + head) * HD + (lane & 3) * 2;
+    for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-      for (int nt = 0; nt < ONT; ++nt) {
-        *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
-            __floats2bfloat162_rn(o[nt][rr * 2] * inv, o[nt][rr * 2 + 1] * inv);
-      }
-    } else {
-      const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
-      float* dst = p.part_o + base * HD + (lane & 3) * 2;
+      for (int rr = 0; rr < 2; ++rr) {
+        const int pr = pr0 + warp * WROWS + mt * 16 + (lane >> 2) + rr * 8;
+        if (pr >= n_packed) continue;
+        const int qrow = pr / G, hg = pr - qrow * G;
+        const int head = kvh * G + hg;
+        const int tok = qs + qrow;
+        if (nsplit <= 1) {
+          const float inv = l[mt][rr] > 0.f ? 1.0f / l[mt][rr] : 0.f;
+          bf16* dst = (bf16*)p.out + ((size_t)tok * H + head) * HD + (lane & 3) * 2;
 #pragma unroll
-      for (int nt = 0; nt < ONT; ++nt)
-        *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][rr * 2], o[nt][rr * 2 + 1]);
-      if ((lane & 3) == 0) {
-        p.part_ml[base * 2] = m[rr] == -INFINITY ? -INFINITY : m[rr] * LN2;
-        p.part_ml[base * 2 + 1] = l[rr];
+          for (int nt = 0; nt < ONT; ++nt) {
+            *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
+                __floats2bfloat162_rn(o[mt][nt][rr * 2] * inv, o[mt][nt][rr * 2 + 1] * inv);
+          }
+        } else {
+          const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
+          float* dst = p.part_o + base * HD + (lane & 3) * 2;
+#pragma unroll
+          for (int nt = 0; nt < ONT; ++nt)
+            *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[mt][nt][rr * 2], o[mt][nt][rr * 2 + 1]);
+          if ((lane & 3) == 0) {
+            p.part_ml[base * 2] = m[mt][rr] == -INFINITY ? -INFINITY : m[mt][rr] * LN2;
+            p.part_ml[base * 2 + 1] = l[mt][rr];
+          }
+        }
       }
     }
   }
 }
+
 // Decoded tokens (row tiles of at most 16 packed rows), persistent and warp-private: every
 // warp walks over work items (request, row tile, key split, kv head) on its own, streams the
 // item's keys and values in tiles of 16 through a three-stage cp.async ring that only it

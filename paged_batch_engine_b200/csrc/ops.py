@@ -323,10 +323,9 @@ def attention_kernel_config(head_dim: int, dtype: torch.dtype, kind: Optional[st
     kind = kind or ("mma" if dtype == torch.bfloat16 and _mma_available() else "simple")
     if kind == "simple":
         return "simple", SIMPLE_TILE_ROWS, SIMPLE_KEY_TILE
-    return "mma", MMA_TILE_ROWS, MMA_KEY_TILE
+    return "mma", (128 if head_dim <= 128 else 64), MMA_KEY_TILE
 
 
-MMA_TILE_ROWS = 64
 MMA_KEY_TILE = 64
 
 

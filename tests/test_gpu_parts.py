@@ -87,6 +87,68 @@ def test_attention_part_whole_and_in_portions(dtype, window):
         assert (got - want).abs().max() <= tol * max(1.0, want.abs().max()), cuts
 
 
+def test_position_encoding_part():
+    from paged_batch_engine_b200.config import PartSpec
+    from paged_batch_engine_b200.parts import build_part
+    rope = build_part("position", PartSpec("rope", dict(theta=50000.0, head_dim=48, rotary_dim=32)), torch.float32, DEV)
+    inv, rot, inter = rope.kernel_args()
+    assert rot == 32 and inter is False and inv.dtype == torch.float32
+    assert torch.equal(inv.cpu(), plain.rope_inv_freq(32, 50000.0))
+    none = build_part("position", PartSpec("none"), torch.float32, DEV)
+    assert none.kernel_args() == (None, 0, False)
+    with pytest.raises(ValueError):
+        build_part("position", PartSpec("rope", dict(theta=1e4, head_dim=16, rotary_dim=18)), torch.float32, DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_alone(dtype):
+    """A pre-norm block built from its BlockSpec, stepped whole and in two portions, against
+    the plain functions put together the same way."""
+    from paged_batch_engine_b200.cache.storage import CacheStorage
+    from paged_batch_engine_b200.config import BlockSpec, PartSpec
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    from paged_batch_engine_b200.parts import build_block
+    torch.manual_seed(3)
+    d, H, KV, hd, inter, T, P, eps = 56, 4, 2, 16, 104, 29, 8, 2e-5
+    norm = PartSpec("rmsnorm", dict(size=d, eps=eps))
+    spec = BlockSpec("prenorm",
+                     PartSpec("attention", dict(hidden_size=d, num_heads=H, num_kv_heads=KV, head_dim=hd,
+                                                position=PartSpec("rope", dict(theta=900.0, head_dim=hd)))),
+                     PartSpec("swiglu", dict(hidden_size=d, intermediate_size=inter)), norm, norm, "blk.",
+                     dict(mixer="att.", feed_forward="ff.", norm_mixer="n1.", norm_feed_forward="n2."))
+    block = build_block(spec, dtype, torch.device(DEV))
+    w = {}
+    for p in block.param_specs():
+        t = torch.randn(p.shape) * (0.5 if "q_proj.w" in p.name or "k_proj.w" in p.name else 0.2)
+        if p.name.endswith("n1.weight") or p.name.endswith("n2.weight"):
+            t = 1 + 0.1 * torch.randn(p.shape)
+        w[p.name] = t.to(dtype if len(p.shape) > 1 else torch.float32)
+    block.load({k: v.to(DEV) for k, v in w.items()})
+    wf = {k: v.float() for k, v in w.items()}
+    x = torch.randn(T, d)
+    cfg = dict(num_attention_heads=H, num_key_value_heads=KV, head_dim=hd, hidden_size=d, rope_theta=900.0)
+    h = plain.rmsnorm(x, wf["blk.n1.weight"], eps)
+    x1 = x + plain.attention_block(h, torch.arange(T), wf, "blk.att.", cfg, None)
+    want = x1 + plain.feed_forward(plain.rmsnorm(x1, wf["blk.n2.weight"], eps), wf, "blk.ff.")
+    storage = CacheStorage([block.mixer.cache_need()], P, 8, 2, dtype, torch.device(DEV), poison=True)
+    keys = [(0,) + k for k in block.mixer.work_keys()]
+    for cuts in ([T], [11, 18]):
+        hnd = storage.manager.add_request()
+        outs, i = [], 0
+        for n in cuts:
+            assert storage.manager.reserve(hnd, n)
+            ctx = _ctx(storage.manager, [StepEntry(hnd, [0] * n)], keys)
+            res = x[i:i + n].clone().to(DEV)
+            res, delta = block.forward(res, None, ctx, storage.layer(0))
+            outs.append((res + delta.float()).cpu())
+            storage.manager.commit(hnd, n)
+            i += n
+        storage.manager.free(hnd)
+        got = torch.cat(outs)
+        tol = 3e-5 if dtype == torch.float32 else 0.04
+        assert (got - want).abs().max() <= tol * max(1.0, want.abs().max()), cuts
+
+
 # ------------------------------------------------------------------ toy parts, defined in the test
 def _toy_decay():
     return 0.75
