@@ -36,7 +36,7 @@ def timed(fn, flush, n=5):
     return sorted(ts)[len(ts) // 2]
 
 
-def attention_case(reqs, H=28, KV=4, hd=128, P=16):
+def attention_case(reqs, H=28, KV=4, hd=128, P=16, kind=None):
     from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
     from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
     pages = sum((c + n + P - 1) // P for c, n in reqs) + 2
@@ -47,7 +47,7 @@ def attention_case(reqs, H=28, KV=4, hd=128, P=16):
         m.reserve(h, c + n)
         m.commit(h, c)
         entries.append(StepEntry(h, [0] * n))
-    kind, tile_rows, _ = ops.attention_kernel_config(hd, torch.bfloat16)
+    kind, tile_rows, _ = ops.attention_kernel_config(hd, torch.bfloat16, kind)
     key = (0, H // KV, tile_rows, None)
     ctx = StepContext(m, entries, torch.device(DEV), [key])
     meta = ctx.attention_work(0, H // KV, tile_rows, None, H, hd)
@@ -75,10 +75,12 @@ def main():
             t = timed(run, flush)
             print(f"attention decode B={B} ctx 2048: {t * 1e3:.1f} us, {kv_bytes / t / 1e6:.0f} GB/s")
     if what in ("attn_prefill", "all"):
-        run, _ = attention_case([(0, 2048)])
-        t = timed(run, flush)
-        flops = 2 * 2 * 28 * 128 * (2048 * 2049 // 2)
-        print(f"attention prefill 2048 tokens: {t * 1e3:.1f} us, {flops / t / 1e9:.0f} TFLOP/s")
+        for kind in ("mma", "tc5"):
+            for T in (2048, 8192):
+                run, _ = attention_case([(0, T)], kind=kind)
+                t = timed(run, flush)
+                flops = 2 * 2 * 28 * 128 * (T * (T + 1) // 2)
+                print(f"attention prefill {T} tokens ({kind}): {t * 1e3:.1f} us, {flops / t / 1e9:.0f} TFLOP/s")
     if what in ("tc5", "all"):
         w = (torch.randn(37888, 3584, device=DEV) * 0.02).to(torch.bfloat16)
         x = torch.randn(2048, 3584, device=DEV).to(torch.bfloat16)

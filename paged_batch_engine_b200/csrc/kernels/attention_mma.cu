@@ -740,7 +740,8 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
   }
   dim3 grid(num_work, p.num_kv_heads);
   const int kinds = (p.kinds & 3) == 0 ? (p.kinds | 3) : p.kinds;
-  if (kinds & 2) launch_k(attn_mma_kernel<false>, grid, NTHREADS, smem_rows, stream, p);
+  // bit 3: the prompt-portion tiles are computed by another kernel (attention_tc5.cu)
+  if ((kinds & 2) && !(kinds & 8)) launch_k(attn_mma_kernel<false>, grid, NTHREADS, smem_rows, stream, p);
   if ((kinds & 1) && (kinds & 4)) {
     // few requests: four warps share every key tile, the shortest path through one work item
     const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;

@@ -1,0 +1,500 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores.
+//
+// One block owns a row tile of 128 packed rows (query row x head of the group) of one
+// key/value head and walks over its keys in tiles of 128:
+//   S = Q K^T     tcgen05.mma, 128 x 128 x head_dim, accumulator in tensor memory (two S
+//                 buffers alternate, so the next tile's scores are computed while this tile's
+//                 softmax runs);
+//   softmax       four warps, ONE THREAD PER ROW: the row's 128 scores come out of tensor
+//                 memory with tcgen05.ld, so maximum, exponentials and sum need no shuffle;
+//   O += P V      P is written as bfloat16 into shared memory in the swizzled layout the MMA
+//                 reads, V is used as it lies in the pages (head_dim contiguous: an MN-major
+//                 B operand), the output accumulator stays in tensor memory and is rescaled
+//                 there (tcgen05.ld / tcgen05.st) only when a row's maximum has grown.
+// Keys and values come from the pages by TMA (cp.async.bulk.tensor 2D, one box per page and
+// 64-wide half of the head, 128-byte swizzle, no multicast); the query tile is copied by the
+// softmax warps once.  Warp 0 lane 0 is the TMA producer, warp 1 lane 0 issues the MMAs,
+// warps 2-5 are the softmax / correction / epilogue warps.
+//
+// Same work list, same split scheme and same outputs as attn_mma_kernel<false>; it takes
+// head sizes 64 and 128 and page sizes 8..128 that divide 128.  Every mbarrier wait is
+// bounded; a wait that runs out sets *err and the roles run to their end, so that tensor
+// memory is always given back.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "attention_params.cuh"
+#include "common.cuh"
+#include "pdl.cuh"
+
+using namespace pbe;
+
+#ifndef PBE_HEAD_DIM
+#error "PBE_HEAD_DIM must be defined"
+#endif
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int HD = PBE_HEAD_DIM;
+static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
+constexpr int BM = 128;                 // packed rows per block = TMEM lanes
+constexpr int BN = 128;                 // keys per tile
+constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
+constexpr int Q_BYTES = BM * HD * 2;
+constexpr int KV_BYTES = BN * HD * 2;   // one K tile or one V tile
+constexpr int P_BYTES = BM * BN * 2;
+constexpr int NTHREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int S_COL = 0, O_COL = 256;   // S buffers at columns 0 and 128, O at 256
+constexpr long long WAIT_LIMIT = 40LL * 1000 * 1000;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  const uint32_t addr = smem_u32(bar);
+  for (long long i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  if (err) atomicExch(err, 1);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// MN-major operand, 128-byte swizzle (V as it lies in the pages: [key][head_dim]): a row of 64
+// head-dim elements is 128 bytes, rows of consecutive keys are 128 bytes apart, groups of 8
+// keys 1024 bytes apart (stride byte offset), the next 64 head-dim elements one whole
+// [128 keys][64] block further (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((BN * 128) >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__device__ __forceinline__ uint32_t make_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// byte offset of element (row, col) in a [rows][64-wide blocks] bf16 tile with 128-byte swizzle
+__device__ __forceinline__ uint32_t swz(int row, int col, int rows) {
+  const int blk = col >> 6, cc = col & 63;
+  return (uint32_t)(blk * rows * 128 + row * 128 + ((((cc >> 3) ^ (row & 7)) << 4) | ((cc & 7) << 1)));
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                AttnParams p, int* err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* Qs = base;                               // [KB][128 rows][128 B]
+  unsigned char* Ks = Qs + Q_BYTES;                       // [2 stages][KB][128 keys][128 B]
+  unsigned char* Vs = Ks + 2 * KV_BYTES;                  // [2 stages][KB][128 keys][128 B]
+  unsigned char* Ps = Vs + 2 * KV_BYTES;                  // [2][128 rows][128 B]
+  __shared__ __align__(8) uint64_t kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_ready;
+  __shared__ uint32_t tmem_base_smem;
+
+  pdl_wait();
+  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  const int r = work[0];
+  if (r < 0) return;
+  const int m_tile = work[1], split = work[2], nsplit = work[3];
+  const int kvh = blockIdx.y;
+  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+  const int n_packed = nq * G;
+  const int pr0 = m_tile * BM;
+  const int rows_here = min(BM, n_packed - pr0);
+  if (rows_here <= 16) return;                            // small tiles belong to the decode kernels
+  const int row_lo = pr0 / G;
+  const int row_hi = (pr0 + rows_here - 1) / G;
+  const int pos0 = sl - nq;
+  const int hi_key = pos0 + row_hi + 1;
+  const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
+  int k_begin = lo_key, k_end = hi_key;
+  if (nsplit > 1) {
+    const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int s0 = lo_req / p.split_keys;
+    k_begin = max(lo_key, (s0 + split) * p.split_keys);
+    k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+  }
+  const int tile0 = (k_begin / BN) * BN;
+  const int n_tiles = k_end > tile0 ? (k_end - tile0 + BN - 1) / BN : 0;
+  const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(&p_full, 4);
+    mbar_init(&o_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_smem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // the query tile: one packed row per softmax thread, into the swizzled K-major layout
+  if (warp >= 2) {
+    const int row = (warp - 2) * 32 + lane;
+    const int pr = pr0 + row;
+    const bf16* src = nullptr;
+    if (pr < n_packed) {
+      const int qrow = pr / G, hg = pr - qrow * G;
+      src = (const bf16*)p.q + ((size_t)(qs + qrow) * H + kvh * G + hg) * HD;
+    }
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      const uint4 v = src ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(Qs + swz(row, c * 8, BM)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the MMA's reads
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_smem;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      const int last_blk = n_tiles > 0 ? (k_end - 1) / P : 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, err)) break;
+        unsigned char* kd = Ks + (size_t)st * KV_BYTES;
+        unsigned char* vd = Vs + (size_t)st * KV_BYTES;
+        mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
+        const int ts = tile0 + j * BN;
+        for (int pg = 0; pg < BN / P; ++pg) {
+          const int blk = (ts + pg * P) / P;
+          int page = blk <= last_blk ? bt[blk] : 0;       // beyond the range: any page, the keys are masked
+          if (page < 0) page = 0;
+          const int y = (page * KV + kvh) * P;
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb) {
+            tma_load_2d(kd + kb * BN * 128 + pg * P * 128, &map_k, kb * 64, y, &kv_full[st]);
+            tma_load_2d(vd + kb * BN * 128 + pg * P * 128, &map_v, kb * 64, y, &kv_full[st]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      // ------------------------------------------------------------ MMA issuer
+      const uint32_t idesc_s = make_idesc(BM, BN, false);
+      const uint32_t idesc_o = make_idesc(BM, HD, true);
+      const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+      bool ok = true;
+      auto issue_qk = [&](int j) {
+        const int st = j & 1;
+        ok = ok && mbar_wait(&kv_full[st], (j >> 1) & 1, err);
+        ok = ok && mbar_wait(&s_empty[st], ((j >> 1) & 1) ^ 1, err);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k_addr = smem_u32(Ks + (size_t)st * KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;     // BM == BN rows per block
+          umma(tmem_base + S_COL + st * BN, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s,
+               ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+      };
+      issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) issue_qk(j + 1);
+        ok = ok && mbar_wait(&p_full, j & 1, err);            // P_j written, O rescaled
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int st = j & 1;
+        const uint32_t v_addr = smem_u32(Vs + (size_t)st * KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          const uint32_t a_off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;   // P: K-major over the keys
+          const uint32_t b_off = ks * 16 * 128;                            // V: 16 keys further down
+          umma(tmem_base + O_COL, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off), idesc_o,
+               (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);
+        umma_commit(&o_ready);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax, correction, epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                   // TMEM lane == row of the tile
+    const int pr = pr0 + row;
+    const bool row_valid = pr < n_packed;
+    const int pos = row_valid ? pos0 + pr / G : -1;
+    const int lo = p.window > 0 ? pos - p.window + 1 : 0;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const int ts = tile0 + j * BN;
+      ok = ok && mbar_wait(&s_full[st], (j >> 1) & 1, err);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // scores of this row: scale, mask, maximum
+      float s[BN];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + S_COL + st * BN + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = ts + c * 32 + i;
+          const bool vis = key >= k_begin && key < k_end && key <= pos && key >= lo;
+          const float x = vis ? v[i] * scale_log2 : -INFINITY;
+          s[c * 32 + i] = x;
+          mx = fmaxf(mx, x);
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[st]);            // the S buffer may be overwritten
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);            // 0 when nothing was visible before
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) {
+        const float e = exp2f(s[i] - m_use);
+        s[i] = e;
+        sum += e;
+      }
+      l_run = l_run * alpha + sum;
+      // the previous tile's P V must be complete before O is rescaled and P overwritten
+      if (j > 0) {
+        ok = ok && mbar_wait(&o_ready, (j - 1) & 1, err);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool grew = m_new > m_run;
+        if (__any_sync(0xffffffffu, grew)) {               // rescale the rows of this warp
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            float v[32];
+            tmem_ld32(lane_addr + O_COL + c * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= alpha;
+            tmem_st32(lane_addr + O_COL + c * 32, v);
+          }
+        }
+      }
+      m_run = m_new;
+      // P as bfloat16, swizzled K-major over the keys
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(s[c * 8 + 2 * i], s[c * 8 + 2 * i + 1]);
+          w[i] = *reinterpret_cast<unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(Ps + swz(row, c * 8, BM)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      // values of keys outside the range are zeroed (P is 0 there, but stale pages may hold NaN)
+      if (ts < k_begin || ts + BN > k_end) {
+        unsigned char* vd = Vs + (size_t)st * KV_BYTES;
+        const int key = ts + row;                          // thread `row` owns key row `row` of the tile
+        if (key < k_begin || key >= k_end) {
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(vd + kb * BN * 128 + row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+    }
+    pdl_launch_dependents();
+    // ---- epilogue: O / l (or the split's partial result)
+    if (n_tiles > 0) {
+      ok = ok && mbar_wait(&o_ready, (n_tiles - 1) & 1, err);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    const float LN2 = 0.6931471805599453f;
+    const int qrow = row_valid ? pr / G : 0, hg = row_valid ? pr - qrow * G : 0;
+    const int head = kvh * G + hg;
+    const int tok = qs + qrow;
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      float v[32];
+      if (n_tiles > 0) {                                   // block-uniform: every lane takes part in the load
+        tmem_ld32(lane_addr + O_COL + c * 32, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      if (!row_valid) continue;                            // rows beyond the request store nothing
+      if (nsplit <= 1) {
+        bf16* dst = (bf16*)p.out + ((size_t)tok * H + head) * HD + c * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          unsigned w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[i * 8 + 2 * k] * inv, v[i * 8 + 2 * k + 1] * inv);
+            w[k] = *reinterpret_cast<unsigned*>(&h);
+          }
+          reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        const size_t pbase = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
+        float* dst = p.part_o + pbase * HD + c * 32;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        if (c == 0) {
+          p.part_ml[pbase * 2] = m_run == -INFINITY ? -INFINITY : m_run * LN2;
+          p.part_ml[pbase * 2 + 1] = l_run;
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+// the pages of one layer as a matrix [pages * kv_heads * page_tokens, head_dim]; boxes of one
+// page (page_tokens rows) by 64 columns
+int make_map(CUtensorMap* map, const void* cache, long long rows, int page_tokens) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_tokens};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+PBE_EXPORT int pbe_attn_tc5_head_dim() { return HD; }
+
+// Prompt-portion tiles (more than 16 packed rows) of the work list; the caller runs a decode
+// kernel for the rest and the merge kernel for split tiles.  num_pages: pages of the cache
+// tensors.  err: device int set to 1 when a bounded wait ran out.
+PBE_EXPORT int pbe_attn_tc5(const AttnParams* params, int num_work, int num_pages, int* err, cudaStream_t stream) {
+  if (num_work <= 0) return 0;
+  AttnParams p = *params;
+  const int P = p.page_tokens;
+  if (p.num_heads % p.num_kv_heads != 0 || p.tile_rows != BM || p.split_keys % BN != 0 || P < 8 || P > 128 ||
+      (P % 8) != 0 || (BN % P) != 0)
+    return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15) || ((uintptr_t)p.q & 15) || ((uintptr_t)p.out & 15))
+    return (int)cudaErrorInvalidValue;
+  CUtensorMap map_k, map_v;
+  const long long rows = (long long)num_pages * p.num_kv_heads * P;
+  int rc = make_map(&map_k, p.k_cache, rows, P);
+  if (rc != 0) return rc;
+  rc = make_map(&map_v, p.v_cache, rows, P);
+  if (rc != 0) return rc;
+  const size_t smem = (size_t)Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  dim3 grid(num_work, p.num_kv_heads);
+  launch_k(attn_tc5_kernel, grid, NTHREADS, smem, stream, map_k, map_v, p, err);
+  return launch_status();
+}

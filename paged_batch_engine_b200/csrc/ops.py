@@ -320,13 +320,24 @@ def attention_kernel_config(head_dim: int, dtype: torch.dtype, kind: Optional[st
     """(kind, tile_rows, key_tile) of the attention kernel used for a head size and dtype."""
     if head_dim % 16 != 0 or head_dim <= 0 or head_dim > 256:
         raise KernelError(f"attention kernels take head sizes 16, 32, ..., 256; got {head_dim}")
+    if kind is None and dtype == torch.bfloat16 and head_dim in (64, 128) and _attention_choice() == "tc5":
+        kind = "tc5"
     kind = kind or ("mma" if dtype == torch.bfloat16 and _mma_available() else "simple")
     if kind == "simple":
         return "simple", SIMPLE_TILE_ROWS, SIMPLE_KEY_TILE
+    if kind == "tc5":
+        return "tc5", 128, 128
     return "mma", (128 if head_dim <= 128 else 64), MMA_KEY_TILE
 
 
 MMA_KEY_TILE = 64
+
+
+def _attention_choice() -> str:
+    """PBE_ATTN=tc5 puts prompt portions of bfloat16 models with head size 64 or 128 on the
+    tcgen05 attention kernel; anything else leaves the mma.sync kernel in place."""
+    import os
+    return os.environ.get("PBE_ATTN", "").strip().lower()
 
 
 def _mma_available() -> bool:
@@ -350,6 +361,12 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
         raise KernelError("the tensor-core attention kernel takes bfloat16")
     lib = "attention_simple" if kind == "simple" else "attention_mma"
     defines = {"PBE_HEAD_DIM": int(head_dim)}
+    tc5 = kind == "tc5"
+    if tc5:
+        if q.dtype != torch.bfloat16 or not tc5_attention_applies(head_dim, page_tokens):
+            raise KernelError("the tcgen05 attention kernel takes bfloat16, head sizes 64 and 128 and page sizes "
+                              "8..128 that divide 128")
+        kind = "mma"
     p = AttnParams(
         q=q.data_ptr(), k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr(), out=out.data_ptr(),
         part_o=meta.part_o.data_ptr() if meta.part_o is not None else None,
@@ -360,6 +377,17 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
         num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
         window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=int(getattr(meta, "kinds", 0)))
+    if tc5:
+        # prompt-portion tiles on the tcgen05 kernel; the decode instances below take the rest
+        err = _tc5_err.get(q.device)
+        if err is None:
+            err = _tc5_err[q.device] = torch.zeros(1, dtype=torch.int32, device=q.device)
+        tfn = _fn("attention_tc5", "pbe_attn_tc5", [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_void_p],
+                  defines)
+        if (p.kinds & 3) == 0 or (p.kinds & 2):
+            _check(tfn(ctypes.byref(p), int(meta.num_work), int(k_cache.shape[0]), _ptr(err), _stream()),
+                   "paged_attention (tcgen05)")
+        p.kinds = (p.kinds | 8) if (p.kinds & 3) else (1 | 8)
     fn = _fn(lib, "pbe_attn_" + kind, [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p], defines)
     _check(fn(ctypes.byref(p), int(meta.num_work), _dtype_code(q), _stream()), "paged_attention")
     if meta.num_split_rows > 0:
@@ -374,11 +402,28 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
     return out
 
 
+def tc5_attention_applies(head_dim: int, page_tokens: int) -> bool:
+    return head_dim in (64, 128) and 8 <= page_tokens <= 128 and page_tokens % 8 == 0 and 128 % page_tokens == 0
+
+
+def tc5_error_flag(device) -> int:
+    """1 if a bounded wait inside a tcgen05 kernel ran out since the last call (then reset)."""
+    err = _tc5_err.get(torch.device(device))
+    if err is None:
+        return 0
+    v = int(err.item())
+    if v:
+        err.zero_()
+    return v
+
+
 def attention_libraries(head_dim: int, dtype: torch.dtype):
     """The (library, defines) pairs a model with this head size needs, for parallel builds."""
     jobs = [("attention_simple", {"PBE_HEAD_DIM": int(head_dim)})]
     if dtype == torch.bfloat16 and _mma_available():
         jobs.append(("attention_mma", {"PBE_HEAD_DIM": int(head_dim)}))
+        if head_dim in (64, 128) and _attention_choice() == "tc5":
+            jobs.append(("attention_tc5", {"PBE_HEAD_DIM": int(head_dim)}))
     return jobs
 
 

@@ -328,6 +328,50 @@ def test_attention_mma_many_decoding_requests(H, KV, hd, P, window):
             assert torch.allclose(got2[i, head], v[j, head // (H // KV)].float(), atol=3e-2), (i, j, head)
 
 
+TC5_SHAPES = [
+    # H, KV, hd, P, window, [(context, new rows)...]
+    (28, 4, 128, 16, None, [(0, 300)]),                           # several key tiles, ragged last row tile
+    (28, 4, 128, 16, None, [(1500, 64), (300, 1), (0, 70)]),      # key splits, a decoded token beside portions
+    (8, 8, 64, 32, None, [(255, 130), (1000, 1), (0, 17)]),       # head size 64, one row per packed row
+    (14, 2, 128, 8, 300, [(700, 40), (290, 20), (0, 400)]),       # window, pages of 8
+    (6, 3, 64, 128, 200, [(100, 500), (513, 3)]),                 # pages as large as the key tile
+    (16, 2, 128, 64, None, [(37, 19), (2000, 2)]),                # 16 rows x 8 heads: the smallest prompt tile
+]
+
+
+@pytest.mark.parametrize("shape", TC5_SHAPES, ids=lambda s: f"H{s[0]}kv{s[1]}hd{s[2]}P{s[3]}w{s[4]}")
+def test_paged_attention_tcgen05(shape):
+    """Prompt portions on the tcgen05 kernel (free pages hold NaN), decoded tokens beside them."""
+    H, KV, hd, P, window, reqs = shape
+    case = AttnCase(H, KV, hd, P, window, reqs, torch.bfloat16, seed=hd + P, kind="tc5")
+    case.write_cache()
+    out = case.run()
+    assert ops().tc5_error_flag(DEV) == 0
+    ref = case.reference()
+    assert torch.isfinite(out).all()
+    assert (out - ref).abs().max().item() < 2e-2
+
+
+def test_attention_tcgen05_far_key_and_window_edge():
+    """One key far back gets all the weight (its value must come through exactly); with a
+    window that ends one key after it, it must not be seen at all."""
+    H, KV, hd, P = 8, 2, 128, 16
+    L, n, far = 900, 40, 131
+    for window, seen in ((None, True), (L - n - far, False), (L - n - far + 1, True)):
+        case = AttnCase(H, KV, hd, P, window, [(L - n, n)], torch.bfloat16, seed=11, kind="tc5")
+        q, k, v, ctx_len, _, _ = case.seqs[0]
+        k[far] = 0
+        k[far, :, 0] = 8.0
+        q[ctx_len, :, 0] = 40.0                            # the portion's first row looks at key `far`
+        v[far] = 3.0
+        case.write_cache()
+        out = case.run()
+        assert ops().tc5_error_flag(DEV) == 0
+        ref = case.reference()
+        assert (out - ref).abs().max().item() < 2e-2
+        assert ((out[0] - 3.0).abs().max().item() < 2e-2) == seen
+
+
 def test_attention_ignores_stale_data_in_reused_and_foreign_pages():
     """Pages beyond a request's length and pages of other requests hold NaN or huge
     values: the result must not change."""
