@@ -302,15 +302,17 @@ attn_mma_kernel(AttnParams p) {
   __shared__ int s_pages[MAX_SMEM_PAGES];
 
   pdl_wait();
-  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  // rows mode: a one-dimensional grid, work-major, so that the heavy tiles at the head of
+  // the work list start first for every key/value head
+  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const int32_t* work = p.work + (size_t)(KEYS ? blockIdx.x : blockIdx.x / KV) * 4;
   const int r = work[0];
   if (r < 0) {
     pdl_launch_dependents();
     return;
   }
   const int m_tile = work[1], split = work[2], nsplit = work[3];
-  const int kvh = blockIdx.y;
-  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const int kvh = KEYS ? blockIdx.y : blockIdx.x % KV;
   const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
   const int pr0 = m_tile * BM;
@@ -741,7 +743,10 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
   dim3 grid(num_work, p.num_kv_heads);
   const int kinds = (p.kinds & 3) == 0 ? (p.kinds | 3) : p.kinds;
   // bit 3: the prompt-portion tiles are computed by another kernel (attention_tc5.cu)
-  if ((kinds & 2) && !(kinds & 8)) launch_k(attn_mma_kernel<false>, grid, NTHREADS, smem_rows, stream, p);
+  if ((kinds & 2) && !(kinds & 8)) {
+    if ((long long)num_work * p.num_kv_heads > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    launch_k(attn_mma_kernel<false>, dim3((unsigned)(num_work * p.num_kv_heads)), NTHREADS, smem_rows, stream, p);
+  }
   if ((kinds & 1) && (kinds & 4)) {
     // few requests: four warps share every key tile, the shortest path through one work item
     const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;

@@ -12,9 +12,11 @@
 //                 B operand), the output accumulator stays in tensor memory and is rescaled
 //                 there (tcgen05.ld / tcgen05.st) only when a row's maximum has grown.
 // Keys and values come from the pages by TMA (cp.async.bulk.tensor 2D, one box per page and
-// 64-wide half of the head, 128-byte swizzle, no multicast); the query tile is copied by the
-// softmax warps once.  Warp 0 lane 0 is the TMA producer, warp 1 lane 0 issues the MMAs,
-// warps 2-5 are the softmax / correction / epilogue warps.
+// 64-wide half of the head, 128-byte swizzle, no multicast) into a ring of three key tiles and
+// a ring of two value tiles: a key tile is free again as soon as its scores are computed, a
+// value tile after its P V.  The query tile is copied by the softmax warps once.  Warp 0 lane 0
+// loads keys, warp 6 lane 0 loads values, warp 1 lane 0 issues the MMAs, warps 2-5 are the
+// softmax / correction / epilogue warps.
 //
 // Same work list, same split scheme and same outputs as attn_mma_kernel<false>; it takes
 // head sizes 64 and 128 and page sizes 8..128 that divide 128.  Every mbarrier wait is
@@ -43,7 +45,8 @@ constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
 constexpr int Q_BYTES = BM * HD * 2;
 constexpr int KV_BYTES = BN * HD * 2;   // one K tile or one V tile
 constexpr int P_BYTES = BM * BN * 2;
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 224;
+constexpr int NK = 3, NV = 2;           // key tiles and value tiles in flight
 constexpr int TMEM_COLS = 512;
 constexpr int S_COL = 0, O_COL = 256;   // S buffers at columns 0 and 128, O at 256
 constexpr long long WAIT_LIMIT = 40LL * 1000 * 1000;
@@ -127,6 +130,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]),
+        "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]),
+        "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]),
+        "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -155,19 +173,21 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* Qs = base;                               // [KB][128 rows][128 B]
-  unsigned char* Ks = Qs + Q_BYTES;                       // [2 stages][KB][128 keys][128 B]
-  unsigned char* Vs = Ks + 2 * KV_BYTES;                  // [2 stages][KB][128 keys][128 B]
-  unsigned char* Ps = Vs + 2 * KV_BYTES;                  // [2][128 rows][128 B]
-  __shared__ __align__(8) uint64_t kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_ready;
+  unsigned char* Ks = Qs + Q_BYTES;                       // [NK stages][KB][128 keys][128 B]
+  unsigned char* Vs = Ks + NK * KV_BYTES;                 // [NV stages][KB][128 keys][128 B]
+  unsigned char* Ps = Vs + NV * KV_BYTES;                 // [2][128 rows][128 B]
+  __shared__ __align__(8) uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], s_empty[2], p_full,
+      o_ready;
   __shared__ uint32_t tmem_base_smem;
 
   pdl_wait();
-  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  const int KV = p.num_kv_heads;
+  const int32_t* work = p.work + (size_t)(blockIdx.x / KV) * 4;
   const int r = work[0];
   if (r < 0) return;
   const int m_tile = work[1], split = work[2], nsplit = work[3];
-  const int kvh = blockIdx.y;
-  const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
+  const int kvh = blockIdx.x % KV;
+  const int H = p.num_heads, G = H / KV, P = p.page_tokens;
   const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
   const int pr0 = m_tile * BM;
@@ -191,10 +211,15 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-#pragma unroll
+    for (int i = 0; i < NK; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < NV; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);
     }
@@ -209,7 +234,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // the query tile: one packed row per softmax thread, into the swizzled K-major layout
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 6) {
     const int row = (warp - 2) * 32 + lane;
     const int pr = pr0 + row;
     const bf16* src = nullptr;
@@ -229,16 +254,21 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_smem;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
     if (lane == 0) {
-      // ------------------------------------------------------------ TMA producer
+      // ------------------------------------------------------------ TMA producers: keys (warp 0), values (warp 6)
+      const bool keys = warp == 0;
+      const int ring = keys ? NK : NV;
+      uint64_t* full = keys ? k_full : v_full;
+      uint64_t* empty = keys ? k_empty : v_empty;
+      unsigned char* tiles = keys ? Ks : Vs;
+      const CUtensorMap* map = keys ? &map_k : &map_v;
       const int last_blk = n_tiles > 0 ? (k_end - 1) / P : 0;
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, err)) break;
-        unsigned char* kd = Ks + (size_t)st * KV_BYTES;
-        unsigned char* vd = Vs + (size_t)st * KV_BYTES;
-        mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
+        const int st = j % ring;
+        if (!mbar_wait(&empty[st], ((j / ring) & 1) ^ 1, err)) break;
+        unsigned char* dst = tiles + (size_t)st * KV_BYTES;
+        mbar_expect_tx(&full[st], KV_BYTES);
         const int ts = tile0 + j * BN;
         for (int pg = 0; pg < BN / P; ++pg) {
           const int blk = (ts + pg * P) / P;
@@ -246,10 +276,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           if (page < 0) page = 0;
           const int y = (page * KV + kvh) * P;
 #pragma unroll
-          for (int kb = 0; kb < KB; ++kb) {
-            tma_load_2d(kd + kb * BN * 128 + pg * P * 128, &map_k, kb * 64, y, &kv_full[st]);
-            tma_load_2d(vd + kb * BN * 128 + pg * P * 128, &map_v, kb * 64, y, &kv_full[st]);
-          }
+          for (int kb = 0; kb < KB; ++kb) tma_load_2d(dst + kb * BN * 128 + pg * P * 128, map, kb * 64, y, &full[st]);
         }
       }
     }
@@ -261,26 +288,28 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
       bool ok = true;
       auto issue_qk = [&](int j) {
-        const int st = j & 1;
-        ok = ok && mbar_wait(&kv_full[st], (j >> 1) & 1, err);
+        const int st = j & 1, kst = j % NK;
+        ok = ok && mbar_wait(&k_full[kst], (j / NK) & 1, err);
         ok = ok && mbar_wait(&s_empty[st], ((j >> 1) & 1) ^ 1, err);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t k_addr = smem_u32(Ks + (size_t)st * KV_BYTES);
+        const uint32_t k_addr = smem_u32(Ks + (size_t)kst * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;     // BM == BN rows per block
           umma(tmem_base + S_COL + st * BN, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s,
                ks > 0 ? 1u : 0u);
         }
+        umma_commit(&k_empty[kst]);                           // the key tile is free once its scores exist
         umma_commit(&s_full[st]);
       };
       issue_qk(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) issue_qk(j + 1);
+        const int vst = j % NV;
+        ok = ok && mbar_wait(&v_full[vst], (j / NV) & 1, err);
         ok = ok && mbar_wait(&p_full, j & 1, err);            // P_j written, O rescaled
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int st = j & 1;
-        const uint32_t v_addr = smem_u32(Vs + (size_t)st * KV_BYTES);
+        const uint32_t v_addr = smem_u32(Vs + (size_t)vst * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           const uint32_t a_off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;   // P: K-major over the keys
@@ -288,7 +317,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           umma(tmem_base + O_COL, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off), idesc_o,
                (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[vst]);
         umma_commit(&o_ready);
       }
     }
@@ -302,43 +331,62 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     const int lo = p.window > 0 ? pos - p.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // tiles whose every key is visible to every row of the block need no mask
+    const int pos_min = pos0 + row_lo;                     // position of the block's first row
+    const int lo_max = p.window > 0 ? pos0 + row_hi - p.window + 1 : 0;
+    float m_run = -INFINITY, l_run = 0.f;                  // maximum in raw score units
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const int ts = tile0 + j * BN;
       ok = ok && mbar_wait(&s_full[st], (j >> 1) & 1, err);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // scores of this row: scale, mask, maximum
+      // this row's 128 scores: all four loads in flight, one wait
       float s[BN];
-      float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld32(lane_addr + S_COL + st * BN + c * 32, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = ts + c * 32 + i;
-          const bool vis = key >= k_begin && key < k_end && key <= pos && key >= lo;
-          const float x = vis ? v[i] * scale_log2 : -INFINITY;
-          s[c * 32 + i] = x;
-          mx = fmaxf(mx, x);
-        }
-      }
+      for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(lane_addr + S_COL + st * BN + c * 32, &s[c * 32]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[st]);            // the S buffer may be overwritten
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);            // 0 when nothing was visible before
-      float sum = 0.f;
+      const bool full_tile = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
+      if (!full_tile) {
 #pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        const float e = exp2f(s[i] - m_use);
-        s[i] = e;
-        sum += e;
+        for (int i = 0; i < BN; ++i) {
+          const int key = ts + i;
+          const bool vis = key >= k_begin && key < k_end && key <= pos && key >= lo;
+          s[i] = vis ? s[i] : -INFINITY;
+        }
       }
-      l_run = l_run * alpha + sum;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        mx0 = fmaxf(mx0, s[i]);
+        mx1 = fmaxf(mx1, s[i + 1]);
+        mx2 = fmaxf(mx2, s[i + 2]);
+        mx3 = fmaxf(mx3, s[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // the running maximum moves only when it has grown by more than 2^8 in the exponent:
+      // until then the old one still keeps every exponential within 256, and O needs no rescale
+      float m_new = fmaxf(m_run, mx);
+      if (m_run != -INFINITY && (m_new - m_run) * scale_log2 <= 8.0f) m_new = m_run;
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = ex2_approx((m_run - m_use) * scale_log2);   // 0 when nothing was visible before
+      const float neg_mc = -m_use * scale_log2;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        s[i] = ex2_approx(fmaf(s[i], scale_log2, neg_mc));
+        s[i + 1] = ex2_approx(fmaf(s[i + 1], scale_log2, neg_mc));
+        s[i + 2] = ex2_approx(fmaf(s[i + 2], scale_log2, neg_mc));
+        s[i + 3] = ex2_approx(fmaf(s[i + 3], scale_log2, neg_mc));
+        sum0 += s[i];
+        sum1 += s[i + 1];
+        sum2 += s[i + 2];
+        sum3 += s[i + 3];
+      }
+      l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
       // the previous tile's P V must be complete before O is rescaled and P overwritten
       if (j > 0) {
         ok = ok && mbar_wait(&o_ready, (j - 1) & 1, err);
@@ -369,7 +417,8 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       }
       // values of keys outside the range are zeroed (P is 0 there, but stale pages may hold NaN)
       if (ts < k_begin || ts + BN > k_end) {
-        unsigned char* vd = Vs + (size_t)st * KV_BYTES;
+        ok = ok && mbar_wait(&v_full[j % NV], (j / NV) & 1, err);   // the tile has landed
+        unsigned char* vd = Vs + (size_t)(j % NV) * KV_BYTES;
         const int key = ts + row;                          // thread `row` owns key row `row` of the tile
         if (key < k_begin || key >= k_end) {
 #pragma unroll
@@ -390,7 +439,6 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       ok = ok && mbar_wait(&o_ready, (n_tiles - 1) & 1, err);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
-    const float LN2 = 0.6931471805599453f;
     const int qrow = row_valid ? pr / G : 0, hg = row_valid ? pr - qrow * G : 0;
     const int head = kvh * G + hg;
     const int tok = qs + qrow;
@@ -424,7 +472,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         for (int i = 0; i < 8; ++i)
           reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         if (c == 0) {
-          p.part_ml[pbase * 2] = m_run == -INFINITY ? -INFINITY : m_run * LN2;
+          p.part_ml[pbase * 2] = m_run == -INFINITY ? -INFINITY : m_run * p.scale;
           p.part_ml[pbase * 2 + 1] = l_run;
         }
       }
@@ -488,13 +536,14 @@ PBE_EXPORT int pbe_attn_tc5(const AttnParams* params, int num_work, int num_page
   if (rc != 0) return rc;
   rc = make_map(&map_v, p.v_cache, rows, P);
   if (rc != 0) return rc;
-  const size_t smem = (size_t)Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024;
+  const size_t smem = (size_t)Q_BYTES + (NK + NV) * KV_BYTES + P_BYTES + 1024;
   static bool opted = false;
   if (!opted) {
     cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     opted = true;
   }
-  dim3 grid(num_work, p.num_kv_heads);
+  if ((long long)num_work * p.num_kv_heads > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  dim3 grid((unsigned)(num_work * p.num_kv_heads));          // work-major: heavy tiles of every head first
   launch_k(attn_tc5_kernel, grid, NTHREADS, smem, stream, map_k, map_v, p, err);
   return launch_status();
 }

@@ -122,6 +122,16 @@ def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.nd
         work[:, 1] = local // ns
         work[:, 2] = local % ns
     work[:, 3] = ns
+    if not fixed_splits and total > 1 and (m_tiles > 1).any():
+        # prompt portions: the tiles with the most keys first, so that the last blocks of the
+        # launch are the short ones (the order of the list has no other meaning)
+        mt = work[:, 1].astype(np.int64)
+        qn, p0 = q_len[req], pos0[req]
+        row_hi = np.minimum(qn - 1, ((mt + 1) * tile_rows - 1) // group_size)
+        hi = p0 + row_hi + 1
+        lo = np.maximum(0, p0 + (mt * tile_rows) // group_size - window + 1) if window else 0
+        cost = np.where(ns > 1, np.minimum(split_keys, hi - lo), hi - lo)
+        work = work[np.argsort(-cost, kind="stable")]
     T = int(q_len.sum())
     tok_split_row = np.full(T, -1, dtype=np.int32)
     is_split = (n_splits > 1) | force_split
