@@ -7,13 +7,14 @@
 //                 softmax runs);
 //   softmax       four warps, ONE THREAD PER ROW: the row's 128 scores come out of tensor
 //                 memory with tcgen05.ld, so maximum, exponentials and sum need no shuffle;
-//   O += P V      P is written as bfloat16 into shared memory in the swizzled layout the MMA
-//                 reads, V is used as it lies in the pages (head_dim contiguous: an MN-major
-//                 B operand), the output accumulator stays in tensor memory and is rescaled
-//                 there (tcgen05.ld / tcgen05.st) only when a row's maximum has grown.
+//   O += P V      P is written as bfloat16 into tensor memory (tcgen05.st, two buffers) and is
+//                 the MMA's A operand from there, V is used as it lies in the pages (head_dim
+//                 contiguous: an MN-major B operand in shared memory), the output accumulator
+//                 stays in tensor memory and is rescaled there (tcgen05.ld / tcgen05.st) only
+//                 when a row's maximum has grown by more than 2^8.
 // Keys and values come from the pages by TMA (cp.async.bulk.tensor 2D, one box per page and
 // 64-wide half of the head, 128-byte swizzle, no multicast) into a ring of three key tiles and
-// a ring of two value tiles: a key tile is free again as soon as its scores are computed, a
+// a ring of three value tiles: a key tile is free again as soon as its scores are computed, a
 // value tile after its P V.  The query tile is copied by the softmax warps once.  Warp 0 lane 0
 // loads keys, warp 6 lane 0 loads values, warp 1 lane 0 issues the MMAs, warps 2-5 are the
 // softmax / correction / epilogue warps.
@@ -44,12 +45,12 @@ constexpr int BN = 128;                 // keys per tile
 constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
 constexpr int Q_BYTES = BM * HD * 2;
 constexpr int KV_BYTES = BN * HD * 2;   // one K tile or one V tile
-constexpr int P_BYTES = BM * BN * 2;
 constexpr int NTHREADS = 224;
-constexpr int NK = 3, NV = 2;           // key tiles and value tiles in flight
+constexpr int NK = 3, NV = 3;           // key tiles and value tiles in flight
 constexpr int TMEM_COLS = 512;
 constexpr int S_COL = 0, O_COL = 256;   // S buffers at columns 0 and 128, O at 256
-constexpr long long WAIT_LIMIT = 40LL * 1000 * 1000;
+constexpr int P_COL = 384;              // P buffers (two bfloat16 per column) at columns 384 and 448
+constexpr long long WAIT_CLOCKS = 2000LL * 1000 * 1000;   // about a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -63,14 +64,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
   const uint32_t addr = smem_u32(bar);
-  for (long long i = 0; i < WAIT_LIMIT; ++i) {
+  const long long t0 = clock64();
+  for (;;) {
     uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
+    if (clock64() - t0 > WAIT_CLOCKS) break;
   }
   if (err) atomicExch(err, 1);
   return false;
@@ -113,6 +116,14 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A from tensor memory (128 lanes x 8 columns of two bfloat16 per k-step), B from shared memory
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -139,6 +150,16 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float* v) {
         "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]),
         "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
       : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -175,7 +196,6 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   unsigned char* Qs = base;                               // [KB][128 rows][128 B]
   unsigned char* Ks = Qs + Q_BYTES;                       // [NK stages][KB][128 keys][128 B]
   unsigned char* Vs = Ks + NK * KV_BYTES;                 // [NV stages][KB][128 keys][128 B]
-  unsigned char* Ps = Vs + NV * KV_BYTES;                 // [2][128 rows][128 B]
   __shared__ __align__(8) uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], s_empty[2], p_full,
       o_ready;
   __shared__ uint32_t tmem_base_smem;
@@ -255,37 +275,44 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   const uint32_t tmem_base = tmem_base_smem;
 
   if (warp == 0 || warp == 6) {
-    if (lane == 0) {
-      // ------------------------------------------------------------ TMA producers: keys (warp 0), values (warp 6)
-      const bool keys = warp == 0;
-      const int ring = keys ? NK : NV;
-      uint64_t* full = keys ? k_full : v_full;
-      uint64_t* empty = keys ? k_empty : v_empty;
-      unsigned char* tiles = keys ? Ks : Vs;
-      const CUtensorMap* map = keys ? &map_k : &map_v;
-      const int last_blk = n_tiles > 0 ? (k_end - 1) / P : 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int st = j % ring;
-        if (!mbar_wait(&empty[st], ((j / ring) & 1) ^ 1, err)) break;
-        unsigned char* dst = tiles + (size_t)st * KV_BYTES;
-        mbar_expect_tx(&full[st], KV_BYTES);
-        const int ts = tile0 + j * BN;
-        for (int pg = 0; pg < BN / P; ++pg) {
-          const int blk = (ts + pg * P) / P;
-          int page = blk <= last_blk ? bt[blk] : 0;       // beyond the range: any page, the keys are masked
-          if (page < 0) page = 0;
-          const int y = (page * KV + kvh) * P;
-#pragma unroll
-          for (int kb = 0; kb < KB; ++kb) tma_load_2d(dst + kb * BN * 128 + pg * P * 128, map, kb * 64, y, &full[st]);
-        }
+    // ------------------------------------------------------------ TMA producers: keys (warp 0), values (warp 6)
+    // lane 0 waits for the free stage and announces the bytes; every page of the tile is then
+    // fetched by a lane of its own (its block-table entry and its boxes)
+    const bool keys = warp == 0;
+    const int ring = keys ? NK : NV;
+    uint64_t* full = keys ? k_full : v_full;
+    uint64_t* empty = keys ? k_empty : v_empty;
+    unsigned char* tiles = keys ? Ks : Vs;
+    const CUtensorMap* map = keys ? &map_k : &map_v;
+    const int last_blk = n_tiles > 0 ? (k_end - 1) / P : 0;
+    const int pages_per_tile = BN / P;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j % ring;
+      int go = 1;
+      if (lane == 0) {
+        go = mbar_wait(&empty[st], ((j / ring) & 1) ^ 1, err) ? 1 : 0;
+        if (go) mbar_expect_tx(&full[st], KV_BYTES);
       }
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) break;
+      unsigned char* dst = tiles + (size_t)st * KV_BYTES;
+      const int ts = tile0 + j * BN;
+      for (int pg = lane; pg < pages_per_tile; pg += 32) {
+        const int blk = ts / P + pg;
+        int page = blk <= last_blk ? bt[blk] : 0;         // beyond the range: any page, the keys are masked
+        if (page < 0) page = 0;
+        const int y = (page * KV + kvh) * P;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) tma_load_2d(dst + kb * BN * 128 + pg * P * 128, map, kb * 64, y, &full[st]);
+      }
+      __syncwarp();
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       // ------------------------------------------------------------ MMA issuer
       const uint32_t idesc_s = make_idesc(BM, BN, false);
       const uint32_t idesc_o = make_idesc(BM, HD, true);
-      const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+      const uint32_t q_addr = smem_u32(Qs);
       bool ok = true;
       auto issue_qk = [&](int j) {
         const int st = j & 1, kst = j % NK;
@@ -312,10 +339,9 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         const uint32_t v_addr = smem_u32(Vs + (size_t)vst * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint32_t a_off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;   // P: K-major over the keys
           const uint32_t b_off = ks * 16 * 128;                            // V: 16 keys further down
-          umma(tmem_base + O_COL, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off), idesc_o,
-               (j > 0 || ks > 0) ? 1u : 0u);
+          umma_ts(tmem_base + O_COL, tmem_base + P_COL + (j & 1) * (BN / 2) + ks * 8, desc_mn_major(v_addr + b_off),
+                  idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[vst]);
         umma_commit(&o_ready);
@@ -387,7 +413,20 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         sum3 += s[i + 3];
       }
       l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
-      // the previous tile's P V must be complete before O is rescaled and P overwritten
+      // P as bfloat16 into this tile's P buffer (its last reader, the P V two tiles back, is
+      // complete: the previous tile waited for it)
+      {
+        uint32_t w[BN / 2];
+#pragma unroll
+        for (int i = 0; i < BN / 2; ++i) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(s[2 * i], s[2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        const uint32_t p_addr = lane_addr + P_COL + (j & 1) * (BN / 2);
+        tmem_st32_nowait(p_addr, &w[0]);
+        tmem_st32_nowait(p_addr + 32, &w[32]);
+      }
+      // the previous tile's P V must be complete before O is rescaled
       if (j > 0) {
         ok = ok && mbar_wait(&o_ready, (j - 1) & 1, err);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -404,17 +443,6 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
       }
       m_run = m_new;
-      // P as bfloat16, swizzled K-major over the keys
-#pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        unsigned w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(s[c * 8 + 2 * i], s[c * 8 + 2 * i + 1]);
-          w[i] = *reinterpret_cast<unsigned*>(&h);
-        }
-        *reinterpret_cast<uint4*>(Ps + swz(row, c * 8, BM)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
       // values of keys outside the range are zeroed (P is 0 there, but stale pages may hold NaN)
       if (ts < k_begin || ts + BN > k_end) {
         ok = ok && mbar_wait(&v_full[j % NV], (j / NV) & 1, err);   // the tile has landed
@@ -427,8 +455,9 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             for (int c = 0; c < 8; ++c)
               *reinterpret_cast<uint4*>(vd + kb * BN * 128 + row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
@@ -536,7 +565,7 @@ PBE_EXPORT int pbe_attn_tc5(const AttnParams* params, int num_work, int num_page
   if (rc != 0) return rc;
   rc = make_map(&map_v, p.v_cache, rows, P);
   if (rc != 0) return rc;
-  const size_t smem = (size_t)Q_BYTES + (NK + NV) * KV_BYTES + P_BYTES + 1024;
+  const size_t smem = (size_t)Q_BYTES + (NK + NV) * KV_BYTES + 1024;
   static bool opted = false;
   if (!opted) {
     cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -320,7 +320,8 @@ def attention_kernel_config(head_dim: int, dtype: torch.dtype, kind: Optional[st
     """(kind, tile_rows, key_tile) of the attention kernel used for a head size and dtype."""
     if head_dim % 16 != 0 or head_dim <= 0 or head_dim > 256:
         raise KernelError(f"attention kernels take head sizes 16, 32, ..., 256; got {head_dim}")
-    if kind is None and dtype == torch.bfloat16 and head_dim in (64, 128) and _attention_choice() == "tc5":
+    if kind is None and dtype == torch.bfloat16 and head_dim in (64, 128) and _attention_choice() != "mma" \
+            and _tc5_available():
         kind = "tc5"
     kind = kind or ("mma" if dtype == torch.bfloat16 and _mma_available() else "simple")
     if kind == "simple":
@@ -334,10 +335,16 @@ MMA_KEY_TILE = 64
 
 
 def _attention_choice() -> str:
-    """PBE_ATTN=tc5 puts prompt portions of bfloat16 models with head size 64 or 128 on the
-    tcgen05 attention kernel; anything else leaves the mma.sync kernel in place."""
+    """Prompt portions of bfloat16 models with head size 64 or 128 run on the tcgen05
+    attention kernel; PBE_ATTN=mma keeps them on the mma.sync kernel."""
     import os
     return os.environ.get("PBE_ATTN", "").strip().lower()
+
+
+def _tc5_available() -> bool:
+    import os
+    from .build import KERNEL_DIR
+    return os.path.isfile(os.path.join(KERNEL_DIR, "attention_tc5.cu"))
 
 
 def _mma_available() -> bool:
@@ -363,9 +370,11 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
     defines = {"PBE_HEAD_DIM": int(head_dim)}
     tc5 = kind == "tc5"
     if tc5:
-        if q.dtype != torch.bfloat16 or not tc5_attention_applies(head_dim, page_tokens):
-            raise KernelError("the tcgen05 attention kernel takes bfloat16, head sizes 64 and 128 and page sizes "
-                              "8..128 that divide 128")
+        if q.dtype != torch.bfloat16 or head_dim not in (64, 128):
+            raise KernelError("the tcgen05 attention kernel takes bfloat16 and head sizes 64 and 128")
+        # its page loads need pages of 8..128 tokens that divide the key tile of 128; with
+        # other page sizes the mma.sync kernel (same work list, same tile rows) does the tiles
+        tc5 = tc5_attention_applies(head_dim, page_tokens)
         kind = "mma"
     p = AttnParams(
         q=q.data_ptr(), k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr(), out=out.data_ptr(),
@@ -422,7 +431,7 @@ def attention_libraries(head_dim: int, dtype: torch.dtype):
     jobs = [("attention_simple", {"PBE_HEAD_DIM": int(head_dim)})]
     if dtype == torch.bfloat16 and _mma_available():
         jobs.append(("attention_mma", {"PBE_HEAD_DIM": int(head_dim)}))
-        if head_dim in (64, 128) and _attention_choice() == "tc5":
+        if head_dim in (64, 128) and _attention_choice() != "mma" and _tc5_available():
             jobs.append(("attention_tc5", {"PBE_HEAD_DIM": int(head_dim)}))
     return jobs
 

@@ -22,7 +22,14 @@ TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_siz
               intermediate_size=208, vocab_size=517, rope_theta=50000.0, rms_norm_eps=3e-6,
               tie_word_embeddings=False, max_position_embeddings=1024, use_sliding_window=True,
               sliding_window=24, max_window_layers=1, hidden_act="silu", eos_token_id=516)
-TINY = {"A": (TINY_A, 0, 16, 8.0), "B": (TINY_B, 1, 8, 4.0), "C": (TINY_C, 2, 8, 6.0)}
+# head size 64 (in bfloat16 its prompt portions run on the tcgen05 attention kernel), three
+# query heads on one key/value head, a window on the second layer
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=96,
+              num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1, head_dim=64,
+              intermediate_size=144, vocab_size=411, rope_theta=20000.0, rms_norm_eps=2e-6,
+              tie_word_embeddings=True, max_position_embeddings=2048, use_sliding_window=True,
+              sliding_window=150, max_window_layers=1, hidden_act="silu", eos_token_id=410)
+TINY = {"A": (TINY_A, 0, 16, 8.0), "B": (TINY_B, 1, 8, 4.0), "C": (TINY_C, 2, 8, 6.0), "D": (TINY_D, 3, 16, 5.0)}
 
 
 def make_model_folder(path, cfg: dict, seed: int, sharpen: float = 1.0, dtype=torch.bfloat16) -> str:

@@ -26,7 +26,7 @@ ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
 TOL_F32 = 2e-5
 TOL_BF16_REL = 0.04
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71], "C": [3, 26, 58, 90]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71], "C": [3, 26, 58, 90], "D": [4, 45, 130, 301]}
 
 
 def requests_for(name, vocab, extra=()):
@@ -65,7 +65,7 @@ def check(got, want, dtype, label):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_schedules_agree_with_plain(tiny_folders, name, dtype):
     cfg, _, page, _ = TINY[name]
     folder = tiny_folders[name]
@@ -85,7 +85,7 @@ def test_schedules_agree_with_plain(tiny_folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_page_reuse(tiny_folders, name, dtype):
     cfg, _, page, _ = TINY[name]
     folder = tiny_folders[name]
