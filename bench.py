@@ -295,7 +295,7 @@ def main():
             points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         result["points"] = points
         T = 2048
-        ms_p = time_prefill(engine, T, repeats=3)
+        ms_p = time_prefill(engine, T, repeats=5)
         flops = T * lin_flops + 2 * 2 * H * hd * L * (T * (T + 1) // 2) + 2 * V * d
         result["prefill"] = {"value": round(T * 1e3 / ms_p, 1), "tokens": T, "ms": round(ms_p, 3),
                              "frac": round(flops / (ms_p * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}

@@ -28,6 +28,7 @@ def timed(fn, flush, n=5):
     for _ in range(n):
         flush.zero_()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(400000)          # the host enqueues fn() meanwhile: no launch latency in the time
         s.record()
         fn()
         e.record()

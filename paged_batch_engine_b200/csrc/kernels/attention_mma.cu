@@ -301,13 +301,15 @@ attn_mma_kernel(AttnParams p) {
   bf16* Vs = Ks + 2 * BN * LDS;                        // [2][BN][LDS]
   __shared__ int s_pages[MAX_SMEM_PAGES];
 
-  pdl_wait();
+  // The work list, the lengths and the block tables are written by the host before the
+  // step's first kernel: they are read before the dependency on the previous kernel is awaited.
   // rows mode: a one-dimensional grid, work-major, so that the heavy tiles at the head of
   // the work list start first for every key/value head
   const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
   const int32_t* work = p.work + (size_t)(KEYS ? blockIdx.x : blockIdx.x / KV) * 4;
   const int r = work[0];
   if (r < 0) {
+    pdl_wait();
     pdl_launch_dependents();
     return;
   }
@@ -318,6 +320,7 @@ attn_mma_kernel(AttnParams p) {
   const int pr0 = m_tile * BM;
   const int rows_here = min(BM, n_packed - pr0);
   if (rows_here <= 0 || (rows_here <= 16) != KEYS) {   // nothing here, or the other instance's work
+    pdl_wait();
     pdl_launch_dependents();
     return;
   }
@@ -339,6 +342,7 @@ attn_mma_kernel(AttnParams p) {
   const bf16* vc = (const bf16*)p.v_cache;
   const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
 
+  pdl_wait();
   // Q tile -> shared (rows beyond the request are zeros)
   for (int c = tid; c < QROWS * CPR; c += NTHREADS) {
     const int i = c / CPR, col = c - i * CPR;

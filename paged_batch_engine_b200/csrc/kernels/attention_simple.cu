@@ -41,8 +41,8 @@ attn_simple_kernel(AttnParams p) {
   float* Ks = Qs + BM * HD;               // [BN][HD + 1]
   float* Vs = Ks + BN * (HD + 1);         // [BN][HD]
 
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int32_t* work = p.work + (size_t)blockIdx.x * 4;
   const int r = work[0];
   if (r < 0) return;
@@ -185,8 +185,8 @@ attn_simple_kernel(AttnParams p) {
 
 template <typename T>
 __global__ void attn_merge_kernel(AttnMergeParams p) {
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int srow = blockIdx.x, head = blockIdx.y;
   const int n = p.split_counts[srow];
   if (n <= 1) return;

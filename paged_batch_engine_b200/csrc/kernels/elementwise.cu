@@ -13,8 +13,8 @@ using namespace pbe;
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int32_t* __restrict__ ids, int d, int vocab) {
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * d;
@@ -71,8 +71,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    const float* __restrict__ gain, TO* __restrict__ out,
                                    const int32_t* __restrict__ row_index, int d, float eps) {
   __shared__ float red[33];
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int r = blockIdx.x;
   const int src = row_index ? row_index[r] : r;
   float* res = residual + (size_t)src * d;
@@ -154,8 +154,8 @@ PBE_EXPORT int pbe_add_rmsnorm(float* residual, const void* delta, int delta_dty
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
                                 size_t total) {
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / inter;
@@ -171,8 +171,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
 template <typename T>
 __global__ void silu_mul_vec4_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
                                      size_t total4) {
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int q = inter / 4;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
        idx += (size_t)gridDim.x * blockDim.x) {

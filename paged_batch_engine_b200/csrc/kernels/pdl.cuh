@@ -4,9 +4,11 @@
 // visible; everything a kernel reads from or writes to activations, the cache or any
 // other buffer of the step comes after that call.  What does not depend on the previous
 // kernel (weights, above all) may be fetched before it.  pdl_launch_dependents() tells
-// the next kernel it may begin launching; it is placed where this kernel's blocks have
-// issued most of their memory traffic.  Inside a captured graph the same launches become
-// programmatic dependency edges.  Every block of every kernel calls pdl_wait() before it
+// the next kernel it may begin launching: the weight-streaming kernels call it where their
+// blocks have issued most of their memory traffic, the short kernels between them (norms,
+// position encoding, merge, activation, sampling) at their very top, before their own
+// wait, so that the next weight-streaming kernel is resident and fetching while they run.
+// Inside a captured graph the same launches become programmatic dependency edges.  Every block of every kernel calls pdl_wait() before it
 // exits, so "the previous kernel completed" always implies that all earlier ones did.
 #pragma once
 #include <cuda_runtime.h>

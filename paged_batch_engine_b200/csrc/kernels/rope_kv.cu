@@ -27,8 +27,8 @@ struct RopeKvParams {
 
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvParams p) {
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
   const int row_width = (H + 2 * KV) * hd;
@@ -118,8 +118,8 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&a)[8]) {
 __global__ void rope_kv_vec_kernel(RopeKvParams p) {
   extern __shared__ float trig[];            // cos[half], sin[half]
   typedef __nv_bfloat16 T;
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
   const int half = hd / 2, half8 = half / 8, hd8 = hd / 8;

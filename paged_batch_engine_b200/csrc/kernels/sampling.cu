@@ -210,8 +210,8 @@ __device__ void block_argmax(const float* row, int V, Shared& sh, float* out_max
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, size_t ld, int V, int32_t* __restrict__ out) {
   __shared__ Shared sh;
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   float mx;
   int idx;
   block_argmax(logits + (size_t)blockIdx.x * ld, V, sh, &mx, &idx);
@@ -231,8 +231,8 @@ argmax_cluster_kernel(const float* __restrict__ logits, size_t ld, int V, int32_
   __shared__ float part_v[ARGMAX_CLUSTER];
   __shared__ int part_i[ARGMAX_CLUSTER];
   cg::cluster_group cluster = cg::this_cluster();
+  pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  pdl_launch_dependents();
   const int rank = (int)cluster.block_rank();
   const int row = blockIdx.x / ARGMAX_CLUSTER;
   const int chunk = ((V + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER + 3) & ~3;
