@@ -1,0 +1,118 @@
+#!/usr/bin/env python3
+"""Whole workloads through the scheduler and the Python entry point, with random weights.
+
+    python bench_serving.py [--workload 1.5b|14b|7b] [--requests N] [--layers L]
+
+``1.5b``: the Qwen2.5-1.5B shape, 64 requests whose prompt lengths are uniform in 16..2048
+(seeded), prompts read in portions of 512 beside the decoding requests, 256 new tokens each.
+``14b``: the Qwen2.5-14B shape, 8 prompts of 8,192 tokens, then 512 new tokens each.
+``7b``: the Qwen2.5-7B shape under the 1.5b workload.
+
+Everything goes through ``Engine.generate``: admission, portions under the token budget,
+mixed steps of prompt portions beside decoded tokens, sampling (greedy), finishing.  Prints
+ONE JSON line: generated tokens a second over the wall clock of the whole run, the prompt
+tokens a second, the number of steps and the host's share of the time by phase (schedule,
+forward = enqueueing the step, sample = waiting for the device and reading the ids, process).
+It is a workload check beside ``bench.py``, whose line is the headline.
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def shape(hidden, layers, heads, kv, inter, vocab, tied):
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=hidden,
+                num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv,
+                intermediate_size=inter, vocab_size=vocab, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=tied, max_position_embeddings=32768, use_sliding_window=False,
+                hidden_act="silu", eos_token_id=151645)
+
+
+SHAPES = {
+    "1.5b": shape(1536, 28, 12, 2, 8960, 151936, True),
+    "7b": shape(3584, 28, 28, 4, 18944, 152064, False),
+    "14b": shape(5120, 48, 40, 8, 13824, 152064, False),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="1.5b", choices=sorted(SHAPES))
+    ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--new-tokens", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (named in the line)")
+    ap.add_argument("--max-batched-tokens", type=int, default=0)
+    ap.add_argument("--prefill-chunk", type=int, default=0)
+    args = ap.parse_args()
+
+    import torch
+    from paged_batch_engine_b200 import Engine, SamplingParams
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.csrc import ops
+
+    cfg = dict(SHAPES[args.workload])
+    layers_full = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    _, typed = load_config(cfg)
+    g = torch.Generator().manual_seed(2024)
+    if args.workload == "14b":
+        n = args.requests or 8
+        lengths = [8192] * n
+        new_tokens = args.new_tokens or 512
+        chunk = args.prefill_chunk or 2048
+    else:
+        n = args.requests or 64
+        lengths = torch.randint(16, 2049, (n,), generator=g).tolist()
+        new_tokens = args.new_tokens or 256
+        chunk = args.prefill_chunk or 512
+    budget = args.max_batched_tokens or max(chunk, 2048)
+    vocab = cfg["vocab_size"]
+    prompts = [torch.randint(0, vocab, (L,), generator=g).tolist() for L in lengths]
+    page = 16
+    max_len = max(lengths) + new_tokens + 16
+    pages = sum((L + new_tokens + page) // page + 1 for L in lengths) + 8
+    engine = Engine(typed, dtype="bfloat16", seed=0, page_size=page, num_pages=pages, max_num_seqs=max(n, 1),
+                    max_num_batched_tokens=budget, prefill_chunk_cap=chunk, max_model_len=max_len)
+    params = SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)
+    # warm-up: kernels loaded, graphs captured for the batch sizes of the run's tail
+    engine.generate([p[:64] for p in prompts[:min(n, 8)]], SamplingParams(max_new_tokens=4, ignore_eos=True))
+    torch.cuda.synchronize()
+    for k in engine.profile:
+        engine.profile[k] = 0 if k == "steps" else 0.0
+    launches0 = ops.launch_count()
+    graphs = engine.runner.graphs
+    captures0, capture_s0 = len(graphs.graphs), graphs.capture_seconds
+    t0 = time.perf_counter()
+    results = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    generated = sum(len(r.output_tokens) for r in results)
+    prof = engine.profile
+    line = {
+        "metric": f"generated tok/s, Qwen2.5-{args.workload.upper()} shape, {n} requests through the scheduler",
+        "value": round(generated / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3),
+        "prompt_tokens": sum(lengths), "prompt_tok_per_s_overall": round(sum(lengths) / wall, 1),
+        "generated_tokens": generated, "steps": prof["steps"],
+        "host_ms_per_step": {k: round(1e3 * prof[k] / max(prof["steps"], 1), 3)
+                             for k in ("schedule", "forward", "sample", "process")},
+        "preemptions": sum(r.preemptions for r in results),
+        "graph_captures": len(graphs.graphs) - captures0,
+        "graph_capture_s": round(graphs.capture_seconds - capture_s0, 3),
+        "kernel_launches_eager": ops.launch_count() - launches0,
+        "config": {"layers": cfg["num_hidden_layers"], "layers_full_model": layers_full, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "page_tokens": page,
+                   "max_batched_tokens": budget, "prefill_chunk": chunk, "new_tokens": new_tokens,
+                   "dtype": "bf16", "data": "synthetic tokens, random weights"},
+    }
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -135,8 +135,23 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None,
     return out
 
 
+_by_request: Dict[tuple, ctypes.CDLL] = {}
+
+
 def load_library(name: str, defines: Optional[Dict[str, object]] = None,
                  extra_flags: Sequence[str] = ()) -> ctypes.CDLL:
+    # the sources are hashed once per (name, defines) and process, not once per call
+    request = (name, tuple(sorted((defines or {}).items())), tuple(extra_flags))
+    lib = _by_request.get(request)
+    if lib is not None:
+        return lib
+    lib = _load_library(name, defines, extra_flags)
+    _by_request[request] = lib
+    return lib
+
+
+def _load_library(name: str, defines: Optional[Dict[str, object]] = None,
+                  extra_flags: Sequence[str] = ()) -> ctypes.CDLL:
     _, out = library_path(name, defines, extra_flags)
     with _lock:
         lib = _loaded.get(out)

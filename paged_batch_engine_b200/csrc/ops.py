@@ -35,7 +35,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of the current stream, without building a torch.cuda.Stream object per launch
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _need_cuda(*tensors):
@@ -66,17 +67,20 @@ def _check(code: int, what: str):
     _launches += 1
 
 
-_sigs_done = set()
+
+
+_fns = {}
 
 
 def _fn(lib_name, fn_name, argtypes, defines=None):
-    lib = load_library(lib_name, defines)
-    fn = getattr(lib, fn_name)
-    key = (id(lib), fn_name)
-    if key not in _sigs_done:
+    key = (lib_name, fn_name, tuple(sorted(defines.items())) if defines else None)
+    fn = _fns.get(key)
+    if fn is None:
+        lib = load_library(lib_name, defines)
+        fn = getattr(lib, fn_name)
         fn.argtypes = argtypes
         fn.restype = c_int
-        _sigs_done.add(key)
+        _fns[key] = fn
     return fn
 
 

@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import time
+
 import numpy as np
 import torch
 
@@ -168,6 +170,7 @@ class DecodeGraphs:
         self.replays = 0
         self.launches_per_replay = 0      # this package's kernels inside one captured step
         self.last_h2d_bytes = 0           # size of the integer buffer copied before a replay
+        self.capture_seconds = 0.0        # host time spent capturing (warm-up run included)
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
@@ -193,7 +196,9 @@ class DecodeGraphs:
         S = _bucket(self._splits_needed(entries, choose_split_keys(B)))
         key = (B, S)
         if key not in self.graphs:
+            t0 = time.perf_counter()
             self.graphs[key] = self._capture(B, S, entries)
+            self.capture_seconds += time.perf_counter() - t0
         graph, ctx, logits = self.graphs[key]
         ctx.fill(entries, runner.model.spec.vocab_size)
         self.last_h2d_bytes = ctx._size * 4
