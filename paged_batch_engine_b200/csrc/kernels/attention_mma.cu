@@ -75,6 +75,12 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct RowInfo {      // the two rows of this thread's accumulator fragment
   int pos[2];         // absolute position of the row's query (-1: no such row)
   int lo[2];          // first visible key
@@ -82,7 +88,9 @@ struct RowInfo {      // the two rows of this thread's accumulator fragment
 
 // One key tile for one warp: NKT 8-key score tiles starting at key `key0` (absolute) which
 // sit at row `krow0` of the shared K and V tiles.  Updates m, l (log2 domain) and o.
-template <int NKT, bool MASK, bool QREG = false>
+// LOCAL_SUM: l holds this thread's share of the row sum (its own columns); the caller adds
+// the four lanes of a row once, at the end, instead of two shuffles a tile.
+template <int NKT, bool MASK, bool QREG = false, bool LOCAL_SUM = false>
 __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
                                              const bf16* __restrict__ Vs, int krow0, int key0,
                                              int k_begin, int k_end, const RowInfo& ri, float scale_log2,
@@ -135,7 +143,7 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     const float m_new = fmaxf(m[r], mx[r]);
     m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;   // nothing visible yet: keep exp2 finite
-    alpha[r] = exp2f(m[r] - m_use[r]);               // m = -inf gives 0, and o is 0 then
+    alpha[r] = ex2_approx(m[r] - m_use[r]);          // m = -inf gives 0, and o is 0 then
     m[r] = m_new;
   }
   float sum[2] = {0.f, 0.f};
@@ -144,22 +152,27 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int r = c >> 1;
-      const float p = exp2f(s[nt][c] - m_use[r]);    // masked: exp2(-inf) = 0
+      const float p = ex2_approx(s[nt][c] - m_use[r]);   // masked: exp2(-inf) = 0
       s[nt][c] = p;
       sum[r] += p;
     }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+    if (!LOCAL_SUM) {
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+    }
     l[r] = l[r] * alpha[r] + sum[r];
   }
+  // the accumulator is rescaled only when some row's maximum moved (rare after the first tiles)
+  if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-  for (int nt = 0; nt < ONT; ++nt) {
-    o[nt][0] *= alpha[0];
-    o[nt][1] *= alpha[0];
-    o[nt][2] *= alpha[1];
-    o[nt][3] *= alpha[1];
+    for (int nt = 0; nt < ONT; ++nt) {
+      o[nt][0] *= alpha[0];
+      o[nt][1] *= alpha[0];
+      o[nt][2] *= alpha[1];
+      o[nt][3] *= alpha[1];
+    }
   }
   // O += P V
 #pragma unroll
@@ -236,7 +249,7 @@ __device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, c
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float m_new = fmaxf(m[mt][r], mx[r]);
       m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
-      alpha[r] = exp2f(m[mt][r] - m_use[r]);
+      alpha[r] = ex2_approx(m[mt][r] - m_use[r]);
       m[mt][r] = m_new;
     }
     float sum[2] = {0.f, 0.f};
@@ -245,7 +258,7 @@ __device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, c
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int r = c >> 1;
-        const float pv = exp2f(s[mt][nt][c] - m_use[r]);
+        const float pv = ex2_approx(s[mt][nt][c] - m_use[r]);
         s[mt][nt][c] = pv;
         sum[r] += pv;
       }
@@ -359,6 +372,7 @@ attn_mma_kernel(AttnParams p) {
   const int blk_first = tile0 / P;
   const int blk_count = n_tiles > 0 ? (k_end - 1) / P - blk_first + 1 : 0;
   const bool pages_in_smem = blk_count <= MAX_SMEM_PAGES;
+  const int pshift = (P & (P - 1)) == 0 ? 31 - __clz(P) : -1;   // pages of a power of two: shifts, no division
   if (pages_in_smem) {
     for (int i = tid; i < blk_count; i += NTHREADS) s_pages[i] = bt[blk_first + i];
     __syncthreads();
@@ -375,10 +389,11 @@ attn_mma_kernel(AttnParams p) {
       bool valid = key >= k_begin && key < k_end;
       size_t off = 0;
       if (valid) {
-        const int blk = key / P;
+        const int blk = pshift >= 0 ? key >> pshift : key / P;
         const int page = pages_in_smem ? s_pages[blk - blk_first] : bt[blk];
         valid = page >= 0;
-        if (valid) off = (((size_t)page * KV + kvh) * P + (key - blk * P)) * HD + col * 8;
+        // 32-bit row index (pages x heads x page tokens stays far below 2^31), one wide multiply
+        if (valid) off = (size_t)((page * KV + kvh) * P + (key - blk * P)) * HD + col * 8;
       }
       cp_async16(kd + j * LDS + col * 8, kc + off, valid);
       cp_async16(vd + j * LDS + col * 8, vc + off, valid);
@@ -575,6 +590,7 @@ attn_decode_kernel(AttnParams p, int num_work) {
   const bf16* vc = (const bf16*)p.v_cache;
   const int total_items = num_work * KV;
   const int g = lane >> 2, c4 = lane & 3;
+  const int pshift = (P & (P - 1)) == 0 ? 31 - __clz(P) : -1;   // pages of a power of two: shifts, no division
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const float LN2 = 0.6931471805599453f;
 
@@ -642,9 +658,9 @@ attn_decode_kernel(AttnParams p, int num_work) {
     int pg = (win + lane) * P < k_end ? bt[win + lane] : -1;
     auto load_tile = [&](int t, int stage) {
       const int ts = tile0 + t * DEC_KEYS;
-      const int last_blk = (ts + DEC_KEYS - 1) / P;
+      const int last_blk = pshift >= 0 ? (ts + DEC_KEYS - 1) >> pshift : (ts + DEC_KEYS - 1) / P;
       if (last_blk >= win + 32) {                      // warp-uniform: slide the window
-        win = ts / P;
+        win = pshift >= 0 ? ts >> pshift : ts / P;
         pg = (win + lane) * P < k_end ? bt[win + lane] : -1;
       }
       bf16* kd = ring + (size_t)stage * 2 * DEC_KEYS * LDS;
@@ -652,12 +668,14 @@ attn_decode_kernel(AttnParams p, int num_work) {
 #pragma unroll
       for (int it = 0; it < (DEC_KEYS * CPR + 31) / 32; ++it) {
         const int c = lane + it * 32;
-        const int j = (c / CPR) % DEC_KEYS, col = c - (c / CPR) * CPR;
+        const int j = c / CPR, col = c - j * CPR;        // j < DEC_KEYS whenever c is in range
         const int key = ts + j;
-        const int blk = key / P;
+        const int blk = pshift >= 0 ? key >> pshift : key / P;
         const int page = __shfl_sync(0xffffffffu, pg, (blk - win) & 31);
         const bool valid = c < DEC_KEYS * CPR && key >= k_begin && key < k_end && page >= 0;
-        const size_t off = valid ? (((size_t)page * KV + kvh) * P + (key - blk * P)) * HD + col * 8 : 0;
+        // 32-bit row index (pages x heads x page tokens stays far below 2^31), one wide multiply
+        const int rowi = valid ? (page * KV + kvh) * P + (key - blk * P) : 0;
+        const size_t off = (size_t)rowi * HD + (valid ? col * 8 : 0);
         if (c < DEC_KEYS * CPR) {
           cp_async16(kd + j * LDS + col * 8, kc + off, valid);
           cp_async16(vd + j * LDS + col * 8, vc + off, valid);
@@ -688,14 +706,21 @@ attn_decode_kernel(AttnParams p, int num_work) {
       const bool interior = key0 >= k_begin && key0 + DEC_KEYS <= k_end && key0 + DEC_KEYS - 1 <= pos_min &&
                             key0 >= lo_max;
       if (interior)
-        process_tile<2, false, true>(nullptr, kt, vt, 0, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane, qa);
+        process_tile<2, false, true, true>(nullptr, kt, vt, 0, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane,
+                                           qa);
       else
-        process_tile<2, true, true>(nullptr, kt, vt, 0, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane, qa);
+        process_tile<2, true, true, true>(nullptr, kt, vt, 0, key0, k_begin, k_end, ri, scale_log2, m, l, o, lane,
+                                          qa);
       __syncwarp();               // the stage may be refilled
       buf = buf + 1 == DEC_STAGES ? 0 : buf + 1;
       fill = fill + 1 == DEC_STAGES ? 0 : fill + 1;
     }
     cp_async_wait<0>();
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {          // the row sums: the four lanes of a row, once
+      l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+      l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+    }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       const int pr = pr0 + g + rr * 8;
