@@ -1,28 +1,35 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores.
 //
 // One block owns a row tile of 128 packed rows (query row x head of the group) of one
-// key/value head and walks over its keys in tiles of 128:
-//   S = Q K^T     tcgen05.mma, 128 x 128 x head_dim, accumulator in tensor memory (two S
+// key/value head and walks over its keys in tiles of 64:
+//   S = Q K^T     tcgen05.mma, 128 x 64 x head_dim, accumulator in tensor memory (two S
 //                 buffers alternate, so the next tile's scores are computed while this tile's
 //                 softmax runs);
-//   softmax       four warps, ONE THREAD PER ROW: the row's 128 scores come out of tensor
+//   softmax       four warps, ONE THREAD PER ROW: the row's 64 scores come out of tensor
 //                 memory with tcgen05.ld, so maximum, exponentials and sum need no shuffle;
-//   O += P V      P is written as bfloat16 into tensor memory (tcgen05.st, two buffers) and is
-//                 the MMA's A operand from there, V is used as it lies in the pages (head_dim
-//                 contiguous: an MN-major B operand in shared memory), the output accumulator
-//                 stays in tensor memory and is rescaled there (tcgen05.ld / tcgen05.st) only
-//                 when a row's maximum has grown by more than 2^8.
-// Keys and values come from the pages by TMA (cp.async.bulk.tensor 2D, one box per page and
-// 64-wide half of the head, 128-byte swizzle, no multicast) into a ring of three key tiles and
-// a ring of three value tiles: a key tile is free again as soon as its scores are computed, a
-// value tile after its P V.  The query tile is copied by the softmax warps once.  Warp 0 lane 0
-// loads keys, warp 6 lane 0 loads values, warp 1 lane 0 issues the MMAs, warps 2-5 are the
-// softmax / correction / epilogue warps.
+//                 masks only on edge tiles; the running maximum moves only after it grew by
+//                 2^8, so the output accumulator is rarely rescaled;
+//   O += P V      P goes back as bfloat16 (tcgen05.st) into the columns its scores came from
+//                 and is the MMA's A operand from tensor memory, V is used as it lies in the
+//                 pages (head_dim contiguous: an MN-major B operand in shared memory), the
+//                 output accumulator stays in tensor memory and is rescaled there
+//                 (tcgen05.ld / tcgen05.st).
+// A block takes 256 columns of tensor memory (two S buffers of 64, O of up to 128) and 97 KB of
+// shared memory, so that TWO BLOCKS SHARE A MULTIPROCESSOR: a block's softmax thread is
+// latency-bound between its phases (barrier, tensor-memory load, store, fence), and the other
+// block's warps fill the exponential unit and the tensor pipe meanwhile; the second block's
+// prologue also hides behind the first one's work.
+// Keys and values come from the pages by TMA (cp.async.bulk.tensor 2D, one box per page - or
+// per 64 keys of a larger page - and 64-wide half of the head, 128-byte swizzle, no
+// multicast), one lane per box, into rings of two key tiles and two value tiles: a key tile is
+// free again as soon as its scores are computed, a value tile after its P V.  The query tile
+// is copied by the softmax warps once.  Warp 0 loads keys, warp 6 loads values, warp 1 lane 0
+// issues the MMAs, warps 2-5 are the softmax / correction / epilogue warps.
 //
 // Same work list, same split scheme and same outputs as attn_mma_kernel<false>; it takes
-// head sizes 64 and 128 and page sizes 8..128 that divide 128.  Every mbarrier wait is
-// bounded; a wait that runs out sets *err and the roles run to their end, so that tensor
-// memory is always given back.
+// head sizes 64 and 128 and page sizes of 8 tokens or more that divide 64 or are a multiple
+// of it.  Every mbarrier wait is bounded; a wait that runs out sets *err and the roles run to
+// their end, so that tensor memory is always given back.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -41,15 +48,14 @@ typedef __nv_bfloat16 bf16;
 constexpr int HD = PBE_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
 constexpr int BM = 128;                 // packed rows per block = TMEM lanes
-constexpr int BN = 128;                 // keys per tile
+constexpr int BN = 64;                  // keys per tile
 constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
 constexpr int Q_BYTES = BM * HD * 2;
 constexpr int KV_BYTES = BN * HD * 2;   // one K tile or one V tile
 constexpr int NTHREADS = 224;
-constexpr int NK = 3, NV = 3;           // key tiles and value tiles in flight
-constexpr int TMEM_COLS = 512;
-constexpr int S_COL = 0, O_COL = 256;   // S buffers at columns 0 and 128, O at 256
-constexpr int P_COL = 384;              // P buffers (two bfloat16 per column) at columns 384 and 448
+constexpr int NK = 2, NV = 2;           // key tiles and value tiles in flight
+constexpr int TMEM_COLS = 256;
+constexpr int S_COL = 0, O_COL = 128;   // S buffers at columns 0 and 64 (P in their first 32 columns), O at 128
 constexpr long long WAIT_CLOCKS = 2000LL * 1000 * 1000;   // about a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -188,7 +194,7 @@ __device__ __forceinline__ uint32_t swz(int row, int col, int rows) {
   return (uint32_t)(blk * rows * 128 + row * 128 + ((((cc >> 3) ^ (row & 7)) << 4) | ((cc & 7) << 1)));
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS, 2)
 attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                 AttnParams p, int* err) {
   extern __shared__ unsigned char smem_raw[];
@@ -196,8 +202,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   unsigned char* Qs = base;                               // [KB][128 rows][128 B]
   unsigned char* Ks = Qs + Q_BYTES;                       // [NK stages][KB][128 keys][128 B]
   unsigned char* Vs = Ks + NK * KV_BYTES;                 // [NV stages][KB][128 keys][128 B]
-  __shared__ __align__(8) uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], s_empty[2], p_full,
-      o_ready;
+  __shared__ __align__(8) uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], p_full, o_ready;
   __shared__ uint32_t tmem_base_smem;
 
   pdl_wait();
@@ -239,10 +244,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
-    }
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
     mbar_init(&p_full, 4);
     mbar_init(&o_ready, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -285,7 +287,8 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     unsigned char* tiles = keys ? Ks : Vs;
     const CUtensorMap* map = keys ? &map_k : &map_v;
     const int last_blk = n_tiles > 0 ? (k_end - 1) / P : 0;
-    const int pages_per_tile = BN / P;
+    const int box_rows = min(P, BN);                       // a page, or the 64 keys of a larger page
+    const int boxes_per_tile = BN / box_rows;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j % ring;
       int go = 1;
@@ -297,13 +300,15 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       if (!go) break;
       unsigned char* dst = tiles + (size_t)st * KV_BYTES;
       const int ts = tile0 + j * BN;
-      for (int pg = lane; pg < pages_per_tile; pg += 32) {
-        const int blk = ts / P + pg;
+      for (int pg = lane; pg < boxes_per_tile; pg += 32) {
+        const int key0 = ts + pg * box_rows;
+        const int blk = key0 / P;
         int page = blk <= last_blk ? bt[blk] : 0;         // beyond the range: any page, the keys are masked
         if (page < 0) page = 0;
-        const int y = (page * KV + kvh) * P;
+        const int y = (page * KV + kvh) * P + (key0 - blk * P);
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb) tma_load_2d(dst + kb * BN * 128 + pg * P * 128, map, kb * 64, y, &full[st]);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(dst + kb * BN * 128 + pg * box_rows * 128, map, kb * 64, y, &full[st]);
       }
       __syncwarp();
     }
@@ -317,22 +322,24 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       auto issue_qk = [&](int j) {
         const int st = j & 1, kst = j % NK;
         ok = ok && mbar_wait(&k_full[kst], (j / NK) & 1, err);
-        ok = ok && mbar_wait(&s_empty[st], ((j >> 1) & 1) ^ 1, err);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(Ks + (size_t)kst * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;     // BM == BN rows per block
-          umma(tmem_base + S_COL + st * BN, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s,
+          const uint32_t q_off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
+          const uint32_t k_off = (ks >> 2) * (BN * 128) + (ks & 3) * 32;
+          umma(tmem_base + S_COL + st * BN, desc_k_major(q_addr + q_off), desc_k_major(k_addr + k_off), idesc_s,
                ks > 0 ? 1u : 0u);
         }
         umma_commit(&k_empty[kst]);                           // the key tile is free once its scores exist
         umma_commit(&s_full[st]);
       };
+      // The S buffer of tile j holds P_j until its P V has read it; the scores of tile j + 2 go
+      // to the same buffer and are issued after that P V: the tensor pipe runs them in order.
       issue_qk(0);
+      if (n_tiles > 1) issue_qk(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) issue_qk(j + 1);
-        const int vst = j % NV;
+        const int st = j & 1, vst = j % NV;
         ok = ok && mbar_wait(&v_full[vst], (j / NV) & 1, err);
         ok = ok && mbar_wait(&p_full, j & 1, err);            // P_j written, O rescaled
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -340,11 +347,12 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           const uint32_t b_off = ks * 16 * 128;                            // V: 16 keys further down
-          umma_ts(tmem_base + O_COL, tmem_base + P_COL + (j & 1) * (BN / 2) + ks * 8, desc_mn_major(v_addr + b_off),
-                  idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_ts(tmem_base + O_COL, tmem_base + S_COL + st * BN + ks * 8, desc_mn_major(v_addr + b_off), idesc_o,
+                  (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[vst]);
         umma_commit(&o_ready);
+        if (j + 2 < n_tiles) issue_qk(j + 2);
       }
     }
   } else {
@@ -367,14 +375,11 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       const int ts = tile0 + j * BN;
       ok = ok && mbar_wait(&s_full[st], (j >> 1) & 1, err);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // this row's 128 scores: all four loads in flight, one wait
+      // this row's 64 scores: both loads in flight, one wait
       float s[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(lane_addr + S_COL + st * BN + c * 32, &s[c * 32]);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[st]);            // the S buffer may be overwritten
       const bool full_tile = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
       if (!full_tile) {
 #pragma unroll
@@ -413,8 +418,8 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         sum3 += s[i + 3];
       }
       l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
-      // P as bfloat16 into this tile's P buffer (its last reader, the P V two tiles back, is
-      // complete: the previous tile waited for it)
+      // P as bfloat16 over the first 32 columns of the scores it came from (this thread has
+      // read its row of them; nobody else touches this lane)
       {
         uint32_t w[BN / 2];
 #pragma unroll
@@ -422,9 +427,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           __nv_bfloat162 h = __floats2bfloat162_rn(s[2 * i], s[2 * i + 1]);
           w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        const uint32_t p_addr = lane_addr + P_COL + (j & 1) * (BN / 2);
-        tmem_st32_nowait(p_addr, &w[0]);
-        tmem_st32_nowait(p_addr + 32, &w[32]);
+        tmem_st32_nowait(lane_addr + S_COL + st * BN, &w[0]);
       }
       // the previous tile's P V must be complete before O is rescaled
       if (j > 0) {
@@ -448,7 +451,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         ok = ok && mbar_wait(&v_full[j % NV], (j / NV) & 1, err);   // the tile has landed
         unsigned char* vd = Vs + (size_t)(j % NV) * KV_BYTES;
         const int key = ts + row;                          // thread `row` owns key row `row` of the tile
-        if (key < k_begin || key >= k_end) {
+        if (row < BN && (key < k_begin || key >= k_end)) {
 #pragma unroll
           for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
@@ -529,14 +532,14 @@ EncodeTiledFn encode_fn() {
   }
   return fn;
 }
-// the pages of one layer as a matrix [pages * kv_heads * page_tokens, head_dim]; boxes of one
-// page (page_tokens rows) by 64 columns
-int make_map(CUtensorMap* map, const void* cache, long long rows, int page_tokens) {
+// the pages of one layer as a matrix [pages * kv_heads * page_tokens, head_dim]; boxes of
+// box_rows rows (a page, or 64 keys of a larger page) by 64 columns
+int make_map(CUtensorMap* map, const void* cache, long long rows, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return (int)cudaErrorNotSupported;
   cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)page_tokens};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -554,16 +557,17 @@ PBE_EXPORT int pbe_attn_tc5(const AttnParams* params, int num_work, int num_page
   if (num_work <= 0) return 0;
   AttnParams p = *params;
   const int P = p.page_tokens;
-  if (p.num_heads % p.num_kv_heads != 0 || p.tile_rows != BM || p.split_keys % BN != 0 || P < 8 || P > 128 ||
-      (P % 8) != 0 || (BN % P) != 0)
+  if (p.num_heads % p.num_kv_heads != 0 || p.tile_rows != BM || p.split_keys % BN != 0 || P < 8 || (P % 8) != 0 ||
+      ((BN % P) != 0 && (P % BN) != 0))
     return (int)cudaErrorInvalidValue;
   if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15) || ((uintptr_t)p.q & 15) || ((uintptr_t)p.out & 15))
     return (int)cudaErrorInvalidValue;
   CUtensorMap map_k, map_v;
   const long long rows = (long long)num_pages * p.num_kv_heads * P;
-  int rc = make_map(&map_k, p.k_cache, rows, P);
+  const int box_rows = P < BN ? P : BN;
+  int rc = make_map(&map_k, p.k_cache, rows, box_rows);
   if (rc != 0) return rc;
-  rc = make_map(&map_v, p.v_cache, rows, P);
+  rc = make_map(&map_v, p.v_cache, rows, box_rows);
   if (rc != 0) return rc;
   const size_t smem = (size_t)Q_BYTES + (NK + NV) * KV_BYTES + 1024;
   static bool opted = false;

@@ -376,8 +376,9 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
     if tc5:
         if q.dtype != torch.bfloat16 or head_dim not in (64, 128):
             raise KernelError("the tcgen05 attention kernel takes bfloat16 and head sizes 64 and 128")
-        # its page loads need pages of 8..128 tokens that divide the key tile of 128; with
-        # other page sizes the mma.sync kernel (same work list, same tile rows) does the tiles
+        # its page loads need pages of 8 tokens or more that divide the key tile of 64 or are a
+        # multiple of it; with other page sizes the mma.sync kernel (same work list, same tile
+        # rows) does the tiles
         tc5 = tc5_attention_applies(head_dim, page_tokens)
         kind = "mma"
     p = AttnParams(
@@ -416,7 +417,8 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
 
 
 def tc5_attention_applies(head_dim: int, page_tokens: int) -> bool:
-    return head_dim in (64, 128) and 8 <= page_tokens <= 128 and page_tokens % 8 == 0 and 128 % page_tokens == 0
+    return head_dim in (64, 128) and page_tokens >= 8 and page_tokens % 8 == 0 and \
+        (64 % page_tokens == 0 or page_tokens % 64 == 0)
 
 
 def tc5_error_flag(device) -> int:
