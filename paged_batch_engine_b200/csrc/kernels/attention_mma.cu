@@ -756,7 +756,7 @@ PBE_EXPORT int pbe_attn_mma_tile_rows() { return BM; }
 PBE_EXPORT int pbe_attn_mma_head_dim() { return HD; }
 
 // params->kinds: bit 0: some row tile has at most 16 packed rows (decoded tokens), bit 1: some
-// has more (prompt portions); neither: unknown, both run.  Bit 2: the step has few requests (at most 16).
+// has more (prompt portions); neither: unknown, both run.  Bit 2: the step has few small row tiles.
 PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, cudaStream_t stream) {
   if (num_work <= 0) return 0;
   AttnParams p = *params;
@@ -776,10 +776,9 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
     if ((long long)num_work * p.num_kv_heads > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
     launch_k(attn_mma_kernel<false>, dim3((unsigned)(num_work * p.num_kv_heads)), NTHREADS, smem_rows, stream, p);
   }
-  // The block-cooperative instance is the shortest path through one work item; it pays while
-  // all of its blocks are resident at once (three a multiprocessor).  With more work items than
-  // that (many requests, or few requests with long contexts and so many key splits) the
-  // persistent warp-private instance streams better.
+  // Bit 2 (set by the host from the number of live work items): few enough small tiles for the
+  // block-cooperative instance, the shortest path through one work item; otherwise the
+  // persistent warp-private instance, which streams better.
   static int sm_count = 0;
   if (sm_count == 0) {
     int dev = 0;
@@ -787,8 +786,7 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const bool few_items = (long long)num_work * p.num_kv_heads <= 3LL * sm_count;
-  if ((kinds & 1) && (kinds & 4) && few_items) {
+  if ((kinds & 1) && (kinds & 4)) {
     // few requests: four warps share every key tile
     const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
     static bool opted_keys = false;

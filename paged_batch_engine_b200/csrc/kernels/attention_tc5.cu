@@ -70,9 +70,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
   const uint32_t addr = smem_u32(bar);
+  uint32_t done;
+  // the common case, the phase is already complete: one probe, no clock read
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+  if (done) return true;
   const long long t0 = clock64();
   for (;;) {
-    uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\n"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
@@ -373,13 +380,26 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const int ts = tile0 + j * BN;
+
+#ifdef PBE_TC5_TRACE   // a debugging build: block 0 records the clock at the phases of its first tiles
+      const bool tr = blockIdx.x == 0 && warp == 2 && lane == 0 && j < 48;
+      if (tr) err[16 + j * 8 + 0] = (int)clock64();
+#endif
       ok = ok && mbar_wait(&s_full[st], (j >> 1) & 1, err);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 1] = (int)clock64();
+#endif
       // this row's 64 scores: both loads in flight, one wait
       float s[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(lane_addr + S_COL + st * BN + c * 32, &s[c * 32]);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 2] = (int)clock64();
+#endif
       const bool full_tile = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
       if (!full_tile) {
 #pragma unroll
@@ -398,6 +418,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         mx3 = fmaxf(mx3, s[i + 3]);
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 3] = (int)clock64();
+#endif
       // the running maximum moves only when it has grown by more than 2^8 in the exponent:
       // until then the old one still keeps every exponential within 256, and O needs no rescale
       float m_new = fmaxf(m_run, mx);
@@ -418,6 +442,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         sum3 += s[i + 3];
       }
       l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 4] = (int)clock64();
+#endif
       // P as bfloat16 over the first 32 columns of the scores it came from (this thread has
       // read its row of them; nobody else touches this lane)
       {
@@ -429,6 +457,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
         tmem_st32_nowait(lane_addr + S_COL + st * BN, &w[0]);
       }
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 5] = (int)clock64();
+#endif
       // the previous tile's P V must be complete before O is rescaled
       if (j > 0) {
         ok = ok && mbar_wait(&o_ready, (j - 1) & 1, err);
@@ -445,6 +477,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           }
         }
       }
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 6] = (int)clock64();
+#endif
       m_run = m_new;
       // values of keys outside the range are zeroed (P is 0 there, but stale pages may hold NaN)
       if (ts < k_begin || ts + BN > k_end) {
@@ -464,6 +500,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
+
+#ifdef PBE_TC5_TRACE
+      if (tr) err[16 + j * 8 + 7] = (int)clock64();
+#endif
     }
     pdl_launch_dependents();
     // ---- epilogue: O / l (or the split's partial result)

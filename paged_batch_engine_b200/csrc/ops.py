@@ -225,7 +225,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
-_tc5_err = {}
+_tc5_err = {}        # per device: the GEMM's flag
+_tc5_attn_err = {}   # per device: the attention kernel's flag (element 0) and room for a debugging trace
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -393,9 +394,9 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=int(getattr(meta, "kinds", 0)))
     if tc5:
         # prompt-portion tiles on the tcgen05 kernel; the decode instances below take the rest
-        err = _tc5_err.get(q.device)
+        err = _tc5_attn_err.get(q.device)
         if err is None:
-            err = _tc5_err[q.device] = torch.zeros(1, dtype=torch.int32, device=q.device)
+            err = _tc5_attn_err[q.device] = torch.zeros(1024, dtype=torch.int32, device=q.device)
         tfn = _fn("attention_tc5", "pbe_attn_tc5", [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_void_p],
                   defines)
         if (p.kinds & 3) == 0 or (p.kinds & 2):
@@ -423,12 +424,12 @@ def tc5_attention_applies(head_dim: int, page_tokens: int) -> bool:
 
 def tc5_error_flag(device) -> int:
     """1 if a bounded wait inside a tcgen05 kernel ran out since the last call (then reset)."""
-    err = _tc5_err.get(torch.device(device))
+    err = _tc5_attn_err.get(torch.device(device))
     if err is None:
         return 0
-    v = int(err.item())
+    v = int(err[0].item())
     if v:
-        err.zero_()
+        err[:1].zero_()
     return v
 
 

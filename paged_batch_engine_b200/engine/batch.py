@@ -35,7 +35,20 @@ def choose_split_keys(num_requests: int) -> int:
 # Steps with at most this many requests run decoded tokens through the block-cooperative
 # instance of the attention kernel (four warps share each key tile: shortest latency per work
 # item); larger steps through the persistent warp-private instance (most bytes in flight).
-DECODE_BLOCK_MAX_REQUESTS = 16
+# The block-cooperative instance of the decode attention kernel (four warps share each key tile)
+# is the shortest path through one work item; it pays while all its blocks (work items x kv
+# heads) are resident at once, three a multiprocessor.  Beyond that the persistent instance,
+# in which every warp streams whole work items, is faster (measured crossover between 256 and
+# 512 items on 148 multiprocessors).
+DECODE_BLOCK_ITEMS_PER_SM = 3
+
+
+def decode_block_max_items(device) -> int:
+    try:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+    except (RuntimeError, AssertionError):
+        sms = 148
+    return DECODE_BLOCK_ITEMS_PER_SM * sms
 
 
 @dataclass
@@ -71,7 +84,9 @@ class AttentionWork:
     tile_rows: int
     part_o: Optional[torch.Tensor] = None
     part_ml: Optional[torch.Tensor] = None
-    kinds: int = 0                  # bit 0: row tiles of at most 16 packed rows exist, bit 1: larger ones
+    kinds: int = 0                  # bit 0: row tiles of at most 16 packed rows exist, bit 1: larger ones,
+    #                                 bit 2: few enough of the small ones for the block-cooperative instance
+    small_items: int = 0            # live work items with at most 16 packed rows
 
 
 def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.ndarray,
@@ -154,17 +169,15 @@ def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.nd
 
 def work_kinds(work: np.ndarray, q_len: np.ndarray, group_size: int, tile_rows: int) -> int:
     """Which instances of the tensor-core attention kernel have work: bit 0 for row tiles of
-    at most 16 packed rows (decoded tokens, tails), bit 1 for larger ones."""
+    at most 16 packed rows (decoded tokens, tails), bit 1 for larger ones; and how many of the
+    small ones there are."""
     live = work[:, 0] >= 0
     if not live.any():
-        return 0
+        return 0, 0
     req = work[live, 0].astype(np.int64)
     rows = np.minimum(tile_rows, q_len[req].astype(np.int64) * group_size - work[live, 1].astype(np.int64) * tile_rows)
     small = rows <= 16
-    kinds = (1 if small.any() else 0) | (2 if (~small).any() else 0)
-    if len(q_len) <= DECODE_BLOCK_MAX_REQUESTS:
-        kinds |= 4
-    return kinds
+    return (1 if small.any() else 0) | (2 if (~small).any() else 0), int(small.sum())
 
 
 class _Packer:
@@ -281,14 +294,14 @@ class StepContext:
         self.state_slots = pk.view(i_state)
         self._groups = [GroupArrays(pk.view(ib), stride, pk.view(isl)) for ib, stride, isl in i_groups]
         self._work: Dict[tuple, AttentionWork] = {}
-        for key, (iw, nw, itsr, ist, isc, ns, max_splits, kinds) in i_work.items():
+        for key, (iw, nw, itsr, ist, isc, ns, max_splits, (kinds, small_items)) in i_work.items():
             g = self._groups[key[0]]
             self._work[key] = AttentionWork(
                 q_start=self.q_start, q_len=self.q_len, seq_len=self.seq_len,
                 block_table=g.block_table, bt_stride=g.bt_stride, work=pk.view(iw), num_work=nw,
                 tok_split_row=pk.view(itsr), split_tokens=pk.view(ist) if ns else None,
                 split_counts=pk.view(isc) if ns else None, num_split_rows=ns, max_splits=max_splits,
-                split_keys=self.split_keys, tile_rows=key[2], kinds=kinds)
+                split_keys=self.split_keys, tile_rows=key[2], kinds=kinds, small_items=small_items)
 
     def group(self, g: int) -> GroupArrays:
         return self._groups[g]
@@ -296,6 +309,8 @@ class StepContext:
     def attention_work(self, group: int, group_size: int, tile_rows: int, window, num_heads: int,
                        head_dim: int) -> AttentionWork:
         w = self._work[(group, group_size, tile_rows, window)]
+        few = w.small_items * (num_heads // group_size) <= decode_block_max_items(self.device)
+        w.kinds = (w.kinds & ~4) | (4 if few else 0)
         if w.num_split_rows and (w.part_o is None or w.part_o.shape[1] != num_heads
                                  or w.part_o.shape[3] != head_dim):
             w.part_o = torch.empty((w.num_split_rows, num_heads, w.max_splits, head_dim),

@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import decode_work_fill
-from .batch import (DECODE_BLOCK_MAX_REQUESTS, AttentionWork, GroupArrays, StepContext, StepEntry,
+from .batch import (AttentionWork, decode_block_max_items, GroupArrays, StepContext, StepEntry,
                     attention_work_arrays, choose_split_keys)
 
 
@@ -96,7 +96,9 @@ class DecodeStepContext(StepContext):
                 block_table=grp.block_table, bt_stride=grp.bt_stride, work=view(f"work{i}"),
                 num_work=B * S, tok_split_row=view(f"tsr{i}"), split_tokens=view(f"st{i}"),
                 split_counts=view(f"sc{i}"), num_split_rows=B, max_splits=S, split_keys=self.split_keys,
-                tile_rows=key[2], kinds=(1 if key[1] <= 16 else 2) | (4 if B <= DECODE_BLOCK_MAX_REQUESTS else 0))
+                tile_rows=key[2], kinds=1 if key[1] <= 16 else 2,
+                # a captured step serves split counts from half its capacity up to all of it
+                small_items=(3 * B * S + 3) // 4)
 
     def _h(self, name):
         v = self._views.get(name)
@@ -152,6 +154,8 @@ class DecodeStepContext(StepContext):
 
     def attention_work(self, group, group_size, tile_rows, window, num_heads, head_dim):
         w = self._work[(group, group_size, tile_rows, window)]
+        few = w.small_items * (num_heads // group_size) <= decode_block_max_items(self.device)
+        w.kinds = (w.kinds & ~4) | (4 if few else 0)
         if w.part_o is None:
             w.part_o = torch.empty((self.batch, num_heads, self.splits, head_dim), dtype=torch.float32,
                                    device=self.device)

@@ -65,10 +65,15 @@ def test_bfloat16_greedy_tokens_are_plain_argmax_up_to_rounding(tiny_folders, na
             assert row.max() - row[tok] <= 0.04 * logits.abs().max(), (name, i)
 
 
-def test_many_requests_at_once(tiny_folders):
-    """Twenty requests decode together (captured steps of 32 rows, the many-requests attention
-    instance); every one must produce what it produces alone."""
+@pytest.mark.parametrize("persistent", [False, True])
+def test_many_requests_at_once(tiny_folders, monkeypatch, persistent):
+    """Twenty requests decode together (captured steps of 32 rows), through either instance of
+    the decode attention kernel (the persistent one is what a step of many work items takes: its
+    threshold is set to zero here); every request must produce what it produces alone."""
     from paged_batch_engine_b200 import SamplingParams
+    from paged_batch_engine_b200.engine import batch
+    if persistent:
+        monkeypatch.setattr(batch, "DECODE_BLOCK_ITEMS_PER_SM", 0)
     cfg, _, page, _ = TINY["C"]
     folder = tiny_folders["C"]
     prompts = prompts_for(cfg["vocab_size"], [3 + 5 * i for i in range(20)], seed=9)

@@ -300,10 +300,12 @@ def test_attention_mma_prompt_tiles_and_mixed_batch():
 
 @pytest.mark.parametrize("H,KV,hd,P,window", [(28, 4, 128, 16, None), (6, 3, 48, 8, 40), (4, 2, 16, 16, None),
                                                (5, 5, 256, 16, None)])
-def test_attention_mma_many_decoding_requests(H, KV, hd, P, window):
-    """More than 16 requests in a step: decoded tokens go through the persistent warp-private
-    instance (one warp streams a whole key split).  Contexts end on and off tile, split and
-    page edges; a few short prompt portions ride along."""
+def test_attention_mma_many_decoding_requests(H, KV, hd, P, window, monkeypatch):
+    """Decoded tokens through the persistent warp-private instance (one warp streams a whole
+    key split), which steps of many work items take: its threshold is set to zero here.
+    Contexts end on and off tile, split and page edges; a few short prompt portions ride along."""
+    from paged_batch_engine_b200.engine import batch
+    monkeypatch.setattr(batch, "DECODE_BLOCK_ITEMS_PER_SM", 0)
     ctxs = [0, 1, 15, 16, 17, 63, 64, 255, 256, 257, 300, 511, 512, 513, 700, 31, 33, 1000, 129, 5]
     reqs = [(c, 1) for c in ctxs] + [(90, 2), (0, 12)]
     case = AttnCase(H, KV, hd, P, window, reqs, torch.bfloat16, seed=hd + len(reqs), kind="mma")
