@@ -198,8 +198,10 @@ PBE_EXPORT int pbe_rope_kv_write(const void* qkv, const float* bias, void* q_out
   if (dtype == PBE_BF16 && !interleaved && inv_freq != nullptr && rotary_dim == head_dim &&
       head_dim % 16 == 0) {
     const int vec_items = (num_heads + num_kv_heads) * (head_dim / 16) + num_kv_heads * (head_dim / 8);
-    int vt = 64;
-    while (vt < 256 && vt < vec_items) vt *= 2;
+    // one pass over the items where a block can hold them (320 at 28 + 4 heads of 128)
+    int vt = ((vec_items + 31) / 32) * 32;
+    if (vt < 64) vt = 64;
+    if (vt > 512) vt = 256;
     launch_k(rope_kv_vec_kernel, num_tokens, vt, head_dim * sizeof(float), stream, p);
     return launch_status();
   }
