@@ -270,6 +270,13 @@ def tc5_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0)
 
 
+def gemm_libraries(dtype: torch.dtype):
+    """The matrix-product libraries a model of this dtype launches (for parallel builds)."""
+    if dtype == torch.float32:
+        return [("sgemm", None)]
+    return [("gemm_skinny", None)] + ([("gemm_tc5", None)] if TC5_MIN_ROWS > 0 else [])
+
+
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (0 < x.shape[0] <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and x.shape[1] % 8 == 0)

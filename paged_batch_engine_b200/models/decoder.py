@@ -59,7 +59,8 @@ class DecoderModel:
             self.lm_head = self.embed     # tied: the head is the embedding table
 
     def kernel_libraries(self):
-        jobs = [("elementwise", None), ("sgemm", None), ("sampling", None)]
+        from ..csrc import ops
+        jobs = [("elementwise", None)] + ops.gemm_libraries(self.dtype)
         for b in self.blocks:
             jobs += b.kernel_libraries(self.dtype)
         seen, out = set(), []

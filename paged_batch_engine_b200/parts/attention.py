@@ -45,7 +45,7 @@ class GQAttention(Mixer):
         return [(self.num_heads // self.num_kv_heads, self.tile_rows, self.window)]
 
     def kernel_libraries(self, dtype):
-        return [("elementwise", None), ("rope_kv", None), ("sgemm", None), ("gemm_skinny", None)] + \
+        return [("elementwise", None), ("rope_kv", None)] + ops.gemm_libraries(dtype) + \
             ops.attention_libraries(self.head_dim, dtype)
 
     # ---- tensors

@@ -21,7 +21,7 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self.w_down = None
 
     def kernel_libraries(self, dtype):
-        return [("elementwise", None), ("sgemm", None), ("gemm_skinny", None), ("gemm_tc5", None)]
+        return [("elementwise", None)] + ops.gemm_libraries(dtype)
 
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size

@@ -144,6 +144,32 @@ def test_schedules_do_not_change_float32_logits_beyond_rounding(tiny_folders):
         assert worst <= 2e-5
 
 
+def test_matrices_stored_in_32_bits_stay_so_in_a_bfloat16_run(tiny_folders, tmp_path):
+    """A checkpoint whose output projection and LM head are stored in float32 beside bfloat16
+    tensors: the bfloat16 run keeps them in float32 (true float32 products for them) and still
+    agrees with the plain implementation; decoded tokens and a prompt portion both."""
+    import shutil
+    from safetensors.torch import load_file, save_file
+    cfg, _, page, _ = TINY["B"]
+    folder = str(tmp_path / "mixed_dtypes")
+    shutil.copytree(tiny_folders["B"], folder)
+    f = os.path.join(folder, "model.safetensors")
+    w = load_file(f)
+    kept = [k for k in w if k.endswith("layers.1.self_attn.o_proj.weight") or k == "lm_head.weight"]
+    assert len(kept) == 2
+    for k in kept:
+        w[k] = w[k].float()
+    save_file(w, f)
+    reqs = requests_for("B", cfg["vocab_size"])
+    want = plain_logits(folder, reqs)
+    runner = make_runner(folder, "bfloat16", page, pool_tokens=256)
+    assert runner.model.lm_head.dtype == torch.float32
+    assert runner.model.blocks[1].mixer.w_o.dtype == torch.float32
+    assert runner.model.blocks[0].mixer.w_o.dtype == torch.bfloat16
+    for label, recs in (("whole", ru.whole(reqs)), ("tail32", ru.tail_decoded(reqs))):
+        check(ru.run_records(runner, recs), want, "bfloat16", f"B/float32 matrices/{label}")
+
+
 def test_trace_run_program(tiny_folders, tmp_path):
     """The program itself, as a user calls it: steps on standard input, <step>.f32 files,
     a ``done`` line after every step, exit code 0."""
