@@ -7,8 +7,9 @@ Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8 from 2,048-
 contexts, timed on the device with CUDA events over K decode steps (each step: one
 host-to-device copy of the step's integers, the captured decode graph, the argmax kernel;
 no host synchronisation between steps).  ``e2e``: the same through ``Engine.step()``, the
-call a user makes: host tokens in, sampled ids read back every step, wall clock between
-synchronisations.  ``prefill``: one step of a 2,048-token prompt.  ``roofline``: bytes a
+call a user makes: host tokens in, sampled ids read back to the host every step (the engine
+launches the next decode step before it reads this one's ids, feeding them on the device),
+wall clock between synchronisations.  ``prefill``: one step of a 2,048-token prompt.  ``roofline``: bytes a
 decode step has to read (every weight once, and the live requests' keys and values)
 divided by its time, against the measured copy bandwidth.  ``points``: decode at batch 1
 and 64.  Weights (15 GB) are far larger than L2 and are streamed once per step, so no L2
@@ -115,6 +116,7 @@ def prepare_decode(engine, batch, context, new_tokens, seed):
             for _ in range(batch)]
     while any(not r.is_decode for r in reqs):
         engine.step()
+        engine.drain()
     return reqs
 
 
@@ -165,7 +167,9 @@ def time_decode_e2e(engine, steps, warmup):
     for _ in range(steps):
         engine.step()
     torch.cuda.synchronize()
-    return (time.perf_counter() - t0) * 1e3 / steps
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    engine.drain()
+    return ms
 
 
 def finish(engine, reqs):

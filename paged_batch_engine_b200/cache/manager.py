@@ -67,6 +67,7 @@ def _host():
             "pbe_cm_num_live": (i32, [vp]),
             "pbe_cm_context_len": (i64, [vp, i64]),
             "pbe_cm_reserved_len": (i64, [vp, i64]),
+            "pbe_cm_max_reserved_len": (i64, [vp, vp, ctypes.c_int]),
             "pbe_cm_num_free_pages": (i32, [vp, i32]),
             "pbe_cm_pool_num_pages": (i32, [vp, i32]),
             "pbe_cm_pool_allocations": (i64, [vp, i32]),
@@ -203,6 +204,15 @@ class CacheManager:
         v = _host().pbe_cm_context_len(self._h, self._handle(handle))
         if v < 0:
             self._raise(int(v), handle)
+        return int(v)
+
+    def max_reserved_len(self, handles: Sequence[int]) -> int:
+        """The longest reserved length (context plus tokens in flight) among the requests."""
+        n = len(handles)
+        arr = (ctypes.c_int64 * max(n, 1))(*[int(h) for h in handles])
+        v = _host().pbe_cm_max_reserved_len(self._h, ctypes.addressof(arr), n)
+        if v < 0:
+            raise CacheError("a request handle of this step is stale or unknown")
         return int(v)
 
     def reserved_len(self, handle: int) -> int:

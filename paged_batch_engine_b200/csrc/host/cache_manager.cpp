@@ -132,6 +132,18 @@ API int64_t pbe_cm_reserved_len(void* h, int64_t handle) {
   Request* r = static_cast<Manager*>(h)->lookup(handle);
   return r ? r->reserved : kStale;
 }
+// The longest reserved length among n requests (one call a decode step instead of one per
+// request): the context a step that fills its reservations will attend over.
+API int64_t pbe_cm_max_reserved_len(void* h, const int64_t* handles, int n) {
+  Manager* m = static_cast<Manager*>(h);
+  int64_t longest = 0;
+  for (int i = 0; i < n; ++i) {
+    Request* r = m->lookup(handles[i]);
+    if (!r) return kStale;
+    if (r->reserved > longest) longest = r->reserved;
+  }
+  return longest;
+}
 API int pbe_cm_num_free_pages(void* h, int g) { return (int)static_cast<Manager*>(h)->pools[g].free_q.size(); }
 API int pbe_cm_pool_num_pages(void* h, int g) { return static_cast<Manager*>(h)->pools[g].num_pages; }
 API int64_t pbe_cm_pool_allocations(void* h, int g) { return static_cast<Manager*>(h)->pools[g].allocations; }
@@ -295,8 +307,9 @@ API int pbe_cm_check(void* h, char* buf, int cap) {
   return 1;
 }
 
-// One decode step's integers for R requests, each bringing one token at position
-// context_len: writes context lengths, state slots, the block-table rows (only entries from
+// One decode step's integers for R requests, each bringing one token at its last reserved
+// position (the context length when the step before it is committed; one more when that step
+// is still in flight and this one was scheduled ahead of it): writes those positions, state slots, the block-table rows (only entries from
 // known[r] on, unless the group is windowed or refresh is set) and the cache slots.
 // bt[g] points at an int32 matrix with row stride bt_stride[g]; known is [n_groups][R].
 // Returns 0, kStale, or kBadArg when a token's page is not held or a row does not fit.
@@ -308,7 +321,9 @@ API int pbe_cm_decode_fill(void* h, int R, const int64_t* handles, int64_t* ctx_
   for (int r = 0; r < R; ++r) {
     Request* req = m->lookup(handles[r]);
     if (!req) return kStale;
-    ctx_before[r] = req->computed;
+    const int64_t pos = req->reserved - 1;
+    if (pos < req->computed) return kBadArg;               // nothing reserved for this step
+    ctx_before[r] = pos;
     state_slots[r] = handles[r] & kSlotMask;
     for (int g = 0; g < G; ++g) {
       const auto& t = req->tables[g];
@@ -319,9 +334,9 @@ API int pbe_cm_decode_fill(void* h, int R, const int64_t* handles, int64_t* ctx_
       const int lo = (refresh || m->windows[g] >= 0) ? 0 : std::min(k, n);
       for (int i = lo; i < n; ++i) row[i] = t[i];
       k = n;
-      const int64_t blk = req->computed / P;
+      const int64_t blk = pos / P;
       if (blk >= n || t[blk] < 0) return kBadArg;
-      slots[g][r] = (int32_t)((int64_t)t[blk] * P + req->computed % P);
+      slots[g][r] = (int32_t)((int64_t)t[blk] * P + pos % P);
     }
   }
   return kOk;

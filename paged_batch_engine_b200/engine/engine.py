@@ -40,7 +40,7 @@ class Engine:
                  kv_cache_memory_utilization: float = 0.80, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 2048, prefill_chunk_cap: int = 512,
                  long_prefill_token_threshold: int = 0, max_model_len: Optional[int] = None,
-                 use_cuda_graphs: bool = True):
+                 use_cuda_graphs: bool = True, decode_ahead: bool = True):
         """``model``: a folder with config.json and safetensors, or a typed configuration /
         config dict, in which case the weights are random from ``seed``.  ``num_pages``:
         pages per layer group; if None the cache takes ``kv_cache_memory_utilization`` of the
@@ -77,6 +77,8 @@ class Engine:
             self.runner.cache, spec.eos_token_ids)
         self.sampler = Sampler(self.device)
         self.use_cuda_graphs = use_cuda_graphs
+        self.decode_ahead = bool(decode_ahead and use_cuda_graphs)   # pipeline decode steps one deep
+        self._pending = None
         self.profile = dict(schedule=0.0, forward=0.0, sample=0.0, process=0.0, steps=0)
 
     # ------------------------------------------------------------------ requests
@@ -91,41 +93,88 @@ class Engine:
         return self.scheduler.add_request(prompt, params)
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_active_requests()
+        return self._pending is not None or self.scheduler.has_active_requests()
 
     # ------------------------------------------------------------------ one step
     def step(self) -> List[Request]:
-        """Runs one scheduler step; returns the requests that finished in it."""
+        """Runs one scheduler step; returns the requests known to have finished.
+
+        Steps of decoded tokens only are pipelined one deep (``decode_ahead``): such a step is
+        launched and left running; the next call first schedules and launches the step after
+        it - its token ids stay on the device, where the running step's sampler leaves them -
+        and only then reads the running step's tokens and does its bookkeeping, so the host's
+        work hides behind the device's.  A request's tokens therefore become known one call
+        later than they are computed; ``drain()`` brings the host up to date."""
         t0 = time.perf_counter()
+        if self._pending is not None:
+            prev, self._pending = self._pending, None
+            ahead = self.scheduler.schedule_ahead(prev[0]) if self.decode_ahead else None
+            if ahead is not None:
+                self._pending = self._launch(ahead, prev[1])
+                self._finish(prev)
+                self.profile["schedule"] += time.perf_counter() - t0
+                self.profile["steps"] += 1
+                return self.scheduler.pop_finished()
+            self._finish(prev)
         out = self.scheduler.schedule_step()
         t1 = time.perf_counter()
-        sampled: List[int] = []
+        self.profile["schedule"] += t1 - t0
+        self.profile["steps"] += 1
         if out.entries:
-            entries = [StepEntry(e.request.handle, e.tokens, [len(e.tokens) - 1] if e.samples else [])
-                       for e in out.entries]
-            rows = [e.request for e in out.entries if e.samples]
-            decode_only = self.use_cuda_graphs and all(len(e.tokens) == 1 and e.samples for e in out.entries)
-            logits = self.runner.step(entries, commit=False, decode_graph=decode_only)
+            launched = self._launch(out, None)
             t2 = time.perf_counter()
-            if rows:
-                sampled = self.sampler.sample(logits, [r.params for r in rows],
-                                              [r.sampling_counter for r in rows],
-                                              [r.tokens if r.params.repetition_penalty != 1.0 else ()
-                                               for r in rows])
+            self.profile["forward"] += t2 - t1
+            if launched[3] is not None and self.decode_ahead:
+                self._pending = launched            # read by the next call, behind the next launch
             else:
-                torch.cuda.current_stream().synchronize()
-        else:
-            t2 = time.perf_counter()
-        t3 = time.perf_counter()
-        self.scheduler.process_outputs(out, sampled)
-        t4 = time.perf_counter()
-        p = self.profile
-        p["schedule"] += t1 - t0
-        p["forward"] += t2 - t1
-        p["sample"] += t3 - t2
-        p["process"] += t4 - t3
-        p["steps"] += 1
+                self._finish(launched)
+                self.profile["sample"] += time.perf_counter() - t2
         return self.scheduler.pop_finished()
+
+    def drain(self) -> List[Request]:
+        """Waits for a step left running by ``step()`` and does its bookkeeping."""
+        if self._pending is not None:
+            prev, self._pending = self._pending, None
+            self._finish(prev)
+        return self.scheduler.pop_finished()
+
+    def _launch(self, out, device_tokens):
+        """Enqueues the step and its sampling.  Returns (out, ids on the device, ids in pinned
+        host memory, event) for a step whose ids are read later, (out, None, ids, None) for one
+        whose ids are already on the host."""
+        entries = [StepEntry(e.request.handle, e.tokens, [len(e.tokens) - 1] if e.samples else [])
+                   for e in out.entries]
+        rows = [e for e in out.entries if e.samples]
+        decode_only = self.use_cuda_graphs and len(rows) == len(entries) and all(len(e.tokens) == 1 for e in rows)
+        logits = self.runner.step(entries, commit=False, decode_graph=decode_only, device_tokens=device_tokens)
+        params = [e.request.params for e in rows]
+        counters = [e.request.sampling_counter if e.counter is None else e.counter for e in rows]
+        later = decode_only and self.decode_ahead and self.runner.graphs is not None and \
+            self.runner.graphs.eligible(entries) and all(p.repetition_penalty == 1.0 for p in params)
+        if device_tokens is not None and not later:
+            raise RuntimeError("a step scheduled ahead must be a captured decode step")
+        if later:
+            dev, host, event = self.sampler.sample_async(logits, params, counters)
+            return out, dev, host, event
+        if rows:
+            ids = self.sampler.sample(logits, params, counters,
+                                      [e.request.tokens if e.request.params.repetition_penalty != 1.0 else ()
+                                       for e in rows])
+        else:
+            torch.cuda.current_stream().synchronize()
+            ids = []
+        return out, None, ids, None
+
+    def _finish(self, launched) -> None:
+        out, _dev, ids, event = launched
+        t0 = time.perf_counter()
+        if event is not None:
+            event.synchronize()
+            ids = ids.tolist()
+        t1 = time.perf_counter()
+        self.scheduler.process_outputs(out, ids)
+        self.profile["sample"] += t1 - t0
+        self.profile["process"] += time.perf_counter() - t1
 
     # ------------------------------------------------------------------ whole requests
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -137,10 +186,10 @@ class Engine:
             raise ValueError("one SamplingParams per prompt, or one for all")
         reqs = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
         finished: Dict[int, Request] = {r.request_id: r for r in self.scheduler.pop_finished()}
-        while self.scheduler.has_active_requests():
+        while self.has_unfinished_requests():
             for r in self.step():
                 finished[r.request_id] = r
-        for r in self.scheduler.pop_finished():
+        for r in self.drain():
             finished[r.request_id] = r
         return [GenerationResult(r.request_id, list(r.prompt), list(r.outputs), r.finish_reason,
                                  r.preemptions) for r in reqs]

@@ -186,14 +186,17 @@ class DecodeGraphs:
 
     def _splits_needed(self, entries, split_keys: int) -> int:
         m = self.runner.cache
-        longest = max(m.context_len(e.handle) for e in entries) + 1
+        longest = m.max_reserved_len([e.handle for e in entries])
         worst = 1
         for _, _, _, window in self.runner._work_keys:
             lo = max(0, longest - 1 - window + 1) if window else 0
             worst = max(worst, (longest + split_keys - 1) // split_keys - lo // split_keys)
         return worst
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``device_tokens`` (int32 on the device, one per entry): the token ids of this step
+        when the host does not know them yet (the step before is still running and they are
+        what it samples); they replace the entries' placeholder ids on the device."""
         runner = self.runner
         R = len(entries)
         B = _bucket(R)
@@ -206,6 +209,8 @@ class DecodeGraphs:
         graph, ctx, logits = self.graphs[key]
         ctx.fill(entries, runner.model.spec.vocab_size)
         self.last_h2d_bytes = ctx._size * 4
+        if device_tokens is not None:
+            ctx.token_ids[:R].copy_(device_tokens[:R], non_blocking=True)
         graph.replay()
         self.replays += 1
         return logits[:R]

@@ -105,11 +105,15 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], commit: bool = True,
-             decode_graph: bool = False) -> torch.Tensor:
+             decode_graph: bool = False, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the entries as one batch; float32 logits [wanted, vocab] on the device.
-        ``decode_graph``: replay a captured CUDA graph when every entry is a single token."""
+        ``decode_graph``: replay a captured CUDA graph when every entry is a single token.
+        ``device_tokens``: the step's token ids as an int32 device tensor (a step scheduled
+        ahead of the one that samples them); captured decode steps only."""
         if decode_graph and self.graphs is not None and self.graphs.eligible(entries):
-            logits = self.graphs.run(entries)
+            logits = self.graphs.run(entries, device_tokens)
+        elif device_tokens is not None:
+            raise ValueError("token ids on the device are taken by captured decode steps only")
         else:
             ctx = StepContext(self.cache, entries, self.device, self._work_keys,
                               vocab_size=self.model.spec.vocab_size)

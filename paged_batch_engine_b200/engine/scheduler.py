@@ -87,6 +87,8 @@ class ScheduledEntry:
     request: Request
     tokens: List[int]
     samples: bool                      # the portion ends the known tokens: its last row is sampled
+    counter: Optional[int] = None      # the request's sampling counter for this row, when it is not
+    #                                    the request's current one (a step scheduled ahead)
 
 
 @dataclass
@@ -112,7 +114,7 @@ class Scheduler:
         self.step_index = 0
         self._next_id = 0
         self.metrics = dict(steps=0, preemptions=0, decode_tokens=0, prefill_tokens=0, no_progress_steps=0,
-                            failed=0)
+                            failed=0, ahead_steps=0, dropped_tokens=0)
 
     # ------------------------------------------------------------------ requests in and out
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
@@ -286,14 +288,58 @@ class Scheduler:
             self.running.remove(req)
             self._fail(req, "prefill_stalled_kv_exhausted")
 
+    # ------------------------------------------------------------------ one step ahead
+    def schedule_ahead(self, prev: SchedulerOutput) -> Optional[SchedulerOutput]:
+        """The step after ``prev`` while ``prev`` still runs on the device and its tokens are
+        not known: possible when ``prev`` is decoded tokens only, nothing waits to be admitted,
+        and every request of ``prev`` goes on whatever it samples now (its length limits are
+        not reached by that token, and sampling needs none of its tokens on the host).  Only an
+        end-of-sequence token cannot be foreseen: a request that stops on ``prev``'s token has
+        one token computed in vain, which ``process_outputs`` drops.  The entries carry
+        placeholder token ids (the step takes them from the device) and keep ``prev``'s order.
+        Returns None when the step cannot be scheduled ahead; nothing is changed then."""
+        if not prev.entries or prev.preempted or self.waiting or len(prev.entries) != len(self.running):
+            return None
+        limit = self.config.max_model_len
+        for e in prev.entries:
+            req, p = e.request, e.request.params
+            if (len(e.tokens) != 1 or not e.samples or req.done or req.status != "running" or req.recompute
+                    or p.repetition_penalty != 1.0 or req.generated + 1 >= p.max_new_tokens
+                    or (limit > 0 and req.target + 1 >= limit)):
+                return None
+        handles = [e.request.handle for e in prev.entries]
+        ok = self.cache.reserve_many(handles, 1)
+        if not all(ok):
+            for h, got in zip(handles, ok):                 # give back what was taken: the usual step decides
+                if got:
+                    self.cache.truncate(h, self.cache.reserved_len(h) - 1)
+            return None
+        self.step_index += 1
+        self.metrics["steps"] += 1
+        self.metrics["ahead_steps"] += 1
+        out = SchedulerOutput()
+        for e in prev.entries:
+            out.entries.append(ScheduledEntry(e.request, [0], True, counter=e.request.sampling_counter + 1))
+        out.num_decode = len(out.entries)
+        self.metrics["decode_tokens"] += out.num_decode
+        return out
+
     # ------------------------------------------------------------------ after the step
     def process_outputs(self, out: SchedulerOutput, sampled: Sequence[int]) -> None:
-        """``sampled``: one token for each entry with ``samples``, in entry order."""
+        """``sampled``: one token for each entry with ``samples``, in entry order.  Entries of
+        requests that ended meanwhile (a step scheduled ahead of the token that stopped them, a
+        cancellation) are dropped with their tokens."""
         it = iter(sampled)
-        if out.entries:
-            self.cache.commit_many([e.request.handle for e in out.entries], [len(e.tokens) for e in out.entries])
+        live = [e for e in out.entries if not e.request.done and e.request.handle is not None]
+        if live:
+            self.cache.commit_many([e.request.handle for e in live], [len(e.tokens) for e in live])
         for e in out.entries:
             req = e.request
+            if req.done or req.handle is None:
+                if e.samples:
+                    next(it, None)
+                    self.metrics["dropped_tokens"] += 1
+                continue
             req.computed += len(e.tokens)
             req.scheduled = 0
             if e.samples:

@@ -19,6 +19,39 @@ class Sampler:
 
     def __init__(self, device):
         self.device = device
+        self._async_slots = []
+        self._async_next = 0
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]):
+        """Launches the sampling of every row and the copy of the ids to pinned host memory;
+        returns (ids on the device, ids on the host, event): the host list is valid once the
+        event has completed.  No row may ask for a repetition penalty (that needs the request's
+        tokens on the host).  Buffers rotate over four steps."""
+        n = logits.shape[0]
+        if any(p.repetition_penalty != 1.0 for p in params):
+            raise ValueError("sample_async does not take a repetition penalty")
+        slot = self._async_slots[self._async_next % len(self._async_slots)] if self._async_slots else None
+        if slot is None or slot[0].numel() < n:
+            cap = max(64, 2 * n)
+            self._async_slots = [(torch.empty(cap, dtype=torch.int32, device=self.device),
+                                  torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                                  torch.cuda.Event()) for _ in range(4)]
+            slot = self._async_slots[0]
+            self._async_next = 0
+        self._async_next += 1
+        dev, host, event = slot
+        if all(p.is_greedy for p in params):
+            ops.argmax(logits, dev[:n])
+        else:
+            floats = np.array([[p.temperature for p in params], [p.top_p for p in params],
+                               [request_sample_uniform(p.seed, c) for p, c in zip(params, counters)]],
+                              dtype=np.float32)
+            fdev = torch.from_numpy(floats).to(self.device)
+            kdev = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
+            ops.sample(logits, fdev[0].contiguous(), kdev, fdev[1].contiguous(), fdev[2].contiguous(), out=dev[:n])
+        host[:n].copy_(dev[:n], non_blocking=True)
+        event.record()
+        return dev[:n], host[:n], event
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
                seen: Sequence[Sequence[int]]) -> List[int]:

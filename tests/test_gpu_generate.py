@@ -49,6 +49,37 @@ def test_greedy_generation_equals_plain(tiny_folders, name):
         assert eng2.generate([p], SamplingParams(max_new_tokens=8, ignore_eos=True))[0].output_tokens == r.output_tokens
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_one_ahead_change_no_token(tiny_folders, dtype):
+    """Decode steps pipelined one deep (the next step launched before this step's tokens are
+    read, its ids fed on the device) against the same engine without the pipeline: greedy and
+    seeded temperature sampling, requests of different lengths, and a request that stops on an
+    end-of-sequence token in the middle (one token is computed in vain and dropped)."""
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["B"]
+    folder = tiny_folders["B"]
+    prompts = prompts_for(cfg["vocab_size"], [3, 11, 26, 7], seed=21)
+    params = [SamplingParams(max_new_tokens=14), SamplingParams(max_new_tokens=9, temperature=0.8, seed=5),
+              SamplingParams(max_new_tokens=20, temperature=1.1, top_k=12, seed=9), SamplingParams(max_new_tokens=17)]
+    plain_run = engine(folder, dtype, page, decode_ahead=False).generate(prompts, params)
+    stop = plain_run[0].output_tokens[5]                  # make request 0 stop there
+    results = []
+    for ahead in (False, True):
+        eng = engine(folder, dtype, page, decode_ahead=ahead)
+        eng.scheduler.eos = {stop}
+        res = eng.generate(prompts, params)
+        results.append([(r.output_tokens, r.finish_reason) for r in res])
+        assert eng.runner.cache.num_live_requests == 0
+        eng.runner.cache.check_invariants()
+        if ahead:
+            assert eng.scheduler.metrics["ahead_steps"] >= 5
+            assert eng.scheduler.metrics["dropped_tokens"] >= 1
+        else:
+            assert eng.scheduler.metrics["ahead_steps"] == 0
+    assert results[0] == results[1]
+    assert results[0][0][1] == "stop" and len(results[0][0][0]) <= 5
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_bfloat16_greedy_tokens_are_plain_argmax_up_to_rounding(tiny_folders, name):
     from paged_batch_engine_b200 import SamplingParams

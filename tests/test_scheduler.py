@@ -191,3 +191,92 @@ def test_uniform_draws_depend_on_seed_and_counter_only():
     p = SamplingParams(temperature=-1, top_p=7, top_k=-3, max_new_tokens=0, min_new_tokens=9).normalized()
     assert (p.temperature, p.top_p, p.top_k, p.max_new_tokens, p.min_new_tokens) == (0.0, 1.0, 0, 1, 1)
     assert p.is_greedy and not SamplingParams(top_k=5).is_greedy
+
+
+def drive_ahead(s, token_fn, max_steps=500):
+    """As the engine pipelines decode steps: the step after a running one is scheduled before
+    the running one's tokens are processed, whenever the scheduler allows it."""
+    log, pending = [], None
+    for _ in range(max_steps):
+        if pending is None and not s.has_active_requests():
+            break
+        if pending is not None:
+            ahead = s.schedule_ahead(pending)
+            s.process_outputs(pending, [token_fn(e.request) for e in pending.entries if e.samples])
+            s.cache.check_invariants()
+            pending = ahead
+            if ahead is not None:
+                log.append(("ahead", [e.request.request_id for e in ahead.entries]))
+                continue
+        out = s.schedule_step()
+        log.append(("step", [(e.request.request_id, len(e.tokens)) for e in out.entries]))
+        pending = out if out.entries else None
+    assert not s.has_active_requests()
+    return log
+
+
+def test_decode_steps_scheduled_one_ahead_give_the_same_tokens():
+    """Two requests decode together; steps are scheduled ahead until a length limit is one
+    token away, an end-of-sequence token drops the token computed in vain, and counters,
+    outputs and pages end as without the pipeline."""
+    outs = []
+    for ahead in (False, True):
+        m, s = make()
+        script = {0: iter([5, 6, 99, 1, 1, 1]), 1: iter(range(10, 40))}
+        a = s.add_request([1, 2, 3], SamplingParams(max_new_tokens=6))              # stops on 99 (EOS) as 3rd token
+        b = s.add_request([4, 5], SamplingParams(max_new_tokens=7, ignore_eos=True))
+        fn = lambda req: next(script[req.request_id])
+        log = drive_ahead(s, fn) if ahead else drive(s, fn)
+        outs.append((a.outputs, a.finish_reason, a.sampling_counter, b.outputs, b.finish_reason, b.sampling_counter))
+        assert m.num_live_requests == 0 and m.num_free_pages() == 64
+        if ahead:
+            assert s.metrics["ahead_steps"] >= 3
+            assert s.metrics["dropped_tokens"] == 1            # a's token after its end-of-sequence
+            assert any(kind == "ahead" for kind, _ in log)
+    # the scripted sampler hands a one more token in the pipelined run (the dropped one), so b's
+    # tokens are the same and a's are cut at the same place
+    assert outs[0][:3] == outs[1][:3] == ([5, 6], "stop", 3)
+    assert outs[0][3:] == outs[1][3:] and len(outs[0][3]) == 7
+
+
+def test_nothing_is_scheduled_ahead_when_it_could_be_wrong():
+    m, s = make(pages=3, page=4)
+    r = s.add_request([1, 2, 3], SamplingParams(max_new_tokens=50, ignore_eos=True))
+    o = s.schedule_step()
+    assert s.schedule_ahead(o) is None                         # a prompt portion: not a decode step
+    s.process_outputs(o, [7])
+    o = s.schedule_step()                                      # first decode step (position 3)
+    assert [len(e.tokens) for e in o.entries] == [1]
+    w = s.add_request([9], SamplingParams(max_new_tokens=2))
+    assert s.schedule_ahead(o) is None                         # a request waits to be admitted
+    s.cancel(w)
+    s.pop_finished()
+    nxt = s.schedule_ahead(o)
+    assert nxt is not None and nxt.entries[0].counter == r.sampling_counter + 1
+    assert m.reserved_len(r.handle) == m.context_len(r.handle) + 2
+    s.process_outputs(o, [7])
+    s.process_outputs(nxt, [7])
+    assert r.outputs == [7, 7, 7] and r.sampling_counter == 3 and m.context_len(r.handle) == 5
+    # pages: 3 x 4 tokens; at 11 tokens reserved the next step ahead finds no page and gives back
+    # what it took, the usual step then preempts or fails as it decides
+    while True:
+        o = s.schedule_step()
+        if not o.entries:
+            break
+        before = m.reserved_len(r.handle)
+        nxt = s.schedule_ahead(o)
+        if nxt is None:
+            assert m.reserved_len(r.handle) == before
+            s.process_outputs(o, [7])
+            if r.done:
+                break
+            continue
+        s.process_outputs(o, [7])
+        s.process_outputs(nxt, [7])
+    m.check_invariants()
+    p = SamplingParams(max_new_tokens=3, repetition_penalty=1.3)
+    m2, s2 = make()
+    q = s2.add_request([1, 2], p)
+    o = s2.schedule_step(); s2.process_outputs(o, [7])
+    o = s2.schedule_step()
+    assert s2.schedule_ahead(o) is None                        # the penalty needs the tokens on the host
