@@ -7,6 +7,8 @@
 (seeded), prompts read in portions of 512 beside the decoding requests, 256 new tokens each.
 ``14b``: the Qwen2.5-14B shape, 8 prompts of 8,192 tokens, then 512 new tokens each.
 ``7b``: the Qwen2.5-7B shape under the 1.5b workload.
+``prompt-sweep``: one prompt of 128 .. 32,768 tokens, whole or in portions, through the model
+runner (8 layers of the 7B shape unless --layers says otherwise).
 
 Everything goes through ``Engine.generate``: admission, portions under the token budget,
 mixed steps of prompt portions beside decoded tokens, sampling (greedy), finishing.  Prints
@@ -40,15 +42,61 @@ SHAPES = {
 }
 
 
+def prompt_sweep(layers):
+    """One prompt of several lengths, whole or in portions, through ``ModelRunner.step`` (the
+    Qwen2.5-7B shape with ``layers`` layers); CUDA-event time of the whole prompt, median of 3."""
+    import torch
+    from paged_batch_engine_b200 import Engine
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    cfg = dict(SHAPES["7b"])
+    layers_full = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers or 8
+    _, typed = load_config(cfg)
+    eng = Engine(typed, dtype="bfloat16", seed=0, page_size=16, num_pages=2200, max_num_seqs=4,
+                 max_num_batched_tokens=40000, prefill_chunk_cap=40000, max_model_len=34000)
+    runner, cache = eng.runner, eng.runner.cache
+    g = torch.Generator().manual_seed(0)
+    d, L, H, KV = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd, inter = d // H, cfg["intermediate_size"]
+    lin = 2 * L * ((H + 2 * KV) * hd * d + d * H * hd + 3 * inter * d)
+    rows = []
+    for total, chunk in ((128, 128), (512, 512), (2048, 2048), (2048, 512), (8192, 8192), (8192, 2048),
+                         (8192, 512), (32768, 8192), (32768, 2048)):
+        times = []
+        for _ in range(3):
+            prompt = torch.randint(0, 1000, (total,), generator=g).tolist()
+            h = cache.add_request()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for lo in range(0, total, chunk):
+                n = min(chunk, total - lo)
+                assert cache.reserve(h, n)
+                runner.step([StepEntry(h, prompt[lo:lo + n], [n - 1] if lo + n == total else [])])
+            stop.record()
+            torch.cuda.synchronize()
+            cache.free(h)
+            times.append(start.elapsed_time(stop))
+        ms = sorted(times)[1]
+        flops = lin * total + 2 * 2 * H * hd * L * (total * (total + 1) // 2)
+        rows.append({"tokens": total, "portion": chunk, "ms": round(ms, 2), "tok_per_s": round(total / ms * 1e3),
+                     "tflops": round(flops / ms / 1e9)})
+    print(json.dumps({"metric": "prompt tok/s over prompt lengths and portion sizes, Qwen2.5-7B shape",
+                      "layers": L, "layers_full_model": layers_full, "dtype": "bf16", "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="1.5b", choices=sorted(SHAPES))
+    ap.add_argument("--workload", default="1.5b", choices=sorted(SHAPES) + ["prompt-sweep"])
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--new-tokens", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (named in the line)")
     ap.add_argument("--max-batched-tokens", type=int, default=0)
     ap.add_argument("--prefill-chunk", type=int, default=0)
     args = ap.parse_args()
+    if args.workload == "prompt-sweep":
+        return prompt_sweep(args.layers)
 
     import torch
     from paged_batch_engine_b200 import Engine, SamplingParams
