@@ -80,6 +80,30 @@ def test_decode_steps_one_ahead_change_no_token(tiny_folders, dtype):
     assert results[0][0][1] == "stop" and len(results[0][0][0]) <= 5
 
 
+def test_cancelling_a_request_while_its_step_runs(tiny_folders):
+    """A request is cancelled while a decode step that holds it is still running (pipelined
+    steps): its token is dropped, its pages go back, the others go on unchanged."""
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    prompts = prompts_for(cfg["vocab_size"], [6, 13, 4], seed=4)
+    sp = SamplingParams(max_new_tokens=12, ignore_eos=True)
+    want = engine(folder, "float32", page).generate(prompts, sp)
+    eng = engine(folder, "float32", page)
+    reqs = [eng.add_request(p, sp) for p in prompts]
+    while len(reqs[1].outputs) < 4:
+        eng.step()
+    assert eng._pending is not None                        # a decode step is in flight
+    eng.scheduler.cancel(reqs[1])
+    while eng.has_unfinished_requests():
+        eng.step()
+    eng.drain()
+    assert reqs[1].finish_reason == "cancelled" and reqs[1].outputs == want[1].output_tokens[:len(reqs[1].outputs)]
+    assert reqs[0].outputs == want[0].output_tokens and reqs[2].outputs == want[2].output_tokens
+    assert eng.runner.cache.num_live_requests == 0
+    eng.runner.cache.check_invariants()
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_bfloat16_greedy_tokens_are_plain_argmax_up_to_rounding(tiny_folders, name):
     from paged_batch_engine_b200 import SamplingParams
