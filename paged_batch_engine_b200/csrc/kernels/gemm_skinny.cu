@@ -68,10 +68,9 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 template <int NT> struct Stages { static constexpr int value = NT == 1 ? 8 : 6; };
 
 // NT: batch tiles of 8 rows (M <= 8 * NT).  A block has WN x WK warps: WN weight-row tiles by
-// WK slices of K.  CL blocks form a thread-block cluster that shares one set of row tiles
+// WK slices of K.  CL blocks may form a thread-block cluster that shares one set of row tiles
 // and splits K CL * WK ways; block 1 hands its partial sums to block 0 through distributed
-// shared memory.  Small matrices use CL = 2 with four warps a block, so that there are enough
-// blocks to fill every SM evenly while all of them are resident at once.
+// shared memory (the launcher below uses CL = 1: it measured no better with clusters).
 //
 // Every thread owns a ring of STAGES slots in shared memory, one slot per block of 32 k:
 // its two 16-byte weight chunks and its NT activation chunks.  cp.async fills the slots
@@ -256,9 +255,13 @@ int launch_cfg(const SkinnyParams& p, int row_blocks, cudaStream_t stream) {
 
 template <int NT, bool SWIGLU, typename TY>
 int launch(const SkinnyParams& p, cudaStream_t stream) {
+  // Arrangements measured on the decode shapes of the 7B model (M = 8, in the captured step):
+  // big matrices (gate/up, LM head): two row tiles by four K slices a block; small ones (QKV,
+  // O, down): one row tile by four K slices, four warps a block, no cluster (a cluster of two
+  // that splits K eight ways was slower by 10 % alone and equal in the step).
   const int tiles = p.tiles;
-  if (tiles >= 148 * 8) return launch_cfg<NT, 4, 2, 1, SWIGLU, TY>(p, (tiles + 3) / 4, stream);
-  return launch_cfg<NT, 1, 4, 2, SWIGLU, TY>(p, tiles, stream);
+  if (tiles >= 148 * 8) return launch_cfg<NT, 2, 4, 1, SWIGLU, TY>(p, (tiles + 1) / 2, stream);
+  return launch_cfg<NT, 1, 4, 1, SWIGLU, TY>(p, tiles, stream);
 }
 }  // namespace
 
