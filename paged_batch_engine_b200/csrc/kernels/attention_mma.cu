@@ -18,6 +18,7 @@
 //
 // Softmax statistics are float32; exponentials are exp2f with log2(e) folded into the
 // score scale.  Compile with -DPBE_HEAD_DIM=<multiple of 16, at most 256>.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 #include "attention_params.cuh"
@@ -300,18 +301,31 @@ __device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, c
   }
 }
 
-// KEYS = false: rows mode, row tiles of more than 16 packed rows (prompt portions).
-// KEYS = true: keys mode, row tiles of at most 16 packed rows (decoded tokens); only 16 query
+// MODE 0: rows mode, row tiles of more than 16 packed rows (prompt portions).
+// MODE 1: keys mode, row tiles of at most 16 packed rows (decoded tokens); only 16 query
 // rows are staged, so that three blocks fit on an SM.  Each instance skips the other's work.
-template <bool KEYS>
-__global__ void __launch_bounds__(NTHREADS, KEYS ? (HD <= 128 ? 3 : 1) : (HD <= 128 ? 2 : 1))
-attn_mma_kernel(AttnParams p) {
+// MODE 2: keys mode for steps of decoded tokens only, fused with what comes before and after
+// it: a cluster of FUSED_SPLITS blocks owns one (request, key/value head); every block takes
+// the query heads of the group straight from the fused QKV projection (bias and rotary
+// position encoding applied here), the block whose key range holds the new token also writes
+// its key and value into the cache, and the partial results of the cluster's blocks are merged
+// through distributed shared memory, each block one slice of the head dimension.  One launch
+// stands for three (position encoding and cache write, attention, merge of the splits).
+constexpr int FUSED_SPLITS = 8;
+
+// NST: key/value tiles in shared memory (two everywhere; the fused mode also has an instance
+// with three, two blocks a multiprocessor, for steps small enough to be resident that way).
+template <int MODE, int NST = 2>
+__global__ void __launch_bounds__(NTHREADS, MODE != 0 ? (HD <= 128 ? (NST == 2 ? 3 : 2) : 1) : (HD <= 128 ? 2 : 1))
+attn_mma_kernel(AttnParams p, AttnFusedParams f) {
+  constexpr bool KEYS = MODE != 0;
+  constexpr bool FUSED = MODE == 2;
   constexpr int QROWS = KEYS ? 16 : BM;
   constexpr int BN = KEYS ? BN_KEYS : BN_ROWS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [QROWS][LDS]
-  bf16* Ks = Qs + QROWS * LDS;                         // [2][BN][LDS]
-  bf16* Vs = Ks + 2 * BN * LDS;                        // [2][BN][LDS]
+  bf16* Ks = Qs + QROWS * LDS;                         // [NST][BN][LDS]
+  bf16* Vs = Ks + NST * BN * LDS;                      // [NST][BN][LDS]
   __shared__ int s_pages[MAX_SMEM_PAGES];
 
   // The work list, the lengths and the block tables are written by the host before the
@@ -319,20 +333,35 @@ attn_mma_kernel(AttnParams p) {
   // rows mode: a one-dimensional grid, work-major, so that the heavy tiles at the head of
   // the work list start first for every key/value head
   const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
-  const int32_t* work = p.work + (size_t)(KEYS ? blockIdx.x : blockIdx.x / KV) * 4;
-  const int r = work[0];
-  if (r < 0) {
-    pdl_wait();
-    pdl_launch_dependents();
-    return;
+  int r, m_tile, split, nsplit, kvh;
+  if constexpr (FUSED) {
+    // grid (FUSED_SPLITS, requests, kv heads), clusters along x: no work list
+    r = blockIdx.y;
+    m_tile = 0;
+    split = blockIdx.x;
+    nsplit = FUSED_SPLITS;
+    kvh = blockIdx.z;
+    if (p.q_len[r] != 1) {      // an idle row of a captured step: the whole cluster leaves
+      pdl_wait();
+      pdl_launch_dependents();
+      return;
+    }
+  } else {
+    const int32_t* work = p.work + (size_t)(KEYS ? blockIdx.x : blockIdx.x / KV) * 4;
+    r = work[0];
+    if (r < 0) {
+      pdl_wait();
+      pdl_launch_dependents();
+      return;
+    }
+    m_tile = work[1], split = work[2], nsplit = work[3];
+    kvh = KEYS ? blockIdx.y : blockIdx.x % KV;
   }
-  const int m_tile = work[1], split = work[2], nsplit = work[3];
-  const int kvh = KEYS ? blockIdx.y : blockIdx.x % KV;
   const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
   const int pr0 = m_tile * BM;
   const int rows_here = min(BM, n_packed - pr0);
-  if (rows_here <= 0 || (rows_here <= 16) != KEYS) {   // nothing here, or the other instance's work
+  if (!FUSED && (rows_here <= 0 || (rows_here <= 16) != KEYS)) {   // nothing here, or the other instance's work
     pdl_wait();
     pdl_launch_dependents();
     return;
@@ -343,7 +372,14 @@ attn_mma_kernel(AttnParams p) {
   const int hi_key = pos0 + row_hi + 1;
   const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
   int k_begin = lo_key, k_end = hi_key;
-  if (nsplit > 1) {
+  int fused_kps = 0;
+  if constexpr (FUSED) {
+    // the request's own length decides its split size: its keys in FUSED_SPLITS equal parts,
+    // rounded up to whole key tiles
+    fused_kps = max(BN, ((hi_key - lo_key + FUSED_SPLITS * BN - 1) / (FUSED_SPLITS * BN)) * BN);
+    k_begin = min(hi_key, lo_key + split * fused_kps);
+    k_end = min(hi_key, lo_key + (split + 1) * fused_kps);
+  } else if (nsplit > 1) {
     const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int s0 = lo_req / p.split_keys;
     k_begin = max(lo_key, (s0 + split) * p.split_keys);
@@ -355,14 +391,16 @@ attn_mma_kernel(AttnParams p) {
   const bf16* vc = (const bf16*)p.v_cache;
   const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
 
-  pdl_wait();
-  // Q tile -> shared (rows beyond the request are zeros)
-  for (int c = tid; c < QROWS * CPR; c += NTHREADS) {
-    const int i = c / CPR, col = c - i * CPR;
-    const int pr = pr0 + i;
-    const bool valid = pr < n_packed;
-    const int row = valid ? pr / G : 0, hg = valid ? pr - row * G : 0;
-    cp_async16(Qs + i * LDS + col * 8, q + ((size_t)(qs + row) * H + kvh * G + hg) * HD + col * 8, valid);
+  if constexpr (!FUSED) {
+    pdl_wait();
+    // Q tile -> shared (rows beyond the request are zeros)
+    for (int c = tid; c < QROWS * CPR; c += NTHREADS) {
+      const int i = c / CPR, col = c - i * CPR;
+      const int pr = pr0 + i;
+      const bool valid = pr < n_packed;
+      const int row = valid ? pr / G : 0, hg = valid ? pr - row * G : 0;
+      cp_async16(Qs + i * LDS + col * 8, q + ((size_t)(qs + row) * H + kvh * G + hg) * HD + col * 8, valid);
+    }
   }
   const int tile0 = (k_begin / BN) * BN;
   const int n_tiles = k_end > tile0 ? (k_end - tile0 + BN - 1) / BN : 0;
@@ -400,8 +438,87 @@ attn_mma_kernel(AttnParams p) {
     }
   };
 
-  if (n_tiles > 0) load_tile(tile0, 0);
-  cp_async_commit();
+  if constexpr (FUSED) {
+    // The keys and values of earlier tokens do not depend on the kernel before this one: the
+    // first key tile is requested before the wait, unless it is the one that holds the new
+    // token (whose key and value this block writes below).
+    const int pos = sl - 1;
+    const bool owner = pos >= k_begin && pos < k_end;
+    const int slot = f.slots[qs];
+    const float posf = (float)f.positions[qs];
+    int issued = 0;                                            // key tiles requested so far, one group each
+    for (; issued < NST - 1 && issued < n_tiles; ++issued) {
+      if (owner && tile0 + (issued + 1) * BN > pos) break;     // the tile with the new token: after the write
+      load_tile(tile0 + issued * BN, issued);
+      cp_async_commit();
+    }
+    pdl_wait();
+    // The new token's query heads (and, in the owner block, its key and value) from the fused
+    // projection: bias, rotary position encoding (pairs i, i + hd/2; angle, sine, cosine and
+    // rotation in float32, one rounding), as rope_kv.cu does.
+    constexpr int HALF = HD / 2;
+    float* trig = reinterpret_cast<float*>(Ks + (NST - 1) * BN * LDS);   // the last buffer: filled last
+    float* qraw = trig + HD;                                          // [G][HD] biased query heads
+    float* kvraw = qraw + 16 * HD;                                    // [2][HD] biased key and value
+    for (int i = tid; i < HALF; i += NTHREADS) sincosf(posf * f.inv_freq[i], &trig[HALF + i], &trig[i]);
+    const int row_width = (H + 2 * KV) * HD;
+    const bf16* in = (const bf16*)f.qkv + (size_t)qs * row_width;
+    const int chunks_q = G * CPR, chunks_kv = owner ? 2 * CPR : 0;
+    for (int c = tid; c < chunks_q + chunks_kv; c += NTHREADS) {
+      int col;
+      float* dst;
+      if (c < chunks_q) {
+        col = kvh * G * HD + c * 8;
+        dst = qraw + c * 8;
+      } else {
+        const int kc_ = c - chunks_q, which = kc_ / CPR, i8 = kc_ - which * CPR;
+        col = (H + which * KV + kvh) * HD + i8 * 8;
+        dst = kvraw + which * HD + i8 * 8;
+      }
+      const uint4 raw = *reinterpret_cast<const uint4*>(in + col);
+      const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+        dst[2 * e] = v.x + (f.bias ? f.bias[col + 2 * e] : 0.f);
+        dst[2 * e + 1] = v.y + (f.bias ? f.bias[col + 2 * e + 1] : 0.f);
+      }
+    }
+    __syncthreads();
+    for (int it = tid; it < 16 * HALF; it += NTHREADS) {
+      const int hg = it / HALF, i = it - hg * HALF;
+      float ra = 0.f, rb = 0.f;
+      if (hg < G) {
+        const float a = qraw[hg * HD + i], b = qraw[hg * HD + i + HALF];
+        const float c = trig[i], sn = trig[HALF + i];
+        ra = a * c - b * sn;
+        rb = b * c + a * sn;
+      }
+      Qs[hg * LDS + i] = __float2bfloat16_rn(ra);
+      Qs[hg * LDS + i + HALF] = __float2bfloat16_rn(rb);
+    }
+    if (owner) {
+      const int page = slot / P, off = slot - page * P;
+      bf16* kdst = (bf16*)p.k_cache + (((size_t)page * KV + kvh) * P + off) * HD;
+      bf16* vdst = (bf16*)p.v_cache + (((size_t)page * KV + kvh) * P + off) * HD;
+      for (int i = tid; i < HALF; i += NTHREADS) {
+        const float a = kvraw[i], b = kvraw[i + HALF];
+        const float c = trig[i], sn = trig[HALF + i];
+        kdst[i] = __float2bfloat16_rn(a * c - b * sn);
+        kdst[i + HALF] = __float2bfloat16_rn(b * c + a * sn);
+      }
+      for (int i = tid; i < HD; i += NTHREADS) vdst[i] = __float2bfloat16_rn(kvraw[HD + i]);
+      __threadfence();          // the tile loads read the new key and value back from memory
+    }
+    __syncthreads();            // Q is complete, the scratch is free, the new key and value are written
+    for (; issued < NST - 1; ++issued) {
+      if (issued < n_tiles) load_tile(tile0 + issued * BN, issued);
+      cp_async_commit();
+    }
+  } else {
+    if (n_tiles > 0) load_tile(tile0, 0);
+    cp_async_commit();
+  }
 
   // rows of this thread's fragments: one 16-row fragment in keys mode, two in rows mode
   constexpr int MT = (KEYS || HD > 128) ? 1 : 2;
@@ -448,12 +565,12 @@ attn_mma_kernel(AttnParams p) {
 
   for (int t = 0; t < n_tiles; ++t) {
     const int ts = tile0 + t * BN;
-    if (t + 1 < n_tiles) load_tile(ts + BN, (t + 1) & 1);
+    if (t + NST - 1 < n_tiles) load_tile(ts + (NST - 1) * BN, (t + NST - 1) % NST);
     cp_async_commit();
-    cp_async_wait<1>();          // tile t (and Q) have landed
+    cp_async_wait<NST - 1>();    // tile t (and Q) have landed
     __syncthreads();
-    const bf16* kt = Ks + (t & 1) * BN * LDS;
-    const bf16* vt = Vs + (t & 1) * BN * LDS;
+    const bf16* kt = Ks + (t % NST) * BN * LDS;
+    const bf16* vt = Vs + (t % NST) * BN * LDS;
     if constexpr (KEYS) {
       const int key0 = ts + warp * 16;
       const bool interior = key0 >= k_begin && key0 + 16 <= k_end && key0 + 15 <= pos_min && key0 >= lo_max;
@@ -475,7 +592,7 @@ attn_mma_kernel(AttnParams p) {
           process_tile<BN / 8, true>(Qw, kt, vt, 0, ts, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
       }
     }
-    __syncthreads();             // everyone is done with buffer t & 1 before it is refilled
+    __syncthreads();             // everyone is done with this buffer before it is refilled
   }
   cp_async_wait<0>();
   pdl_launch_dependents();      // the keys and values are read: the next kernel may start launching
@@ -519,7 +636,16 @@ attn_mma_kernel(AttnParams p) {
       const int qrow = pr / G, hg = pr - qrow * G;
       const int head = kvh * G + hg;
       const int tok = qs + qrow;
-      if (nsplit <= 1) {
+      if constexpr (FUSED) {
+        // this block's result for the cluster's merge: after the four warps' partial sums
+        float* cl_o = reinterpret_cast<float*>(Vs);        // [16][HD]
+        float* cl_ml = cl_o + 16 * HD;                       // [16][2]
+        cl_o[row * HD + d] = acc;
+        if (d == 0) {
+          cl_ml[row * 2] = mm;
+          cl_ml[row * 2 + 1] = ll;
+        }
+      } else if (nsplit <= 1) {
         ((bf16*)p.out)[((size_t)tok * H + head) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
       } else {
         const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
@@ -529,6 +655,44 @@ attn_mma_kernel(AttnParams p) {
           p.part_ml[base * 2 + 1] = ll;
         }
       }
+    }
+    if constexpr (FUSED) {
+      // merge across the cluster: every block combines one slice of the head dimension of all
+      // blocks' partial results, read through distributed shared memory
+      namespace cg = cooperative_groups;
+      cg::cluster_group cluster = cg::this_cluster();
+      float* cl_o = reinterpret_cast<float*>(Vs);
+      float* cl_ml = cl_o + 16 * HD;
+      cluster.sync();
+      constexpr int SLICE = (HD + FUSED_SPLITS - 1) / FUSED_SPLITS;
+      const int d0 = split * SLICE;
+      for (int idx = tid; idx < rows_here * SLICE; idx += NTHREADS) {
+        const int row = idx / SLICE, d = d0 + (idx - row * SLICE);
+        if (d >= HD) continue;
+        float ms[FUSED_SPLITS], ls[FUSED_SPLITS], os[FUSED_SPLITS];
+        float mm = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < FUSED_SPLITS; ++s) {
+          const float* ro = cluster.map_shared_rank(cl_o, s);
+          const float* rml = cluster.map_shared_rank(cl_ml, s);
+          ms[s] = rml[row * 2];
+          ls[s] = rml[row * 2 + 1];
+          os[s] = ro[row * HD + d];
+          mm = fmaxf(mm, ms[s]);
+        }
+        float ll = 0.f, acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < FUSED_SPLITS; ++s) {
+          if (ms[s] != -INFINITY) {
+            const float w = exp2f(ms[s] - mm);
+            ll += ls[s] * w;
+            acc += os[s] * w;
+          }
+        }
+        const int head = kvh * G + row;                    // one query row: packed row == head of the group
+        ((bf16*)p.out)[((size_t)qs * H + head) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      }
+      cluster.sync();           // nobody leaves while its shared memory may still be read
     }
     return;
   }
@@ -766,7 +930,7 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
   const size_t smem_rows = sizeof(bf16) * (size_t)(BM + 4 * BN_ROWS) * LDS;
   static bool opted = false;
   if (!opted) {
-    cudaFuncSetAttribute(attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
+    cudaFuncSetAttribute(attn_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
     opted = true;
   }
   dim3 grid(num_work, p.num_kv_heads);
@@ -774,7 +938,8 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
   // bit 3: the prompt-portion tiles are computed by another kernel (attention_tc5.cu)
   if ((kinds & 2) && !(kinds & 8)) {
     if ((long long)num_work * p.num_kv_heads > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-    launch_k(attn_mma_kernel<false>, dim3((unsigned)(num_work * p.num_kv_heads)), NTHREADS, smem_rows, stream, p);
+    launch_k(attn_mma_kernel<0>, dim3((unsigned)(num_work * p.num_kv_heads)), NTHREADS, smem_rows, stream, p,
+             AttnFusedParams{});
   }
   // Bit 2 (set by the host from the number of live work items): few enough small tiles for the
   // block-cooperative instance, the shortest path through one work item; otherwise the
@@ -791,10 +956,10 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
     const size_t smem_keys = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
     static bool opted_keys = false;
     if (!opted_keys) {
-      cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+      cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
       opted_keys = true;
     }
-    launch_k(attn_mma_kernel<true>, grid, NTHREADS, smem_keys, stream, p);
+    launch_k(attn_mma_kernel<1>, grid, NTHREADS, smem_keys, stream, p, AttnFusedParams{});
   } else if (kinds & 1) {
     const size_t smem_dec = sizeof(bf16) * (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_KEYS * LDS;
     static int dec_blocks = 0;
@@ -806,5 +971,43 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
     const int blocks = min(dec_blocks, (items + DEC_WARPS - 1) / DEC_WARPS);
     launch_k(attn_decode_kernel, blocks, DEC_WARPS * 32, smem_dec, stream, p, num_work);
   }
+  return launch_status();
+}
+
+// A step of decoded tokens only, one launch for position encoding, cache write, attention and
+// the merge of the key splits (MODE 2 above).  The key range of a request may span at most
+// FUSED_SPLITS * 512 keys; the caller keeps longer contexts and large batches on the other path.
+PBE_EXPORT int pbe_attn_decode_fused_max_keys() { return FUSED_SPLITS * 512; }
+PBE_EXPORT int pbe_attn_decode_fused_splits() { return FUSED_SPLITS; }
+PBE_EXPORT int pbe_attn_decode_fused(const AttnParams* params, const AttnFusedParams* fused, int dtype,
+                                     cudaStream_t stream) {
+  AttnParams p = *params;
+  AttnFusedParams f = *fused;
+  if (f.num_requests <= 0) return 0;
+  if (dtype != PBE_BF16 || p.num_heads % p.num_kv_heads != 0 || p.num_heads / p.num_kv_heads > 16 ||
+      f.qkv == nullptr || f.inv_freq == nullptr || f.slots == nullptr || f.positions == nullptr ||
+      f.num_requests > 65535 || p.num_kv_heads > 65535)
+    return (int)cudaErrorInvalidValue;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const size_t smem2 = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
+  const size_t smem3 = sizeof(bf16) * (size_t)(16 + 6 * BN_KEYS) * LDS;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(attn_mma_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    if (HD <= 128) cudaFuncSetAttribute(attn_mma_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+    opted = true;
+  }
+  const dim3 grid(FUSED_SPLITS, f.num_requests, p.num_kv_heads);
+  // three key tiles in flight where all blocks are resident two a multiprocessor, else two
+  if (HD <= 128 && (long long)FUSED_SPLITS * f.num_requests * p.num_kv_heads <= 2LL * sm_count)
+    launch_k_cluster(attn_mma_kernel<2, 3>, grid, NTHREADS, smem3, stream, FUSED_SPLITS, p, f);
+  else
+    launch_k_cluster(attn_mma_kernel<2, 2>, grid, NTHREADS, smem2, stream, FUSED_SPLITS, p, f);
   return launch_status();
 }

@@ -26,6 +26,18 @@ struct AttnParams {
                             // bit 2: few requests, small tiles go to the block-cooperative instance
 };
 
+// What the fused decode kernel needs beyond AttnParams: it applies the bias and the rotary
+// position encoding to the new token's query, key and value itself, writes the key and value
+// into the cache, and merges its key splits inside a thread-block cluster.
+struct AttnFusedParams {
+  const void* qkv;            // [T, (H + 2*KV) * hd] the fused projection's output
+  const float* bias;          // [(H + 2*KV) * hd] or null
+  const int32_t* positions;   // [T]
+  const int32_t* slots;       // [T]: page * page_tokens + offset of the new token
+  const float* inv_freq;      // [hd / 2], pairs (i, i + hd/2)
+  int num_requests;           // rows of the grid (requests beyond the live ones have q_len 0)
+};
+
 struct AttnMergeParams {
   const float* part_o;
   const float* part_ml;

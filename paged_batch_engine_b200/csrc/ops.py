@@ -424,6 +424,71 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
     return out
 
 
+# The block-cooperative instance of the decode attention kernel (four warps share each key tile)
+# is the shortest path through one work item; it pays while all its blocks (work items x kv
+# heads) are resident at once, three a multiprocessor.  Beyond that the persistent instance,
+# in which every warp streams whole work items, is faster (measured crossover between 256 and
+# 512 items on 148 multiprocessors).
+DECODE_BLOCK_ITEMS_PER_SM = 3
+
+
+_sm_counts = {}
+
+
+def decode_block_max_items(device) -> int:
+    sms = _sm_counts.get(device)
+    if sms is None:
+        try:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+        except (RuntimeError, AssertionError):
+            sms = 148
+        _sm_counts[device] = sms
+    return DECODE_BLOCK_ITEMS_PER_SM * sms
+
+
+class AttnFusedParams(ctypes.Structure):
+    _fields_ = [("qkv", c_void_p), ("bias", c_void_p), ("positions", c_void_p), ("slots", c_void_p),
+                ("inv_freq", c_void_p), ("num_requests", c_int)]
+
+
+FUSED_DECODE_SPLITS = 8          # blocks of a cluster in the fused decode attention kernel
+FUSED_DECODE_MAX_KEYS = 8 * 512  # the longest key range it takes (its splits hold at most 512 keys)
+
+
+def fused_decode_attention_applies(dtype: torch.dtype, head_dim: int, group_size: int) -> bool:
+    import os
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and group_size <= 16
+            and _mma_available() and os.environ.get("PBE_DECODE_FUSED", "1") != "0")
+
+
+def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, slots, inv_freq, num_requests,
+                           num_heads, num_kv_heads, head_dim, scale, window, page_tokens):
+    """A step of decoded tokens only (one row a request): bias and rotary position encoding of
+    the new token's query, key and value, the cache write, attention over the pages and the
+    merge of the key splits in ONE launch (clusters of 8 blocks, one per request and key/value
+    head).  ``qkv``: the fused projection's output [T, (H + 2 KV) hd]; ``out``: [T, H hd]."""
+    _need_cuda(qkv, bias, k_cache, v_cache, out, positions, slots, inv_freq)
+    _need_contiguous(qkv, k_cache, v_cache, out)
+    if qkv.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the fused decode attention kernel takes bfloat16")
+    p = AttnParams(
+        q=None, k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr(), out=out.data_ptr(),
+        part_o=None, part_ml=None,
+        q_start=meta.q_start.data_ptr(), q_len=meta.q_len.data_ptr(), seq_len=meta.seq_len.data_ptr(),
+        block_table=meta.block_table.data_ptr(), work=None, tok_split_row=None, bt_stride=int(meta.bt_stride),
+        num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
+        window=int(window or 0), split_keys=int(meta.split_keys), max_splits=FUSED_DECODE_SPLITS,
+        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=1)
+    f = AttnFusedParams(qkv=qkv.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
+                        positions=positions.data_ptr(), slots=slots.data_ptr(), inv_freq=inv_freq.data_ptr(),
+                        num_requests=int(num_requests))
+    fn = _fn("attention_mma", "pbe_attn_decode_fused",
+             [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnFusedParams), c_int, c_void_p],
+             {"PBE_HEAD_DIM": int(head_dim)})
+    _check(fn(ctypes.byref(p), ctypes.byref(f), _dtype_code(qkv), _stream()), "attention_decode_fused")
+    return out
+
+
 def tc5_attention_applies(head_dim: int, page_tokens: int) -> bool:
     return head_dim in (64, 128) and page_tokens >= 8 and page_tokens % 8 == 0 and \
         (64 % page_tokens == 0 or page_tokens % 64 == 0)

@@ -20,6 +20,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..csrc import ops
+
 from ..cache.manager import CacheManager
 
 SPLIT_KEYS = 256          # keys per split of a short request's long key range, many requests
@@ -35,20 +37,6 @@ def choose_split_keys(num_requests: int) -> int:
 # Steps with at most this many requests run decoded tokens through the block-cooperative
 # instance of the attention kernel (four warps share each key tile: shortest latency per work
 # item); larger steps through the persistent warp-private instance (most bytes in flight).
-# The block-cooperative instance of the decode attention kernel (four warps share each key tile)
-# is the shortest path through one work item; it pays while all its blocks (work items x kv
-# heads) are resident at once, three a multiprocessor.  Beyond that the persistent instance,
-# in which every warp streams whole work items, is faster (measured crossover between 256 and
-# 512 items on 148 multiprocessors).
-DECODE_BLOCK_ITEMS_PER_SM = 3
-
-
-def decode_block_max_items(device) -> int:
-    try:
-        sms = torch.cuda.get_device_properties(device).multi_processor_count
-    except (RuntimeError, AssertionError):
-        sms = 148
-    return DECODE_BLOCK_ITEMS_PER_SM * sms
 
 
 @dataclass
@@ -87,6 +75,8 @@ class AttentionWork:
     kinds: int = 0                  # bit 0: row tiles of at most 16 packed rows exist, bit 1: larger ones,
     #                                 bit 2: few enough of the small ones for the block-cooperative instance
     small_items: int = 0            # live work items with at most 16 packed rows
+    decode_rows: int = 0            # rows of a step of decoded tokens only (0: the step has prompt portions)
+    longest_keys: int = 0           # the longest context of the step (a captured step: of its capacity)
 
 
 def attention_work_arrays(q_len: np.ndarray, seq_len: np.ndarray, q_start: np.ndarray,
@@ -301,7 +291,9 @@ class StepContext:
                 block_table=g.block_table, bt_stride=g.bt_stride, work=pk.view(iw), num_work=nw,
                 tok_split_row=pk.view(itsr), split_tokens=pk.view(ist) if ns else None,
                 split_counts=pk.view(isc) if ns else None, num_split_rows=ns, max_splits=max_splits,
-                split_keys=self.split_keys, tile_rows=key[2], kinds=kinds, small_items=small_items)
+                split_keys=self.split_keys, tile_rows=key[2], kinds=kinds, small_items=small_items,
+                decode_rows=R if int(q_len.max(initial=0)) == 1 and int(q_len.min(initial=1)) == 1 else 0,
+                longest_keys=int(seq_len.max(initial=0)))
 
     def group(self, g: int) -> GroupArrays:
         return self._groups[g]
@@ -309,7 +301,7 @@ class StepContext:
     def attention_work(self, group: int, group_size: int, tile_rows: int, window, num_heads: int,
                        head_dim: int) -> AttentionWork:
         w = self._work[(group, group_size, tile_rows, window)]
-        few = w.small_items * (num_heads // group_size) <= decode_block_max_items(self.device)
+        few = w.small_items * (num_heads // group_size) <= ops.decode_block_max_items(self.device)
         w.kinds = (w.kinds & ~4) | (4 if few else 0)
         if w.num_split_rows and (w.part_o is None or w.part_o.shape[1] != num_heads
                                  or w.part_o.shape[3] != head_dim):

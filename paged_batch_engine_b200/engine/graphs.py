@@ -21,7 +21,8 @@ import numpy as np
 import torch
 
 from ..cache.manager import decode_work_fill
-from .batch import (AttentionWork, decode_block_max_items, GroupArrays, StepContext, StepEntry,
+from ..csrc import ops
+from .batch import (AttentionWork, GroupArrays, StepContext, StepEntry,
                     attention_work_arrays, choose_split_keys)
 
 
@@ -98,7 +99,7 @@ class DecodeStepContext(StepContext):
                 split_counts=view(f"sc{i}"), num_split_rows=B, max_splits=S, split_keys=self.split_keys,
                 tile_rows=key[2], kinds=1 if key[1] <= 16 else 2,
                 # a captured step serves split counts from half its capacity up to all of it
-                small_items=(3 * B * S + 3) // 4)
+                small_items=(3 * B * S + 3) // 4, decode_rows=B, longest_keys=S * self.split_keys)
 
     def _h(self, name):
         v = self._views.get(name)
@@ -154,7 +155,7 @@ class DecodeStepContext(StepContext):
 
     def attention_work(self, group, group_size, tile_rows, window, num_heads, head_dim):
         w = self._work[(group, group_size, tile_rows, window)]
-        few = w.small_items * (num_heads // group_size) <= decode_block_max_items(self.device)
+        few = w.small_items * (num_heads // group_size) <= ops.decode_block_max_items(self.device)
         w.kinds = (w.kinds & ~4) | (4 if few else 0)
         if w.part_o is None:
             w.part_o = torch.empty((self.batch, num_heads, self.splits, head_dim), dtype=torch.float32,

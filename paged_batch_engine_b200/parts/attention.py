@@ -7,6 +7,7 @@ import torch
 
 from ..config.specs import PartSpec
 from ..csrc import ops
+
 from ..weights.loader import ParamSpec
 from .base import KVNeed, Mixer, build_part, register_part
 
@@ -77,19 +78,35 @@ class GQAttention(Mixer):
             self.b_o = tensors.pop(prefix + "o_proj.bias").to(torch.float32).contiguous()
 
     # ---- compute
+    def _fused_decode(self, meta, cache, inv_freq, rotary_dim, interleaved) -> bool:
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        return (meta.decode_rows > 0 and cache.writes and inv_freq is not None and rotary_dim == hd
+                and not interleaved and self.kernel_kind != "simple"
+                and ops.fused_decode_attention_applies(self.dtype, hd, H // KV)
+                and 0 < meta.longest_keys <= ops.FUSED_DECODE_MAX_KEYS
+                and meta.decode_rows * KV * ops.FUSED_DECODE_SPLITS <= ops.decode_block_max_items(meta.q_len.device))
+
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = ops.linear(x, self.w_qkv, None, out_dtype=self.dtype)
-        q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         inv_freq, rotary_dim, interleaved = self.position.kernel_args()
         group = ctx.group(cache.group)
         k_pages, v_pages = cache.k, cache.v
+        meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
+        if self._fused_decode(meta, cache, inv_freq, rotary_dim, interleaved):
+            # decoded tokens only, few requests, contexts up to 4,096 keys: position encoding, cache
+            # write, attention and the merge of the key splits in one launch
+            out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
+            ops.attention_decode_fused(qkv, self.b_qkv, k_pages, v_pages, out, meta, ctx.positions, group.slots,
+                                       inv_freq, meta.decode_rows, H, KV, hd, self.scale, self.window,
+                                       ctx.page_tokens)
+            return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
+        q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         ops.rope_kv_write(qkv, self.b_qkv, q, k_pages if cache.writes else None,
                           v_pages if cache.writes else None, ctx.positions, group.slots, inv_freq,
                           H, KV, hd, rotary_dim, ctx.page_tokens, interleaved)
         out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
-        meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
         ops.paged_attention(q, k_pages, v_pages, out, meta, H, KV, hd, self.scale, self.window,
                             ctx.page_tokens, kind=self.kernel_kind)
         return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)

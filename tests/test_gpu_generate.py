@@ -126,9 +126,9 @@ def test_many_requests_at_once(tiny_folders, monkeypatch, persistent):
     the decode attention kernel (the persistent one is what a step of many work items takes: its
     threshold is set to zero here); every request must produce what it produces alone."""
     from paged_batch_engine_b200 import SamplingParams
-    from paged_batch_engine_b200.engine import batch
+    from paged_batch_engine_b200.csrc import ops as pbe_ops
     if persistent:
-        monkeypatch.setattr(batch, "DECODE_BLOCK_ITEMS_PER_SM", 0)
+        monkeypatch.setattr(pbe_ops, "DECODE_BLOCK_ITEMS_PER_SM", 0)
     cfg, _, page, _ = TINY["C"]
     folder = tiny_folders["C"]
     prompts = prompts_for(cfg["vocab_size"], [3 + 5 * i for i in range(20)], seed=9)

@@ -304,8 +304,8 @@ def test_attention_mma_many_decoding_requests(H, KV, hd, P, window, monkeypatch)
     """Decoded tokens through the persistent warp-private instance (one warp streams a whole
     key split), which steps of many work items take: its threshold is set to zero here.
     Contexts end on and off tile, split and page edges; a few short prompt portions ride along."""
-    from paged_batch_engine_b200.engine import batch
-    monkeypatch.setattr(batch, "DECODE_BLOCK_ITEMS_PER_SM", 0)
+    from paged_batch_engine_b200.csrc import ops as pbe_ops
+    monkeypatch.setattr(pbe_ops, "DECODE_BLOCK_ITEMS_PER_SM", 0)
     ctxs = [0, 1, 15, 16, 17, 63, 64, 255, 256, 257, 300, 511, 512, 513, 700, 31, 33, 1000, 129, 5]
     reqs = [(c, 1) for c in ctxs] + [(90, 2), (0, 12)]
     case = AttnCase(H, KV, hd, P, window, reqs, torch.bfloat16, seed=hd + len(reqs), kind="mma")
@@ -509,3 +509,68 @@ def test_gemm_tc5(M, N, K):
         ref = plain.swiglu(want[:, :N // 2].float().cpu(), want[:, N // 2:].float().cpu())
         assert act.shape == (M, N // 2)
         assert (act - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("H,KV,hd,P,window,ctxs", [
+    (28, 4, 128, 16, None, [2047, 300, 0, 1, 255, 256, 257, 4000]),
+    (6, 3, 48, 8, 40, [0, 5, 39, 40, 41, 100, 700]),
+    (4, 2, 16, 16, None, [15, 16, 17, 2300]),
+    (8, 1, 64, 32, 600, [1000, 599, 600, 601, 3000]),
+    (5, 5, 256, 16, None, [20, 600]),
+])
+def test_attention_decode_fused(H, KV, hd, P, window, ctxs):
+    """One launch for bias, rotary position encoding, cache write, attention and the merge of
+    the key splits of decoded tokens, against the separate kernels' plain references: the
+    output, and the key and value it writes into the (NaN-filled) cache."""
+    from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+    from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
+    o = ops()
+    g = torch.Generator().manual_seed(hd + len(ctxs))
+    R = len(ctxs)
+    pages = sum((c + 1 + P - 1) // P for c in ctxs) + 3
+    m = CacheManager([KVGroupSpec((0,), KV, hd, window)], P, pages, max_requests=32, lifo=True)
+    m.set_free_order(0, torch.randperm(pages, generator=g).tolist())
+    kc = torch.full((pages, KV, P, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((pages, KV, P, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    theta = 10000.0
+    inv_freq = plain.rope_inv_freq(hd, theta).to(DEV)
+    width = (H + 2 * KV) * hd
+    qkv = (torch.randn(R, width, generator=g) * 0.7).to(torch.bfloat16)
+    bias = torch.randn(width, generator=g) * 0.3
+    entries, want_out, new_k, new_v = [], [], [], []
+    for r, c in enumerate(ctxs):
+        h = m.add_request()
+        assert m.reserve(h, c + 1)
+        k = torch.randn(c + 1, KV, hd, generator=g).to(torch.bfloat16)
+        v = torch.randn(c + 1, KV, hd, generator=g).to(torch.bfloat16)
+        row = qkv[r].float() + bias
+        q_new = plain.rope_rotate_half(row[:H * hd].view(1, H, hd), torch.tensor([c]), theta).to(torch.bfloat16)
+        k_new = plain.rope_rotate_half(row[H * hd:(H + KV) * hd].view(1, KV, hd), torch.tensor([c]), theta).to(torch.bfloat16)
+        v_new = row[(H + KV) * hd:].view(1, KV, hd).to(torch.bfloat16)
+        k[c], v[c] = k_new[0], v_new[0]
+        table = m.block_table(h)
+        for pos in range(c):                                   # the context; the new token's slot stays NaN
+            kc[table[pos // P], :, pos % P] = k[pos].to(DEV)
+            vc[table[pos // P], :, pos % P] = v[pos].to(DEV)
+        m.commit(h, c)
+        qfull = torch.zeros(c + 1, H, hd)
+        qfull[c] = q_new[0].float()
+        want_out.append(plain.causal_attention(qfull, k.float(), v.float(), hd ** -0.5, window)[c])
+        new_k.append((table[c // P], c % P, k_new[0]))
+        new_v.append((table[c // P], c % P, v_new[0]))
+        entries.append(StepEntry(h, [0]))
+    G = H // KV
+    _, tile_rows, _ = o.attention_kernel_config(hd, torch.bfloat16, "mma")
+    ctx = StepContext(m, entries, torch.device(DEV), [(0, G, tile_rows, window)])
+    meta = ctx.attention_work(0, G, tile_rows, window, H, hd)
+    assert meta.decode_rows == R
+    out = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.attention_decode_fused(qkv.to(DEV), bias.to(DEV), kc, vc, out, meta, ctx.positions, ctx.group(0).slots,
+                             inv_freq, R, H, KV, hd, hd ** -0.5, window, P)
+    got = out.float().cpu().view(R, H, hd)
+    want = torch.stack(want_out)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= 2 ** -6 * max(1.0, want.abs().max().item())
+    for (page, off, kn), (_, _, vn) in zip(new_k, new_v):
+        assert (kc[page, :, off].float().cpu() - kn.float()).abs().max().item() <= 2 ** -6 * max(1.0, kn.float().abs().max().item())
+        assert torch.equal(vc[page, :, off].cpu(), vn)
