@@ -334,6 +334,8 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   // the work list start first for every key/value head
   const int H = p.num_heads, KV = p.num_kv_heads, G = H / KV, P = p.page_tokens;
   int r, m_tile, split, nsplit, kvh;
+  int fused_slot = 0;
+  float fused_posf = 0.f;
   if constexpr (FUSED) {
     // grid (FUSED_SPLITS, requests, kv heads), clusters along x: no work list
     r = blockIdx.y;
@@ -341,6 +343,8 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     split = blockIdx.x;
     nsplit = FUSED_SPLITS;
     kvh = blockIdx.z;
+    fused_slot = f.slots[r];    // requested together with the lengths: one round of loads
+    fused_posf = (float)f.positions[r];
     if (p.q_len[r] != 1) {      // an idle row of a captured step: the whole cluster leaves
       pdl_wait();
       pdl_launch_dependents();
@@ -357,7 +361,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     m_tile = work[1], split = work[2], nsplit = work[3];
     kvh = KEYS ? blockIdx.y : blockIdx.x % KV;
   }
-  const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+  // fused mode: one row a request, in request order, so the request's row is its index and
+  // nothing below waits for a second round of loads
+  const int qs = FUSED ? r : p.q_start[r], nq = FUSED ? 1 : p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
   const int pr0 = m_tile * BM;
   const int rows_here = min(BM, n_packed - pr0);
@@ -444,8 +450,6 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     // token (whose key and value this block writes below).
     const int pos = sl - 1;
     const bool owner = pos >= k_begin && pos < k_end;
-    const int slot = f.slots[qs];
-    const float posf = (float)f.positions[qs];
     int issued = 0;                                            // key tiles requested so far, one group each
     for (; issued < NST - 1 && issued < n_tiles; ++issued) {
       if (owner && tile0 + (issued + 1) * BN > pos) break;     // the tile with the new token: after the write
@@ -460,7 +464,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     float* trig = reinterpret_cast<float*>(Ks + (NST - 1) * BN * LDS);   // the last buffer: filled last
     float* qraw = trig + HD;                                          // [G][HD] biased query heads
     float* kvraw = qraw + 16 * HD;                                    // [2][HD] biased key and value
-    for (int i = tid; i < HALF; i += NTHREADS) sincosf(posf * f.inv_freq[i], &trig[HALF + i], &trig[i]);
+    for (int i = tid; i < HALF; i += NTHREADS) sincosf(fused_posf * f.inv_freq[i], &trig[HALF + i], &trig[i]);
     const int row_width = (H + 2 * KV) * HD;
     const bf16* in = (const bf16*)f.qkv + (size_t)qs * row_width;
     const int chunks_q = G * CPR, chunks_kv = owner ? 2 * CPR : 0;
@@ -498,7 +502,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       Qs[hg * LDS + i + HALF] = __float2bfloat16_rn(rb);
     }
     if (owner) {
-      const int page = slot / P, off = slot - page * P;
+      const int page = fused_slot / P, off = fused_slot - page * P;
       bf16* kdst = (bf16*)p.k_cache + (((size_t)page * KV + kvh) * P + off) * HD;
       bf16* vdst = (bf16*)p.v_cache + (((size_t)page * KV + kvh) * P + off) * HD;
       for (int i = tid; i < HALF; i += NTHREADS) {
@@ -617,19 +621,25 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       }
     }
     __syncthreads();
-    for (int idx = tid; idx < rows_here * HD; idx += NTHREADS) {
-      const int row = idx / HD, d = idx - row * HD;
+    // four consecutive columns a thread: the weights of the four warps are computed once per item
+    for (int idx = tid; idx < rows_here * (HD / 4); idx += NTHREADS) {
+      const int row = idx / (HD / 4), d = (idx - row * (HD / 4)) * 4;
       float mm = -INFINITY;
 #pragma unroll
       for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sc_ml[(w * 16 + row) * 2]);
-      float ll = 0.f, acc = 0.f;
+      float ll = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const float mw = sc_ml[(w * 16 + row) * 2];
         if (mw != -INFINITY) {
-          const float f = exp2f(mw - mm);
-          ll += sc_ml[(w * 16 + row) * 2 + 1] * f;
-          acc += sc_o[(w * 16 + row) * HD + d] * f;
+          const float fw = ex2_approx(mw - mm);
+          ll += sc_ml[(w * 16 + row) * 2 + 1] * fw;
+          const float4 ov = *reinterpret_cast<const float4*>(sc_o + (w * 16 + row) * HD + d);
+          acc.x += ov.x * fw;
+          acc.y += ov.y * fw;
+          acc.z += ov.z * fw;
+          acc.w += ov.w * fw;
         }
       }
       const int pr = pr0 + row;
@@ -640,16 +650,19 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
         // this block's result for the cluster's merge: after the four warps' partial sums
         float* cl_o = reinterpret_cast<float*>(Vs);        // [16][HD]
         float* cl_ml = cl_o + 16 * HD;                       // [16][2]
-        cl_o[row * HD + d] = acc;
+        *reinterpret_cast<float4*>(cl_o + row * HD + d) = acc;
         if (d == 0) {
           cl_ml[row * 2] = mm;
           cl_ml[row * 2 + 1] = ll;
         }
       } else if (nsplit <= 1) {
-        ((bf16*)p.out)[((size_t)tok * H + head) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+        bf16* dst = (bf16*)p.out + ((size_t)tok * H + head) * HD + d;
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
       } else {
         const size_t base = ((size_t)p.tok_split_row[tok] * H + head) * p.max_splits + split;
-        p.part_o[base * HD + d] = acc;
+        *reinterpret_cast<float4*>(p.part_o + base * HD + d) = acc;
         if (d == 0) {
           p.part_ml[base * 2] = mm == -INFINITY ? -INFINITY : mm * LN2;   // natural-log domain for the merge
           p.part_ml[base * 2 + 1] = ll;
@@ -664,33 +677,47 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       float* cl_o = reinterpret_cast<float*>(Vs);
       float* cl_ml = cl_o + 16 * HD;
       cluster.sync();
-      constexpr int SLICE = (HD + FUSED_SPLITS - 1) / FUSED_SPLITS;
+      // every block merges HD / 8 columns (in groups of four where the head size allows) of
+      // every row over the cluster's blocks
+      constexpr int VEC = (HD % (4 * FUSED_SPLITS) == 0) ? 4 : 2;       // HD is a multiple of 16
+      constexpr int SLICE = HD / FUSED_SPLITS;                          // columns a block merges
       const int d0 = split * SLICE;
-      for (int idx = tid; idx < rows_here * SLICE; idx += NTHREADS) {
-        const int row = idx / SLICE, d = d0 + (idx - row * SLICE);
-        if (d >= HD) continue;
-        float ms[FUSED_SPLITS], ls[FUSED_SPLITS], os[FUSED_SPLITS];
-        float mm = -INFINITY;
+      for (int idx = tid; idx < rows_here * (SLICE / VEC); idx += NTHREADS) {
+        const int row = idx / (SLICE / VEC), d = d0 + (idx - row * (SLICE / VEC)) * VEC;
+        float ms[FUSED_SPLITS], mm = -INFINITY;
 #pragma unroll
-        for (int s = 0; s < FUSED_SPLITS; ++s) {
-          const float* ro = cluster.map_shared_rank(cl_o, s);
-          const float* rml = cluster.map_shared_rank(cl_ml, s);
-          ms[s] = rml[row * 2];
-          ls[s] = rml[row * 2 + 1];
-          os[s] = ro[row * HD + d];
-          mm = fmaxf(mm, ms[s]);
+        for (int sidx = 0; sidx < FUSED_SPLITS; ++sidx) {
+          ms[sidx] = cluster.map_shared_rank(cl_ml, sidx)[row * 2];
+          mm = fmaxf(mm, ms[sidx]);
         }
-        float ll = 0.f, acc = 0.f;
+        float ll = 0.f, acc[VEC];
 #pragma unroll
-        for (int s = 0; s < FUSED_SPLITS; ++s) {
-          if (ms[s] != -INFINITY) {
-            const float w = exp2f(ms[s] - mm);
-            ll += ls[s] * w;
-            acc += os[s] * w;
+        for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int sidx = 0; sidx < FUSED_SPLITS; ++sidx) {
+          if (ms[sidx] != -INFINITY) {
+            const float w = ex2_approx(ms[sidx] - mm);
+            ll += cluster.map_shared_rank(cl_ml, sidx)[row * 2 + 1] * w;
+            const float* ro = cluster.map_shared_rank(cl_o, sidx) + row * HD + d;
+            if constexpr (VEC == 4) {
+              const float4 ov = *reinterpret_cast<const float4*>(ro);
+              acc[0] += ov.x * w;
+              acc[1] += ov.y * w;
+              acc[2] += ov.z * w;
+              acc[3] += ov.w * w;
+            } else {
+              const float2 ov = *reinterpret_cast<const float2*>(ro);
+              acc[0] += ov.x * w;
+              acc[1] += ov.y * w;
+            }
           }
         }
+        const float inv = ll > 0.f ? 1.0f / ll : 0.f;
         const int head = kvh * G + row;                    // one query row: packed row == head of the group
-        ((bf16*)p.out)[((size_t)qs * H + head) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        bf16* dst = (bf16*)p.out + ((size_t)qs * H + head) * HD + d;
+#pragma unroll
+        for (int e = 0; e < VEC; e += 2)
+          *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
       }
       cluster.sync();           // nobody leaves while its shared memory may still be read
     }

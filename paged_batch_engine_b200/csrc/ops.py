@@ -466,7 +466,8 @@ def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, sl
     """A step of decoded tokens only (one row a request): bias and rotary position encoding of
     the new token's query, key and value, the cache write, attention over the pages and the
     merge of the key splits in ONE launch (clusters of 8 blocks, one per request and key/value
-    head).  ``qkv``: the fused projection's output [T, (H + 2 KV) hd]; ``out``: [T, H hd]."""
+    head).  ``qkv``: the fused projection's output [T, (H + 2 KV) hd]; ``out``: [T, H hd];
+    row r of both belongs to request r (a step of decoded tokens has its rows in that order)."""
     _need_cuda(qkv, bias, k_cache, v_cache, out, positions, slots, inv_freq)
     _need_contiguous(qkv, k_cache, v_cache, out)
     if qkv.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
