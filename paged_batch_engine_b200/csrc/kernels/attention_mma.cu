@@ -305,17 +305,19 @@ __device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, c
 // MODE 1: keys mode, row tiles of at most 16 packed rows (decoded tokens); only 16 query
 // rows are staged, so that three blocks fit on an SM.  Each instance skips the other's work.
 // MODE 2: keys mode for steps of decoded tokens only, fused with what comes before and after
-// it: a cluster of FUSED_SPLITS blocks owns one (request, key/value head); every block takes
+// it: a cluster of CS blocks (8, 4, 2 or 1: as many as keep the whole step resident at once)
+// owns one (request, key/value head); every block takes
 // the query heads of the group straight from the fused QKV projection (bias and rotary
 // position encoding applied here), the block whose key range holds the new token also writes
 // its key and value into the cache, and the partial results of the cluster's blocks are merged
 // through distributed shared memory, each block one slice of the head dimension.  One launch
 // stands for three (position encoding and cache write, attention, merge of the splits).
-constexpr int FUSED_SPLITS = 8;
+constexpr int FUSED_MAX_SPLITS = 8;
+constexpr int FUSED_MAX_KEYS_PER_BLOCK = 4096;     // beyond that the other path streams better
 
 // NST: key/value tiles in shared memory (two everywhere; the fused mode also has an instance
 // with three, two blocks a multiprocessor, for steps small enough to be resident that way).
-template <int MODE, int NST = 2>
+template <int MODE, int NST = 2, int CS = 1>
 __global__ void __launch_bounds__(NTHREADS, MODE != 0 ? (HD <= 128 ? (NST == 2 ? 3 : 2) : 1) : (HD <= 128 ? 2 : 1))
 attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   constexpr bool KEYS = MODE != 0;
@@ -337,11 +339,11 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   int fused_slot = 0;
   float fused_posf = 0.f;
   if constexpr (FUSED) {
-    // grid (FUSED_SPLITS, requests, kv heads), clusters along x: no work list
+    // grid (CS, requests, kv heads), clusters along x: no work list
     r = blockIdx.y;
     m_tile = 0;
     split = blockIdx.x;
-    nsplit = FUSED_SPLITS;
+    nsplit = CS;
     kvh = blockIdx.z;
     fused_slot = f.slots[r];    // requested together with the lengths: one round of loads
     fused_posf = (float)f.positions[r];
@@ -380,9 +382,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   int k_begin = lo_key, k_end = hi_key;
   int fused_kps = 0;
   if constexpr (FUSED) {
-    // the request's own length decides its split size: its keys in FUSED_SPLITS equal parts,
-    // rounded up to whole key tiles
-    fused_kps = max(BN, ((hi_key - lo_key + FUSED_SPLITS * BN - 1) / (FUSED_SPLITS * BN)) * BN);
+    // the request's own length (and the cluster size the step's size chose) decides its split
+    // size: its keys in CS equal parts, rounded up to whole key tiles
+    fused_kps = max(BN, ((hi_key - lo_key + CS * BN - 1) / (CS * BN)) * BN);
     k_begin = min(hi_key, lo_key + split * fused_kps);
     k_end = min(hi_key, lo_key + (split + 1) * fused_kps);
   } else if (nsplit > 1) {
@@ -671,34 +673,33 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     }
     if constexpr (FUSED) {
       // merge across the cluster: every block combines one slice of the head dimension of all
-      // blocks' partial results, read through distributed shared memory
+      // blocks' partial results, read through distributed shared memory (a cluster of one block
+      // just normalises its own)
       namespace cg = cooperative_groups;
       cg::cluster_group cluster = cg::this_cluster();
       float* cl_o = reinterpret_cast<float*>(Vs);
       float* cl_ml = cl_o + 16 * HD;
-      cluster.sync();
-      // every block merges HD / 8 columns (in groups of four where the head size allows) of
-      // every row over the cluster's blocks
-      constexpr int VEC = (HD % (4 * FUSED_SPLITS) == 0) ? 4 : 2;       // HD is a multiple of 16
-      constexpr int SLICE = HD / FUSED_SPLITS;                          // columns a block merges
+      if constexpr (CS > 1) cluster.sync(); else __syncthreads();
+      constexpr int SLICE = HD / CS;                                    // columns a block merges (HD % 16 == 0)
+      constexpr int VEC = (SLICE % 4 == 0) ? 4 : 2;
       const int d0 = split * SLICE;
       for (int idx = tid; idx < rows_here * (SLICE / VEC); idx += NTHREADS) {
         const int row = idx / (SLICE / VEC), d = d0 + (idx - row * (SLICE / VEC)) * VEC;
-        float ms[FUSED_SPLITS], mm = -INFINITY;
+        float ms[CS], mm = -INFINITY;
 #pragma unroll
-        for (int sidx = 0; sidx < FUSED_SPLITS; ++sidx) {
-          ms[sidx] = cluster.map_shared_rank(cl_ml, sidx)[row * 2];
+        for (int sidx = 0; sidx < CS; ++sidx) {
+          ms[sidx] = (CS > 1 ? cluster.map_shared_rank(cl_ml, sidx) : cl_ml)[row * 2];
           mm = fmaxf(mm, ms[sidx]);
         }
         float ll = 0.f, acc[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
 #pragma unroll
-        for (int sidx = 0; sidx < FUSED_SPLITS; ++sidx) {
+        for (int sidx = 0; sidx < CS; ++sidx) {
           if (ms[sidx] != -INFINITY) {
             const float w = ex2_approx(ms[sidx] - mm);
-            ll += cluster.map_shared_rank(cl_ml, sidx)[row * 2 + 1] * w;
-            const float* ro = cluster.map_shared_rank(cl_o, sidx) + row * HD + d;
+            ll += (CS > 1 ? cluster.map_shared_rank(cl_ml, sidx) : cl_ml)[row * 2 + 1] * w;
+            const float* ro = (CS > 1 ? cluster.map_shared_rank(cl_o, sidx) : cl_o) + row * HD + d;
             if constexpr (VEC == 4) {
               const float4 ov = *reinterpret_cast<const float4*>(ro);
               acc[0] += ov.x * w;
@@ -719,7 +720,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
         for (int e = 0; e < VEC; e += 2)
           *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
       }
-      cluster.sync();           // nobody leaves while its shared memory may still be read
+      if constexpr (CS > 1) cluster.sync();   // nobody leaves while its shared memory may still be read
     }
     return;
   }
@@ -1002,18 +1003,35 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
 }
 
 // A step of decoded tokens only, one launch for position encoding, cache write, attention and
-// the merge of the key splits (MODE 2 above).  The key range of a request may span at most
-// FUSED_SPLITS * 512 keys; the caller keeps longer contexts and large batches on the other path.
-PBE_EXPORT int pbe_attn_decode_fused_max_keys() { return FUSED_SPLITS * 512; }
-PBE_EXPORT int pbe_attn_decode_fused_splits() { return FUSED_SPLITS; }
-PBE_EXPORT int pbe_attn_decode_fused(const AttnParams* params, const AttnFusedParams* fused, int dtype,
+// the merge of the key splits (MODE 2 above).  ``splits``: blocks per (request, key/value head),
+// 8, 4, 2 or 1; the caller picks the largest with which the whole step is resident at once and
+// keeps steps on the other path whose blocks would get more than pbe_attn_decode_fused_max_keys()
+// keys each.
+PBE_EXPORT int pbe_attn_decode_fused_max_keys() { return FUSED_MAX_KEYS_PER_BLOCK; }
+PBE_EXPORT int pbe_attn_decode_fused_splits() { return FUSED_MAX_SPLITS; }
+
+namespace {
+template <int NST, int CS>
+void launch_fused(const AttnParams& p, const AttnFusedParams& f, cudaStream_t stream) {
+  const size_t smem = sizeof(bf16) * (size_t)(16 + 2 * NST * BN_KEYS) * LDS;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(attn_mma_kernel<2, NST, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  launch_k_cluster(attn_mma_kernel<2, NST, CS>, dim3(CS, f.num_requests, p.num_kv_heads), NTHREADS, smem, stream, CS,
+                   p, f);
+}
+}  // namespace
+
+PBE_EXPORT int pbe_attn_decode_fused(const AttnParams* params, const AttnFusedParams* fused, int dtype, int splits,
                                      cudaStream_t stream) {
   AttnParams p = *params;
   AttnFusedParams f = *fused;
   if (f.num_requests <= 0) return 0;
   if (dtype != PBE_BF16 || p.num_heads % p.num_kv_heads != 0 || p.num_heads / p.num_kv_heads > 16 ||
       f.qkv == nullptr || f.inv_freq == nullptr || f.slots == nullptr || f.positions == nullptr ||
-      f.num_requests > 65535 || p.num_kv_heads > 65535)
+      f.num_requests > 65535 || p.num_kv_heads > 65535 || (splits != 8 && splits != 4 && splits != 2 && splits != 1))
     return (int)cudaErrorInvalidValue;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -1022,19 +1040,16 @@ PBE_EXPORT int pbe_attn_decode_fused(const AttnParams* params, const AttnFusedPa
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const size_t smem2 = sizeof(bf16) * (size_t)(16 + 4 * BN_KEYS) * LDS;
-  const size_t smem3 = sizeof(bf16) * (size_t)(16 + 6 * BN_KEYS) * LDS;
-  static bool opted = false;
-  if (!opted) {
-    cudaFuncSetAttribute(attn_mma_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    if (HD <= 128) cudaFuncSetAttribute(attn_mma_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
-    opted = true;
-  }
-  const dim3 grid(FUSED_SPLITS, f.num_requests, p.num_kv_heads);
   // three key tiles in flight where all blocks are resident two a multiprocessor, else two
-  if (HD <= 128 && (long long)FUSED_SPLITS * f.num_requests * p.num_kv_heads <= 2LL * sm_count)
-    launch_k_cluster(attn_mma_kernel<2, 3>, grid, NTHREADS, smem3, stream, FUSED_SPLITS, p, f);
-  else
-    launch_k_cluster(attn_mma_kernel<2, 2>, grid, NTHREADS, smem2, stream, FUSED_SPLITS, p, f);
+  const bool three = HD <= 128 && (long long)splits * f.num_requests * p.num_kv_heads <= 2LL * sm_count;
+  if (splits == 8) {
+    if (three) launch_fused<3, 8>(p, f, stream); else launch_fused<2, 8>(p, f, stream);
+  } else if (splits == 4) {
+    if (three) launch_fused<3, 4>(p, f, stream); else launch_fused<2, 4>(p, f, stream);
+  } else if (splits == 2) {
+    if (three) launch_fused<3, 2>(p, f, stream); else launch_fused<2, 2>(p, f, stream);
+  } else {
+    if (three) launch_fused<3, 1>(p, f, stream); else launch_fused<2, 1>(p, f, stream);
+  }
   return launch_status();
 }

@@ -451,8 +451,18 @@ class AttnFusedParams(ctypes.Structure):
                 ("inv_freq", c_void_p), ("num_requests", c_int)]
 
 
-FUSED_DECODE_SPLITS = 8          # blocks of a cluster in the fused decode attention kernel
-FUSED_DECODE_MAX_KEYS = 8 * 512  # the longest key range it takes (its splits hold at most 512 keys)
+FUSED_DECODE_MAX_KEYS_PER_BLOCK = 4096   # beyond that the other path streams better
+
+
+def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int, device) -> int:
+    """Blocks per (request, key/value head) of the fused decode attention kernel: the largest of
+    8, 4, 2, 1 with which every block of the step is resident at once; 0 when even one block each
+    is too many, or when a block would get more keys than the kernel is meant for."""
+    cap = decode_block_max_items(device)
+    for splits in (8, 4, 2, 1):
+        if num_requests * num_kv_heads * splits <= cap:
+            return splits if 0 < longest_keys <= splits * FUSED_DECODE_MAX_KEYS_PER_BLOCK else 0
+    return 0
 
 
 def fused_decode_attention_applies(dtype: torch.dtype, head_dim: int, group_size: int) -> bool:
@@ -462,7 +472,7 @@ def fused_decode_attention_applies(dtype: torch.dtype, head_dim: int, group_size
 
 
 def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, slots, inv_freq, num_requests,
-                           num_heads, num_kv_heads, head_dim, scale, window, page_tokens):
+                           num_heads, num_kv_heads, head_dim, scale, window, page_tokens, splits=8):
     """A step of decoded tokens only (one row a request): bias and rotary position encoding of
     the new token's query, key and value, the cache write, attention over the pages and the
     merge of the key splits in ONE launch (clusters of 8 blocks, one per request and key/value
@@ -478,15 +488,15 @@ def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, sl
         q_start=meta.q_start.data_ptr(), q_len=meta.q_len.data_ptr(), seq_len=meta.seq_len.data_ptr(),
         block_table=meta.block_table.data_ptr(), work=None, tok_split_row=None, bt_stride=int(meta.bt_stride),
         num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
-        window=int(window or 0), split_keys=int(meta.split_keys), max_splits=FUSED_DECODE_SPLITS,
+        window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(splits),
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=1)
     f = AttnFusedParams(qkv=qkv.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
                         positions=positions.data_ptr(), slots=slots.data_ptr(), inv_freq=inv_freq.data_ptr(),
                         num_requests=int(num_requests))
     fn = _fn("attention_mma", "pbe_attn_decode_fused",
-             [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnFusedParams), c_int, c_void_p],
+             [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnFusedParams), c_int, c_int, c_void_p],
              {"PBE_HEAD_DIM": int(head_dim)})
-    _check(fn(ctypes.byref(p), ctypes.byref(f), _dtype_code(qkv), _stream()), "attention_decode_fused")
+    _check(fn(ctypes.byref(p), ctypes.byref(f), _dtype_code(qkv), int(splits), _stream()), "attention_decode_fused")
     return out
 
 

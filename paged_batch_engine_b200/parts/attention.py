@@ -78,13 +78,14 @@ class GQAttention(Mixer):
             self.b_o = tensors.pop(prefix + "o_proj.bias").to(torch.float32).contiguous()
 
     # ---- compute
-    def _fused_decode(self, meta, cache, inv_freq, rotary_dim, interleaved) -> bool:
+    def _fused_decode(self, meta, cache, inv_freq, rotary_dim, interleaved) -> int:
+        """Blocks per (request, key/value head) for the fused decode kernel, 0: not this step."""
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        return (meta.decode_rows > 0 and cache.writes and inv_freq is not None and rotary_dim == hd
+        if not (meta.decode_rows > 0 and cache.writes and inv_freq is not None and rotary_dim == hd
                 and not interleaved and self.kernel_kind != "simple"
-                and ops.fused_decode_attention_applies(self.dtype, hd, H // KV)
-                and 0 < meta.longest_keys <= ops.FUSED_DECODE_MAX_KEYS
-                and meta.decode_rows * KV * ops.FUSED_DECODE_SPLITS <= ops.decode_block_max_items(meta.q_len.device))
+                and ops.fused_decode_attention_applies(self.dtype, hd, H // KV)):
+            return 0
+        return ops.fused_decode_splits(meta.decode_rows, KV, meta.longest_keys, meta.q_len.device)
 
     def forward(self, x, ctx, cache):
         T = x.shape[0]
@@ -94,13 +95,14 @@ class GQAttention(Mixer):
         group = ctx.group(cache.group)
         k_pages, v_pages = cache.k, cache.v
         meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
-        if self._fused_decode(meta, cache, inv_freq, rotary_dim, interleaved):
-            # decoded tokens only, few requests, contexts up to 4,096 keys: position encoding, cache
+        splits = self._fused_decode(meta, cache, inv_freq, rotary_dim, interleaved)
+        if splits:
+            # decoded tokens only, every block of the step resident at once: position encoding, cache
             # write, attention and the merge of the key splits in one launch
             out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
             ops.attention_decode_fused(qkv, self.b_qkv, k_pages, v_pages, out, meta, ctx.positions, group.slots,
                                        inv_freq, meta.decode_rows, H, KV, hd, self.scale, self.window,
-                                       ctx.page_tokens)
+                                       ctx.page_tokens, splits=splits)
             return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
         q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         ops.rope_kv_write(qkv, self.b_qkv, q, k_pages if cache.writes else None,

@@ -518,7 +518,8 @@ def test_gemm_tc5(M, N, K):
     (8, 1, 64, 32, 600, [1000, 599, 600, 601, 3000]),
     (5, 5, 256, 16, None, [20, 600]),
 ])
-def test_attention_decode_fused(H, KV, hd, P, window, ctxs):
+@pytest.mark.parametrize("splits", [8, 4, 2, 1])
+def test_attention_decode_fused(H, KV, hd, P, window, ctxs, splits):
     """One launch for bias, rotary position encoding, cache write, attention and the merge of
     the key splits of decoded tokens, against the separate kernels' plain references: the
     output, and the key and value it writes into the (NaN-filled) cache."""
@@ -566,7 +567,7 @@ def test_attention_decode_fused(H, KV, hd, P, window, ctxs):
     assert meta.decode_rows == R
     out = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     o.attention_decode_fused(qkv.to(DEV), bias.to(DEV), kc, vc, out, meta, ctx.positions, ctx.group(0).slots,
-                             inv_freq, R, H, KV, hd, hd ** -0.5, window, P)
+                             inv_freq, R, H, KV, hd, hd ** -0.5, window, P, splits=splits)
     got = out.float().cpu().view(R, H, hd)
     want = torch.stack(want_out)
     assert torch.isfinite(got).all()
