@@ -460,8 +460,16 @@ def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int,
     is too many, or when a block would get more keys than the kernel is meant for."""
     cap = decode_block_max_items(device)
     for splits in (8, 4, 2, 1):
-        if num_requests * num_kv_heads * splits <= cap:
-            return splits if 0 < longest_keys <= splits * FUSED_DECODE_MAX_KEYS_PER_BLOCK else 0
+        blocks = num_requests * num_kv_heads * splits
+        if blocks <= cap:
+            per_block = (longest_keys + splits - 1) // splits
+            if not 0 < per_block <= FUSED_DECODE_MAX_KEYS_PER_BLOCK:
+                return 0
+            # a handful of blocks with thousands of keys each (one or two requests with very long
+            # contexts) stream better as many small work items on the other path
+            if per_block > 1536 and blocks < 200:
+                return 0
+            return splits
     return 0
 
 
