@@ -65,7 +65,20 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-template <int NT> struct Stages { static constexpr int value = NT == 1 ? 8 : 6; };
+// Ring depths measured in the captured decode step of the 7B shape (M = 8): the big matrices
+// (two blocks of eight warps a multiprocessor) with 6 slots leave room for the next kernel's
+// blocks to become resident and fetch their first weights early; the small ones (four warps a
+// block, two blocks a multiprocessor) stream best with 14 (8 / 8 -> 6 / 14: 3.43 -> 3.29 ms).
+#ifndef PBE_SKINNY_STAGES_BIG
+#define PBE_SKINNY_STAGES_BIG 6
+#endif
+#ifndef PBE_SKINNY_STAGES_SMALL
+#define PBE_SKINNY_STAGES_SMALL 14
+#endif
+// ring depth: by batch tiles and by the number of warps of the arrangement (8: big matrices)
+template <int NT, int WARPS> struct Stages {
+  static constexpr int value = NT == 1 ? (WARPS >= 8 ? PBE_SKINNY_STAGES_BIG : PBE_SKINNY_STAGES_SMALL) : 6;
+};
 
 // NT: batch tiles of 8 rows (M <= 8 * NT).  A block has WN x WK warps: WN weight-row tiles by
 // WK slices of K.  CL blocks may form a thread-block cluster that shares one set of row tiles
@@ -80,7 +93,7 @@ template <int NT> struct Stages { static constexpr int value = NT == 1 ? 8 : 6; 
 template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY>
 __global__ void __launch_bounds__(WN * WK * 32)
 gemm_skinny_kernel(SkinnyParams p) {
-  constexpr int STAGES = Stages<NT>::value;
+  constexpr int STAGES = Stages<NT, WN * WK>::value;
   constexpr int SLOT = 2 + NT;                       // 16-byte chunks per thread and stage
   extern __shared__ __align__(16) uint4 ring[];      // [WN * WK][STAGES][SLOT][32]
   __shared__ float red[WK][WN][NT][32][4];
@@ -241,7 +254,7 @@ gemm_skinny_kernel(SkinnyParams p) {
 
 template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY>
 int launch_cfg(const SkinnyParams& p, int row_blocks, cudaStream_t stream) {
-  constexpr size_t smem = sizeof(uint4) * WN * WK * Stages<NT>::value * (2 + NT) * 32;
+  constexpr size_t smem = sizeof(uint4) * WN * WK * Stages<NT, WN * WK>::value * (2 + NT) * 32;
   static bool opted = false;
   if (!opted) {
     cudaFuncSetAttribute(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY>,
