@@ -115,71 +115,85 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&a)[8]) {
   *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__global__ void rope_kv_vec_kernel(RopeKvParams p) {
-  extern __shared__ float trig[];            // cos[half], sin[half]
+constexpr int ROPE_TOKENS_PER_BLOCK = 4;   // tokens a block of the vector kernel handles (when there are many)
+
+__global__ void rope_kv_vec_kernel(RopeKvParams p, int tokens_per_block) {
+  extern __shared__ float trig[];            // [tokens_per_block][cos[half], sin[half]]
   typedef __nv_bfloat16 T;
   pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t0 = blockIdx.x * tokens_per_block;
+  const int nt = min(tokens_per_block, p.num_tokens - t0);
   const int H = p.num_heads, KV = p.num_kv_heads, hd = p.head_dim;
   const int half = hd / 2, half8 = half / 8, hd8 = hd / 8;
-  float* cs = trig;
-  float* sn = trig + half;
-  const float pos = (float)p.positions[t];
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * p.inv_freq[i], &sn[i], &cs[i]);
+  // sines and cosines of the block's tokens first, all at once, then one barrier
+  for (int i = threadIdx.x; i < nt * half; i += blockDim.x) {
+    const int tt = i / half, j = i - tt * half;
+    sincosf((float)p.positions[t0 + tt] * p.inv_freq[j], &trig[tt * hd + half + j], &trig[tt * hd + j]);
+  }
   __syncthreads();
   const int row_width = (H + 2 * KV) * hd;
-  const T* in = (const T*)p.qkv + (size_t)t * row_width;
-  const int slot = p.slots ? p.slots[t] : -1;
-  const bool write_kv = p.k_cache != nullptr && slot >= 0;
-  const int page = write_kv ? slot / p.page_tokens : 0;
-  const int off = write_kv ? slot - page * p.page_tokens : 0;
   const int n_rot = (H + KV) * half8;
   const int n_v = KV * hd8;
-  for (int item = threadIdx.x; item < n_rot + n_v; item += blockDim.x) {
-    if (item < n_rot) {
-      const int head = item / half8;
-      const int j = (item - head * half8) * 8;
-      const int base = head * hd;
-      T* dst;
-      if (head < H) {
-        dst = (T*)p.q_out + (size_t)t * H * hd + (size_t)head * hd;
-      } else {
-        if (!write_kv) continue;
-        dst = (T*)p.k_cache + (((size_t)page * KV + (head - H)) * p.page_tokens + off) * hd;
-      }
-      float a[8], b[8];
-      load8(in + base + j, a);
-      load8(in + base + j + half, b);
-      if (p.bias) {
+  for (int tt = 0; tt < nt; ++tt) {
+    const int t = t0 + tt;
+    const float* cs = trig + tt * hd;
+    const float* sn = cs + half;
+    const T* in = (const T*)p.qkv + (size_t)t * row_width;
+    const int slot = p.slots ? p.slots[t] : -1;
+    const bool write_kv = p.k_cache != nullptr && slot >= 0;
+    const int page = write_kv ? slot / p.page_tokens : 0;
+    const int off = write_kv ? slot - page * p.page_tokens : 0;
+    for (int item = threadIdx.x; item < n_rot + n_v; item += blockDim.x) {
+      if (item < n_rot) {
+        const int head = item / half8;
+        const int j = (item - head * half8) * 8;
+        const int base = head * hd;
+        T* dst;
+        if (head < H) {
+          dst = (T*)p.q_out + (size_t)t * H * hd + (size_t)head * hd;
+        } else {
+          if (!write_kv) continue;
+          dst = (T*)p.k_cache + (((size_t)page * KV + (head - H)) * p.page_tokens + off) * hd;
+        }
+        float a[8], b[8];
+        load8(in + base + j, a);
+        load8(in + base + j + half, b);
+        if (p.bias) {
+          const float4 ba0 = *reinterpret_cast<const float4*>(p.bias + base + j);
+          const float4 ba1 = *reinterpret_cast<const float4*>(p.bias + base + j + 4);
+          const float4 bb0 = *reinterpret_cast<const float4*>(p.bias + base + j + half);
+          const float4 bb1 = *reinterpret_cast<const float4*>(p.bias + base + j + half + 4);
+          a[0] += ba0.x; a[1] += ba0.y; a[2] += ba0.z; a[3] += ba0.w;
+          a[4] += ba1.x; a[5] += ba1.y; a[6] += ba1.z; a[7] += ba1.w;
+          b[0] += bb0.x; b[1] += bb0.y; b[2] += bb0.z; b[3] += bb0.w;
+          b[4] += bb1.x; b[5] += bb1.y; b[6] += bb1.z; b[7] += bb1.w;
+        }
+        float ra[8], rb[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          a[e] += p.bias[base + j + e];
-          b[e] += p.bias[base + j + half + e];
+          const float c = cs[j + e], s = sn[j + e];
+          ra[e] = a[e] * c - b[e] * s;
+          rb[e] = b[e] * c + a[e] * s;
         }
+        store8(dst + j, ra);
+        store8(dst + j + half, rb);
+      } else {
+        if (!write_kv) continue;
+        const int e8 = item - n_rot;
+        const int kvh = e8 / hd8, i = (e8 - kvh * hd8) * 8;
+        const int col = (H + KV) * hd + kvh * hd + i;
+        float a[8];
+        load8(in + col, a);
+        if (p.bias) {
+          const float4 b0 = *reinterpret_cast<const float4*>(p.bias + col);
+          const float4 b1 = *reinterpret_cast<const float4*>(p.bias + col + 4);
+          a[0] += b0.x; a[1] += b0.y; a[2] += b0.z; a[3] += b0.w;
+          a[4] += b1.x; a[5] += b1.y; a[6] += b1.z; a[7] += b1.w;
+        }
+        T* dst = (T*)p.v_cache + (((size_t)page * KV + kvh) * p.page_tokens + off) * hd;
+        store8(dst + i, a);
       }
-      float ra[8], rb[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float c = cs[j + e], s = sn[j + e];
-        ra[e] = a[e] * c - b[e] * s;
-        rb[e] = b[e] * c + a[e] * s;
-      }
-      store8(dst + j, ra);
-      store8(dst + j + half, rb);
-    } else {
-      if (!write_kv) continue;
-      const int e8 = item - n_rot;
-      const int kvh = e8 / hd8, i = (e8 - kvh * hd8) * 8;
-      const int col = (H + KV) * hd + kvh * hd + i;
-      float a[8];
-      load8(in + col, a);
-      if (p.bias) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] += p.bias[col + e];
-      }
-      T* dst = (T*)p.v_cache + (((size_t)page * KV + kvh) * p.page_tokens + off) * hd;
-      store8(dst + i, a);
     }
   }
 }
@@ -202,7 +216,11 @@ PBE_EXPORT int pbe_rope_kv_write(const void* qkv, const float* bias, void* q_out
     int vt = ((vec_items + 31) / 32) * 32;
     if (vt < 64) vt = 64;
     if (vt > 512) vt = 256;
-    launch_k(rope_kv_vec_kernel, num_tokens, vt, head_dim * sizeof(float), stream, p);
+    // many tokens: four a block (one round of sines and cosines, one barrier); few: one a block
+    const int tpb = num_tokens >= 4 * 148 * ROPE_TOKENS_PER_BLOCK ? ROPE_TOKENS_PER_BLOCK : 1;
+    if ((((uintptr_t)bias) & 15) != 0) return (int)cudaErrorInvalidValue;
+    launch_k(rope_kv_vec_kernel, (num_tokens + tpb - 1) / tpb, vt, (size_t)tpb * head_dim * sizeof(float), stream, p,
+             tpb);
     return launch_status();
   }
   int threads = 128;
