@@ -187,8 +187,9 @@ def load_host_library(name: str) -> ctypes.CDLL:
     if not os.path.isfile(source):
         raise BuildError(f"no host source {source}")
     h = hashlib.sha256()
-    with open(source, "rb") as f:
-        h.update(f.read())
+    for path in [source] + _headers():            # host sources may include the kernels' plain structs
+        with open(path, "rb") as f:
+            h.update(f.read())
     h.update(repr(HOST_FLAGS).encode())
     out = os.path.join(build_dir(), f"libpbe_host_{name}-{h.hexdigest()[:16]}.so")
     with _lock:

@@ -60,6 +60,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Launches made on this package's behalf by the host library."""
+    global _launches
+    _launches += int(n)
+
+
 def _check(code: int, what: str):
     global _launches
     if code != 0:
@@ -401,9 +407,7 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=int(getattr(meta, "kinds", 0)))
     if tc5:
         # prompt-portion tiles on the tcgen05 kernel; the decode instances below take the rest
-        err = _tc5_attn_err.get(q.device)
-        if err is None:
-            err = _tc5_attn_err[q.device] = torch.zeros(1024, dtype=torch.int32, device=q.device)
+        err = tc5_attention_error_buffer(q.device)
         tfn = _fn("attention_tc5", "pbe_attn_tc5", [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p, c_void_p],
                   defines)
         if (p.kinds & 3) == 0 or (p.kinds & 2):
@@ -506,6 +510,14 @@ def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, sl
              {"PBE_HEAD_DIM": int(head_dim)})
     _check(fn(ctypes.byref(p), ctypes.byref(f), _dtype_code(qkv), int(splits), _stream()), "attention_decode_fused")
     return out
+
+
+def tc5_attention_error_buffer(device) -> torch.Tensor:
+    """Element 0: set by the tcgen05 attention kernel when a bounded wait ran out."""
+    err = _tc5_attn_err.get(device)
+    if err is None:
+        err = _tc5_attn_err[device] = torch.zeros(1024, dtype=torch.int32, device=device)
+    return err
 
 
 def tc5_attention_applies(head_dim: int, page_tokens: int) -> bool:

@@ -208,6 +208,7 @@ class _Packer:
 
 class StepContext:
     """Everything the parts read about the step besides their input rows."""
+    captured = False              # True for the fixed-layout context of a captured decode step
 
     def __init__(self, manager: CacheManager, entries: Sequence[StepEntry], device, work_keys,
                  vocab_size: Optional[int] = None, min_bt_stride: int = 1):

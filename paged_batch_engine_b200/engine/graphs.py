@@ -15,7 +15,9 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import gc
 import time
+import weakref
 
 import numpy as np
 import torch
@@ -35,6 +37,7 @@ def _bucket(n: int, cap: Optional[int] = None) -> int:
 
 class DecodeStepContext(StepContext):
     """A StepContext whose arrays are fixed views of one persistent buffer."""
+    captured = True               # its launches are recorded once and replayed
 
     def __init__(self, manager, device, work_keys, batch: int, splits: int, bt_strides: Sequence[int]):
         self.manager, self.device = manager, device
@@ -169,7 +172,9 @@ class DecodeGraphs:
     """Captured decode steps of one runner, keyed by (batch bucket, split bucket)."""
 
     def __init__(self, runner, max_context: int):
-        self.runner = runner
+        # no reference cycle with the runner: an engine that goes out of use is freed at once,
+        # not by a later garbage collection that might fall into another engine's capture
+        self.runner = weakref.proxy(runner)
         self.max_context = int(max_context)
         self.graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, DecodeStepContext, torch.Tensor]] = {}
         self.replays = 0
@@ -237,7 +242,17 @@ class DecodeGraphs:
         from ..csrc import ops
         before = ops.launch_count()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = runner.model.forward(ctx, runner.storage)
+        # Destroying another engine's captured graphs (or pinned buffers) while this capture is
+        # open would invalidate it: collect what is collectable now, and keep the collector off
+        # until the capture has ended.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = runner.model.forward(ctx, runner.storage)
+        finally:
+            if gc_was_on:
+                gc.enable()
         self.launches_per_replay = ops.launch_count() - before
         return graph, ctx, logits

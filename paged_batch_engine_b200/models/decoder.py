@@ -23,6 +23,7 @@ class DecoderModel:
             raise ValueError(f"run dtype must be float32 or bfloat16, got {dtype}")
         self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
         self.blocks = [build_block(b, dtype, self.device) for b in spec.blocks]
+        self._native = None       # the blocks' descriptors for the host library (False: not this model)
         self.final_norm = build_part("norm", spec.final_norm, dtype, self.device)
         self.embed = None
         self.lm_head = None
@@ -88,6 +89,41 @@ class DecoderModel:
         return keys
 
     # ------------------------------------------------------------------ compute
+    def _native_descs(self, ctx):
+        """The blocks' descriptors for the host library's block executor, or None when this
+        model or this step stays with the Python parts: a block of other parts, a run order that
+        reads another layer's cache, a mixer with state of its own, a captured step (its launches
+        are recorded once and replayed, the interpreter's cost does not recur)."""
+        from ..csrc import native_exec
+        if self.dtype != torch.bfloat16 or not native_exec.enabled() or getattr(ctx, "captured", False):
+            return None
+        if self._native is None:
+            descs = [native_exec.block_desc(b) for b in self.blocks]
+            ok = all(d is not None for d in descs) and all(st.writes_cache for st in self.spec.run_order)
+            self._native = descs if ok else False
+        return self._native or None
+
+    def _forward_native(self, descs, ctx, storage, residual):
+        from ..csrc import native_exec
+        s = self.spec
+        T = residual.shape[0]
+        buffers, steps = {}, {}
+        deltas = [torch.empty((T, s.hidden_size), dtype=self.dtype, device=self.device) for _ in range(2)]
+        delta_in = None
+        for i, step in enumerate(s.run_order):
+            block = self.blocks[step.block]
+            cache = storage.layer(step.cache_layer, step.writes_cache)
+            m = block.mixer
+            key = (cache.group, m.num_heads, m.num_kv_heads, m.head_dim, m.tile_rows, m.window, m.kernel_kind)
+            sd = steps.get(key)
+            if sd is None:
+                sd = steps[key] = native_exec.step_desc(block, ctx, cache, residual, buffers)
+            fns = native_exec._exec_fns(m.head_dim, m.kernel_kind == "tc5")
+            delta_out = deltas[i & 1]
+            native_exec.run_block(descs[step.block], fns, sd, delta_in, delta_out, cache.k, cache.v)
+            delta_in = delta_out
+        return delta_in
+
     def forward(self, ctx, storage) -> torch.Tensor:
         """Runs the step's rows through every run step; returns float32 logits at the
         wanted rows, [wanted, vocab]."""
@@ -96,10 +132,14 @@ class DecoderModel:
         residual = torch.empty((T, s.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(residual, self.embed, ctx.token_ids)
         delta = None
-        for step in s.run_order:
-            block = self.blocks[step.block]
-            residual, delta = block.forward(residual, delta, ctx,
-                                            storage.layer(step.cache_layer, step.writes_cache))
+        native = self._native_descs(ctx)
+        if native is not None:
+            delta = self._forward_native(native, ctx, storage, residual)
+        else:
+            for step in s.run_order:
+                block = self.blocks[step.block]
+                residual, delta = block.forward(residual, delta, ctx,
+                                                storage.layer(step.cache_layer, step.writes_cache))
         if ctx.num_wanted == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.add_norm(residual, delta, rows=ctx.want_rows)
