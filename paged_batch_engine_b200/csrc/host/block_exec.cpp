@@ -10,6 +10,8 @@
 // Plain host C++: no CUDA headers, streams and handles are opaque pointers.
 #include <stdint.h>
 
+#include <chrono>
+
 #include "../kernels/attention_params.cuh"
 
 #define API extern "C" __attribute__((visibility("default")))
@@ -83,6 +85,8 @@ struct PbeStepDesc {
 };
 
 namespace {
+double g_stage_ns[16];        // host time spent in each stage's launcher (two clock reads a stage: tens of ns)
+long long g_stage_calls[16];
 // y[T, N] = x[T, K] w[N, K]^T, bfloat16 in and out, float32 accumulation
 int linear(const PbeExecFns* fn, const PbeStepDesc* s, const void* x, const void* w, void* y, int T, int N, int K,
            stream_t stream) {
@@ -105,11 +109,14 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
   const int T = s->num_rows, d = b->hidden, H = b->heads, KV = b->kv_heads, hd = b->head_dim;
   if (T <= 0) return 0;
   int rc, launches = 0;
-#define STAGE(n, call)                          \
-  do {                                          \
-    rc = (call);                                \
-    if (rc != 0) return -((n)*1000000 + rc);    \
-    ++launches;                                 \
+#define STAGE(n, call)                                                                              \
+  do {                                                                                              \
+    const auto t0_ = std::chrono::steady_clock::now();                                              \
+    rc = (call);                                                                                    \
+    g_stage_ns[n] += std::chrono::duration<double, std::nano>(std::chrono::steady_clock::now() - t0_).count(); \
+    ++g_stage_calls[n];                                                                             \
+    if (rc != 0) return -((n)*1000000 + rc);                                                        \
+    ++launches;                                                                                     \
   } while (0)
   STAGE(1, fn->add_rmsnorm(s->residual, delta_in, kBF16, b->norm1, s->x, kBF16, nullptr, T, d, b->eps1, stream));
   STAGE(2, linear(fn, s, s->x, b->w_qkv, s->qkv, T, (H + 2 * KV) * hd, d, stream));
@@ -164,6 +171,18 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
   STAGE(10, linear(fn, s, s->act, b->w_down, delta_out, T, d, b->inter, stream));
 #undef STAGE
   return launches;
+}
+
+// Host nanoseconds and calls per stage since the last reset (out: [16] doubles, [16] counts).
+API void pbe_exec_profile(double* ns, long long* calls, int reset) {
+  for (int i = 0; i < 16; ++i) {
+    ns[i] = g_stage_ns[i];
+    calls[i] = g_stage_calls[i];
+    if (reset) {
+      g_stage_ns[i] = 0;
+      g_stage_calls[i] = 0;
+    }
+  }
 }
 
 API int pbe_exec_abi() { return (int)(sizeof(PbeExecFns) + sizeof(PbeBlockDesc) * 1000 + sizeof(PbeStepDesc)); }

@@ -103,6 +103,14 @@ def run_block(block: BlockDesc, fns: ExecFns, step: StepDesc, delta_in: Optional
     ops.count_launches(rc)
 
 
+def stage_profile(reset: bool = True) -> dict:
+    """Host microseconds per call of each stage's launcher since the last reset."""
+    ns = (ctypes.c_double * 16)()
+    calls = (ctypes.c_longlong * 16)()
+    _lib().pbe_exec_profile(ns, calls, 1 if reset else 0)
+    return {_STAGES[i]: round(ns[i] / calls[i] / 1e3, 2) for i in _STAGES if calls[i]}
+
+
 def block_desc(block) -> Optional[BlockDesc]:
     """The descriptor of a pre-norm block of RMSNorm, grouped-query attention with rotate-half
     rotary position encoding, and SwiGLU, all in bfloat16; None for anything else (those blocks

@@ -243,9 +243,7 @@ class DecodeGraphs:
         before = ops.launch_count()
         graph = torch.cuda.CUDAGraph()
         # Destroying another engine's captured graphs (or pinned buffers) while this capture is
-        # open would invalidate it: collect what is collectable now, and keep the collector off
-        # until the capture has ended.
-        gc.collect()
+        # open would invalidate it: the collector stays off until the capture has ended.
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
