@@ -19,9 +19,9 @@
 typedef void* stream_t;
 
 namespace {
-constexpr int kF32 = 0, kBF16 = 1;                       // dtype codes of the kernel libraries
+constexpr int kBF16 = 1;                                 // dtype code of the kernel libraries
 constexpr int kOpN = 0, kOpT = 1;                        // cublasOperation_t
-constexpr int kR16BF = 14, kR32F = 0;                    // cudaDataType
+constexpr int kR16BF = 14;                               // cudaDataType
 constexpr int kCompute32F = 68, kGemmDefaultTensorOp = 99;
 constexpr int kSkinnyMaxRows = 16;
 }  // namespace

@@ -55,7 +55,7 @@ def _addr(fn) -> int:
     return ctypes.cast(fn, c_void_p).value
 
 
-def _exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
+def exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
     """The launchers' addresses for one head size (the attention libraries are built per head size)."""
     key = (int(head_dim), bool(use_tc5))
     f = _fns.get(key)
@@ -155,7 +155,7 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
     meta = ctx.attention_work(cache.group, H // KV, m.tile_rows, m.window, H, hd)
     group = ctx.group(cache.group)
     inv_freq, rotary_dim, interleaved = m.position.kernel_args()
-    splits = m._fused_decode(meta, cache, inv_freq, rotary_dim, interleaved)
+    splits = m.fused_decode_splits(meta, cache, inv_freq, rotary_dim, interleaved)
     ap = ops.AttnParams(
         q=None, k_cache=None, v_cache=None, out=None,
         part_o=meta.part_o.data_ptr() if meta.part_o is not None else None,

@@ -78,7 +78,7 @@ class GQAttention(Mixer):
             self.b_o = tensors.pop(prefix + "o_proj.bias").to(torch.float32).contiguous()
 
     # ---- compute
-    def _fused_decode(self, meta, cache, inv_freq, rotary_dim, interleaved) -> int:
+    def fused_decode_splits(self, meta, cache, inv_freq, rotary_dim, interleaved) -> int:
         """Blocks per (request, key/value head) for the fused decode kernel, 0: not this step."""
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         if not (meta.decode_rows > 0 and cache.writes and inv_freq is not None and rotary_dim == hd
@@ -95,7 +95,7 @@ class GQAttention(Mixer):
         group = ctx.group(cache.group)
         k_pages, v_pages = cache.k, cache.v
         meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
-        splits = self._fused_decode(meta, cache, inv_freq, rotary_dim, interleaved)
+        splits = self.fused_decode_splits(meta, cache, inv_freq, rotary_dim, interleaved)
         if splits:
             # decoded tokens only, every block of the step resident at once: position encoding, cache
             # write, attention and the merge of the key splits in one launch
