@@ -575,3 +575,66 @@ def test_attention_decode_fused(H, KV, hd, P, window, ctxs, splits):
     for (page, off, kn), (_, _, vn) in zip(new_k, new_v):
         assert (kc[page, :, off].float().cpu() - kn.float()).abs().max().item() <= 2 ** -6 * max(1.0, kn.float().abs().max().item())
         assert torch.equal(vc[page, :, off].cpu(), vn)
+
+
+@pytest.mark.parametrize("window", [None, 700])
+def test_attention_decode_fused_one_key_stands_out(window):
+    """One key gets all the weight (rotation switched off by zero frequencies, so that the
+    score is the plain dot product): at the first key, on both sides of the kernel's own split
+    boundaries (2,101 keys in 8 parts of 320; 700 in parts of 128 with the window), in the last
+    page, at the new token itself, and - with a window - at the window's first key; just outside
+    the window it must not be seen."""
+    from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+    from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
+    o = ops()
+    H, KV, hd, P, ctx_len = 8, 2, 64, 16, 2100
+    lo = 0 if window is None else ctx_len - window + 1           # first visible key of the new token
+    part = 320 if window is None else 128                         # keys per block: ceil(span / 512) * 64
+    targets = [lo, lo + part - 1, lo + part, lo + 4 * part - 1, lo + 4 * part, 2099, ctx_len]   # ctx_len: its own key
+    if window is not None:
+        targets = [t for t in targets if t >= lo] + [lo - 1]       # the last one is outside the window
+    R = len(targets)
+    g = torch.Generator().manual_seed(5)
+    pages = R * ((ctx_len + 1 + P - 1) // P) + 2
+    m = CacheManager([KVGroupSpec((0,), KV, hd, window)], P, pages, max_requests=R)
+    kc = torch.full((pages, KV, P, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((pages, KV, P, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    width = (H + 2 * KV) * hd
+    qkv = torch.zeros(R, width)
+    qkv[:, 0:H * hd:hd] = 40.0                                     # every query head: 40 e0
+    entries, values = [], []
+    for r, j in enumerate(targets):
+        h = m.add_request()
+        assert m.reserve(h, ctx_len + 1)
+        k = torch.randn(ctx_len + 1, KV, hd, generator=g) * 0.05
+        v = torch.randn(ctx_len + 1, KV, hd, generator=g)
+        k[:, :, 0] = 0
+        if j < ctx_len:
+            k[j, :, 0] = 8.0
+        else:
+            qkv[r, H * hd:(H + KV) * hd:hd] = 8.0                  # the new token's own key stands out
+        new_v = torch.randn(KV, hd, generator=g)
+        qkv[r, (H + KV) * hd:] = new_v.reshape(-1)
+        v[ctx_len] = new_v
+        table = m.block_table(h)
+        for pos in range(ctx_len):
+            kc[table[pos // P], :, pos % P] = k[pos].to(torch.bfloat16).to(DEV)
+            vc[table[pos // P], :, pos % P] = v[pos].to(torch.bfloat16).to(DEV)
+        m.commit(h, ctx_len)
+        values.append(v[j].to(torch.bfloat16).float())
+        entries.append(StepEntry(h, [0]))
+    G = H // KV
+    _, tile_rows, _ = o.attention_kernel_config(hd, torch.bfloat16, "mma")
+    ctx = StepContext(m, entries, torch.device(DEV), [(0, G, tile_rows, window)])
+    meta = ctx.attention_work(0, G, tile_rows, window, H, hd)
+    out = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    inv_freq = torch.zeros(hd // 2, device=DEV)
+    o.attention_decode_fused(qkv.to(torch.bfloat16).to(DEV), None, kc, vc, out, meta, ctx.positions,
+                             ctx.group(0).slots, inv_freq, R, H, KV, hd, hd ** -0.5, window, P, splits=8)
+    got = out.float().cpu().view(R, H, hd)
+    assert torch.isfinite(got).all()
+    for r, j in enumerate(targets):
+        seen = window is None or j >= lo
+        for head in range(H):
+            close = torch.allclose(got[r, head], values[r][head // G], atol=3e-2)
+            assert close == seen, (r, j, head, seen)
