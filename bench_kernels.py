@@ -2,7 +2,7 @@
 """Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
 each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
 
-    python bench_kernels.py [skinny|attn_decode|attn_prefill|tc5|all] [--once]
+    python bench_kernels.py [skinny|attn_decode|attn_fused|attn_prefill|tc5|all] [--once]
 
 Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
 buffer is written between launches, so every launch starts with a cold L2)."""
@@ -61,6 +61,33 @@ def attention_case(reqs, H=28, KV=4, hd=128, P=16, kind=None):
     return run, sum(c + n for c, n in reqs) * KV * hd * 2 * 2
 
 
+def fused_decode_case(B, ctx_len, H=28, KV=4, hd=128, P=16):
+    """One decoded token a request through the fused kernel (position encoding, cache write,
+    attention, merge of the key splits in one launch)."""
+    from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
+    from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
+    pages = B * ((ctx_len + 1 + P - 1) // P) + 2
+    m = CacheManager([KVGroupSpec((0,), KV, hd)], P, pages, max_requests=B)
+    entries = []
+    for _ in range(B):
+        h = m.add_request()
+        m.reserve(h, ctx_len + 1)
+        m.commit(h, ctx_len)
+        entries.append(StepEntry(h, [0]))
+    ctx = StepContext(m, entries, torch.device(DEV), [(0, H // KV, 128, None)])
+    meta = ctx.attention_work(0, H // KV, 128, None, H, hd)
+    k = torch.randn(pages, KV, P, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(pages, KV, P, hd, device=DEV).to(torch.bfloat16)
+    qkv = torch.randn(B, (H + 2 * KV) * hd, device=DEV).to(torch.bfloat16)
+    bias = torch.randn((H + 2 * KV) * hd, device=DEV)
+    inv_freq = (1e6 ** (-torch.arange(0, hd, 2, dtype=torch.float32) / hd)).to(DEV)
+    out = torch.empty(B, H * hd, dtype=torch.bfloat16, device=DEV)
+    splits = ops.fused_decode_splits(B, KV, ctx_len + 1, torch.device(DEV))
+    run = lambda: ops.attention_decode_fused(qkv, bias, k, v, out, meta, ctx.positions, ctx.group(0).slots, inv_freq,
+                                             B, H, KV, hd, hd ** -0.5, None, P, splits=splits)
+    return run, B * (ctx_len + 1) * KV * hd * 2 * 2, splits
+
+
 def main():
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
@@ -75,6 +102,12 @@ def main():
             run, kv_bytes = attention_case([(2047, 1)] * B)
             t = timed(run, flush)
             print(f"attention decode B={B} ctx 2048: {t * 1e3:.1f} us, {kv_bytes / t / 1e6:.0f} GB/s")
+    if what in ("attn_fused", "all"):
+        for B, ctx_len in ((1, 2048), (8, 2048), (8, 8192), (64, 2048)):
+            run, kv_bytes, splits = fused_decode_case(B, ctx_len)
+            t = timed(run, flush)
+            print(f"fused decode attention B={B} ctx {ctx_len} ({splits} blocks a cluster): {t * 1e3:.1f} us, "
+                  f"{kv_bytes / t / 1e6:.0f} GB/s")
     if what in ("attn_prefill", "all"):
         for kind in ("mma", "tc5"):
             for T in (2048, 8192):

@@ -313,6 +313,7 @@ __device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, c
 // through distributed shared memory, each block one slice of the head dimension.  One launch
 // stands for three (position encoding and cache write, attention, merge of the splits).
 constexpr int FUSED_MAX_SPLITS = 8;
+constexpr int FUSED_NEWKV = 2 * HD;
 constexpr int FUSED_MAX_KEYS_PER_BLOCK = 4096;     // beyond that the other path streams better
 
 // NST: key/value tiles in shared memory (two everywhere; the fused mode also has an instance
@@ -329,6 +330,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   bf16* Ks = Qs + QROWS * LDS;                         // [NST][BN][LDS]
   bf16* Vs = Ks + NST * BN * LDS;                      // [NST][BN][LDS]
   __shared__ int s_pages[MAX_SMEM_PAGES];
+  __shared__ bf16 s_newkv[FUSED_NEWKV];                // fused mode: the new token's key and value rows
 
   // The work list, the lengths and the block tables are written by the host before the
   // step's first kernel: they are read before the dependency on the previous kernel is awaited.
@@ -432,7 +434,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       if ((BN * CPR) % NTHREADS != 0 && c >= BN * CPR) break;
       const int j = c / CPR, col = c - j * CPR;
       const int key = ts + j;
-      bool valid = key >= k_begin && key < k_end;
+      // fused mode: the new token's own row is not read from the cache (this very launch writes
+      // it); it is put into the tile from shared memory once the tile has landed
+      bool valid = key >= k_begin && key < k_end && !(FUSED && key == sl - 1);
       size_t off = 0;
       if (valid) {
         const int blk = pshift >= 0 ? key >> pshift : key / P;
@@ -448,14 +452,11 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
 
   if constexpr (FUSED) {
     // The keys and values of earlier tokens do not depend on the kernel before this one: the
-    // first key tile is requested before the wait, unless it is the one that holds the new
-    // token (whose key and value this block writes below).
+    // first key tiles are requested before the wait.
     const int pos = sl - 1;
     const bool owner = pos >= k_begin && pos < k_end;
-    int issued = 0;                                            // key tiles requested so far, one group each
-    for (; issued < NST - 1 && issued < n_tiles; ++issued) {
-      if (owner && tile0 + (issued + 1) * BN > pos) break;     // the tile with the new token: after the write
-      load_tile(tile0 + issued * BN, issued);
+    for (int i = 0; i < NST - 1; ++i) {
+      if (i < n_tiles) load_tile(tile0 + i * BN, i);
       cp_async_commit();
     }
     pdl_wait();
@@ -507,20 +508,23 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       const int page = fused_slot / P, off = fused_slot - page * P;
       bf16* kdst = (bf16*)p.k_cache + (((size_t)page * KV + kvh) * P + off) * HD;
       bf16* vdst = (bf16*)p.v_cache + (((size_t)page * KV + kvh) * P + off) * HD;
+      // into the cache for the steps to come, and into shared memory for this one
       for (int i = tid; i < HALF; i += NTHREADS) {
         const float a = kvraw[i], b = kvraw[i + HALF];
         const float c = trig[i], sn = trig[HALF + i];
-        kdst[i] = __float2bfloat16_rn(a * c - b * sn);
-        kdst[i + HALF] = __float2bfloat16_rn(b * c + a * sn);
+        const bf16 ka = __float2bfloat16_rn(a * c - b * sn), kb = __float2bfloat16_rn(b * c + a * sn);
+        kdst[i] = ka;
+        kdst[i + HALF] = kb;
+        s_newkv[i] = ka;
+        s_newkv[i + HALF] = kb;
       }
-      for (int i = tid; i < HD; i += NTHREADS) vdst[i] = __float2bfloat16_rn(kvraw[HD + i]);
-      __threadfence();          // the tile loads read the new key and value back from memory
+      for (int i = tid; i < HD; i += NTHREADS) {
+        const bf16 vv = __float2bfloat16_rn(kvraw[HD + i]);
+        vdst[i] = vv;
+        s_newkv[HD + i] = vv;
+      }
     }
-    __syncthreads();            // Q is complete, the scratch is free, the new key and value are written
-    for (; issued < NST - 1; ++issued) {
-      if (issued < n_tiles) load_tile(tile0 + issued * BN, issued);
-      cp_async_commit();
-    }
+    __syncthreads();            // Q is complete, the scratch is free
   } else {
     if (n_tiles > 0) load_tile(tile0, 0);
     cp_async_commit();
@@ -575,6 +579,18 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     cp_async_commit();
     cp_async_wait<NST - 1>();    // tile t (and Q) have landed
     __syncthreads();
+    if constexpr (FUSED) {
+      const int pos = sl - 1;
+      if (pos >= k_begin && pos < k_end && pos >= ts && pos < ts + BN) {   // block-uniform: the new token's tile
+        bf16* krow = Ks + ((t % NST) * BN + (pos - ts)) * LDS;
+        bf16* vrow = Vs + ((t % NST) * BN + (pos - ts)) * LDS;
+        for (int i = tid; i < HD; i += NTHREADS) {
+          krow[i] = s_newkv[i];
+          vrow[i] = s_newkv[HD + i];
+        }
+        __syncthreads();
+      }
+    }
     const bf16* kt = Ks + (t % NST) * BN * LDS;
     const bf16* vt = Vs + (t % NST) * BN * LDS;
     if constexpr (KEYS) {
