@@ -127,6 +127,8 @@ def block_desc(block) -> Optional[BlockDesc]:
     tensors = [m.w_qkv, m.w_o, f.w_gate_up, f.w_down]
     if any(t is None or t.dtype != torch.bfloat16 or not t.is_contiguous() for t in tensors):
         return None
+    if m.position.applies_itself:
+        return None
     inv_freq, rotary_dim, interleaved = m.position.kernel_args()
     if inv_freq is None or rotary_dim != m.head_dim or interleaved:
         return None

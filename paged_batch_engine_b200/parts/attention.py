@@ -62,7 +62,7 @@ class GQAttention(Mixer):
                       ParamSpec(prefix + "v_proj.bias", (kv_out,))]
         if self.o_bias:
             specs.append(ParamSpec(prefix + "o_proj.bias", (self.hidden_size,)))
-        return specs
+        return specs + self.position.param_specs(prefix + "position.")
 
     def load(self, tensors, prefix):
         ws = [tensors.pop(prefix + f"{n}_proj.weight") for n in "qkv"]
@@ -76,6 +76,7 @@ class GQAttention(Mixer):
         self.w_o = tensors.pop(prefix + "o_proj.weight").contiguous()
         if self.o_bias:
             self.b_o = tensors.pop(prefix + "o_proj.bias").to(torch.float32).contiguous()
+        self.position.load(tensors, prefix + "position.")
 
     # ---- compute
     def fused_decode_splits(self, meta, cache, inv_freq, rotary_dim, interleaved) -> int:
@@ -87,11 +88,28 @@ class GQAttention(Mixer):
             return 0
         return ops.fused_decode_splits(meta.decode_rows, KV, meta.longest_keys, meta.q_len.device)
 
+    def _apply_position(self, qkv, positions):
+        T = qkv.shape[0]
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        f = qkv.float()
+        if self.b_qkv is not None:
+            f = f + self.b_qkv
+        q, k = self.position.apply(f[:, :H * hd].reshape(T, H, hd), f[:, H * hd:(H + KV) * hd].reshape(T, KV, hd),
+                                   positions)
+        return torch.cat([q.reshape(T, H * hd), k.reshape(T, KV * hd), f[:, (H + KV) * hd:]], dim=1).to(self.dtype)
+
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = ops.linear(x, self.w_qkv, None, out_dtype=self.dtype)
-        inv_freq, rotary_dim, interleaved = self.position.kernel_args()
+        bias = self.b_qkv
+        if self.position.applies_itself:
+            # a position encoding with code of its own: it gets q and k with the bias added and
+            # the kernel below only copies (no rotation, no bias)
+            qkv, bias = self._apply_position(qkv, ctx.positions), None
+            inv_freq, rotary_dim, interleaved = None, 0, False
+        else:
+            inv_freq, rotary_dim, interleaved = self.position.kernel_args()
         group = ctx.group(cache.group)
         k_pages, v_pages = cache.k, cache.v
         meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
@@ -100,12 +118,12 @@ class GQAttention(Mixer):
             # decoded tokens only, every block of the step resident at once: position encoding, cache
             # write, attention and the merge of the key splits in one launch
             out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
-            ops.attention_decode_fused(qkv, self.b_qkv, k_pages, v_pages, out, meta, ctx.positions, group.slots,
+            ops.attention_decode_fused(qkv, bias, k_pages, v_pages, out, meta, ctx.positions, group.slots,
                                        inv_freq, meta.decode_rows, H, KV, hd, self.scale, self.window,
                                        ctx.page_tokens, splits=splits)
             return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
         q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
-        ops.rope_kv_write(qkv, self.b_qkv, q, k_pages if cache.writes else None,
+        ops.rope_kv_write(qkv, bias, q, k_pages if cache.writes else None,
                           v_pages if cache.writes else None, ctx.positions, group.slots, inv_freq,
                           H, KV, hd, rotary_dim, ctx.page_tokens, interleaved)
         out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)

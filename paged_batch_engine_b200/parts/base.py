@@ -12,7 +12,9 @@ Interfaces
 Norm:       ``add_norm(residual, delta, rows=None) -> normed``: residual += delta (float32,
             in place), then the normalised rows in the run dtype.
 PositionEncoding: ``kernel_args() -> (inv_freq | None, rotary_dim, interleaved)`` for the
-            mixer that applies it, or ``apply(q, k, positions)`` for one that brings its own code.
+            mixer that applies it; one that brings its own code sets ``applies_itself`` and has
+            ``apply(q, k, positions) -> (q, k)`` on float32 [rows, heads, head_dim] tensors
+            (projection bias already added); its tensors live under the mixer's prefix + "position.".
 Mixer:      ``cache_need() -> KVNeed | StateNeed | None`` (what it keeps between steps) and
             ``forward(x, ctx, cache) -> y`` over all rows of the step.
 FeedForward: ``forward(x, ctx) -> y``.
@@ -64,7 +66,12 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    applies_itself = False      # True: the mixer calls apply() instead of handing kernel_args() to its kernel
+
     def kernel_args(self):
+        raise NotImplementedError
+
+    def apply(self, q, k, positions):
         raise NotImplementedError
 
 

@@ -324,3 +324,185 @@ def test_toy_architecture_registers_builds_and_steps():
                 assert out.shape == want[rid][:len(out)].shape
                 err = (out - want[rid][:len(out)]).abs().max().item()
                 assert err <= tol * max(1.0, want[rid].abs().max().item()), (dtype, plan, rid, err)
+
+
+# ------------------------------------------------------------------ a toy feed-forward with routing, a toy position encoding
+def make_toy_routed_ffn_class():
+    from paged_batch_engine_b200.parts import FeedForward
+    from paged_batch_engine_b200.weights import ParamSpec
+
+    class ToyRoutedFFN(FeedForward):
+        """Router logits x R^T in float32, softmax over the ``top_k`` largest, and the weighted sum
+        of those experts' relu(x A_e^T) B_e^T: a feed-forward whose experts are chosen per token."""
+
+        def __init__(self, hidden_size, experts, expert_size, top_k, dtype, device):
+            self.d, self.E, self.m, self.k, self.dtype = hidden_size, experts, expert_size, top_k, dtype
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "router", (self.E, self.d)),
+                    ParamSpec(prefix + "a", (self.E * self.m, self.d)), ParamSpec(prefix + "b", (self.E * self.d, self.m))]
+
+        def load(self, tensors, prefix):
+            self.router = tensors.pop(prefix + "router").float()
+            self.a = tensors.pop(prefix + "a").float().view(self.E, self.m, self.d)
+            self.b = tensors.pop(prefix + "b").float().view(self.E, self.d, self.m)
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            top, idx = (xf @ self.router.t()).topk(self.k, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            y = torch.zeros_like(xf)
+            for e in range(self.E):
+                rows, slot = (idx == e).nonzero(as_tuple=True)
+                if len(rows):
+                    h = torch.relu(xf[rows] @ self.a[e].t()) @ self.b[e].t()
+                    y.index_add_(0, rows, h * gate[rows, slot].unsqueeze(1))
+            return y.to(self.dtype)
+
+    return ToyRoutedFFN
+
+
+def make_toy_position_class():
+    from paged_batch_engine_b200.parts import PositionEncoding
+    from paged_batch_engine_b200.weights import ParamSpec
+
+    class ToyTablePosition(PositionEncoding):
+        """q and k get a learned vector of their position (modulo ``period``) added: a position
+        encoding with a tensor of its own and code of its own."""
+        applies_itself = True
+
+        def __init__(self, head_dim, period, dtype, device):
+            self.hd, self.period = head_dim, period
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "table", (self.period, self.hd))]
+
+        def load(self, tensors, prefix):
+            self.table = tensors.pop(prefix + "table").float()
+
+        def apply(self, q, k, positions):
+            add = self.table[(positions % self.period).long()].unsqueeze(1)
+            return q + add, k + add
+
+    return ToyTablePosition
+
+
+def plain_toy_routed_ffn(f, w, p, E, top_k):
+    """Per token: the top_k router logits, their softmax, the weighted experts."""
+    out = []
+    for t in range(f.shape[0]):
+        logits = w[p + "router"] @ f[t]
+        order = sorted(range(E), key=lambda e: -logits[e].item())[:top_k]
+        gate = torch.softmax(torch.stack([logits[e] for e in order]), 0)
+        y = torch.zeros_like(f[t])
+        for g, e in zip(gate, order):
+            a = w[p + "a"].view(E, -1, f.shape[1])[e]
+            b = w[p + "b"].view(E, f.shape[1], -1)[e]
+            y = y + g * (b @ torch.relu(a @ f[t]))
+        out.append(y)
+    return torch.stack(out)
+
+
+def plain_toy_model_2(c, w, tokens):
+    """Block 0: attention with the table position encoding, routed feed-forward; block 1:
+    attention with rotary encoding and a window, SwiGLU."""
+    T, H, KV, hd = len(tokens), c["heads"], c["kv"], c["hd"]
+    pos = torch.arange(T)
+    x = plain.embedding(tokens, w["emb"])
+    h = plain.rmsnorm(x, w["A.n1.weight"], c["eps"])
+    q = plain.linear(h, w["A.at.q_proj.weight"], w["A.at.q_proj.bias"]).view(T, H, hd)
+    k = plain.linear(h, w["A.at.k_proj.weight"], w["A.at.k_proj.bias"]).view(T, KV, hd)
+    v = plain.linear(h, w["A.at.v_proj.weight"], w["A.at.v_proj.bias"]).view(T, KV, hd)
+    add = w["A.at.position.table"][pos % c["period"]].unsqueeze(1)
+    o = plain.causal_attention(q + add, k + add, v, hd ** -0.5)
+    x = x + plain.linear(o.reshape(T, H * hd), w["A.at.o_proj.weight"])
+    f = plain.rmsnorm(x, w["A.n2.weight"], c["eps"])
+    x = x + plain_toy_routed_ffn(f, w, "A.ff.", c["experts"], c["top_k"])
+    acfg = dict(num_attention_heads=H, num_key_value_heads=KV, head_dim=hd, hidden_size=c["d"], rope_theta=c["theta"])
+    h = plain.rmsnorm(x, w["B.n1.weight"], c["eps"])
+    x = x + plain.attention_block(h, pos, w, "B.at.", acfg, c["window"])
+    f = plain.rmsnorm(x, w["B.n2.weight"], c["eps"])
+    x = x + plain.feed_forward(f, w, "B.ff.")
+    return plain.linear(plain.rmsnorm(x, w["fn.weight"], c["eps"]), w["head"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_toy_routed_feed_forward_and_toy_position_encoding(dtype):
+    """A feed-forward with routing and a position encoding with code and a tensor of its own, both
+    defined here, are registered, chosen layer by layer beside the package's own parts, and
+    stepped whole, in portions and token by token, with no change to the package."""
+    from paged_batch_engine_b200.config import (BlockSpec, ModelSpec, PartSpec, RunStep, load_config,
+                                                register_architecture)
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    from paged_batch_engine_b200.engine.runner import ModelRunner, build_model
+    from paged_batch_engine_b200.parts import register_part
+    from paged_batch_engine_b200.weights import random_state_dict
+
+    register_part("feed_forward", "toy_routed", make_toy_routed_ffn_class(), replace=True)
+    register_part("position", "toy_table", make_toy_position_class(), replace=True)
+
+    @dataclass
+    class Toy2Config:
+        d: int = 48
+        heads: int = 6
+        kv: int = 3
+        hd: int = 32
+        inter: int = 72
+        vocab: int = 101
+        eps: float = 3e-6
+        theta: float = 500.0
+        period: int = 7
+        experts: int = 3
+        expert_size: int = 20
+        top_k: int = 1
+        window: int = 24
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+        def model_spec(self):
+            norm = PartSpec("rmsnorm", dict(size=self.d, eps=self.eps))
+            att = dict(hidden_size=self.d, num_heads=self.heads, num_kv_heads=self.kv, head_dim=self.hd)
+            att_a = PartSpec("attention", dict(att, position=PartSpec("toy_table", dict(head_dim=self.hd, period=self.period))))
+            att_b = PartSpec("attention", dict(att, window=self.window,
+                                               position=PartSpec("rope", dict(theta=self.theta, head_dim=self.hd))))
+            routed = PartSpec("toy_routed", dict(hidden_size=self.d, experts=self.experts, expert_size=self.expert_size,
+                                                 top_k=self.top_k))
+            dense = PartSpec("swiglu", dict(hidden_size=self.d, intermediate_size=self.inter))
+            names = dict(norm_mixer="n1.", norm_feed_forward="n2.", feed_forward="ff.", mixer="at.")
+            blocks = (BlockSpec("prenorm", att_a, routed, norm, norm, "A.", names),
+                      BlockSpec("prenorm", att_b, dense, norm, norm, "B.", names))
+            return ModelSpec("Toy2ForCausalLM", self.d, self.vocab, blocks, (RunStep(0, 0), RunStep(1, 1)), norm,
+                             "emb", "fn.", "head", 512)
+
+    register_architecture("Toy2ForCausalLM", Toy2Config, replace=True)
+    # one expert a token in float32; in bfloat16 every expert with its softmax weight, so that a
+    # near tie between two router logits cannot send a token to another expert than the plain one
+    top_k = 1 if dtype == torch.float32 else 3
+    arch, cfg = load_config({"architectures": ["Toy2ForCausalLM"], "top_k": top_k})
+    model = build_model(cfg, dtype, torch.device(DEV))
+    assert [type(n).__name__ for n in model.cache_needs] == ["KVNeed", "KVNeed"]
+    assert model.cache_needs[0].window is None and model.cache_needs[1].window == 24
+    sd = random_state_dict(model.param_specs(), seed=5, dtype=torch.float32)
+    assert "A.at.position.table" in sd and "A.ff.router" in sd
+    sd["A.at.position.table"] = sd["A.at.position.table"] * 20      # the position term decides the scores
+    sd["A.ff.router"] = sd["A.ff.router"] * 30
+    if dtype == torch.bfloat16:
+        sd = {k: (v.to(torch.bfloat16) if v.dim() > 1 else v) for k, v in sd.items()}
+    model.build_kernels()
+    model.load({k: v.to(DEV) for k, v in sd.items()})
+    runner = ModelRunner(model, page_tokens=8, num_pages=16, max_requests=2)
+    toks = torch.randint(0, 101, (45,), generator=torch.Generator().manual_seed(4)).tolist()
+    want = plain_toy_model_2(cfg.__dict__, {n: t.float() for n, t in sd.items()}, toks)
+    tol = 3e-5 if dtype == torch.float32 else 0.05
+    for cuts in ([45], [13, 2, 22] + [1] * 8, [40, 5]):
+        h = runner.cache.add_request()
+        got, i = [], 0
+        for n in cuts:
+            assert runner.cache.reserve(h, n)
+            got.append(runner.step([StepEntry(h, toks[i:i + n], list(range(n)))]).float().cpu())
+            i += n
+        runner.cache.free(h)
+        err = (torch.cat(got) - want).abs().max().item()
+        assert err <= tol * max(1.0, want.abs().max().item()), (dtype, cuts, err)
