@@ -97,6 +97,23 @@ def library_path(name: str, defines: Optional[Dict[str, object]] = None,
     return source, os.path.join(build_dir(), fname)
 
 
+def _drop_older_builds(out: str) -> None:
+    """After a build: libraries of the same name and defines made from earlier sources (same file
+    name up to the hash) are of no use any more and only grow the build folder."""
+    folder, fname = os.path.split(out)
+    stem = fname[:fname.rfind("-") + 1]
+    try:
+        for other in os.listdir(folder):
+            if other != fname and other.startswith(stem) and other.endswith(".so") and \
+                    len(other) == len(fname):
+                try:
+                    os.remove(os.path.join(folder, other))
+                except OSError:
+                    pass
+    except OSError:
+        pass
+
+
 def compile_library(name: str, defines: Optional[Dict[str, object]] = None,
                     extra_flags: Sequence[str] = (), verbose: bool = True) -> str:
     """Build one library if it is not there yet; returns its path."""
@@ -130,6 +147,7 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None,
             os.remove(tmp)
         raise BuildError(f"nvcc failed for {source} ({' '.join(cmd)}):\n{log}")
     os.replace(tmp, out)
+    _drop_older_builds(out)
     if verbose:
         print(f"[pbe] built {label} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out
@@ -209,6 +227,7 @@ def load_host_library(name: str) -> ctypes.CDLL:
                 os.remove(tmp)
             raise BuildError(f"{cxx} failed for {source}:\n{proc.stdout}")
         os.replace(tmp, out)
+        _drop_older_builds(out)
     with _lock:
         lib = _loaded.get(out)
         if lib is None:

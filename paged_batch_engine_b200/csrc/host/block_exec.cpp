@@ -136,6 +136,8 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
     fp.slots = s->slots;
     fp.inv_freq = b->inv_freq;
     fp.num_requests = s->decode_rows;
+    fp.num_pages = s->num_pages;
+    fp.tiles_by_page = 0;
     ap.q = nullptr;
     ap.max_splits = s->fused_splits;
     ap.kinds = 1;

@@ -1,7 +1,8 @@
 // Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16, float32
 // accumulation), flash style: scores, softmax statistics and the output accumulator never
-// leave the registers, keys and values stream from the pages through shared memory with
-// cp.async double buffering.
+// leave the registers, keys and values stream from the pages through shared memory, double or
+// triple buffered (bulk copies of whole rows that report to an mbarrier of the buffer; the
+// warp-private decode instance uses cp.async).
 //
 // Work decomposition is the one of attention_simple.cu and the two kernels are
 // interchangeable: a request's rows are packed with the query heads that share a key/value
@@ -21,8 +22,12 @@
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "attention_params.cuh"
 #include "common.cuh"
+#include "kv_tensor_map.cuh"
 #include "pdl.cuh"
 
 using namespace pbe;
@@ -54,6 +59,52 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
+// Key and value rows come from the pages as bulk copies (one row of a head a copy, one copy a
+// thread and tile) that report to an mbarrier of the tile's buffer; the barrier's phase ends when
+// every row has either landed or been filled with zeros by its thread.
+__device__ int g_wait_gave_up = 0;     // a bounded mbarrier wait ran out (never in a correct run)
+constexpr long long WAIT_CLOCKS = 2000000000LL;
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_row(void* smem_dst, const void* gmem, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem), "r"(bytes), "r"(bar) : "memory");
+}
+[[maybe_unused]] __device__ __forceinline__ void tma_box(void* smem_dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_wait(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  if (done) return;
+  const long long t0 = clock64();
+  // once any wait has run out, the later ones of the launch give up at once
+  while (*reinterpret_cast<volatile int*>(&g_wait_gave_up) == 0) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return;
+    if (clock64() - t0 > WAIT_CLOCKS) break;
+  }
+  atomicExch(&g_wait_gave_up, 1);
+}
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -82,6 +133,26 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+#ifdef PBE_ATTN_TRACE
+// clock stamps of thread 0 of block (0,0,0): [16 + 8 tile + k]
+__device__ long long g_trace[1024];
+#define TRACE(ptr, k) do { if (ptr) (ptr)[k] = clock64(); } while (0)
+#else
+#define TRACE(ptr, k) do { } while (0)
+#endif
+
+// Where the 16-byte chunk `chunk` of row `row` of a key or value tile lies.  Padded layout: rows
+// of LDS elements.  Swizzled layout (tiles that arrived as tensor-map boxes): the head dimension
+// in blocks of 64 elements, each block ROWS rows of 128 bytes, chunks exchanged by the row's low bits.
+template <bool SWZ, int ROWS>
+__device__ __forceinline__ const bf16* tile_chunk(const bf16* tile, int row, int chunk) {
+  if constexpr (SWZ)
+    return reinterpret_cast<const bf16*>(reinterpret_cast<const char*>(tile) + (chunk >> 3) * (ROWS * 128) + row * 128 +
+                                         (((chunk & 7) ^ (row & 7)) << 4));
+  else
+    return tile + row * LDS + chunk * 8;
+}
+
 struct RowInfo {      // the two rows of this thread's accumulator fragment
   int pos[2];         // absolute position of the row's query (-1: no such row)
   int lo[2];          // first visible key
@@ -91,18 +162,28 @@ struct RowInfo {      // the two rows of this thread's accumulator fragment
 // sit at row `krow0` of the shared K and V tiles.  Updates m, l (log2 domain) and o.
 // LOCAL_SUM: l holds this thread's share of the row sum (its own columns); the caller adds
 // the four lanes of a row once, at the end, instead of two shuffles a tile.
-template <int NKT, bool MASK, bool QREG = false, bool LOCAL_SUM = false>
+template <int NKT, bool MASK, bool QREG = false, bool LOCAL_SUM = false, bool SWZ = false, int ROWS = 64>
 __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
                                              const bf16* __restrict__ Vs, int krow0, int key0,
                                              int k_begin, int k_end, const RowInfo& ri, float scale_log2,
                                              float (&m)[2], float (&l)[2], float (&o)[ONT][4], int lane,
-                                             const unsigned (*qreg)[4] = nullptr) {
+                                             const unsigned (*qreg)[4] = nullptr, long long* tr = nullptr) {
   float s[NKT][4];
 #pragma unroll
   for (int nt = 0; nt < NKT; ++nt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
-  // S = Q K^T
+  // S = Q K^T.  A warp with only 16 keys has two score tiles, i.e. two chains of dependent
+  // products over the head dimension: the odd k-steps go to accumulators of their own, which
+  // halves the chain (its latency is what a decode tile waits for).
+  constexpr bool TWO_CHAINS = NKT <= 2 && KSTEPS >= 2;
+  float s2[TWO_CHAINS ? NKT : 1][4];
+  if constexpr (TWO_CHAINS) {
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s2[nt][c] = 0.f;
+  }
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
     unsigned a[4];
@@ -116,11 +197,28 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
     for (int np = 0; np < NKT / 2; ++np) {
       unsigned b[4];
       const int krow = krow0 + np * 16 + (lane & 7) + 8 * (lane >> 4);
-      ldmatrix_x4(b, Ks + krow * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
-      mma_bf16(s[2 * np], a, b[0], b[1]);
-      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+      ldmatrix_x4(b, tile_chunk<SWZ, ROWS>(Ks, krow, ks * 2 + ((lane >> 3) & 1)));
+      if constexpr (TWO_CHAINS) {
+        if (ks & 1) {
+          mma_bf16(s2[2 * np], a, b[0], b[1]);
+          mma_bf16(s2[2 * np + 1], a, b[2], b[3]);
+        } else {
+          mma_bf16(s[2 * np], a, b[0], b[1]);
+          mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+        }
+      } else {
+        mma_bf16(s[2 * np], a, b[0], b[1]);
+        mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+      }
     }
   }
+  if constexpr (TWO_CHAINS) {
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[nt][c] += s2[nt][c];
+  }
+  TRACE(tr, 2);
   // scale, mask, running maximum
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -175,6 +273,7 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
       o[nt][3] *= alpha[1];
     }
   }
+  TRACE(tr, 3);
   // O += P V
 #pragma unroll
   for (int kk = 0; kk < NKT / 2; ++kk) {
@@ -187,11 +286,14 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
 #pragma unroll
     for (int dp = 0; dp < ONT / 2; ++dp) {
       unsigned b[4];
-      ldmatrix_x4_trans(b, Vs + vrow * LDS + dp * 16 + 8 * (lane >> 4));
+      ldmatrix_x4_trans(b, tile_chunk<SWZ, ROWS>(Vs, vrow, dp * 2 + (lane >> 4)));
       mma_bf16(o[2 * dp], a, b[0], b[1]);
       mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
     }
   }
+#ifdef PBE_ATTN_TRACE
+  if (tr) { tr[5] = __float_as_int(o[0][0]) & 0; tr[4] = clock64(); }    // after the last product's result is there
+#endif
 }
 
 // The same for a warp that owns 32 rows (two 16-row fragments): every key and value fragment
@@ -320,17 +422,26 @@ constexpr int FUSED_MAX_KEYS_PER_BLOCK = 4096;     // beyond that the other path
 // with three, two blocks a multiprocessor, for steps small enough to be resident that way).
 template <int MODE, int NST = 2, int CS = 1>
 __global__ void __launch_bounds__(NTHREADS, MODE != 0 ? (HD <= 128 ? (NST == 2 ? 3 : 2) : 1) : (HD <= 128 ? 2 : 1))
-attn_mma_kernel(AttnParams p, AttnFusedParams f) {
+attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v) {
   constexpr bool KEYS = MODE != 0;
   constexpr bool FUSED = MODE == 2;
   constexpr int QROWS = KEYS ? 16 : BM;
   constexpr int BN = KEYS ? BN_KEYS : BN_ROWS;
+  // Fused mode, head sizes in steps of 64, page sizes that divide the key tile (or the other
+  // way round): a key tile arrives as one tensor-map box a page and 64 columns, in the swizzled
+  // layout, a handful of copies a tile instead of one a row.
+  constexpr bool BY_PAGE_HD = FUSED && HD % 64 == 0;
+  const bool by_page = BY_PAGE_HD && f.tiles_by_page != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [QROWS][LDS]
-  bf16* Ks = Qs + QROWS * LDS;                         // [NST][BN][LDS]
-  bf16* Vs = Ks + NST * BN * LDS;                      // [NST][BN][LDS]
+  bf16* Ks = Qs + QROWS * LDS;                         // [NST][BN][LDS], or [NST][HD / 64][BN][64] swizzled
+  if (by_page) Ks = reinterpret_cast<bf16*>(reinterpret_cast<unsigned char*>(Ks) + ((1024u - (smem_u32(Ks) & 1023u)) & 1023u));
+  const int tile_elems = by_page ? BN * HD : BN * LDS;
+  bf16* Vs = Ks + NST * tile_elems;
   __shared__ int s_pages[MAX_SMEM_PAGES];
   __shared__ bf16 s_newkv[FUSED_NEWKV];                // fused mode: the new token's key and value rows
+  __shared__ __align__(8) unsigned long long s_full[NST];   // tile buffer i holds its tile
 
   // The work list, the lengths and the block tables are written by the host before the
   // step's first kernel: they are read before the dependency on the previous kernel is awaited.
@@ -421,32 +532,81 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   const int blk_count = n_tiles > 0 ? (k_end - 1) / P - blk_first + 1 : 0;
   const bool pages_in_smem = blk_count <= MAX_SMEM_PAGES;
   const int pshift = (P & (P - 1)) == 0 ? 31 - __clz(P) : -1;   // pages of a power of two: shifts, no division
-  if (pages_in_smem) {
+  if (pages_in_smem)
     for (int i = tid; i < blk_count; i += NTHREADS) s_pages[i] = bt[blk_first + i];
-    __syncthreads();
+  if (tid == 0) {
+    // one arrival a row of keys and of values, or one for the whole tile when it comes by pages
+    for (int i = 0; i < NST; ++i) mbar_init(&s_full[i], by_page ? 1 : 2 * BN);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // One row (a key's or a value's head) a thread: a bulk copy that reports to the buffer's
+  // barrier, or zeros where there is no such key.
+  // by pages: this thread's box of every tile (which tensor, which page of the tile, which 64 columns)
+  bool box_mine = false;
+  int box_key = 0, box_x = 0, box_dst = 0;
+  const CUtensorMap* box_map = &map_k;
+  if constexpr (BY_PAGE_HD) {
+    if (by_page) {
+      const int box_rows = min(P, BN), boxes = BN / box_rows;
+      constexpr int KB = HD / 64;
+      const int op = warp + (NTHREADS / 32) * lane;
+      box_mine = op < 2 * boxes * KB;
+      const int which = op / (boxes * KB), rest = op - which * boxes * KB;
+      const int pg = rest / KB, kb = rest - pg * KB;
+      box_key = pg * box_rows;
+      box_x = kb * 64;
+      box_dst = which * NST * tile_elems * 2 + kb * (BN * 128) + pg * box_rows * 128;   // bytes from Ks
+      box_map = which ? &map_v : &map_k;
+    }
   }
   auto load_tile = [&](int ts, int buf) {
-    bf16* kd = Ks + buf * BN * LDS;
-    bf16* vd = Vs + buf * BN * LDS;
-#pragma unroll
-    for (int it = 0; it < (BN * CPR + NTHREADS - 1) / NTHREADS; ++it) {
-      const int c = tid + it * NTHREADS;
-      if ((BN * CPR) % NTHREADS != 0 && c >= BN * CPR) break;
-      const int j = c / CPR, col = c - j * CPR;
+    const unsigned bar = smem_u32(&s_full[buf]);
+    if constexpr (BY_PAGE_HD) {
+      if (by_page) {
+        // Thread 0 announces the bytes; the boxes (page x 64 columns x keys or values) are dealt
+        // round the warps, one lane each, so that no warp issues more than its share (a copy costs
+        // its issuing warp some eighty clocks).  Copies that complete before the announcement only
+        // drive the barrier's byte count below zero for a while: its one arrival is still pending.
+        // A box whose keys lie outside the block's range comes from any page: those keys are masked
+        // and their value rows are cleared after the tile has landed.
+        if (tid == 0) mbar_arrive_expect_tx(bar, 2 * BN * HD * 2);
+        if (box_mine) {
+          const int key0 = ts + box_key;
+          const int blk = pshift >= 0 ? key0 >> pshift : key0 / P;
+          int page = 0;
+          if (key0 < k_end && blk >= blk_first) page = pages_in_smem ? s_pages[blk - blk_first] : bt[blk];
+          if (page < 0) page = 0;
+          const int y = (page * KV + kvh) * P + (key0 - blk * P);
+          tma_box(reinterpret_cast<unsigned char*>(Ks) + box_dst + buf * (tile_elems * 2), box_map, box_x, y, bar);
+        }
+        return;
+      }
+    }
+    for (int rr = tid; rr < 2 * BN; rr += NTHREADS) {
+      const int which = rr / BN, j = rr - which * BN;
       const int key = ts + j;
+      bf16* dst = (which ? Vs : Ks) + (buf * BN + j) * LDS;
       // fused mode: the new token's own row is not read from the cache (this very launch writes
       // it); it is put into the tile from shared memory once the tile has landed
       bool valid = key >= k_begin && key < k_end && !(FUSED && key == sl - 1);
-      size_t off = 0;
       if (valid) {
         const int blk = pshift >= 0 ? key >> pshift : key / P;
         const int page = pages_in_smem ? s_pages[blk - blk_first] : bt[blk];
         valid = page >= 0;
-        // 32-bit row index (pages x heads x page tokens stays far below 2^31), one wide multiply
-        if (valid) off = (size_t)((page * KV + kvh) * P + (key - blk * P)) * HD + col * 8;
+        if (valid) {
+          // 32-bit row index (pages x heads x page tokens stays far below 2^31), one wide multiply
+          const size_t off = (size_t)((page * KV + kvh) * P + (key - blk * P)) * HD;
+          mbar_arrive_expect_tx(bar, HD * 2);
+          bulk_row(dst, (which ? vc : kc) + off, HD * 2, bar);
+        }
       }
-      cp_async16(kd + j * LDS + col * 8, kc + off, valid);
-      cp_async16(vd + j * LDS + col * 8, vc + off, valid);
+      if (!valid) {
+#pragma unroll
+        for (int c = 0; c < CPR; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        fence_proxy_async();      // a later tile's copy lands on these bytes
+        mbar_arrive(bar);
+      }
     }
   };
 
@@ -455,16 +615,14 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
     // first key tiles are requested before the wait.
     const int pos = sl - 1;
     const bool owner = pos >= k_begin && pos < k_end;
-    for (int i = 0; i < NST - 1; ++i) {
+    for (int i = 0; i < NST - 1; ++i)
       if (i < n_tiles) load_tile(tile0 + i * BN, i);
-      cp_async_commit();
-    }
     pdl_wait();
     // The new token's query heads (and, in the owner block, its key and value) from the fused
     // projection: bias, rotary position encoding (pairs i, i + hd/2; angle, sine, cosine and
     // rotation in float32, one rounding), as rope_kv.cu does.
     constexpr int HALF = HD / 2;
-    float* trig = reinterpret_cast<float*>(Ks + (NST - 1) * BN * LDS);   // the last buffer: filled last
+    float* trig = reinterpret_cast<float*>(Ks + (NST - 1) * tile_elems);   // the last buffer: filled last
     float* qraw = trig + HD;                                          // [G][HD] biased query heads
     float* kvraw = qraw + 16 * HD;                                    // [2][HD] biased key and value
     for (int i = tid; i < HALF; i += NTHREADS) sincosf(fused_posf * f.inv_freq[i], &trig[HALF + i], &trig[i]);
@@ -524,10 +682,13 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
         s_newkv[HD + i] = vv;
       }
     }
+    fence_proxy_async();        // the scratch was written here and a tile's copies land on it next
     __syncthreads();            // Q is complete, the scratch is free
   } else {
+    cp_async_commit();          // the Q tile
     if (n_tiles > 0) load_tile(tile0, 0);
-    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();            // Q is in shared memory
   }
 
   // rows of this thread's fragments: one 16-row fragment in keys mode, two in rows mode
@@ -573,33 +734,83 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
   const int pos_last = pos0 + (pr0 + wrow0 + max(wrows, 1) - 1) / G;
   const int lo_max = p.window > 0 ? max(0, pos_last - p.window + 1) : 0;
 
+#ifdef PBE_ATTN_TRACE
+  const bool tracing = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+  if (tracing) g_trace[0] = clock64();
+#endif
   for (int t = 0; t < n_tiles; ++t) {
     const int ts = tile0 + t * BN;
+#ifdef PBE_ATTN_TRACE
+    long long* tr = tracing && t < 100 ? g_trace + 16 + 8 * t : nullptr;
+#else
+    long long* tr = nullptr;
+#endif
     if (t + NST - 1 < n_tiles) load_tile(ts + (NST - 1) * BN, (t + NST - 1) % NST);
-    cp_async_commit();
-    cp_async_wait<NST - 1>();    // tile t (and Q) have landed
-    __syncthreads();
+    TRACE(tr, 0);
+    mbar_wait(smem_u32(&s_full[t % NST]), (t / NST) & 1);    // every row of tile t has landed or is zeros
+    TRACE(tr, 1);
+    bf16* kt = Ks + (t % NST) * tile_elems;
+    bf16* vt = Vs + (t % NST) * tile_elems;
     if constexpr (FUSED) {
       const int pos = sl - 1;
-      if (pos >= k_begin && pos < k_end && pos >= ts && pos < ts + BN) {   // block-uniform: the new token's tile
-        bf16* krow = Ks + ((t % NST) * BN + (pos - ts)) * LDS;
-        bf16* vrow = Vs + ((t % NST) * BN + (pos - ts)) * LDS;
-        for (int i = tid; i < HD; i += NTHREADS) {
-          krow[i] = s_newkv[i];
-          vrow[i] = s_newkv[HD + i];
+      const bool new_here = pos >= k_begin && pos < k_end && pos >= ts && pos < ts + BN;   // block-uniform
+      const bool ragged = by_page && (ts < k_begin || ts + BN > k_end);                    // block-uniform
+      if (ragged) {
+        // whole pages came: value rows of keys outside the range hold whatever the pages held
+        // (their weight is zero, but zero times anything must stay zero)
+        for (int c = tid; c < BN * (HD / 64); c += NTHREADS) {
+          const int j = c % BN, kb = c / BN;
+          const int key = ts + j;
+          if (key < k_begin || key >= k_end) {
+            uint4* row = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(vt) + kb * (BN * 128) + j * 128);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) row[q] = make_uint4(0u, 0u, 0u, 0u);
+            fence_proxy_async();      // a later tile's boxes land on these bytes
+          }
         }
-        __syncthreads();
       }
+      if (new_here) {
+        const int j = pos - ts;
+        for (int i = tid; i < HD; i += NTHREADS) {
+          bf16* kd;
+          bf16* vd;
+          if (by_page) {
+            const int off = (i >> 6) * (BN * 64) + j * 64 + ((((i & 63) >> 3) ^ (j & 7)) << 3) + (i & 7);
+            kd = kt + off;
+            vd = vt + off;
+          } else {
+            kd = kt + j * LDS + i;
+            vd = vt + j * LDS + i;
+          }
+          *kd = s_newkv[i];
+          *vd = s_newkv[HD + i];
+        }
+      }
+      if (ragged || new_here) __syncthreads();
     }
-    const bf16* kt = Ks + (t % NST) * BN * LDS;
-    const bf16* vt = Vs + (t % NST) * BN * LDS;
     if constexpr (KEYS) {
       const int key0 = ts + warp * 16;
       const bool interior = key0 >= k_begin && key0 + 16 <= k_end && key0 + 15 <= pos_min && key0 >= lo_max;
-      if (interior)
-        process_tile<2, false>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
-      else
-        process_tile<2, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0], o[0], lane);
+      bool done = false;
+      if constexpr (BY_PAGE_HD) {
+        if (by_page) {
+          if (interior)
+            process_tile<2, false, false, true, true, BN>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2,
+                                                           m[0], l[0], o[0], lane, nullptr, tr);
+          else
+            process_tile<2, true, false, true, true, BN>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2,
+                                                          m[0], l[0], o[0], lane, nullptr, tr);
+          done = true;
+        }
+      }
+      if (!done) {
+        if (interior)
+          process_tile<2, false, false, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0],
+                                              o[0], lane, nullptr, tr);
+        else
+          process_tile<2, true, false, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0],
+                                             o[0], lane, nullptr, tr);
+      }
     } else if (warp_has_rows) {
       const bool interior = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
       if constexpr (MT == 2) {
@@ -615,12 +826,18 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       }
     }
     __syncthreads();             // everyone is done with this buffer before it is refilled
+    TRACE(tr, 6);
   }
-  cp_async_wait<0>();
   pdl_launch_dependents();      // the keys and values are read: the next kernel may start launching
 
   const float LN2 = 0.6931471805599453f;
   if constexpr (KEYS) {
+    // every lane summed its own columns of the rows: the four lanes of a row, once
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      l[0][rr] += __shfl_xor_sync(0xffffffffu, l[0][rr], 1);
+      l[0][rr] += __shfl_xor_sync(0xffffffffu, l[0][rr], 2);
+    }
     // merge the four warps' partial results: reuse the K/V buffers as float scratch
     __syncthreads();
     float* sc_o = reinterpret_cast<float*>(Ks);          // [4][16][HD]
@@ -666,7 +883,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       const int tok = qs + qrow;
       if constexpr (FUSED) {
         // this block's result for the cluster's merge: after the four warps' partial sums
-        float* cl_o = reinterpret_cast<float*>(Vs);        // [16][HD]
+        float* cl_o = reinterpret_cast<float*>(Vs) + 256;  // [16][HD], past the end of the warps' scratch
         float* cl_ml = cl_o + 16 * HD;                       // [16][2]
         *reinterpret_cast<float4*>(cl_o + row * HD + d) = acc;
         if (d == 0) {
@@ -693,7 +910,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f) {
       // just normalises its own)
       namespace cg = cooperative_groups;
       cg::cluster_group cluster = cg::this_cluster();
-      float* cl_o = reinterpret_cast<float*>(Vs);
+      float* cl_o = reinterpret_cast<float*>(Vs) + 256;
       float* cl_ml = cl_o + 16 * HD;
       if constexpr (CS > 1) cluster.sync(); else __syncthreads();
       constexpr int SLICE = HD / CS;                                    // columns a block merges (HD % 16 == 0)
@@ -962,6 +1179,17 @@ attn_decode_kernel(AttnParams p, int num_work) {
 
 PBE_EXPORT int pbe_attn_mma_tile_rows() { return BM; }
 PBE_EXPORT int pbe_attn_mma_head_dim() { return HD; }
+#ifdef PBE_ATTN_TRACE
+PBE_EXPORT int pbe_attn_mma_trace(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * (size_t)n);
+}
+#endif
+// 1 once a bounded wait for a key tile ran out (the results of that launch are not valid)
+PBE_EXPORT int pbe_attn_mma_wait_gave_up() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_wait_gave_up, sizeof(int));
+  return v;
+}
 
 // params->kinds: bit 0: some row tile has at most 16 packed rows (decoded tokens), bit 1: some
 // has more (prompt portions); neither: unknown, both run.  Bit 2: the step has few small row tiles.
@@ -983,7 +1211,7 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
   if ((kinds & 2) && !(kinds & 8)) {
     if ((long long)num_work * p.num_kv_heads > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
     launch_k(attn_mma_kernel<0>, dim3((unsigned)(num_work * p.num_kv_heads)), NTHREADS, smem_rows, stream, p,
-             AttnFusedParams{});
+             AttnFusedParams{}, CUtensorMap{}, CUtensorMap{});
   }
   // Bit 2 (set by the host from the number of live work items): few enough small tiles for the
   // block-cooperative instance, the shortest path through one work item; otherwise the
@@ -1003,7 +1231,7 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
       cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
       opted_keys = true;
     }
-    launch_k(attn_mma_kernel<1>, grid, NTHREADS, smem_keys, stream, p, AttnFusedParams{});
+    launch_k(attn_mma_kernel<1>, grid, NTHREADS, smem_keys, stream, p, AttnFusedParams{}, CUtensorMap{}, CUtensorMap{});
   } else if (kinds & 1) {
     const size_t smem_dec = sizeof(bf16) * (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_KEYS * LDS;
     static int dec_blocks = 0;
@@ -1028,15 +1256,19 @@ PBE_EXPORT int pbe_attn_decode_fused_splits() { return FUSED_MAX_SPLITS; }
 
 namespace {
 template <int NST, int CS>
-void launch_fused(const AttnParams& p, const AttnFusedParams& f, cudaStream_t stream) {
+void launch_fused(const AttnParams& p, const AttnFusedParams& f, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                  cudaStream_t stream) {
+  // the padded layout is the larger one: the swizzled tiles with their alignment fit inside
   const size_t smem = sizeof(bf16) * (size_t)(16 + 2 * NST * BN_KEYS) * LDS;
+  static_assert(HD % 64 != 0 || (16 + 2 * 2 * BN_KEYS) * LDS * 2 >= 16 * LDS * 2 + 1024 + 2 * 2 * BN_KEYS * HD * 2,
+                "the swizzled tiles must fit into the padded layout's shared memory");
   static bool opted = false;
   if (!opted) {
     cudaFuncSetAttribute(attn_mma_kernel<2, NST, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     opted = true;
   }
   launch_k_cluster(attn_mma_kernel<2, NST, CS>, dim3(CS, f.num_requests, p.num_kv_heads), NTHREADS, smem, stream, CS,
-                   p, f);
+                   p, f, map_k, map_v);
 }
 }  // namespace
 
@@ -1056,16 +1288,34 @@ PBE_EXPORT int pbe_attn_decode_fused(const AttnParams* params, const AttnFusedPa
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
+  // Key tiles by tensor-map boxes, one a page: head sizes in steps of 64, pages of 8, 16, 32, 64
+  // tokens or a multiple of 64, the number of pages known, aligned caches.  PBE_DECODE_TILES=rows
+  // keeps the row-by-row copies.
+  CUtensorMap map_k = {}, map_v = {};
+  f.tiles_by_page = 0;
+  const int P = p.page_tokens;
+  static const bool rows_only = [] {
+    const char* e = getenv("PBE_DECODE_TILES");
+    return e != nullptr && strcmp(e, "rows") == 0;
+  }();
+  if (HD % 64 == 0 && !rows_only && f.num_pages > 0 && P >= 8 && P % 8 == 0 && (BN_KEYS % P == 0 || P % BN_KEYS == 0) &&
+      (((uintptr_t)p.k_cache | (uintptr_t)p.v_cache) & 15) == 0) {
+    const long long rows = (long long)f.num_pages * p.num_kv_heads * P;
+    const int box_rows = P < BN_KEYS ? P : BN_KEYS;
+    if (make_kv_tensor_map(&map_k, p.k_cache, rows, HD, box_rows) == 0 &&
+        make_kv_tensor_map(&map_v, p.v_cache, rows, HD, box_rows) == 0)
+      f.tiles_by_page = 1;
+  }
   // three key tiles in flight where all blocks are resident two a multiprocessor, else two
   const bool three = HD <= 128 && (long long)splits * f.num_requests * p.num_kv_heads <= 2LL * sm_count;
   if (splits == 8) {
-    if (three) launch_fused<3, 8>(p, f, stream); else launch_fused<2, 8>(p, f, stream);
+    if (three) launch_fused<3, 8>(p, f, map_k, map_v, stream); else launch_fused<2, 8>(p, f, map_k, map_v, stream);
   } else if (splits == 4) {
-    if (three) launch_fused<3, 4>(p, f, stream); else launch_fused<2, 4>(p, f, stream);
+    if (three) launch_fused<3, 4>(p, f, map_k, map_v, stream); else launch_fused<2, 4>(p, f, map_k, map_v, stream);
   } else if (splits == 2) {
-    if (three) launch_fused<3, 2>(p, f, stream); else launch_fused<2, 2>(p, f, stream);
+    if (three) launch_fused<3, 2>(p, f, map_k, map_v, stream); else launch_fused<2, 2>(p, f, map_k, map_v, stream);
   } else {
-    if (three) launch_fused<3, 1>(p, f, stream); else launch_fused<2, 1>(p, f, stream);
+    if (three) launch_fused<3, 1>(p, f, map_k, map_v, stream); else launch_fused<2, 1>(p, f, map_k, map_v, stream);
   }
   return launch_status();
 }

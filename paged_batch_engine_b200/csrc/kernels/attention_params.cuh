@@ -36,6 +36,8 @@ struct AttnFusedParams {
   const int32_t* slots;       // [T]: page * page_tokens + offset of the new token
   const float* inv_freq;      // [hd / 2], pairs (i, i + hd/2)
   int num_requests;           // rows of the grid (requests beyond the live ones have q_len 0)
+  int num_pages;              // pages of the cache tensors (0: unknown; the tiles then come row by row)
+  int tiles_by_page;          // set by the launcher: key tiles arrive as one tensor-map box a page
 };
 
 struct AttnMergeParams {

@@ -452,7 +452,7 @@ def decode_block_max_items(device) -> int:
 
 class AttnFusedParams(ctypes.Structure):
     _fields_ = [("qkv", c_void_p), ("bias", c_void_p), ("positions", c_void_p), ("slots", c_void_p),
-                ("inv_freq", c_void_p), ("num_requests", c_int)]
+                ("inv_freq", c_void_p), ("num_requests", c_int), ("num_pages", c_int), ("tiles_by_page", c_int)]
 
 
 FUSED_DECODE_MAX_KEYS_PER_BLOCK = 4096   # beyond that the other path streams better
@@ -504,7 +504,7 @@ def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, sl
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=1)
     f = AttnFusedParams(qkv=qkv.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
                         positions=positions.data_ptr(), slots=slots.data_ptr(), inv_freq=inv_freq.data_ptr(),
-                        num_requests=int(num_requests))
+                        num_requests=int(num_requests), num_pages=int(k_cache.shape[0]), tiles_by_page=0)
     fn = _fn("attention_mma", "pbe_attn_decode_fused",
              [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnFusedParams), c_int, c_int, c_void_p],
              {"PBE_HEAD_DIM": int(head_dim)})
@@ -534,6 +534,13 @@ def tc5_error_flag(device) -> int:
     if v:
         err[:1].zero_()
     return v
+
+
+def attention_mma_wait_flag(head_dim: int) -> int:
+    """1 once a bounded wait for a key tile ran out inside the mma.sync attention kernels of this
+    head size (never in a correct run; the launch's results are not valid then)."""
+    fn = _fn("attention_mma", "pbe_attn_mma_wait_gave_up", [], {"PBE_HEAD_DIM": int(head_dim)})
+    return int(fn())
 
 
 def attention_libraries(head_dim: int, dtype: torch.dtype):

@@ -570,6 +570,7 @@ def test_attention_decode_fused(H, KV, hd, P, window, ctxs, splits):
                              inv_freq, R, H, KV, hd, hd ** -0.5, window, P, splits=splits)
     got = out.float().cpu().view(R, H, hd)
     want = torch.stack(want_out)
+    assert o.attention_mma_wait_flag(hd) == 0      # no bounded wait for a key tile ran out
     assert torch.isfinite(got).all()
     assert (got - want).abs().max().item() <= 2 ** -6 * max(1.0, want.abs().max().item())
     for (page, off, kn), (_, _, vn) in zip(new_k, new_v):
