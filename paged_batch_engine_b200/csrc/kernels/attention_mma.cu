@@ -162,28 +162,24 @@ struct RowInfo {      // the two rows of this thread's accumulator fragment
 // sit at row `krow0` of the shared K and V tiles.  Updates m, l (log2 domain) and o.
 // LOCAL_SUM: l holds this thread's share of the row sum (its own columns); the caller adds
 // the four lanes of a row once, at the end, instead of two shuffles a tile.
-template <int NKT, bool MASK, bool QREG = false, bool LOCAL_SUM = false, bool SWZ = false, int ROWS = 64>
+template <int NKT, bool MASK, bool QREG = false, bool LOCAL_SUM = false, bool SWZ = false, int ROWS = 64,
+          int CHAINS = 2>
 __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const bf16* __restrict__ Ks,
                                              const bf16* __restrict__ Vs, int krow0, int key0,
                                              int k_begin, int k_end, const RowInfo& ri, float scale_log2,
                                              float (&m)[2], float (&l)[2], float (&o)[ONT][4], int lane,
                                              const unsigned (*qreg)[4] = nullptr, long long* tr = nullptr) {
-  float s[NKT][4];
-#pragma unroll
-  for (int nt = 0; nt < NKT; ++nt)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
   // S = Q K^T.  A warp with only 16 keys has two score tiles, i.e. two chains of dependent
-  // products over the head dimension: the odd k-steps go to accumulators of their own, which
-  // halves the chain (its latency is what a decode tile waits for).
-  constexpr bool TWO_CHAINS = NKT <= 2 && KSTEPS >= 2;
-  float s2[TWO_CHAINS ? NKT : 1][4];
-  if constexpr (TWO_CHAINS) {
+  // products over the head dimension, and the latency of a product is several times its issue
+  // interval: the k-steps are dealt round CHAINS accumulator sets that are added at the end.
+  constexpr int NCH = (NKT <= 2 && KSTEPS % CHAINS == 0) ? CHAINS : 1;
+  float sc[NCH][NKT][4];
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
     for (int nt = 0; nt < NKT; ++nt)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) s2[nt][c] = 0.f;
-  }
+      for (int c = 0; c < 4; ++c) sc[ch][nt][c] = 0.f;
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
     unsigned a[4];
@@ -198,26 +194,20 @@ __device__ __forceinline__ void process_tile(const bf16* __restrict__ Qw, const 
       unsigned b[4];
       const int krow = krow0 + np * 16 + (lane & 7) + 8 * (lane >> 4);
       ldmatrix_x4(b, tile_chunk<SWZ, ROWS>(Ks, krow, ks * 2 + ((lane >> 3) & 1)));
-      if constexpr (TWO_CHAINS) {
-        if (ks & 1) {
-          mma_bf16(s2[2 * np], a, b[0], b[1]);
-          mma_bf16(s2[2 * np + 1], a, b[2], b[3]);
-        } else {
-          mma_bf16(s[2 * np], a, b[0], b[1]);
-          mma_bf16(s[2 * np + 1], a, b[2], b[3]);
-        }
-      } else {
-        mma_bf16(s[2 * np], a, b[0], b[1]);
-        mma_bf16(s[2 * np + 1], a, b[2], b[3]);
-      }
+      mma_bf16(sc[ks % NCH][2 * np], a, b[0], b[1]);
+      mma_bf16(sc[ks % NCH][2 * np + 1], a, b[2], b[3]);
     }
   }
-  if constexpr (TWO_CHAINS) {
+  float s[NKT][4];
 #pragma unroll
-    for (int nt = 0; nt < NKT; ++nt)
+  for (int nt = 0; nt < NKT; ++nt)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) s[nt][c] += s2[nt][c];
-  }
+    for (int c = 0; c < 4; ++c) {
+      float v = sc[0][nt][c];
+#pragma unroll
+      for (int ch = 1; ch < NCH; ++ch) v += sc[ch][nt][c];
+      s[nt][c] = v;
+    }
   TRACE(tr, 2);
   // scale, mask, running maximum
   float mx[2] = {-INFINITY, -INFINITY};
@@ -723,6 +713,14 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
       for (int c = 0; c < 4; ++c) o[mt][nt][c] = 0.f;
   }
   const bf16* Qw = Qs + (KEYS ? 0 : warp * WROWS) * LDS;
+  // The fused instance with two blocks a multiprocessor has registers to spare: the query
+  // fragments, the same for every key tile, stay in registers.
+  constexpr bool Q_IN_REGS = FUSED && NST == 3 && HD <= 128;
+  unsigned qa[Q_IN_REGS ? KSTEPS : 1][4];
+  if constexpr (Q_IN_REGS) {
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) ldmatrix_x4(qa[ks], Qw + (lane & 15) * LDS + ks * 16 + 8 * (lane >> 4));
+  }
   const bool warp_has_rows = KEYS || (warp * WROWS < rows_here);
   // A key tile needs no mask for this warp when every key in it is visible to every one of
   // the warp's existing rows: the tile lies inside the block's key range, ends at or before
@@ -795,21 +793,21 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
       if constexpr (BY_PAGE_HD) {
         if (by_page) {
           if (interior)
-            process_tile<2, false, false, true, true, BN>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2,
-                                                           m[0], l[0], o[0], lane, nullptr, tr);
+            process_tile<2, false, Q_IN_REGS, true, true, BN, Q_IN_REGS ? 4 : 2>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0],
+                                                               scale_log2, m[0], l[0], o[0], lane, qa, tr);
           else
-            process_tile<2, true, false, true, true, BN>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2,
-                                                          m[0], l[0], o[0], lane, nullptr, tr);
+            process_tile<2, true, Q_IN_REGS, true, true, BN, Q_IN_REGS ? 4 : 2>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0],
+                                                              scale_log2, m[0], l[0], o[0], lane, qa, tr);
           done = true;
         }
       }
       if (!done) {
         if (interior)
-          process_tile<2, false, false, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0],
-                                              o[0], lane, nullptr, tr);
+          process_tile<2, false, Q_IN_REGS, true, false, 64, Q_IN_REGS ? 4 : 2>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0],
+                                                  l[0], o[0], lane, qa, tr);
         else
-          process_tile<2, true, false, true>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0], l[0],
-                                             o[0], lane, nullptr, tr);
+          process_tile<2, true, Q_IN_REGS, true, false, 64, Q_IN_REGS ? 4 : 2>(Qw, kt, vt, warp * 16, key0, k_begin, k_end, ri[0], scale_log2, m[0],
+                                                 l[0], o[0], lane, qa, tr);
       }
     } else if (warp_has_rows) {
       const bool interior = ts >= k_begin && ts + BN <= k_end && ts + BN - 1 <= pos_min && ts >= lo_max;
