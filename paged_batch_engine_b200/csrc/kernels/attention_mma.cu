@@ -406,7 +406,7 @@ __device__ __forceinline__ void process_tile_rows(const bf16* __restrict__ Qw, c
 // stands for three (position encoding and cache write, attention, merge of the splits).
 constexpr int FUSED_MAX_SPLITS = 8;
 constexpr int FUSED_NEWKV = 2 * HD;
-constexpr int FUSED_MAX_KEYS_PER_BLOCK = 4096;     // beyond that the other path streams better
+constexpr int FUSED_MAX_KEYS_PER_BLOCK = 32768;    // beyond that the other path takes the step
 
 // NST: key/value tiles in shared memory (two everywhere; the fused mode also has an instance
 // with three, two blocks a multiprocessor, for steps small enough to be resident that way).

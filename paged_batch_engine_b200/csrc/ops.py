@@ -7,6 +7,7 @@ a CUDA device is an error, and so is a failed build of the kernel library.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -455,7 +456,7 @@ class AttnFusedParams(ctypes.Structure):
                 ("inv_freq", c_void_p), ("num_requests", c_int), ("num_pages", c_int), ("tiles_by_page", c_int)]
 
 
-FUSED_DECODE_MAX_KEYS_PER_BLOCK = 4096   # beyond that the other path streams better
+FUSED_DECODE_MAX_KEYS_PER_BLOCK = 32768   # beyond that the other path takes the step
 
 
 def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int, device) -> int:
@@ -469,9 +470,9 @@ def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int,
             per_block = (longest_keys + splits - 1) // splits
             if not 0 < per_block <= FUSED_DECODE_MAX_KEYS_PER_BLOCK:
                 return 0
-            # a handful of blocks with thousands of keys each (one or two requests with very long
-            # contexts) stream better as many small work items on the other path
-            if per_block > 1536 and blocks < 200:
+            # a few dozen blocks with thousands of keys each (one request with a very long context)
+            # stream better as many small work items on the other path
+            if per_block > 1536 and blocks < 64:
                 return 0
             return splits
     return 0

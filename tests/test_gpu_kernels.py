@@ -517,6 +517,10 @@ def test_gemm_tc5(M, N, K):
     (4, 2, 16, 16, None, [15, 16, 17, 2300]),
     (8, 1, 64, 32, 600, [1000, 599, 600, 601, 3000]),
     (5, 5, 256, 16, None, [20, 600]),
+    (4, 2, 64, 8, None, [9000, 8191]),          # more pages a block than the kernel keeps in shared memory
+    (4, 1, 128, 64, None, [200, 5000, 63, 64]),  # a page is a whole key tile
+    (2, 1, 64, 128, 900, [300, 129, 2000]),      # a page is two key tiles
+    (3, 1, 64, 24, None, [100, 1000]),           # a page size the tensor-map boxes do not take: rows one by one
 ])
 @pytest.mark.parametrize("splits", [8, 4, 2, 1])
 def test_attention_decode_fused(H, KV, hd, P, window, ctxs, splits):
