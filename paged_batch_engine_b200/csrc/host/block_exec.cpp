@@ -128,6 +128,7 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
   ap.num_kv_heads = KV;
   ap.window = b->window;
   ap.scale = b->scale;
+  ap.num_pages = s->num_pages;
   if (s->fused_splits > 0) {
     AttnFusedParams fp;
     fp.qkv = s->qkv;
@@ -136,8 +137,6 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
     fp.slots = s->slots;
     fp.inv_freq = b->inv_freq;
     fp.num_requests = s->decode_rows;
-    fp.num_pages = s->num_pages;
-    fp.tiles_by_page = 0;
     ap.q = nullptr;
     ap.max_splits = s->fused_splits;
     ap.kinds = 1;

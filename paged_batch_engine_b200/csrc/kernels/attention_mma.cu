@@ -418,11 +418,11 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
   constexpr bool FUSED = MODE == 2;
   constexpr int QROWS = KEYS ? 16 : BM;
   constexpr int BN = KEYS ? BN_KEYS : BN_ROWS;
-  // Fused mode, head sizes in steps of 64, page sizes that divide the key tile (or the other
+  // Keys modes, head sizes in steps of 64, page sizes that divide the key tile (or the other
   // way round): a key tile arrives as one tensor-map box a page and 64 columns, in the swizzled
   // layout, a handful of copies a tile instead of one a row.
-  constexpr bool BY_PAGE_HD = FUSED && HD % 64 == 0;
-  const bool by_page = BY_PAGE_HD && f.tiles_by_page != 0;
+  constexpr bool BY_PAGE_HD = KEYS && HD % 64 == 0;
+  const bool by_page = BY_PAGE_HD && (p.kinds & 16) != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);        // [QROWS][LDS]
   bf16* Ks = Qs + QROWS * LDS;                         // [NST][BN][LDS], or [NST][HD / 64][BN][64] swizzled
@@ -749,10 +749,10 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     TRACE(tr, 1);
     bf16* kt = Ks + (t % NST) * tile_elems;
     bf16* vt = Vs + (t % NST) * tile_elems;
-    if constexpr (FUSED) {
+    {
       const int pos = sl - 1;
-      const bool new_here = pos >= k_begin && pos < k_end && pos >= ts && pos < ts + BN;   // block-uniform
-      const bool ragged = by_page && (ts < k_begin || ts + BN > k_end);                    // block-uniform
+      const bool new_here = FUSED && pos >= k_begin && pos < k_end && pos >= ts && pos < ts + BN;   // block-uniform
+      const bool ragged = by_page && (ts < k_begin || ts + BN > k_end);                             // block-uniform
       if (ragged) {
         // whole pages came: value rows of keys outside the range hold whatever the pages held
         // (their weight is zero, but zero times anything must stay zero)
@@ -767,21 +767,23 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
           }
         }
       }
-      if (new_here) {
-        const int j = pos - ts;
-        for (int i = tid; i < HD; i += NTHREADS) {
-          bf16* kd;
-          bf16* vd;
-          if (by_page) {
-            const int off = (i >> 6) * (BN * 64) + j * 64 + ((((i & 63) >> 3) ^ (j & 7)) << 3) + (i & 7);
-            kd = kt + off;
-            vd = vt + off;
-          } else {
-            kd = kt + j * LDS + i;
-            vd = vt + j * LDS + i;
+      if constexpr (FUSED) {
+        if (new_here) {
+          const int j = pos - ts;
+          for (int i = tid; i < HD; i += NTHREADS) {
+            bf16* kd;
+            bf16* vd;
+            if (by_page) {
+              const int off = (i >> 6) * (BN * 64) + j * 64 + ((((i & 63) >> 3) ^ (j & 7)) << 3) + (i & 7);
+              kd = kt + off;
+              vd = vt + off;
+            } else {
+              kd = kt + j * LDS + i;
+              vd = vt + j * LDS + i;
+            }
+            *kd = s_newkv[i];
+            *vd = s_newkv[HD + i];
           }
-          *kd = s_newkv[i];
-          *vd = s_newkv[HD + i];
         }
       }
       if (ragged || new_here) __syncthreads();
@@ -1175,6 +1177,28 @@ attn_decode_kernel(AttnParams p, int num_work) {
 }
 }  // namespace
 
+namespace {
+// Key tiles by tensor-map boxes, one a page: head sizes in steps of 64, pages of 8, 16, 32, 64
+// tokens or a multiple of 64, the number of pages known, aligned caches.  Sets bit 4 of p.kinds.
+// PBE_DECODE_TILES=rows keeps the row-by-row copies.
+void tiles_by_page(AttnParams& p, CUtensorMap* map_k, CUtensorMap* map_v) {
+  p.kinds &= ~16;
+  const int P = p.page_tokens;
+  static const bool rows_only = [] {
+    const char* e = getenv("PBE_DECODE_TILES");
+    return e != nullptr && strcmp(e, "rows") == 0;
+  }();
+  if (HD % 64 != 0 || rows_only || p.num_pages <= 0 || P < 8 || P % 8 != 0 || (BN_KEYS % P != 0 && P % BN_KEYS != 0) ||
+      (((uintptr_t)p.k_cache | (uintptr_t)p.v_cache) & 15) != 0)
+    return;
+  const long long rows = (long long)p.num_pages * p.num_kv_heads * P;
+  const int box_rows = P < BN_KEYS ? P : BN_KEYS;
+  if (make_kv_tensor_map(map_k, p.k_cache, rows, HD, box_rows) == 0 &&
+      make_kv_tensor_map(map_v, p.v_cache, rows, HD, box_rows) == 0)
+    p.kinds |= 16;
+}
+}  // namespace
+
 PBE_EXPORT int pbe_attn_mma_tile_rows() { return BM; }
 PBE_EXPORT int pbe_attn_mma_head_dim() { return HD; }
 #ifdef PBE_ATTN_TRACE
@@ -1204,6 +1228,7 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
     opted = true;
   }
   dim3 grid(num_work, p.num_kv_heads);
+  p.kinds &= ~16;            // the launcher's own bit
   const int kinds = (p.kinds & 3) == 0 ? (p.kinds | 3) : p.kinds;
   // bit 3: the prompt-portion tiles are computed by another kernel (attention_tc5.cu)
   if ((kinds & 2) && !(kinds & 8)) {
@@ -1229,7 +1254,10 @@ PBE_EXPORT int pbe_attn_mma(const AttnParams* params, int num_work, int dtype, c
       cudaFuncSetAttribute(attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
       opted_keys = true;
     }
-    launch_k(attn_mma_kernel<1>, grid, NTHREADS, smem_keys, stream, p, AttnFusedParams{}, CUtensorMap{}, CUtensorMap{});
+    CUtensorMap map_k = {}, map_v = {};
+    AttnParams pk = p;
+    tiles_by_page(pk, &map_k, &map_v);
+    launch_k(attn_mma_kernel<1>, grid, NTHREADS, smem_keys, stream, pk, AttnFusedParams{}, map_k, map_v);
   } else if (kinds & 1) {
     const size_t smem_dec = sizeof(bf16) * (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_KEYS * LDS;
     static int dec_blocks = 0;
@@ -1286,24 +1314,8 @@ PBE_EXPORT int pbe_attn_decode_fused(const AttnParams* params, const AttnFusedPa
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  // Key tiles by tensor-map boxes, one a page: head sizes in steps of 64, pages of 8, 16, 32, 64
-  // tokens or a multiple of 64, the number of pages known, aligned caches.  PBE_DECODE_TILES=rows
-  // keeps the row-by-row copies.
   CUtensorMap map_k = {}, map_v = {};
-  f.tiles_by_page = 0;
-  const int P = p.page_tokens;
-  static const bool rows_only = [] {
-    const char* e = getenv("PBE_DECODE_TILES");
-    return e != nullptr && strcmp(e, "rows") == 0;
-  }();
-  if (HD % 64 == 0 && !rows_only && f.num_pages > 0 && P >= 8 && P % 8 == 0 && (BN_KEYS % P == 0 || P % BN_KEYS == 0) &&
-      (((uintptr_t)p.k_cache | (uintptr_t)p.v_cache) & 15) == 0) {
-    const long long rows = (long long)f.num_pages * p.num_kv_heads * P;
-    const int box_rows = P < BN_KEYS ? P : BN_KEYS;
-    if (make_kv_tensor_map(&map_k, p.k_cache, rows, HD, box_rows) == 0 &&
-        make_kv_tensor_map(&map_v, p.v_cache, rows, HD, box_rows) == 0)
-      f.tiles_by_page = 1;
-  }
+  tiles_by_page(p, &map_k, &map_v);
   // three key tiles in flight where all blocks are resident two a multiprocessor, else two
   const bool three = HD <= 128 && (long long)splits * f.num_requests * p.num_kv_heads <= 2LL * sm_count;
   if (splits == 8) {

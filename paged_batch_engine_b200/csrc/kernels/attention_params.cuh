@@ -23,7 +23,9 @@ struct AttnParams {
   int tile_rows;            // packed rows (query row x head of the group) per row tile
   float scale;
   int kinds;                // tensor-core kernel: bit 0 small row tiles present, bit 1 large ones (0: unknown);
-                            // bit 2: few requests, small tiles go to the block-cooperative instance
+                            // bit 2: few requests, small tiles go to the block-cooperative instance;
+                            // bit 4 (set by the launcher): key tiles arrive as one tensor-map box a page
+  int num_pages;            // pages of the cache tensors (0: unknown; key tiles then come row by row)
 };
 
 // What the fused decode kernel needs beyond AttnParams: it applies the bias and the rotary
@@ -36,8 +38,6 @@ struct AttnFusedParams {
   const int32_t* slots;       // [T]: page * page_tokens + offset of the new token
   const float* inv_freq;      // [hd / 2], pairs (i, i + hd/2)
   int num_requests;           // rows of the grid (requests beyond the live ones have q_len 0)
-  int num_pages;              // pages of the cache tensors (0: unknown; the tiles then come row by row)
-  int tiles_by_page;          // set by the launcher: key tiles arrive as one tensor-map box a page
 };
 
 struct AttnMergeParams {

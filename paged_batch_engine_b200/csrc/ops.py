@@ -322,7 +322,8 @@ class AttnParams(ctypes.Structure):
                 ("work", c_void_p), ("tok_split_row", c_void_p),
                 ("bt_stride", c_int), ("num_heads", c_int), ("num_kv_heads", c_int),
                 ("page_tokens", c_int), ("window", c_int), ("split_keys", c_int),
-                ("max_splits", c_int), ("tile_rows", c_int), ("scale", c_float), ("kinds", c_int)]
+                ("max_splits", c_int), ("tile_rows", c_int), ("scale", c_float), ("kinds", c_int),
+                ("num_pages", c_int)]
 
 
 class AttnMergeParams(ctypes.Structure):
@@ -405,7 +406,8 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
         tok_split_row=meta.tok_split_row.data_ptr(), bt_stride=int(meta.bt_stride),
         num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
         window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
-        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=int(getattr(meta, "kinds", 0)))
+        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=int(getattr(meta, "kinds", 0)),
+        num_pages=int(k_cache.shape[0]))
     if tc5:
         # prompt-portion tiles on the tcgen05 kernel; the decode instances below take the rest
         err = tc5_attention_error_buffer(q.device)
@@ -453,7 +455,7 @@ def decode_block_max_items(device) -> int:
 
 class AttnFusedParams(ctypes.Structure):
     _fields_ = [("qkv", c_void_p), ("bias", c_void_p), ("positions", c_void_p), ("slots", c_void_p),
-                ("inv_freq", c_void_p), ("num_requests", c_int), ("num_pages", c_int), ("tiles_by_page", c_int)]
+                ("inv_freq", c_void_p), ("num_requests", c_int)]
 
 
 FUSED_DECODE_MAX_KEYS_PER_BLOCK = 32768   # beyond that the other path takes the step
@@ -470,9 +472,9 @@ def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int,
             per_block = (longest_keys + splits - 1) // splits
             if not 0 < per_block <= FUSED_DECODE_MAX_KEYS_PER_BLOCK:
                 return 0
-            # a few dozen blocks with thousands of keys each (one request with a very long context)
-            # stream better as many small work items on the other path
-            if per_block > 1536 and blocks < 64:
+            # a few dozen blocks with thousands of keys each (one or two requests with very long
+            # contexts) stream better as many small work items on the other path
+            if per_block > 1536 and blocks <= 64:
                 return 0
             return splits
     return 0
@@ -502,10 +504,10 @@ def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, sl
         block_table=meta.block_table.data_ptr(), work=None, tok_split_row=None, bt_stride=int(meta.bt_stride),
         num_heads=int(num_heads), num_kv_heads=int(num_kv_heads), page_tokens=int(page_tokens),
         window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(splits),
-        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=1)
+        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=1, num_pages=int(k_cache.shape[0]))
     f = AttnFusedParams(qkv=qkv.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
                         positions=positions.data_ptr(), slots=slots.data_ptr(), inv_freq=inv_freq.data_ptr(),
-                        num_requests=int(num_requests), num_pages=int(k_cache.shape[0]), tiles_by_page=0)
+                        num_requests=int(num_requests))
     fn = _fn("attention_mma", "pbe_attn_decode_fused",
              [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnFusedParams), c_int, c_int, c_void_p],
              {"PBE_HEAD_DIM": int(head_dim)})
