@@ -39,6 +39,26 @@ __device__ __forceinline__ float key_value(uint32_t k) {
   return __uint_as_float(u);
 }
 
+// A pass over a row with LOADS_AHEAD loads in flight a thread: one load at a time leaves a
+// block waiting for the L2's latency 150 times over a vocabulary of 150,000.
+constexpr int LOADS_AHEAD = 8;
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int V, F&& f) {
+  for (int i0 = threadIdx.x; i0 < V; i0 += THREADS * LOADS_AHEAD) {
+    float xs[LOADS_AHEAD];
+#pragma unroll
+    for (int u = 0; u < LOADS_AHEAD; ++u) {
+      const int i = i0 + u * THREADS;
+      xs[u] = i < V ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < LOADS_AHEAD; ++u) {
+      const int i = i0 + u * THREADS;
+      if (i < V) f(clean(xs[u]), i);
+    }
+  }
+}
+
 struct Cut {          // an element of the ordered list and the weight up to and including it
   uint32_t key;
   int token;
@@ -54,12 +74,14 @@ struct Shared {
   int imax;
   float wmaxv[NWARPS];
   int wmaxi[NWARPS];
+  float wminv[NWARPS];
+  float fmin;
 };
 
 __device__ __forceinline__ u64 weight_of(float x, float mx, float temp, bool count_mode) {
   if (count_mode) return 1ull;
   const float w = expf((x - mx) / temp);
-  return (u64)((double)w * 1099511627776.0);   // 2^40
+  return __float2ull_rz(w * 1099511627776.0f);   // 2^40: a power of two, the product is exact
 }
 
 __device__ __forceinline__ bool in_domain(uint32_t key, int token, bool limited, const Cut& lim) {
@@ -150,7 +172,10 @@ __device__ Cut select_by_weight(const float* row, int V, float mx, float temp, b
   long long want;   // how many tied elements are needed to reach the target
   if (target <= base) want = 1;
   else if (w_tie == 0) want = total;
-  else want = (long long)((target - base + w_tie - 1) / w_tie);
+  else {
+    const u64 need = target - base;          // no "+ w_tie - 1": the target may be the largest u64
+    want = (long long)(need / w_tie + (need % w_tie != 0 ? 1 : 0));
+  }
   if (want < 1) want = 1;
   if (want > total) want = total;
   if (tid == 0) sh.found = -1;
@@ -174,36 +199,42 @@ __device__ Cut select_by_weight(const float* row, int V, float mx, float temp, b
   return c;
 }
 
-__device__ void block_argmax(const float* row, int V, Shared& sh, float* out_max, int* out_idx) {
+// out_min (optional): the smallest logit above -inf (+inf when there is none)
+__device__ void block_argmax(const float* row, int V, Shared& sh, float* out_max, int* out_idx,
+                             float* out_min = nullptr) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float best = -INFINITY;
+  float best = -INFINITY, low = INFINITY;
   int idx = 0x7fffffff;
-  for (int i = tid; i < V; i += THREADS) {
-    const float x = clean(row[i]);
+  for_each_logit(row, V, [&](float x, int i) {
     if (x > best || (x == best && i < idx)) { best = x; idx = i; }
-  }
+    if (x > -INFINITY) low = fminf(low, x);
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ob = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
     if (ob > best || (ob == best && oi < idx)) { best = ob; idx = oi; }
+    low = fminf(low, __shfl_xor_sync(0xffffffffu, low, o));
   }
   __syncthreads();
-  if (lane == 0) { sh.wmaxv[warp] = best; sh.wmaxi[warp] = idx; }
+  if (lane == 0) { sh.wmaxv[warp] = best; sh.wmaxi[warp] = idx; sh.wminv[warp] = low; }
   __syncthreads();
   if (tid == 0) {
-    float b = sh.wmaxv[0];
+    float b = sh.wmaxv[0], mn = sh.wminv[0];
     int bi = sh.wmaxi[0];
     for (int w = 1; w < NWARPS; ++w) {
       if (sh.wmaxv[w] > b || (sh.wmaxv[w] == b && sh.wmaxi[w] < bi)) { b = sh.wmaxv[w]; bi = sh.wmaxi[w]; }
+      mn = fminf(mn, sh.wminv[w]);
     }
     if (bi == 0x7fffffff) bi = 0;   // a row of NaN / -inf: token 0, like a scan that never improves
     sh.fmax = b;
     sh.imax = bi;
+    sh.fmin = mn;
   }
   __syncthreads();
   *out_max = sh.fmax;
   *out_idx = sh.imax;
+  if (out_min) *out_min = sh.fmin;
   __syncthreads();
 }
 
@@ -257,17 +288,234 @@ argmax_cluster_kernel(const float* __restrict__ logits, size_t ld, int V, int32_
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The quick way to the same element.  One pass over the row puts every element into one of NB
+// bins by its distance from the maximum (a monotone function of the logit, so the bins are
+// ranges of the ordered list) and sums each bin's count and weight; the bin that holds the wanted
+// element follows from a prefix sum over the bins, its few hundred elements are gathered, sorted
+// by (key descending, token ascending) and scanned.  The radix descent above remains for rows
+// whose bin is too crowded for the list (thousands of equal logits).
+constexpr int NB = THREADS;        // one bin a thread in the prefix sums
+constexpr int LIST_CAP = 4096;
+
+struct Quick {
+  unsigned limb[3][NB];            // a bin's weight while it is summed: 14-bit limbs of every weight, so
+                                   // that 32-bit shared-memory atomics do (2^14 x 2^18 elements < 2^32)
+  u64 wsum[NB];
+  u64 cumw[NB + 1];                // weight of the bins before this one
+  unsigned cnt[NB];
+  unsigned cumc[NB + 1];
+  u64 list[LIST_CAP];              // (key << 32) | (0xffffffff - token): descending = the order
+  u64 warp_tot[NWARPS];
+  u64 pick_cum;
+  int n_list, chosen, first_idx, last_bin;
+};
+
+struct Limit {                     // the domain: the ordered list up to and including this element
+  bool on;
+  uint32_t key;
+  int token, bin;
+};
+
+__device__ __forceinline__ int value_bin(float x, float mx, float scale) {
+  if (!(x > -INFINITY)) return NB - 1;
+  const int b = (int)((mx - x) * scale);       // saturates; never negative
+  return min(b, NB - 1);
+}
+
+// exclusive prefix sum over the threads of the block; *total gets the sum
+__device__ u64 block_exclusive_scan(u64 v, Quick& q, u64* total) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  u64 inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 up = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += up;
+  }
+  __syncthreads();
+  if (lane == 31) q.warp_tot[warp] = inc;
+  __syncthreads();
+  u64 before = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) {
+    const u64 t = q.warp_tot[w];
+    if (w < warp) before += t;
+    all += t;
+  }
+  *total = all;
+  return before + inc - v;
+}
+
+// The bins of a row: counts, weights and their prefix sums.
+__device__ void fill_bins(const float* row, int V, float mx, float temp, float scale, Quick& q) {
+  const int tid = threadIdx.x;
+  q.cnt[tid] = 0;
+  q.limb[0][tid] = q.limb[1][tid] = q.limb[2][tid] = 0;
+  if (tid == 0) q.last_bin = 0;
+  __syncthreads();
+  for_each_logit(row, V, [&](float x, int) {
+    const int b = value_bin(x, mx, scale);
+    atomicAdd(&q.cnt[b], 1u);
+    const u64 w = weight_of(x, mx, temp, false);      // at most 2^40
+    const unsigned l0 = (unsigned)w & 0x3fffu, l1 = (unsigned)(w >> 14) & 0x3fffu, l2 = (unsigned)(w >> 28);
+    if (l0) atomicAdd(&q.limb[0][b], l0);
+    if (l1) atomicAdd(&q.limb[1][b], l1);
+    if (l2) atomicAdd(&q.limb[2][b], l2);
+  });
+  __syncthreads();
+  q.wsum[tid] = (u64)q.limb[0][tid] + ((u64)q.limb[1][tid] << 14) + ((u64)q.limb[2][tid] << 28);
+  if (q.cnt[tid] > 0) atomicMax(&q.last_bin, tid);
+  u64 tot;
+  const u64 ec = block_exclusive_scan((u64)q.cnt[tid], q, &tot);
+  q.cumc[tid] = (unsigned)ec;
+  if (tid == 0) q.cumc[NB] = (unsigned)tot;
+  const u64 ew = block_exclusive_scan(q.wsum[tid], q, &tot);
+  q.cumw[tid] = ew;
+  if (tid == 0) q.cumw[NB] = tot;
+  __syncthreads();
+}
+
+// First element of the ordered list, inside the domain, whose weight is positive and whose
+// inclusive cumulative weight (count in count mode) reaches `target`; the domain's last element
+// if there is none: what select_by_weight returns.  In count mode *weight_cum gets the cumulative
+// weight at that element.  false (block-uniform): the element's bin is too crowded for the list.
+__device__ bool select_quick(const float* row, int V, float mx, float temp, float scale, bool count_mode, u64 target,
+                             const Limit& lim, Quick& q, Cut* out, int* out_bin, u64* weight_cum) {
+  const int tid = threadIdx.x;
+  const int last_bin = lim.on ? lim.bin : q.last_bin;
+  __syncthreads();
+  if (tid == 0) {
+    q.chosen = last_bin;
+    q.n_list = 0;
+    q.first_idx = 0x7fffffff;
+  }
+  __syncthreads();
+  {
+    const u64 hb = count_mode ? (u64)q.cnt[tid] : q.wsum[tid];
+    const u64 before = count_mode ? (u64)q.cumc[tid] : q.cumw[tid];
+    if (tid < last_bin && hb > 0 && before + hb >= target) atomicMin(&q.chosen, tid);
+  }
+  __syncthreads();
+  const int bin = q.chosen;
+  if (q.cnt[bin] > (unsigned)LIST_CAP) return false;
+  // the bin's elements inside the domain
+  for_each_logit(row, V, [&](float x, int i) {
+    if (value_bin(x, mx, scale) != bin) return;
+    const uint32_t key = order_key(x);
+    if (lim.on && !(key > lim.key || (key == lim.key && i <= lim.token))) return;
+    const int pos = atomicAdd(&q.n_list, 1);
+    q.list[pos] = ((u64)key << 32) | (u64)(0xffffffffu - (uint32_t)i);
+  });
+  __syncthreads();
+  const int n = q.n_list;
+  if (n <= 0) return false;        // cannot be: the bin has elements and the limit element is its own
+  int n2 = 32;
+  while (n2 < n) n2 <<= 1;
+  for (int i = n + tid; i < n2; i += THREADS) q.list[i] = 0;     // below every real key
+  __syncthreads();
+  if (n2 <= THREADS) {
+    // few elements: every element counts the larger ones (all are different: the token is part
+    // of them) and moves to that place; no barrier but two
+    const u64 mine = tid < n2 ? q.list[tid] : 0;
+    int rank = 0;
+    if (tid < n) {
+      for (int j = 0; j < n; ++j) rank += q.list[j] > mine ? 1 : 0;
+    }
+    __syncthreads();
+    if (tid < n) q.list[rank] = mine;
+    __syncthreads();
+  } else {
+    // bitonic sort, descending
+    for (int k = 2; k <= n2; k <<= 1) {
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        for (int i = tid; i < n2; i += THREADS) {
+          const int partner = i ^ j;
+          if (partner > i) {
+            const u64 a = q.list[i], b = q.list[partner];
+            const bool down = (i & k) == 0;
+            if (down ? a < b : a > b) {
+              q.list[i] = b;
+              q.list[partner] = a;
+            }
+          }
+        }
+        __syncthreads();
+      }
+    }
+  }
+  // running sum along the sorted list, a few consecutive elements a thread
+  const int ipt = (n2 + THREADS - 1) / THREADS;       // 1 .. LIST_CAP / THREADS
+  constexpr int MAX_IPT = LIST_CAP / THREADS;
+  u64 w[MAX_IPT], rw[MAX_IPT];
+  u64 mine = 0;
+#pragma unroll
+  for (int j = 0; j < MAX_IPT; ++j) {
+    const int idx = tid * ipt + j;
+    w[j] = rw[j] = 0;
+    if (j < ipt && idx < n) {
+      rw[j] = weight_of(key_value((uint32_t)(q.list[idx] >> 32)), mx, temp, false);
+      w[j] = count_mode ? 1ull : rw[j];
+    }
+    mine += w[j];
+  }
+  u64 tot;
+  const u64 start = block_exclusive_scan(mine, q, &tot) + (count_mode ? (u64)q.cumc[bin] : q.cumw[bin]);
+  {
+    u64 run = start;
+#pragma unroll
+    for (int j = 0; j < MAX_IPT; ++j) {
+      const int idx = tid * ipt + j;
+      if (j < ipt && idx < n) {
+        run += w[j];
+        if (w[j] > 0 && run >= target) {
+          atomicMin(&q.first_idx, idx);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int pick = q.first_idx == 0x7fffffff ? n - 1 : q.first_idx;
+  u64 real_before = 0;           // this thread's weights up to and including the element
+  {
+    u64 run = start;
+#pragma unroll
+    for (int j = 0; j < MAX_IPT; ++j) {
+      const int idx = tid * ipt + j;
+      if (j < ipt && idx < n && idx <= pick) {
+        run += w[j];
+        real_before += rw[j];
+        if (idx == pick) q.pick_cum = run;
+      }
+    }
+  }
+  u64 real_tot = 0;
+  if (count_mode) block_exclusive_scan(real_before, q, &real_tot);
+  __syncthreads();
+  const u64 e = q.list[pick];
+  out->key = (uint32_t)(e >> 32);
+  out->token = (int)(0xffffffffu - (uint32_t)e);
+  out->cum = q.pick_cum;
+  *out_bin = bin;
+  if (weight_cum) *weight_cum = q.cumw[bin] + real_tot;
+  __syncthreads();
+  return true;
+}
+
+// mode 1: the radix descent only (for tests that compare the two ways)
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, size_t ld, int V,
               const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ uniform,
-              int32_t* __restrict__ out) {
+              int32_t* __restrict__ out, int mode) {
   __shared__ Shared sh;
+  extern __shared__ __align__(16) unsigned char quick_raw[];
+  Quick& q = *reinterpret_cast<Quick*>(quick_raw);
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
-  float mx;
+  float mx, mn;
   int amax;
-  block_argmax(row, V, sh, &mx, &amax);
+  block_argmax(row, V, sh, &mx, &amax, &mn);
   const float t_in = temperature[r];
   const int k_in = top_k[r];
   const float p_in = fminf(fmaxf(top_p[r], 0.f), 1.f);
@@ -276,6 +524,52 @@ sample_kernel(const float* __restrict__ logits, size_t ld, int V,
     return;
   }
   const float temp = fmaxf(t_in, 1e-6f);
+  const float u = fminf(fmaxf(uniform[r], 0.f), 0.99999994f);
+  if (mode != 1 && V < (1 << 18)) {      // (the limbs of a bin's weight sum hold 2^18 elements)
+    // bins over the logits from the maximum down to the smallest one, but no further than where
+    // weights have long vanished (masks of -1e9 would otherwise stretch the bins): what lies
+    // below shares the last bin
+    const float reach = fminf(mx - mn, fmaxf(64.f * temp, 32.f));
+    const float scale = reach > 0.f ? (float)(NB - 1) / reach : 0.f;
+    fill_bins(row, V, mx, temp, scale, q);
+    Limit lim;
+    lim.on = false; lim.key = 0; lim.token = 0; lim.bin = 0;
+    u64 kept = q.cumw[NB];
+    bool ok = true;
+    Cut c;
+    int bin = 0;
+    if (k_in > 0 && k_in < V) {
+      u64 wc = 0;
+      ok = select_quick(row, V, mx, temp, scale, true, (u64)k_in, lim, q, &c, &bin, &wc);
+      if (ok) {
+        lim.on = true; lim.key = c.key; lim.token = c.token; lim.bin = bin;
+        kept = wc;
+      }
+    }
+    if (ok && kept == 0) {
+      if (threadIdx.x == 0) out[r] = amax;
+      return;
+    }
+    if (ok && p_in < 1.f) {
+      u64 tp = (u64)((double)p_in * (double)kept);
+      if ((double)tp < (double)p_in * (double)kept) ++tp;   // ceil: cumulative >= top_p * total
+      ok = select_quick(row, V, mx, temp, scale, false, tp, lim, q, &c, &bin, nullptr);
+      if (ok) {
+        lim.on = true; lim.key = c.key; lim.token = c.token; lim.bin = bin;
+        kept = c.cum;
+      }
+    }
+    if (ok) {
+      u64 draw = (u64)((double)u * (double)kept);
+      if ((double)draw < (double)u * (double)kept) ++draw;
+      ok = select_quick(row, V, mx, temp, scale, false, draw, lim, q, &c, &bin, nullptr);
+      if (ok) {
+        if (threadIdx.x == 0) out[r] = c.token >= 0 ? c.token : amax;
+        return;
+      }
+    }
+    __syncthreads();
+  }
   Cut lim;
   lim.key = 0; lim.token = 0; lim.cum = 0;
   bool limited = false;
@@ -298,7 +592,6 @@ sample_kernel(const float* __restrict__ logits, size_t ld, int V,
     limited = true;
     kept = nucleus.cum;
   }
-  const float u = fminf(fmaxf(uniform[r], 0.f), 0.99999994f);
   u64 draw = (u64)((double)u * (double)kept);
   if ((double)draw < (double)u * (double)kept) ++draw;
   Cut pick = select_by_weight(row, V, mx, temp, false, draw, limited, lim, sh);
@@ -319,6 +612,10 @@ __global__ void penalty_kernel(float* logits, size_t ld, int V, const int32_t* r
 }
 }  // namespace
 
+namespace {
+int g_sample_mode = 0;
+}
+
 PBE_EXPORT int pbe_argmax(const float* logits, long long ld, int num_rows, int vocab, int32_t* out,
                           cudaStream_t stream) {
   if (num_rows <= 0) return 0;
@@ -333,9 +630,20 @@ PBE_EXPORT int pbe_sample(const float* logits, long long ld, int num_rows, int v
                           const float* temperature, const int32_t* top_k, const float* top_p,
                           const float* uniform, int32_t* out, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  sample_kernel<<<num_rows, THREADS, 0, stream>>>(logits, (size_t)ld, vocab, temperature, top_k,
-                                                  top_p, uniform, out);
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
+    opted = true;
+  }
+  sample_kernel<<<num_rows, THREADS, sizeof(Quick), stream>>>(logits, (size_t)ld, vocab, temperature, top_k,
+                                                               top_p, uniform, out, g_sample_mode);
   return launch_status();
+}
+
+// 0: the quick way with the radix descent behind it; 1: the radix descent only
+PBE_EXPORT int pbe_sample_set_mode(int mode) {
+  g_sample_mode = mode;
+  return 0;
 }
 
 PBE_EXPORT int pbe_apply_penalty(float* logits, long long ld, int vocab, const int32_t* rows,

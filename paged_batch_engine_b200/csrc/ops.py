@@ -589,6 +589,12 @@ def sample(logits, temperature, top_k, top_p, uniform, out=None) -> torch.Tensor
     return out
 
 
+def sample_set_mode(mode: int) -> None:
+    """0 (default): the sampling kernel's binned selection with the radix descent behind it; 1: the
+    radix descent only.  Both give the same token; the switch is for tests that compare them."""
+    _fn("sampling", "pbe_sample_set_mode", [c_int])(int(mode))
+
+
 def apply_penalty(logits, rows, tokens, penalties):
     """logits[rows[i], tokens[i]] is divided by penalties[i] when positive, multiplied
     otherwise; every (row, token) pair appears once."""

@@ -433,6 +433,56 @@ def test_sampler_matches_the_reference_algorithm(vocab):
     assert mismatches <= 2
 
 
+@pytest.mark.parametrize("vocab", [1, 2, 33, 1003, 152064])
+def test_sampler_binned_selection_equals_the_radix_descent(vocab):
+    """The kernel's quick way (bins by distance from the maximum, one bin sorted) and its radix
+    descent pick the same token: random rows, scaled rows, masks of -inf and of -1e9, rows of
+    equal logits (whose one crowded bin sends the quick way to the descent anyway), ties at the
+    top, and every combination of temperature, top-k and top-p."""
+    g = torch.Generator().manual_seed(vocab)
+    settings = [(0.8, 0, 1.0), (1.0, 40, 1.0), (0.7, 0, 0.9), (1.3, 50, 0.5), (0.1, 50, 0.9), (0.0, 5, 1.0),
+                (1.0, 1, 1.0), (0.5, 0, 0.01), (5.0, 0, 0.999), (1.0, 3000, 0.95), (1e-3, 0, 1.0), (1.0, 10 ** 6, 0.3)]
+    kinds = 8
+    n = len(settings) * kinds * 3
+    logits = torch.randn(n, vocab, generator=g) * 2.0
+    t, k, p = [], [], []
+    i = 0
+    for st in settings:
+        for kind in range(kinds):
+            for _ in range(3):
+                row = logits[i]
+                if kind == 1:
+                    row *= 10.0
+                elif kind == 2:
+                    row *= 0.01
+                elif kind == 3:
+                    row[torch.rand(vocab, generator=g) < 0.5] = float("-inf")
+                elif kind == 4:
+                    row[torch.rand(vocab, generator=g) < 0.7] = -1e9
+                elif kind == 5:
+                    row.fill_(0.25)
+                elif kind == 6:
+                    row.copy_(row.round())
+                elif kind == 7:
+                    row[: max(1, vocab // 3)] = row.max() + 1.0       # a third of the row ties for the top
+                t.append(st[0]); k.append(st[1]); p.append(st[2])
+                i += 1
+    u = torch.rand(n, generator=g)
+    u[::7] = 0.0
+    u[3::11] = 0.99999994
+    args = (logits.to(DEV), torch.tensor(t, dtype=torch.float32, device=DEV), torch.tensor(k, dtype=torch.int32, device=DEV),
+            torch.tensor(p, dtype=torch.float32, device=DEV), u.to(DEV))
+    o = ops()
+    try:
+        o.sample_set_mode(1)
+        slow = o.sample(*args).cpu()
+    finally:
+        o.sample_set_mode(0)
+    quick = o.sample(*args).cpu()
+    bad = (slow != quick).nonzero().flatten().tolist()
+    assert not bad, [(j, t[j], k[j], p[j], float(u[j]), int(slow[j]), int(quick[j])) for j in bad[:5]]
+
+
 def test_sampler_does_not_depend_on_the_batch_and_follows_the_distribution():
     torch.manual_seed(8)
     V, n = 1003, 4000
