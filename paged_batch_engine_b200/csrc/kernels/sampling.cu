@@ -297,18 +297,30 @@ argmax_cluster_kernel(const float* __restrict__ logits, size_t ld, int V, int32_
 // whose bin is too crowded for the list (thousands of equal logits).
 constexpr int NB = THREADS;        // one bin a thread in the prefix sums
 constexpr int LIST_CAP = 4096;
+constexpr int SAMPLE_CLUSTER = 8;  // blocks that share a row of a large vocabulary
+
+struct Picked {                    // a selection's result, handed to every block of the cluster
+  uint32_t key;
+  int token, bin, ok;
+  u64 cum, weight_cum;
+};
 
 struct Quick {
-  unsigned limb[3][NB];            // a bin's weight while it is summed: 14-bit limbs of every weight, so
-                                   // that 32-bit shared-memory atomics do (2^14 x 2^18 elements < 2^32)
-  u64 wsum[NB];
-  u64 cumw[NB + 1];                // weight of the bins before this one
-  unsigned cnt[NB];
-  unsigned cumc[NB + 1];
-  u64 list[LIST_CAP];              // (key << 32) | (0xffffffff - token): descending = the order
+  unsigned limb[3][NB];            // this block's share of a bin's weight while it is summed: 14-bit limbs
+                                   // of every weight, so that 32-bit shared-memory atomics do
+                                   // (2^14 x 2^18 elements < 2^32)
+  unsigned cnt_part[NB];           // this block's share of the bins' counts
+  u64 wsum[NB];                    // the row's bins: weight,
+  u64 cumw[NB + 1];                // weight of the bins before,
+  unsigned cnt[NB];                // count,
+  unsigned cumc[NB + 1];           // count of the bins before
+  u64 list[LIST_CAP];              // (key << 32) | (0xffffffff - token): descending = the order (block 0's is used)
   u64 warp_tot[NWARPS];
   u64 pick_cum;
   int n_list, chosen, first_idx, last_bin;
+  float part_max[SAMPLE_CLUSTER], part_min[SAMPLE_CLUSTER];
+  int part_idx[SAMPLE_CLUSTER];
+  Picked picked;
 };
 
 struct Limit {                     // the domain: the ordered list up to and including this element
@@ -316,6 +328,20 @@ struct Limit {                     // the domain: the ordered list up to and inc
   uint32_t key;
   int token, bin;
 };
+
+// One block or a cluster of CL blocks on a row: barriers and the other blocks' shared memory.
+template <int CL> __device__ __forceinline__ void sync_row() {
+  if constexpr (CL > 1) cooperative_groups::this_cluster().sync();
+  else __syncthreads();
+}
+template <int CL, typename T> __device__ __forceinline__ T* of_block(T* p, int rank) {
+  if constexpr (CL > 1) return cooperative_groups::this_cluster().map_shared_rank(p, rank);
+  else return p;
+}
+template <int CL> __device__ __forceinline__ int block_rank() {
+  if constexpr (CL > 1) return (int)cooperative_groups::this_cluster().block_rank();
+  else return 0;
+}
 
 __device__ __forceinline__ int value_bin(float x, float mx, float scale) {
   if (!(x > -INFINITY)) return NB - 1;
@@ -346,47 +372,69 @@ __device__ u64 block_exclusive_scan(u64 v, Quick& q, u64* total) {
   return before + inc - v;
 }
 
-// The bins of a row: counts, weights and their prefix sums.
-__device__ void fill_bins(const float* row, int V, float mx, float temp, float scale, Quick& q) {
+// The bins of a row: counts, weights and their prefix sums, in every block of the cluster.
+// slice: this block's part of the row (first token `lo`, `n` tokens).
+template <int CL>
+__device__ void fill_bins(const float* slice, int n, float mx, float temp, float scale, Quick& q) {
   const int tid = threadIdx.x;
-  q.cnt[tid] = 0;
+  q.cnt_part[tid] = 0;
   q.limb[0][tid] = q.limb[1][tid] = q.limb[2][tid] = 0;
-  if (tid == 0) q.last_bin = 0;
+  if (tid == 0) {
+    q.last_bin = 0;
+    q.n_list = 0;
+  }
   __syncthreads();
-  for_each_logit(row, V, [&](float x, int) {
+  for_each_logit(slice, n, [&](float x, int) {
     const int b = value_bin(x, mx, scale);
-    atomicAdd(&q.cnt[b], 1u);
+    atomicAdd(&q.cnt_part[b], 1u);
     const u64 w = weight_of(x, mx, temp, false);      // at most 2^40
     const unsigned l0 = (unsigned)w & 0x3fffu, l1 = (unsigned)(w >> 14) & 0x3fffu, l2 = (unsigned)(w >> 28);
     if (l0) atomicAdd(&q.limb[0][b], l0);
     if (l1) atomicAdd(&q.limb[1][b], l1);
     if (l2) atomicAdd(&q.limb[2][b], l2);
   });
-  __syncthreads();
-  q.wsum[tid] = (u64)q.limb[0][tid] + ((u64)q.limb[1][tid] << 14) + ((u64)q.limb[2][tid] << 28);
-  if (q.cnt[tid] > 0) atomicMax(&q.last_bin, tid);
+  sync_row<CL>();
+  // bin `tid` of the whole row: the sum over the blocks' shares (the same in every block)
+  unsigned c = 0;
+  u64 w = 0;
+#pragma unroll
+  for (int r = 0; r < CL; ++r) {
+    const Quick* o = of_block<CL>(&q, r);
+    c += o->cnt_part[tid];
+    w += (u64)o->limb[0][tid] + ((u64)o->limb[1][tid] << 14) + ((u64)o->limb[2][tid] << 28);
+  }
+  q.cnt[tid] = c;
+  q.wsum[tid] = w;
+  if (c > 0) atomicMax(&q.last_bin, tid);
   u64 tot;
-  const u64 ec = block_exclusive_scan((u64)q.cnt[tid], q, &tot);
+  const u64 ec = block_exclusive_scan((u64)c, q, &tot);
   q.cumc[tid] = (unsigned)ec;
   if (tid == 0) q.cumc[NB] = (unsigned)tot;
-  const u64 ew = block_exclusive_scan(q.wsum[tid], q, &tot);
+  const u64 ew = block_exclusive_scan(w, q, &tot);
   q.cumw[tid] = ew;
   if (tid == 0) q.cumw[NB] = tot;
-  __syncthreads();
+  // every block has read the others' shares: from here on a block may leave (a crowded bin sends
+  // all but block 0 home) without another block still reading its shared memory
+  sync_row<CL>();
 }
 
 // First element of the ordered list, inside the domain, whose weight is positive and whose
 // inclusive cumulative weight (count in count mode) reaches `target`; the domain's last element
 // if there is none: what select_by_weight returns.  In count mode *weight_cum gets the cumulative
-// weight at that element.  false (block-uniform): the element's bin is too crowded for the list.
-__device__ bool select_quick(const float* row, int V, float mx, float temp, float scale, bool count_mode, u64 target,
-                             const Limit& lim, Quick& q, Cut* out, int* out_bin, u64* weight_cum) {
+// weight at that element.  false (the same in every block of the row): the element's bin is too
+// crowded for the list.  Every block gathers from its slice (first token `lo`) into block 0's
+// list; block 0 sorts, scans and hands the result to all.
+template <int CL>
+__device__ bool select_quick(const float* slice, int lo, int n_slice, float mx, float temp, float scale,
+                             bool count_mode, u64 target, const Limit& lim, Quick& q, Cut* out, int* out_bin,
+                             u64* weight_cum) {
   const int tid = threadIdx.x;
+  const int rank = block_rank<CL>();
+  Quick* q0 = of_block<CL>(&q, 0);
   const int last_bin = lim.on ? lim.bin : q.last_bin;
   __syncthreads();
   if (tid == 0) {
     q.chosen = last_bin;
-    q.n_list = 0;
     q.first_idx = 0x7fffffff;
   }
   __syncthreads();
@@ -398,111 +446,130 @@ __device__ bool select_quick(const float* row, int V, float mx, float temp, floa
   __syncthreads();
   const int bin = q.chosen;
   if (q.cnt[bin] > (unsigned)LIST_CAP) return false;
-  // the bin's elements inside the domain
-  for_each_logit(row, V, [&](float x, int i) {
+  // the bin's elements inside the domain (block 0's counter is zero: it is reset after every use,
+  // a row barrier before the next)
+  for_each_logit(slice, n_slice, [&](float x, int i) {
     if (value_bin(x, mx, scale) != bin) return;
     const uint32_t key = order_key(x);
-    if (lim.on && !(key > lim.key || (key == lim.key && i <= lim.token))) return;
-    const int pos = atomicAdd(&q.n_list, 1);
-    q.list[pos] = ((u64)key << 32) | (u64)(0xffffffffu - (uint32_t)i);
+    const int token = lo + i;
+    if (lim.on && !(key > lim.key || (key == lim.key && token <= lim.token))) return;
+    const int pos = atomicAdd(&q0->n_list, 1);
+    q0->list[pos] = ((u64)key << 32) | (u64)(0xffffffffu - (uint32_t)token);
   });
-  __syncthreads();
-  const int n = q.n_list;
-  if (n <= 0) return false;        // cannot be: the bin has elements and the limit element is its own
-  int n2 = 32;
-  while (n2 < n) n2 <<= 1;
-  for (int i = n + tid; i < n2; i += THREADS) q.list[i] = 0;     // below every real key
-  __syncthreads();
-  if (n2 <= THREADS) {
-    // few elements: every element counts the larger ones (all are different: the token is part
-    // of them) and moves to that place; no barrier but two
-    const u64 mine = tid < n2 ? q.list[tid] : 0;
-    int rank = 0;
-    if (tid < n) {
-      for (int j = 0; j < n; ++j) rank += q.list[j] > mine ? 1 : 0;
-    }
-    __syncthreads();
-    if (tid < n) q.list[rank] = mine;
-    __syncthreads();
-  } else {
-    // bitonic sort, descending
-    for (int k = 2; k <= n2; k <<= 1) {
-      for (int j = k >> 1; j > 0; j >>= 1) {
-        for (int i = tid; i < n2; i += THREADS) {
-          const int partner = i ^ j;
-          if (partner > i) {
-            const u64 a = q.list[i], b = q.list[partner];
-            const bool down = (i & k) == 0;
-            if (down ? a < b : a > b) {
-              q.list[i] = b;
-              q.list[partner] = a;
+  sync_row<CL>();
+  if (rank == 0) {
+    const int n = q.n_list;
+    Picked res;
+    res.ok = n > 0 ? 1 : 0;        // n = 0 cannot be: the bin has elements and the limit element is its own
+    res.key = 0; res.token = -1; res.bin = bin; res.cum = 0; res.weight_cum = 0;
+    if (n > 0) {
+      int n2 = 32;
+      while (n2 < n) n2 <<= 1;
+      for (int i = n + tid; i < n2; i += THREADS) q.list[i] = 0;     // below every real key
+      __syncthreads();
+      if (n2 <= THREADS) {
+        // few elements: every element counts the larger ones (all are different: the token is part
+        // of them) and moves to that place
+        const u64 mine = tid < n2 ? q.list[tid] : 0;
+        int place = 0;
+        if (tid < n) {
+          for (int j = 0; j < n; ++j) place += q.list[j] > mine ? 1 : 0;
+        }
+        __syncthreads();
+        if (tid < n) q.list[place] = mine;
+        __syncthreads();
+      } else {
+        // bitonic sort, descending
+        for (int k = 2; k <= n2; k <<= 1) {
+          for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < n2; i += THREADS) {
+              const int partner = i ^ j;
+              if (partner > i) {
+                const u64 a = q.list[i], b = q.list[partner];
+                const bool down = (i & k) == 0;
+                if (down ? a < b : a > b) {
+                  q.list[i] = b;
+                  q.list[partner] = a;
+                }
+              }
+            }
+            __syncthreads();
+          }
+        }
+      }
+      // running sum along the sorted list, a few consecutive elements a thread
+      const int ipt = (n2 + THREADS - 1) / THREADS;       // 1 .. LIST_CAP / THREADS
+      constexpr int MAX_IPT = LIST_CAP / THREADS;
+      u64 w[MAX_IPT], rw[MAX_IPT];
+      u64 mine = 0;
+#pragma unroll
+      for (int j = 0; j < MAX_IPT; ++j) {
+        const int idx = tid * ipt + j;
+        w[j] = rw[j] = 0;
+        if (j < ipt && idx < n) {
+          rw[j] = weight_of(key_value((uint32_t)(q.list[idx] >> 32)), mx, temp, false);
+          w[j] = count_mode ? 1ull : rw[j];
+        }
+        mine += w[j];
+      }
+      u64 tot;
+      const u64 start = block_exclusive_scan(mine, q, &tot) + (count_mode ? (u64)q.cumc[bin] : q.cumw[bin]);
+      {
+        u64 run = start;
+#pragma unroll
+        for (int j = 0; j < MAX_IPT; ++j) {
+          const int idx = tid * ipt + j;
+          if (j < ipt && idx < n) {
+            run += w[j];
+            if (w[j] > 0 && run >= target) {
+              atomicMin(&q.first_idx, idx);
+              break;
             }
           }
         }
-        __syncthreads();
       }
-    }
-  }
-  // running sum along the sorted list, a few consecutive elements a thread
-  const int ipt = (n2 + THREADS - 1) / THREADS;       // 1 .. LIST_CAP / THREADS
-  constexpr int MAX_IPT = LIST_CAP / THREADS;
-  u64 w[MAX_IPT], rw[MAX_IPT];
-  u64 mine = 0;
+      __syncthreads();
+      const int pick = q.first_idx == 0x7fffffff ? n - 1 : q.first_idx;
+      u64 real_before = 0;           // this thread's weights up to and including the element
+      {
+        u64 run = start;
 #pragma unroll
-  for (int j = 0; j < MAX_IPT; ++j) {
-    const int idx = tid * ipt + j;
-    w[j] = rw[j] = 0;
-    if (j < ipt && idx < n) {
-      rw[j] = weight_of(key_value((uint32_t)(q.list[idx] >> 32)), mx, temp, false);
-      w[j] = count_mode ? 1ull : rw[j];
-    }
-    mine += w[j];
-  }
-  u64 tot;
-  const u64 start = block_exclusive_scan(mine, q, &tot) + (count_mode ? (u64)q.cumc[bin] : q.cumw[bin]);
-  {
-    u64 run = start;
-#pragma unroll
-    for (int j = 0; j < MAX_IPT; ++j) {
-      const int idx = tid * ipt + j;
-      if (j < ipt && idx < n) {
-        run += w[j];
-        if (w[j] > 0 && run >= target) {
-          atomicMin(&q.first_idx, idx);
-          break;
+        for (int j = 0; j < MAX_IPT; ++j) {
+          const int idx = tid * ipt + j;
+          if (j < ipt && idx < n && idx <= pick) {
+            run += w[j];
+            real_before += rw[j];
+            if (idx == pick) q.pick_cum = run;
+          }
         }
       }
+      u64 real_tot = 0;
+      block_exclusive_scan(real_before, q, &real_tot);
+      __syncthreads();
+      const u64 e = q.list[pick];
+      res.key = (uint32_t)(e >> 32);
+      res.token = (int)(0xffffffffu - (uint32_t)e);
+      res.cum = q.pick_cum;
+      res.weight_cum = q.cumw[bin] + real_tot;
     }
+    __syncthreads();
+    if (tid == 0) q.n_list = 0;
+    if (tid < CL) *of_block<CL>(&q.picked, tid) = res;
   }
-  __syncthreads();
-  const int pick = q.first_idx == 0x7fffffff ? n - 1 : q.first_idx;
-  u64 real_before = 0;           // this thread's weights up to and including the element
-  {
-    u64 run = start;
-#pragma unroll
-    for (int j = 0; j < MAX_IPT; ++j) {
-      const int idx = tid * ipt + j;
-      if (j < ipt && idx < n && idx <= pick) {
-        run += w[j];
-        real_before += rw[j];
-        if (idx == pick) q.pick_cum = run;
-      }
-    }
-  }
-  u64 real_tot = 0;
-  if (count_mode) block_exclusive_scan(real_before, q, &real_tot);
-  __syncthreads();
-  const u64 e = q.list[pick];
-  out->key = (uint32_t)(e >> 32);
-  out->token = (int)(0xffffffffu - (uint32_t)e);
-  out->cum = q.pick_cum;
-  *out_bin = bin;
-  if (weight_cum) *weight_cum = q.cumw[bin] + real_tot;
-  __syncthreads();
-  return true;
+  sync_row<CL>();
+  const Picked res = q.picked;
+  out->key = res.key;
+  out->token = res.token;
+  out->cum = res.cum;
+  *out_bin = res.bin;
+  if (weight_cum) *weight_cum = res.weight_cum;
+  return res.ok != 0;
 }
 
-// mode 1: the radix descent only (for tests that compare the two ways)
+// One block a row, or a cluster of CL blocks a row (large vocabularies: each block takes a slice
+// of the row for every pass; block 0 sorts the gathered bin and writes the token).
+// mode 1: the radix descent only (for tests that compare the two ways).
+template <int CL>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, size_t ld, int V,
               const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
@@ -511,27 +578,55 @@ sample_kernel(const float* __restrict__ logits, size_t ld, int V,
   __shared__ Shared sh;
   extern __shared__ __align__(16) unsigned char quick_raw[];
   Quick& q = *reinterpret_cast<Quick*>(quick_raw);
-  const int r = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int rank = block_rank<CL>();
+  const int r = blockIdx.x / CL;
   const float* row = logits + (size_t)r * ld;
-  float mx, mn;
-  int amax;
-  block_argmax(row, V, sh, &mx, &amax, &mn);
+  const int chunk = CL > 1 ? (((V + CL - 1) / CL + 3) & ~3) : V;
+  const int lo = min(V, rank * chunk), n_slice = min(V, lo + chunk) - lo;
+  const float* slice = row + lo;
+  float mx = -INFINITY, mn = INFINITY;
+  int amax = 0x7fffffff;
+  if (n_slice > 0) {
+    block_argmax(slice, n_slice, sh, &mx, &amax, &mn);
+    amax += lo;
+  }
+  if constexpr (CL > 1) {
+    if (threadIdx.x < CL) {
+      Quick* o = of_block<CL>(&q, threadIdx.x);
+      o->part_max[rank] = mx;
+      o->part_idx[rank] = amax;
+      o->part_min[rank] = mn;
+    }
+    sync_row<CL>();
+    mx = q.part_max[0]; amax = q.part_idx[0]; mn = q.part_min[0];
+#pragma unroll
+    for (int i = 1; i < CL; ++i) {
+      const float v = q.part_max[i];
+      const int vi = q.part_idx[i];
+      if (v > mx || (v == mx && vi < amax)) { mx = v; amax = vi; }
+      mn = fminf(mn, q.part_min[i]);
+    }
+  }
+  if (amax == 0x7fffffff) amax = 0;
+  const bool writer = rank == 0 && threadIdx.x == 0;
   const float t_in = temperature[r];
   const int k_in = top_k[r];
   const float p_in = fminf(fmaxf(top_p[r], 0.f), 1.f);
   if ((t_in <= 0.f && k_in <= 0 && p_in >= 1.f) || !(mx > -INFINITY)) {
-    if (threadIdx.x == 0) out[r] = amax;
+    if (writer) out[r] = amax;
     return;
   }
   const float temp = fmaxf(t_in, 1e-6f);
   const float u = fminf(fmaxf(uniform[r], 0.f), 0.99999994f);
-  if (mode != 1 && V < (1 << 18)) {      // (the limbs of a bin's weight sum hold 2^18 elements)
+  if (mode != 1 && chunk < (1 << 18)) {      // (the limbs of a bin's weight sum hold 2^18 elements)
     // bins over the logits from the maximum down to the smallest one, but no further than where
     // weights have long vanished (masks of -1e9 would otherwise stretch the bins): what lies
     // below shares the last bin
     const float reach = fminf(mx - mn, fmaxf(64.f * temp, 32.f));
     const float scale = reach > 0.f ? (float)(NB - 1) / reach : 0.f;
-    fill_bins(row, V, mx, temp, scale, q);
+    fill_bins<CL>(slice, n_slice, mx, temp, scale, q);
     Limit lim;
     lim.on = false; lim.key = 0; lim.token = 0; lim.bin = 0;
     u64 kept = q.cumw[NB];
@@ -540,20 +635,20 @@ sample_kernel(const float* __restrict__ logits, size_t ld, int V,
     int bin = 0;
     if (k_in > 0 && k_in < V) {
       u64 wc = 0;
-      ok = select_quick(row, V, mx, temp, scale, true, (u64)k_in, lim, q, &c, &bin, &wc);
+      ok = select_quick<CL>(slice, lo, n_slice, mx, temp, scale, true, (u64)k_in, lim, q, &c, &bin, &wc);
       if (ok) {
         lim.on = true; lim.key = c.key; lim.token = c.token; lim.bin = bin;
         kept = wc;
       }
     }
     if (ok && kept == 0) {
-      if (threadIdx.x == 0) out[r] = amax;
+      if (writer) out[r] = amax;
       return;
     }
     if (ok && p_in < 1.f) {
       u64 tp = (u64)((double)p_in * (double)kept);
       if ((double)tp < (double)p_in * (double)kept) ++tp;   // ceil: cumulative >= top_p * total
-      ok = select_quick(row, V, mx, temp, scale, false, tp, lim, q, &c, &bin, nullptr);
+      ok = select_quick<CL>(slice, lo, n_slice, mx, temp, scale, false, tp, lim, q, &c, &bin, nullptr);
       if (ok) {
         lim.on = true; lim.key = c.key; lim.token = c.token; lim.bin = bin;
         kept = c.cum;
@@ -562,14 +657,16 @@ sample_kernel(const float* __restrict__ logits, size_t ld, int V,
     if (ok) {
       u64 draw = (u64)((double)u * (double)kept);
       if ((double)draw < (double)u * (double)kept) ++draw;
-      ok = select_quick(row, V, mx, temp, scale, false, draw, lim, q, &c, &bin, nullptr);
+      ok = select_quick<CL>(slice, lo, n_slice, mx, temp, scale, false, draw, lim, q, &c, &bin, nullptr);
       if (ok) {
-        if (threadIdx.x == 0) out[r] = c.token >= 0 ? c.token : amax;
+        if (writer) out[r] = c.token >= 0 ? c.token : amax;
         return;
       }
     }
     __syncthreads();
   }
+  // the radix descent over the whole row, by one block
+  if (rank != 0) return;
   Cut lim;
   lim.key = 0; lim.token = 0; lim.cum = 0;
   bool limited = false;
@@ -632,11 +729,17 @@ PBE_EXPORT int pbe_sample(const float* logits, long long ld, int num_rows, int v
   if (num_rows <= 0) return 0;
   static bool opted = false;
   if (!opted) {
-    cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
+    cudaFuncSetAttribute(sample_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
+    cudaFuncSetAttribute(sample_kernel<SAMPLE_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
     opted = true;
   }
-  sample_kernel<<<num_rows, THREADS, sizeof(Quick), stream>>>(logits, (size_t)ld, vocab, temperature, top_k,
-                                                               top_p, uniform, out, g_sample_mode);
+  // a cluster a row where a row is long and every block of the step finds a multiprocessor at once
+  if (g_sample_mode != 1 && vocab >= 8 * THREADS && num_rows * SAMPLE_CLUSTER <= 148)
+    launch_k_cluster(sample_kernel<SAMPLE_CLUSTER>, num_rows * SAMPLE_CLUSTER, THREADS, sizeof(Quick), stream,
+                     SAMPLE_CLUSTER, logits, (size_t)ld, vocab, temperature, top_k, top_p, uniform, out, g_sample_mode);
+  else
+    launch_k(sample_kernel<1>, num_rows, THREADS, sizeof(Quick), stream, logits, (size_t)ld, vocab, temperature, top_k,
+             top_p, uniform, out, g_sample_mode);
   return launch_status();
 }
 

@@ -433,7 +433,7 @@ def test_sampler_matches_the_reference_algorithm(vocab):
     assert mismatches <= 2
 
 
-@pytest.mark.parametrize("vocab", [1, 2, 33, 1003, 152064])
+@pytest.mark.parametrize("vocab", [1, 2, 33, 1003, 8192, 8193, 152064])
 def test_sampler_binned_selection_equals_the_radix_descent(vocab):
     """The kernel's quick way (bins by distance from the maximum, one bin sorted) and its radix
     descent pick the same token: random rows, scaled rows, masks of -inf and of -1e9, rows of
@@ -478,9 +478,13 @@ def test_sampler_binned_selection_equals_the_radix_descent(vocab):
         slow = o.sample(*args).cpu()
     finally:
         o.sample_set_mode(0)
-    quick = o.sample(*args).cpu()
-    bad = (slow != quick).nonzero().flatten().tolist()
-    assert not bad, [(j, t[j], k[j], p[j], float(u[j]), int(slow[j]), int(quick[j])) for j in bad[:5]]
+    # all rows at once (a block a row), and a few rows a call (a cluster of blocks a row when the
+    # vocabulary is large)
+    for rows_a_call in (n, 16):
+        quick = torch.cat([o.sample(*[a[i:i + rows_a_call].contiguous() for a in args]).cpu()
+                           for i in range(0, n, rows_a_call)])
+        bad = (slow != quick).nonzero().flatten().tolist()
+        assert not bad, (rows_a_call, [(j, t[j], k[j], p[j], float(u[j]), int(slow[j]), int(quick[j])) for j in bad[:5]])
 
 
 def test_sampler_does_not_depend_on_the_batch_and_follows_the_distribution():
