@@ -707,10 +707,65 @@ __global__ void penalty_kernel(float* logits, size_t ld, int V, const int32_t* r
   const float x = *p, pen = penalties[i];
   *p = x > 0.f ? x / pen : x * pen;
 }
+
+// The repetition penalty without the host: a byte per (request slot, token) says whether the
+// request has had the token.  seen[slot(i)][tokens[i]] = 1; slots == null: all in `slot`.
+__global__ void seen_mark_kernel(unsigned char* seen, size_t ld, int V, const int32_t* slots, int slot,
+                                 const int32_t* tokens, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int s = slots ? slots[i] : slot;
+  const int tok = tokens[i];
+  if (s < 0 || tok < 0 || tok >= V) return;
+  seen[(size_t)s * ld + tok] = 1;
+}
+
+// logits[r, t] /= penalty (positive) or *= penalty (otherwise) for every token t that row r's
+// request slot has seen; rows with slot < 0 are left alone.  Four tokens a thread (ld % 4 == 0).
+__global__ void penalty_seen_kernel(float* logits, size_t ld, int V, const unsigned char* seen, size_t seen_ld,
+                                    const int32_t* slots, const float* penalties) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int s = slots[r];
+  if (s < 0) return;
+  const int t0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (t0 >= V) return;
+  const unsigned m = *reinterpret_cast<const unsigned*>(seen + (size_t)s * seen_ld + t0);
+  if (m == 0) return;
+  const float pen = penalties[r];
+  float* row = logits + (size_t)r * ld;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (((m >> (8 * j)) & 0xffu) && t0 + j < V) {
+      const float x = row[t0 + j];
+      row[t0 + j] = x > 0.f ? x / pen : x * pen;
+    }
+  }
+}
 }  // namespace
 
 namespace {
 int g_sample_mode = 0;
+}
+
+// seen: [slots, seen_ld] bytes, seen_ld a multiple of 4 and at least vocab.
+PBE_EXPORT int pbe_seen_mark(unsigned char* seen, long long seen_ld, int vocab, const int32_t* slots, int slot,
+                             const int32_t* tokens, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  launch_k(seen_mark_kernel, (n + 255) / 256, 256, 0, stream, seen, (size_t)seen_ld, vocab, slots, slot, tokens, n);
+  return launch_status();
+}
+
+PBE_EXPORT int pbe_penalty_seen(float* logits, long long ld, int num_rows, int vocab, const unsigned char* seen,
+                                long long seen_ld, const int32_t* slots, const float* penalties, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (seen_ld % 4 != 0 || seen_ld < vocab || num_rows > 65535) return (int)cudaErrorInvalidValue;
+  launch_k(penalty_seen_kernel, dim3((vocab + 1023) / 1024, num_rows), 256, 0, stream, logits, (size_t)ld, vocab, seen,
+           (size_t)seen_ld, slots, penalties);
+  return launch_status();
 }
 
 PBE_EXPORT int pbe_argmax(const float* logits, long long ld, int num_rows, int vocab, int32_t* out,

@@ -589,6 +589,31 @@ def sample(logits, temperature, top_k, top_p, uniform, out=None) -> torch.Tensor
     return out
 
 
+def seen_mark(seen: torch.Tensor, tokens: torch.Tensor, slots: Optional[torch.Tensor] = None, slot: int = -1) -> None:
+    """seen[slots[i], tokens[i]] = 1 (``slots`` None: all in row ``slot``).  seen: uint8
+    [slots, ld], tokens and slots int32 on the device; slots below 0 are skipped."""
+    _need_cuda(seen, tokens, slots)
+    if seen.dtype != torch.uint8 or tokens.dtype != torch.int32 or (slots is not None and slots.dtype != torch.int32):
+        raise KernelError("seen_mark: a uint8 table, int32 tokens and slots")
+    fn = _fn("sampling", "pbe_seen_mark", [c_void_p, c_ll, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(seen), seen.stride(0), seen.shape[1], _ptr(slots), int(slot), _ptr(tokens), tokens.numel(),
+              _stream()), "seen_mark")
+
+
+def penalty_seen(logits: torch.Tensor, seen: torch.Tensor, slots: torch.Tensor, penalties: torch.Tensor) -> torch.Tensor:
+    """The repetition penalty from the table of seen tokens: row r of ``logits`` takes the
+    tokens marked in seen[slots[r]] (slot below 0: the row is left alone)."""
+    _need_cuda(logits, seen, slots, penalties)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or seen.dtype != torch.uint8 or \
+            slots.dtype != torch.int32 or penalties.dtype != torch.float32 or slots.numel() != n or penalties.numel() != n:
+        raise KernelError("penalty_seen: wrong dtypes or sizes")
+    fn = _fn("sampling", "pbe_penalty_seen", [c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), n, V, _ptr(seen), seen.stride(0), _ptr(slots), _ptr(penalties),
+              _stream()), "penalty_seen")
+    return logits
+
+
 def sample_set_mode(mode: int) -> None:
     """0 (default): the sampling kernel's binned selection with the radix descent behind it; 1: the
     radix descent only.  Both give the same token; the switch is for tests that compare them."""

@@ -75,7 +75,7 @@ class Engine:
                             long_prefill_token_threshold=long_prefill_token_threshold,
                             max_model_len=self.max_model_len),
             self.runner.cache, spec.eos_token_ids)
-        self.sampler = Sampler(self.device)
+        self.sampler = Sampler(self.device, max_requests=max_num_seqs)
         self.use_cuda_graphs = use_cuda_graphs
         self.decode_ahead = bool(decode_ahead and use_cuda_graphs)   # pipeline decode steps one deep
         self._pending = None
@@ -114,7 +114,7 @@ class Engine:
                 self._finish(prev)
                 self.profile["schedule"] += time.perf_counter() - t0
                 self.profile["steps"] += 1
-                return self.scheduler.pop_finished()
+                return self._pop_finished()
             self._finish(prev)
         out = self.scheduler.schedule_step()
         t1 = time.perf_counter()
@@ -129,14 +129,20 @@ class Engine:
             else:
                 self._finish(launched)
                 self.profile["sample"] += time.perf_counter() - t2
-        return self.scheduler.pop_finished()
+        return self._pop_finished()
+
+    def _pop_finished(self) -> List[Request]:
+        done = self.scheduler.pop_finished()
+        for r in done:
+            self.sampler.untrack(r.request_id)
+        return done
 
     def drain(self) -> List[Request]:
         """Waits for a step left running by ``step()`` and does its bookkeeping."""
         if self._pending is not None:
             prev, self._pending = self._pending, None
             self._finish(prev)
-        return self.scheduler.pop_finished()
+        return self._pop_finished()
 
     def _launch(self, out, device_tokens):
         """Enqueues the step and its sampling.  Returns (out, ids on the device, ids in pinned
@@ -150,16 +156,21 @@ class Engine:
         params = [e.request.params for e in rows]
         counters = [e.request.sampling_counter if e.counter is None else e.counter for e in rows]
         later = decode_only and self.decode_ahead and self.runner.graphs is not None and \
-            self.runner.graphs.eligible(entries) and all(p.repetition_penalty == 1.0 for p in params)
+            self.runner.graphs.eligible(entries)
         if device_tokens is not None and not later:
             raise RuntimeError("a step scheduled ahead must be a captured decode step")
+        # a request with a repetition penalty gets its row of seen tokens on the device the first
+        # time it is sampled (all it has so far: after a preemption its generated tokens too)
+        keys = [e.request.request_id for e in rows]
+        vocab = self.runner.model.spec.vocab_size
+        for e in rows:
+            if e.request.params.repetition_penalty != 1.0 and not self.sampler.tracked(e.request.request_id):
+                self.sampler.track(e.request.request_id, e.request.tokens, vocab)
         if later:
-            dev, host, event = self.sampler.sample_async(logits, params, counters)
+            dev, host, event = self.sampler.sample_async(logits, params, counters, keys)
             return out, dev, host, event
         if rows:
-            ids = self.sampler.sample(logits, params, counters,
-                                      [e.request.tokens if e.request.params.repetition_penalty != 1.0 else ()
-                                       for e in rows])
+            ids = self.sampler.sample(logits, params, counters, keys=keys)
         else:
             torch.cuda.current_stream().synchronize()
             ids = []
@@ -185,7 +196,7 @@ class Engine:
         if len(sampling_params) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
         reqs = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
-        finished: Dict[int, Request] = {r.request_id: r for r in self.scheduler.pop_finished()}
+        finished: Dict[int, Request] = {r.request_id: r for r in self._pop_finished()}
         while self.has_unfinished_requests():
             for r in self.step():
                 finished[r.request_id] = r

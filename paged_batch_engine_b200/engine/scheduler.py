@@ -304,7 +304,7 @@ class Scheduler:
         for e in prev.entries:
             req, p = e.request, e.request.params
             if (len(e.tokens) != 1 or not e.samples or req.done or req.status != "running" or req.recompute
-                    or p.repetition_penalty != 1.0 or req.generated + 1 >= p.max_new_tokens
+                    or req.generated + 1 >= p.max_new_tokens
                     or (limit > 0 and req.target + 1 >= limit)):
                 return None
         handles = [e.request.handle for e in prev.entries]

@@ -17,19 +17,73 @@ class Sampler:
     kernel.  The reference sends every batch with top_k outside 1..32 or with a penalty
     through the host with the whole logits matrix (infMain/source/model/qwen2.cpp:1870-1987)."""
 
-    def __init__(self, device):
+    def __init__(self, device, max_requests: int = 0):
         self.device = device
         self._async_slots = []
         self._async_next = 0
+        # the repetition penalty's table of seen tokens: a row of bytes per tracked request, made
+        # when the first request with a penalty arrives
+        self._seen = None
+        self._seen_rows = max(int(max_requests), 8)
+        self._slot_of = {}
+        self._free_slots: List[int] = []
 
-    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]):
+    # ------------------------------------------------------------------ seen tokens, on the device
+    def tracked(self, key) -> bool:
+        return key in self._slot_of
+
+    def track(self, key, tokens: Sequence[int], vocab: int) -> None:
+        """Starts a row of seen tokens for request ``key`` with the tokens it has so far; from
+        then on every token sampled for it is marked on the device, so that the penalty needs
+        nothing from the host."""
+        if key in self._slot_of:
+            return
+        if self._seen is None or self._seen.shape[1] < vocab:
+            ld = (vocab + 15) // 16 * 16
+            self._seen = torch.zeros((self._seen_rows, ld), dtype=torch.uint8, device=self.device)
+            self._free_slots = list(range(self._seen_rows - 1, -1, -1))
+            self._slot_of = {}
+        if not self._free_slots:
+            more = torch.zeros_like(self._seen)
+            self._free_slots = list(range(2 * self._seen_rows - 1, self._seen_rows - 1, -1))
+            self._seen = torch.cat([self._seen, more])
+            self._seen_rows *= 2
+        slot = self._free_slots.pop()
+        self._slot_of[key] = slot
+        self._seen[slot].zero_()
+        if len(tokens):
+            ids = torch.from_numpy(np.asarray(tokens, dtype=np.int32)).to(self.device)
+            ops.seen_mark(self._seen, ids, None, slot)
+
+    def untrack(self, key) -> None:
+        slot = self._slot_of.pop(key, None)
+        if slot is not None:
+            self._free_slots.append(slot)
+
+    def _penalty_rows(self, params: Sequence[SamplingParams], keys):
+        """(slots, penalties) on the device for the rows of a step, or None when no row has a
+        tracked request with a penalty."""
+        if keys is None or self._seen is None:
+            return None
+        slots = [self._slot_of.get(k, -1) if p.repetition_penalty != 1.0 else -1 for p, k in zip(params, keys)]
+        if all(s < 0 for s in slots):
+            return None
+        pack = np.array([slots, [0] * len(slots)], dtype=np.int32)
+        pack[1] = np.array([p.repetition_penalty for p in params], dtype=np.float32).view(np.int32)
+        dev = torch.from_numpy(pack).to(self.device)
+        return dev[0], dev[1].view(torch.float32)
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
+                     keys=None):
         """Launches the sampling of every row and the copy of the ids to pinned host memory;
         returns (ids on the device, ids on the host, event): the host list is valid once the
-        event has completed.  No row may ask for a repetition penalty (that needs the request's
-        tokens on the host).  Buffers rotate over four steps."""
+        event has completed.  ``keys``: the rows' request keys; a row with a repetition penalty
+        must belong to a tracked request (``track``).  Buffers rotate over four steps."""
         n = logits.shape[0]
-        if any(p.repetition_penalty != 1.0 for p in params):
-            raise ValueError("sample_async does not take a repetition penalty")
+        pen = self._penalty_rows(params, keys)
+        if any(p.repetition_penalty != 1.0 and (keys is None or not self.tracked(k))
+               for p, k in zip(params, keys if keys is not None else [None] * n)):
+            raise ValueError("sample_async: a row with a repetition penalty needs a tracked request")
         slot = self._async_slots[self._async_next % len(self._async_slots)] if self._async_slots else None
         if slot is None or slot[0].numel() < n:
             cap = max(64, 2 * n)
@@ -40,6 +94,8 @@ class Sampler:
             self._async_next = 0
         self._async_next += 1
         dev, host, event = slot
+        if pen is not None:
+            ops.penalty_seen(logits, self._seen, pen[0], pen[1])
         if all(p.is_greedy for p in params):
             ops.argmax(logits, dev[:n])
         else:
@@ -49,33 +105,44 @@ class Sampler:
             fdev = torch.from_numpy(floats).to(self.device)
             kdev = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
             ops.sample(logits, fdev[0].contiguous(), kdev, fdev[1].contiguous(), fdev[2].contiguous(), out=dev[:n])
+        if pen is not None:
+            ops.seen_mark(self._seen, dev[:n], pen[0])
         host[:n].copy_(dev[:n], non_blocking=True)
         event.record()
         return dev[:n], host[:n], event
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
-               seen: Sequence[Sequence[int]]) -> List[int]:
+               seen: Sequence[Sequence[int]] = (), keys=None) -> List[int]:
+        """The rows' tokens, on the host.  The repetition penalty takes its tokens from the
+        tracked requests' table on the device (``keys``: the rows' request keys), or, without
+        keys, from ``seen`` (a list of token lists, one per row)."""
         n = logits.shape[0]
         if n == 0:
             return []
         if all(p.is_greedy for p in params):
             return ops.argmax(logits).cpu().tolist()
-        pen_rows, pen_tokens, pen_vals = [], [], []
-        for r, p in enumerate(params):
-            if p.repetition_penalty != 1.0:
-                uniq = sorted(set(int(t) for t in seen[r]))
-                pen_rows += [r] * len(uniq)
-                pen_tokens += uniq
-                pen_vals += [p.repetition_penalty] * len(uniq)
-        if pen_rows:
-            pack = np.array([pen_rows, pen_tokens], dtype=np.int32)
-            dev = torch.from_numpy(pack).to(self.device)
-            ops.apply_penalty(logits, dev[0].contiguous(), dev[1].contiguous(),
-                              torch.tensor(pen_vals, dtype=torch.float32, device=self.device))
+        pen = self._penalty_rows(params, keys)
+        if pen is not None:
+            ops.penalty_seen(logits, self._seen, pen[0], pen[1])
+        elif keys is None:
+            pen_rows, pen_tokens, pen_vals = [], [], []
+            for r, p in enumerate(params):
+                if p.repetition_penalty != 1.0 and r < len(seen):
+                    uniq = sorted(set(int(t) for t in seen[r]))
+                    pen_rows += [r] * len(uniq)
+                    pen_tokens += uniq
+                    pen_vals += [p.repetition_penalty] * len(uniq)
+            if pen_rows:
+                pack = np.array([pen_rows, pen_tokens], dtype=np.int32)
+                dev = torch.from_numpy(pack).to(self.device)
+                ops.apply_penalty(logits, dev[0].contiguous(), dev[1].contiguous(),
+                                  torch.tensor(pen_vals, dtype=torch.float32, device=self.device))
         floats = np.array([[p.temperature for p in params], [p.top_p for p in params],
                            [request_sample_uniform(p.seed, c) for p, c in zip(params, counters)]],
                           dtype=np.float32)
         fdev = torch.from_numpy(floats).to(self.device)
         kdev = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
         out = ops.sample(logits, fdev[0].contiguous(), kdev, fdev[1].contiguous(), fdev[2].contiguous())
+        if pen is not None:
+            ops.seen_mark(self._seen, out, pen[0])
         return out.cpu().tolist()

@@ -183,6 +183,31 @@ def test_temperature_sampling_follows_the_reference_algorithm(tiny_folders):
     assert any(len(set(r.output_tokens)) > 3 for r in res)     # it really sampled
 
 
+def test_repetition_penalty_with_steps_in_flight_and_after_preemption(tiny_folders):
+    """Requests with a repetition penalty decode through captured steps launched one ahead (their
+    seen tokens live on the device) and give the tokens of an engine that reads every step before
+    the next, also when pages run out and requests are recomputed."""
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    prompts = prompts_for(cfg["vocab_size"], [20, 25, 30, 18], seed=11)
+    params = [SamplingParams(max_new_tokens=30, temperature=t, top_k=k, repetition_penalty=pen, seed=3 + i, ignore_eos=True)
+              for i, (t, k, pen) in enumerate([(0.0, 0, 50.0), (0.9, 30, 1.2), (0.7, 0, 1.0), (1.2, 0, 0.8)])]
+    plainly = engine(folder, "float32", page, num_pages=64, use_cuda_graphs=False).generate(prompts, params)
+    ahead_engine = engine(folder, "float32", page, num_pages=64)
+    ahead = ahead_engine.generate(prompts, params)
+    assert ahead_engine.scheduler.metrics["ahead_steps"] > 0
+    tight_engine = engine(folder, "float32", page, num_pages=9)
+    tight = tight_engine.generate(prompts, params)
+    assert tight_engine.scheduler.metrics["preemptions"] > 0
+    for a, b, c in zip(plainly, ahead, tight):
+        assert a.output_tokens == b.output_tokens == c.output_tokens
+    assert not ahead_engine.sampler._slot_of and not tight_engine.sampler._slot_of      # rows given back
+    # the greedy request with a penalty of 50 hardly ever repeats a token, the plain greedy one does
+    free = engine(folder, "float32", page, num_pages=64).generate(prompts[:1], SamplingParams(max_new_tokens=30, ignore_eos=True))
+    assert len(set(ahead[0].output_tokens)) >= 25 > len(set(free[0].output_tokens))
+
+
 def test_few_pages_preempt_and_recompute_without_changing_tokens(tiny_folders):
     from paged_batch_engine_b200 import SamplingParams
     cfg, _, page, _ = TINY["A"]

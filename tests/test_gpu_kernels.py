@@ -513,6 +513,32 @@ def test_repetition_penalty():
     assert logits.cpu().tolist() == [[1.0, -4.0, 2.0, 0.5], [2.0, 3.0, -1.0, 2.0]]
 
 
+def test_repetition_penalty_from_the_table_of_seen_tokens():
+    """seen_mark + penalty_seen do what apply_penalty does with host lists: every token a slot
+    has seen once, rows without a slot untouched, a vocabulary that is no multiple of four."""
+    o = ops()
+    V, slots_n = 1003, 5
+    g = torch.Generator().manual_seed(3)
+    seen = torch.zeros(slots_n, 1008, dtype=torch.uint8, device=DEV)
+    hist = {1: [5, 5, 1002, 17, 0], 3: [999, 1001, 4]}
+    for slot, toks in hist.items():
+        o.seen_mark(seen, torch.tensor(toks, dtype=torch.int32, device=DEV), None, slot)
+    # marks by row: (slot, token) pairs, a slot of -1 is skipped
+    o.seen_mark(seen, torch.tensor([7, 8, 9], dtype=torch.int32, device=DEV),
+                torch.tensor([1, -1, 3], dtype=torch.int32, device=DEV))
+    hist[1].append(7); hist[3].append(9)
+    assert int(seen.sum()) == len(set(hist[1])) + len(set(hist[3]))
+    logits = torch.randn(4, V, generator=g)
+    want = logits.clone()
+    row_slots, pens = [3, -1, 1, 1], [1.5, 2.0, 0.5, 1.3]
+    for r, (sl, pen) in enumerate(zip(row_slots, pens)):
+        for t in set(hist.get(sl, [])):
+            want[r, t] = want[r, t] / pen if want[r, t] > 0 else want[r, t] * pen
+    got = o.penalty_seen(logits.to(DEV), seen, torch.tensor(row_slots, dtype=torch.int32, device=DEV),
+                         torch.tensor(pens, device=DEV)).cpu()
+    assert torch.equal(got, want)
+
+
 # ------------------------------------------------------------------ weight-streaming GEMM for few rows
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(64, 64), (1000, 88), (517, 192), (4608, 3584), (320, 2368)])
