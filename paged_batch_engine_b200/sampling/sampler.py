@@ -78,9 +78,10 @@ class Sampler:
         """Launches the sampling of every row and the copy of the ids to pinned host memory;
         returns (ids on the device, ids on the host, event): the host list is valid once the
         event has completed.  ``keys``: the rows' request keys; a row with a repetition penalty
-        must belong to a tracked request (``track``).  Buffers rotate over four steps."""
+        must belong to a tracked request (``track``).  Nothing here waits for the device: the
+        rows' parameters go up from pinned memory (a copy from pageable memory would first wait
+        for the stream, i.e. for the step that is still running).  Buffers rotate over four steps."""
         n = logits.shape[0]
-        pen = self._penalty_rows(params, keys)
         if any(p.repetition_penalty != 1.0 and (keys is None or not self.tracked(k))
                for p, k in zip(params, keys if keys is not None else [None] * n)):
             raise ValueError("sample_async: a row with a repetition penalty needs a tracked request")
@@ -89,24 +90,37 @@ class Sampler:
             cap = max(64, 2 * n)
             self._async_slots = [(torch.empty(cap, dtype=torch.int32, device=self.device),
                                   torch.empty(cap, dtype=torch.int32, pin_memory=True),
-                                  torch.cuda.Event()) for _ in range(4)]
+                                  torch.cuda.Event(),
+                                  torch.empty((6, cap), dtype=torch.int32, device=self.device),
+                                  torch.empty((6, cap), dtype=torch.int32, pin_memory=True)) for _ in range(4)]
             slot = self._async_slots[0]
             self._async_next = 0
         self._async_next += 1
-        dev, host, event = slot
-        if pen is not None:
-            ops.penalty_seen(logits, self._seen, pen[0], pen[1])
+        dev, host, event, pdev, phost = slot
         if all(p.is_greedy for p in params):
             ops.argmax(logits, dev[:n])
         else:
-            floats = np.array([[p.temperature for p in params], [p.top_p for p in params],
-                               [request_sample_uniform(p.seed, c) for p, c in zip(params, counters)]],
-                              dtype=np.float32)
-            fdev = torch.from_numpy(floats).to(self.device)
-            kdev = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
-            ops.sample(logits, fdev[0].contiguous(), kdev, fdev[1].contiguous(), fdev[2].contiguous(), out=dev[:n])
-        if pen is not None:
-            ops.seen_mark(self._seen, dev[:n], pen[0])
+            # rows of the parameter block: temperature, top_p, uniform (float32 bits), top_k, the
+            # penalty's slot of seen tokens (-1: none), the penalty (float32 bits)
+            event.synchronize()              # the copy that last read this pinned block is over (four steps ago)
+            block = phost.numpy()
+            fl = block.view(np.float32)
+            fl[0, :n] = [p.temperature for p in params]
+            fl[1, :n] = [p.top_p for p in params]
+            fl[2, :n] = [request_sample_uniform(p.seed, c) for p, c in zip(params, counters)]
+            block[3, :n] = [p.top_k for p in params]
+            slots = [self._slot_of.get(k, -1) if p.repetition_penalty != 1.0 else -1
+                     for p, k in zip(params, keys if keys is not None else [None] * n)]
+            block[4, :n] = slots
+            fl[5, :n] = [p.repetition_penalty for p in params]
+            pdev[:, :n].copy_(phost[:, :n], non_blocking=True)
+            fdev = pdev.view(torch.float32)
+            penalised = any(sl >= 0 for sl in slots)
+            if penalised:
+                ops.penalty_seen(logits, self._seen, pdev[4, :n], fdev[5, :n])
+            ops.sample(logits, fdev[0, :n], pdev[3, :n], fdev[1, :n], fdev[2, :n], out=dev[:n])
+            if penalised:
+                ops.seen_mark(self._seen, dev[:n], pdev[4, :n])
         host[:n].copy_(dev[:n], non_blocking=True)
         event.record()
         return dev[:n], host[:n], event
