@@ -785,16 +785,32 @@ PBE_EXPORT int pbe_sample(const float* logits, long long ld, int num_rows, int v
   static bool opted = false;
   if (!opted) {
     cudaFuncSetAttribute(sample_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
+    cudaFuncSetAttribute(sample_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
+    cudaFuncSetAttribute(sample_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
     cudaFuncSetAttribute(sample_kernel<SAMPLE_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Quick));
     opted = true;
   }
-  // a cluster a row where a row is long and every block of the step finds a multiprocessor at once
-  if (g_sample_mode != 1 && vocab >= 8 * THREADS && num_rows * SAMPLE_CLUSTER <= 148)
-    launch_k_cluster(sample_kernel<SAMPLE_CLUSTER>, num_rows * SAMPLE_CLUSTER, THREADS, sizeof(Quick), stream,
-                     SAMPLE_CLUSTER, logits, (size_t)ld, vocab, temperature, top_k, top_p, uniform, out, g_sample_mode);
-  else
-    launch_k(sample_kernel<1>, num_rows, THREADS, sizeof(Quick), stream, logits, (size_t)ld, vocab, temperature, top_k,
-             top_p, uniform, out, g_sample_mode);
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  // a cluster a row where a row is long: the largest of 8, 4, 2 blocks with which every block of
+  // the step finds a multiprocessor at once (a block fills one)
+  int cl = 1;
+  if (g_sample_mode != 1 && vocab >= 8 * THREADS) {
+    for (cl = SAMPLE_CLUSTER; cl > 1 && (long long)num_rows * cl > sm_count; cl >>= 1) {}
+  }
+#define PBE_SAMPLE_LAUNCH(CL)                                                                              \
+  launch_k_cluster(sample_kernel<CL>, num_rows * CL, THREADS, sizeof(Quick), stream, CL, logits, (size_t)ld, vocab, \
+                   temperature, top_k, top_p, uniform, out, g_sample_mode)
+  if (cl == 8) PBE_SAMPLE_LAUNCH(8);
+  else if (cl == 4) PBE_SAMPLE_LAUNCH(4);
+  else if (cl == 2) PBE_SAMPLE_LAUNCH(2);
+  else PBE_SAMPLE_LAUNCH(1);
+#undef PBE_SAMPLE_LAUNCH
   return launch_status();
 }
 

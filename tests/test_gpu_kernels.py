@@ -480,7 +480,7 @@ def test_sampler_binned_selection_equals_the_radix_descent(vocab):
         o.sample_set_mode(0)
     # all rows at once (a block a row), and a few rows a call (a cluster of blocks a row when the
     # vocabulary is large)
-    for rows_a_call in (n, 16):
+    for rows_a_call in (n, 60, 30, 16):      # clusters of 1, 2, 4 and 8 blocks a row
         quick = torch.cat([o.sample(*[a[i:i + rows_a_call].contiguous() for a in args]).cpu()
                            for i in range(0, n, rows_a_call)])
         bad = (slow != quick).nonzero().flatten().tolist()
