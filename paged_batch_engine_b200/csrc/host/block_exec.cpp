@@ -23,7 +23,7 @@ constexpr int kBF16 = 1;                                 // dtype code of the ke
 constexpr int kOpN = 0, kOpT = 1;                        // cublasOperation_t
 constexpr int kR16BF = 14;                               // cudaDataType
 constexpr int kCompute32F = 68, kGemmDefaultTensorOp = 99;
-constexpr int kSkinnyMaxRows = 16;
+constexpr int kSkinnyMaxRows = 8;      // the same limit as the Python parts use
 }  // namespace
 
 struct PbeExecFns {

@@ -204,7 +204,8 @@ def sgemm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
     return out
 
 
-SKINNY_MAX_ROWS = 16     # batches of at most this many rows take the weight-streaming kernel; 0: never
+SKINNY_MAX_ROWS = 8      # batches of at most this many rows take the weight-streaming kernel (0: never); with 9 to
+                         # 16 rows its two-tile instance loses to the library GEMM (4.39 against 3.48 ms a step)
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
