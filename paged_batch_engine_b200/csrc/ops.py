@@ -464,8 +464,9 @@ FUSED_DECODE_MAX_KEYS_PER_BLOCK = 32768   # beyond that the other path takes the
 
 def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int, device) -> int:
     """Blocks per (request, key/value head) of the fused decode attention kernel: the largest of
-    8, 4, 2, 1 with which every block of the step is resident at once; 0 when even one block each
-    is too many, or when a block would get more keys than the kernel is meant for."""
+    8, 4, 2, 1 with which every block of the step is resident at once; 1 for steps too large for
+    that (their blocks run in waves: batch 128 at 2,048 tokens 16,900 -> 20,600 tok/s against the
+    separate kernels); 0 when a block would get more keys than the kernel is meant for."""
     cap = decode_block_max_items(device)
     for splits in (8, 4, 2, 1):
         blocks = num_requests * num_kv_heads * splits
@@ -478,7 +479,7 @@ def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int,
             if per_block > 1536 and blocks <= 64:
                 return 0
             return splits
-    return 0
+    return 1 if 0 < longest_keys <= FUSED_DECODE_MAX_KEYS_PER_BLOCK else 0
 
 
 def fused_decode_attention_applies(dtype: torch.dtype, head_dim: int, group_size: int) -> bool:
