@@ -35,6 +35,14 @@ def _bucket(n: int, cap: Optional[int] = None) -> int:
     return b if cap is None else min(b, max(cap, n))
 
 
+def _batch_bucket(n: int) -> int:
+    """Rows of the captured step that takes n requests: powers of two, and from 24 on also the
+    sizes half-way (24, 48, 96 ...), so that padding rows cost the projections at most a third
+    (33 requests in a step of 64 rows took 4.26 ms, 32 in their own 3.87)."""
+    b = _bucket(n)
+    return 3 * b // 4 if b >= 32 and n <= 3 * b // 4 else b
+
+
 class DecodeStepContext(StepContext):
     """A StepContext whose arrays are fixed views of one persistent buffer."""
     captured = True               # its launches are recorded once and replayed
@@ -205,7 +213,7 @@ class DecodeGraphs:
         what it samples); they replace the entries' placeholder ids on the device."""
         runner = self.runner
         R = len(entries)
-        B = _bucket(R)
+        B = _batch_bucket(R)
         S = _bucket(self._splits_needed(entries, choose_split_keys(B)))
         key = (B, S)
         if key not in self.graphs:
