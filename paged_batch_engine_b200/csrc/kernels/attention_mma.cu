@@ -1284,13 +1284,16 @@ namespace {
 template <int NST, int CS>
 void launch_fused(const AttnParams& p, const AttnFusedParams& f, const CUtensorMap& map_k, const CUtensorMap& map_v,
                   cudaStream_t stream) {
-  // the padded layout is the larger one: the swizzled tiles with their alignment fit inside
-  const size_t smem = sizeof(bf16) * (size_t)(16 + 2 * NST * BN_KEYS) * LDS;
+  // the padded layout is the larger one; the swizzled tiles with their alignment take less, which
+  // lets three blocks of the two-tile instance share a multiprocessor at head size 128
+  const size_t smem_padded = sizeof(bf16) * (size_t)(16 + 2 * NST * BN_KEYS) * LDS;
+  const size_t smem_pages = sizeof(bf16) * (size_t)16 * LDS + 1024 + sizeof(bf16) * (size_t)2 * NST * BN_KEYS * HD;
   static_assert(HD % 64 != 0 || (16 + 2 * 2 * BN_KEYS) * LDS * 2 >= 16 * LDS * 2 + 1024 + 2 * 2 * BN_KEYS * HD * 2,
                 "the swizzled tiles must fit into the padded layout's shared memory");
+  const size_t smem = (p.kinds & 16) ? smem_pages : smem_padded;
   static bool opted = false;
   if (!opted) {
-    cudaFuncSetAttribute(attn_mma_kernel<2, NST, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_mma_kernel<2, NST, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_padded);
     opted = true;
   }
   launch_k_cluster(attn_mma_kernel<2, NST, CS>, dim3(CS, f.num_requests, p.num_kv_heads), NTHREADS, smem, stream, CS,
