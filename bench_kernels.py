@@ -2,7 +2,7 @@
 """Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
 each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
 
-    python bench_kernels.py [skinny|attn_decode|attn_fused|attn_prefill|tc5|all] [--once]
+    python bench_kernels.py [skinny|attn_decode|attn_fused|attn_prefill|tc5|sample|all] [--once]
 
 Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
 buffer is written between launches, so every launch starts with a cold L2)."""
@@ -122,6 +122,19 @@ def main():
         print(f"gemm_tc5 gate_up+SwiGLU M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
         t = timed(lambda: torch.mm(x, w.t()), flush)
         print(f"library GEMM gate_up M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
+    if what in ("sample", "all"):
+        V = 152064
+        for B in (1, 8, 64, 256):
+            logits = torch.randn(B, V, device=DEV) * 3
+            u = torch.rand(B, device=DEV)
+            out = torch.empty(B, dtype=torch.int32, device=DEV)
+            row = [f"argmax {timed(lambda: ops.argmax(logits, out), flush) * 1e3:.1f} us"]
+            for name, (T, k, p) in (("temperature", (0.8, 0, 1.0)), ("+ top-k 50", (0.8, 50, 1.0)), ("+ top-p 0.9", (0.8, 0, 0.9)),
+                                    ("+ both", (0.8, 50, 0.9))):
+                a = (torch.full((B,), T, device=DEV), torch.full((B,), k, dtype=torch.int32, device=DEV),
+                     torch.full((B,), p, device=DEV))
+                row.append(f"{name} {timed(lambda: ops.sample(logits, a[0], a[1], a[2], u, out), flush) * 1e3:.1f} us")
+            print(f"sampling {B} rows of {V}: " + "; ".join(row))
 
 
 if __name__ == "__main__":
