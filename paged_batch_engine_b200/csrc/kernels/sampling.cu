@@ -1,5 +1,5 @@
 // Sampling over float32 logits: greedy argmax, temperature, top-k, top-p and the
-// repetition penalty, one block per row, no host round trip and no sort.
+// repetition penalty, a block or a cluster of blocks per row, no host round trip.
 //
 // Semantics are those of the reference's host sampler (infMain/source/model/qwen2.cpp:
 // 104-203): candidates ordered by (logit descending, token ascending); the first top_k of
@@ -9,11 +9,14 @@
 // sampler (argmax_kernel.cu:272-405) covers only top_k <= 32 with one thread merging the
 // candidates; everything else goes through the host with the whole logits matrix.
 //
-// Here every "first element of the ordered list whose cumulative weight reaches a
-// target" is found by a radix descent over the order-preserving integer image of the
-// logit, four bits a pass, with per-thread histograms in registers.  Weights are summed as
-// 64-bit fixed point (2^-40 units), so sums are exact, order-independent and the result
-// is the same whatever else is in the batch.
+// Weights are summed as 64-bit fixed point (2^-40 units), so sums are exact,
+// order-independent and the result is the same whatever else is in the batch.  Every "first
+// element of the ordered list whose cumulative weight reaches a target" is found in two steps:
+// one pass over the row sums count and weight of 1,024 bins by distance from the maximum, a
+// prefix sum names the element's bin, and that bin's elements are gathered, sorted and scanned
+// (select_quick).  Rows whose bin is too crowded for that (thousands of equal logits) take a
+// radix descent over the order-preserving integer image of the logit, four bits a pass, with
+// per-thread histograms in registers (select_by_weight); both give the same element.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
