@@ -208,6 +208,41 @@ def test_repetition_penalty_with_steps_in_flight_and_after_preemption(tiny_folde
     assert len(set(ahead[0].output_tokens)) >= 25 > len(set(free[0].output_tokens))
 
 
+def test_random_requests_give_the_same_tokens_however_the_engine_runs_them(tiny_folders):
+    """Eighty requests of random lengths and random sampling settings (temperature, top-k, top-p,
+    repetition penalty, end of sequence on or off) through four engines - every launch from the
+    interpreter, captured steps launched ahead, so few pages that requests are preempted and
+    recomputed, tiny portions - give the same tokens in float32; no page and no row of seen tokens
+    is lost."""
+    import random
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    rnd = random.Random(5)
+    V = cfg["vocab_size"]
+    prompts, params = [], []
+    for i in range(80):
+        n = rnd.choice([1, 2, 7, 16, 17, 40, 90])
+        prompts.append([rnd.randrange(V) for _ in range(n)])
+        params.append(SamplingParams(max_new_tokens=rnd.choice([1, 2, 5, 20, 45]), temperature=rnd.choice([0.0, 0.7, 1.0, 1.5]),
+                                     top_k=rnd.choice([0, 1, 5, 50]), top_p=rnd.choice([1.0, 0.9, 0.3]),
+                                     repetition_penalty=rnd.choice([1.0, 1.0, 1.2, 0.8, 3.0]), seed=i,
+                                     ignore_eos=rnd.random() < 0.7))
+    outs = []
+    for kw in (dict(use_cuda_graphs=False, num_pages=300), dict(num_pages=300), dict(num_pages=30, max_num_seqs=10),
+               dict(num_pages=300, max_num_batched_tokens=33, prefill_chunk_cap=16)):
+        eng = engine(folder, "float32", page, **kw)
+        res = eng.generate(prompts, params)
+        eng.runner.cache.check_invariants()
+        assert eng.runner.cache.num_free_pages() == kw["num_pages"]
+        assert not eng.sampler._slot_of
+        outs.append([r.output_tokens for r in res])
+        if kw.get("num_pages") == 30:
+            assert eng.scheduler.metrics["preemptions"] > 0
+    for o in outs[1:]:
+        assert o == outs[0]
+
+
 def test_few_pages_preempt_and_recompute_without_changing_tokens(tiny_folders):
     from paged_batch_engine_b200 import SamplingParams
     cfg, _, page, _ = TINY["A"]
