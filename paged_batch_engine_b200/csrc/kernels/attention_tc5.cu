@@ -35,6 +35,7 @@
 
 #include "attention_params.cuh"
 #include "common.cuh"
+#include "kv_tensor_map.cuh"
 #include "pdl.cuh"
 
 using namespace pbe;
@@ -558,34 +559,6 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-// the pages of one layer as a matrix [pages * kv_heads * page_tokens, head_dim]; boxes of
-// box_rows rows (a page, or 64 keys of a larger page) by 64 columns
-int make_map(CUtensorMap* map, const void* cache, long long rows, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return (int)cudaErrorNotSupported;
-  cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
-}
 }  // namespace
 
 PBE_EXPORT int pbe_attn_tc5_head_dim() { return HD; }
@@ -605,9 +578,9 @@ PBE_EXPORT int pbe_attn_tc5(const AttnParams* params, int num_work, int num_page
   CUtensorMap map_k, map_v;
   const long long rows = (long long)num_pages * p.num_kv_heads * P;
   const int box_rows = P < BN ? P : BN;
-  int rc = make_map(&map_k, p.k_cache, rows, box_rows);
+  int rc = make_kv_tensor_map(&map_k, p.k_cache, rows, HD, box_rows);
   if (rc != 0) return rc;
-  rc = make_map(&map_v, p.v_cache, rows, box_rows);
+  rc = make_kv_tensor_map(&map_v, p.v_cache, rows, HD, box_rows);
   if (rc != 0) return rc;
   const size_t smem = (size_t)Q_BYTES + (NK + NV) * KV_BYTES + 1024;
   static bool opted = false;
