@@ -269,8 +269,7 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] 
 
 # Projections of many rows: the vendor GEMM library by default (it runs two-SM tiles and is
 # the faster one); PBE_GEMM=tc5 in the environment sends them through gemm_tc5 instead.
-import os as _os
-TC5_MIN_ROWS = 128 if _os.environ.get("PBE_GEMM", "") == "tc5" else 0     # 0: never
+TC5_MIN_ROWS = 128 if os.environ.get("PBE_GEMM", "") == "tc5" else 0     # 0: never
 
 
 def tc5_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -358,18 +357,15 @@ MMA_KEY_TILE = 64
 def _attention_choice() -> str:
     """Prompt portions of bfloat16 models with head size 64 or 128 run on the tcgen05
     attention kernel; PBE_ATTN=mma keeps them on the mma.sync kernel."""
-    import os
     return os.environ.get("PBE_ATTN", "").strip().lower()
 
 
 def _tc5_available() -> bool:
-    import os
     from .build import KERNEL_DIR
     return os.path.isfile(os.path.join(KERNEL_DIR, "attention_tc5.cu"))
 
 
 def _mma_available() -> bool:
-    import os
     from .build import KERNEL_DIR
     return os.path.isfile(os.path.join(KERNEL_DIR, "attention_mma.cu"))
 
@@ -483,7 +479,6 @@ def fused_decode_splits(num_requests: int, num_kv_heads: int, longest_keys: int,
 
 
 def fused_decode_attention_applies(dtype: torch.dtype, head_dim: int, group_size: int) -> bool:
-    import os
     return (dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and group_size <= 16
             and _mma_available() and os.environ.get("PBE_DECODE_FUSED", "1") != "0")
 
