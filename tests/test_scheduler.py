@@ -282,3 +282,18 @@ def test_nothing_is_scheduled_ahead_when_it_could_be_wrong():
     # a repetition penalty does not keep a step from being scheduled ahead: the sampler keeps the
     # request's seen tokens on the device
     assert s2.schedule_ahead(o) is not None
+
+
+def test_sizes_of_captured_decode_steps_and_key_splits():
+    """Captured decode steps come in powers of two and, from 24 rows on, the sizes half-way; the
+    padding never exceeds a third of the rows from 16 requests on.  Key splits are 512 keys for
+    at most four requests (the first bucket edge) and 256 beyond, by the bucket as by the count."""
+    from paged_batch_engine_b200.engine.batch import choose_split_keys
+    from paged_batch_engine_b200.engine.graphs import _batch_bucket
+    assert [_batch_bucket(n) for n in (1, 2, 3, 5, 8, 9, 16, 17, 24, 25, 32, 33, 48, 49, 64, 65, 96, 97, 128, 200)] == \
+        [1, 2, 4, 8, 8, 16, 16, 24, 24, 32, 32, 48, 48, 64, 64, 96, 96, 128, 128, 256]
+    for n in range(1, 600):
+        b = _batch_bucket(n)
+        assert b >= n and (n < 16 or (b - n) * 3 <= b)
+        assert choose_split_keys(n) == choose_split_keys(b)
+    assert choose_split_keys(4) == 512 and choose_split_keys(5) == 256
