@@ -73,12 +73,30 @@ def _find_build_dir() -> str:
 
 
 def _headers() -> List[str]:
-    return sorted(os.path.join(KERNEL_DIR, n) for n in os.listdir(KERNEL_DIR) if n.endswith(".cuh"))
+    return sorted(os.path.join(KERNEL_DIR, n) for n in os.listdir(KERNEL_DIR) if n.endswith((".cuh", ".h")))
+
+
+def _included_sources(source: str, seen: Optional[set] = None) -> List[str]:
+    """Files of the kernel folder that ``source`` pulls in with ``#include "..."`` and that are
+    not headers (one library compiles another's .cu into itself), recursively."""
+    seen = set() if seen is None else seen
+    out: List[str] = []
+    with open(source, "r", errors="replace") as f:
+        for line in f:
+            line = line.strip()
+            if line.startswith("#include") and '"' in line:
+                name = line.split('"')[1]
+                path = os.path.join(KERNEL_DIR, name)
+                if not name.endswith((".cuh", ".h")) and os.path.isfile(path) and path not in seen:
+                    seen.add(path)
+                    out.append(path)
+                    out += _included_sources(path, seen)
+    return out
 
 
 def _key(source: str, defines: Dict[str, object], extra: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for path in [source] + _headers():
+    for path in [source] + _included_sources(source) + _headers():
         with open(path, "rb") as f:
             h.update(f.read())
     h.update(repr(sorted(defines.items())).encode())

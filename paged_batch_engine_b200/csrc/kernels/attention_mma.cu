@@ -1184,10 +1184,8 @@ namespace {
 void tiles_by_page(AttnParams& p, CUtensorMap* map_k, CUtensorMap* map_v) {
   p.kinds &= ~16;
   const int P = p.page_tokens;
-  static const bool rows_only = [] {
-    const char* e = getenv("PBE_DECODE_TILES");
-    return e != nullptr && strcmp(e, "rows") == 0;
-  }();
+  const char* env = getenv("PBE_DECODE_TILES");       // read at every launch: a test can switch it
+  const bool rows_only = env != nullptr && strcmp(env, "rows") == 0;
   if (HD % 64 != 0 || rows_only || p.num_pages <= 0 || P < 8 || P % 8 != 0 || (BN_KEYS % P != 0 && P % BN_KEYS != 0) ||
       (((uintptr_t)p.k_cache | (uintptr_t)p.v_cache) & 15) != 0)
     return;
@@ -1211,6 +1209,13 @@ PBE_EXPORT int pbe_attn_mma_wait_gave_up() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_wait_gave_up, sizeof(int));
   return v;
+}
+// The device address of that flag on the current device (0 on failure), so that the host can
+// have it read and cleared by a kernel together with the other kernels' flags.
+PBE_EXPORT unsigned long long pbe_attn_mma_wait_flag_address() {
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_wait_gave_up) != cudaSuccess) return 0ULL;
+  return (unsigned long long)ptr;
 }
 
 // params->kinds: bit 0: some row tile has at most 16 packed rows (decoded tokens), bit 1: some

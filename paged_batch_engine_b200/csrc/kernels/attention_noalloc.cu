@@ -32,6 +32,10 @@ int scratch_address(float** out) {
 }
 }  // namespace
 
+// The size of the built-in scratch in floats, for callers that size their requests by it.
+extern "C" __attribute__((visibility("default")))
+long long pbe_attn_noalloc_scratch_floats() { return (long long)PBE_NOALLOC_SCRATCH_FLOATS; }
+
 extern "C" __attribute__((visibility("default")))
 int pbe_attn_simple_noalloc(const AttnParams* attn, int num_work, const AttnMergeParams* merge,
                             int split_rows, int dtype, cudaStream_t stream) {

@@ -42,6 +42,8 @@ extern "C" {
 #endif
 int pbe_attn_simple_noalloc(const AttnParams* attn, int num_work, const AttnMergeParams* merge,
                             int split_rows, int dtype, cudaStream_t stream);
+/* PBE_NOALLOC_SCRATCH_FLOATS as the loaded library was built with. */
+long long pbe_attn_noalloc_scratch_floats(void);
 #ifdef __cplusplus
 }
 #endif

@@ -251,3 +251,24 @@ PBE_EXPORT int pbe_silu_mul(const void* in, void* out, int dtype, int rows, int 
              (__nv_bfloat16*)out, inter, total);
   return launch_status();
 }
+
+// ------------------------------------------------------------------ kernel status word
+// Kernels with bounded waits (tcgen05 attention and GEMM, the mbarrier tile rings of the
+// mma.sync attention) record a wait that ran out in a flag of their own.  This kernel folds up
+// to 32 such flags into one word (bit i: flag i was set) and clears the flags it found set, so
+// the host learns of an invalid launch with the same copy that brings the sampled ids back.
+__global__ void collect_status_kernel(const unsigned long long* __restrict__ flag_addresses, int n,
+                                      int* __restrict__ out) {
+  unsigned word = 0;
+  for (int i = 0; i < n && i < 32; ++i) {
+    int* flag = reinterpret_cast<int*>(flag_addresses[i]);
+    if (flag != nullptr && atomicExch(flag, 0) != 0) word |= 1u << i;
+  }
+  *out = (int)word;
+}
+
+PBE_EXPORT int pbe_collect_status(const unsigned long long* flag_addresses, int n, int* out,
+                                  cudaStream_t stream) {
+  collect_status_kernel<<<1, 1, 0, stream>>>(flag_addresses, n, out);
+  return pbe::launch_status();
+}

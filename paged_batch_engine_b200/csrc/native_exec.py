@@ -61,6 +61,7 @@ def exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
     f = _fns.get(key)
     if f is None:
         defines = {"PBE_HEAD_DIM": int(head_dim)}
+        ops._mma_flag_heads.add(int(head_dim))
         ew, rope, skinny = load_library("elementwise"), load_library("rope_kv"), load_library("gemm_skinny")
         mma, simple = load_library("attention_mma", defines), load_library("attention_simple", defines)
         cublas = ctypes.CDLL("libcublas.so.12")            # the one torch has loaded: its handle is used

@@ -17,11 +17,15 @@ import torch
 from .build import load_library
 from .ops import AttnMergeParams, AttnParams, KernelError, _dtype_code, _stream
 
-SCRATCH_FLOATS = 2 * 1024 * 1024
-
-
 def library(head_dim: int) -> ctypes.CDLL:
     return load_library("attention_noalloc", {"PBE_HEAD_DIM": int(head_dim)})
+
+
+def scratch_floats(head_dim: int) -> int:
+    """The size of the built-in scratch array in floats, asked of the library itself."""
+    fn = library(head_dim).pbe_attn_noalloc_scratch_floats
+    fn.argtypes, fn.restype = [], ctypes.c_longlong
+    return int(fn())
 
 
 def paged_attention_noalloc(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale,

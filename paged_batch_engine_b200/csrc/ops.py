@@ -415,6 +415,8 @@ def paged_attention(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, hea
                    "paged_attention (tcgen05)")
         p.kinds = (p.kinds | 8) if (p.kinds & 3) else (1 | 8)
     fn = _fn(lib, "pbe_attn_" + kind, [ctypes.POINTER(AttnParams), c_int, c_int, c_void_p], defines)
+    if kind == "mma":
+        _mma_flag_heads.add(int(head_dim))
     _check(fn(ctypes.byref(p), int(meta.num_work), _dtype_code(q), _stream()), "paged_attention")
     if meta.num_split_rows > 0:
         mp = AttnMergeParams(part_o=meta.part_o.data_ptr(), part_ml=meta.part_ml.data_ptr(),
@@ -508,6 +510,7 @@ def attention_decode_fused(qkv, bias, k_cache, v_cache, out, meta, positions, sl
     fn = _fn("attention_mma", "pbe_attn_decode_fused",
              [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnFusedParams), c_int, c_int, c_void_p],
              {"PBE_HEAD_DIM": int(head_dim)})
+    _mma_flag_heads.add(int(head_dim))
     _check(fn(ctypes.byref(p), ctypes.byref(f), _dtype_code(qkv), int(splits), _stream()), "attention_decode_fused")
     return out
 
@@ -541,6 +544,72 @@ def attention_mma_wait_flag(head_dim: int) -> int:
     head size (never in a correct run; the launch's results are not valid then)."""
     fn = _fn("attention_mma", "pbe_attn_mma_wait_gave_up", [], {"PBE_HEAD_DIM": int(head_dim)})
     return int(fn())
+
+
+# ------------------------------------------------------------------ the kernels' status word
+_STATUS_NAMES = {}      # device -> names of the flags, in bit order
+_status_state = {}      # device -> (addresses on the device, number of flags, key of the sources)
+_mma_flag_heads = set() # head sizes whose mma.sync attention library this process has launched
+
+
+def _status_sources(device):
+    """(name, device address) of every flag a bounded wait of this package's kernels can set
+    on ``device``, in a fixed order."""
+    device = torch.device(device)
+    out = []
+    err = _tc5_attn_err.get(device)
+    if err is not None:
+        out.append(("tcgen05 attention", err.data_ptr()))
+    err = _tc5_err.get(device)
+    if err is not None:
+        out.append(("tcgen05 GEMM", err.data_ptr()))
+    for hd in sorted(_mma_flag_heads):
+        fn = _fns.get(("attention_mma", "pbe_attn_mma_wait_flag_address", (("PBE_HEAD_DIM", hd),)))
+        if fn is None:
+            lib = load_library("attention_mma", {"PBE_HEAD_DIM": hd})
+            fn = lib.pbe_attn_mma_wait_flag_address
+            fn.argtypes, fn.restype = [], ctypes.c_ulonglong
+            _fns[("attention_mma", "pbe_attn_mma_wait_flag_address", (("PBE_HEAD_DIM", hd),))] = fn
+        with torch.cuda.device(device):
+            addr = int(fn())
+        if addr:
+            out.append((f"mma.sync attention (head size {hd})", addr))
+    return out[:32]
+
+
+def collect_status(out: torch.Tensor) -> torch.Tensor:
+    """Launches a kernel that writes into ``out`` (int32, one element, on the device) a word
+    with bit i set when flag i of ``status_names(device)`` was set, and clears those flags.
+    A flag is set by a kernel whose bounded wait ran out: the results of that launch are not
+    valid.  Costs one launch of one thread; nothing waits."""
+    _need_cuda(out)
+    device = out.device
+    src = _status_sources(device)
+    key = tuple(src)
+    st = _status_state.get(device)
+    if st is None or st[2] != key:
+        import numpy as np
+        addrs = torch.from_numpy(np.array([a for _, a in src] + [0], dtype=np.uint64).view(np.int64)).to(device)
+        st = _status_state[device] = (addrs, len(src), key)
+        _STATUS_NAMES[device] = [n for n, _ in src]
+    fn = _fn("elementwise", "pbe_collect_status", [c_void_p, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(st[0]), st[1], _ptr(out), _stream()), "collect_status")
+    return out
+
+
+def status_message(device, word: int) -> str:
+    names = _STATUS_NAMES.get(torch.device(device), [])
+    hit = [names[i] if i < len(names) else f"flag {i}" for i in range(32) if (int(word) >> i) & 1]
+    return ("a bounded wait ran out inside: " + ", ".join(hit) +
+            "; the results of that step are not valid (the flags have been cleared)")
+
+
+def raise_on_kernel_status(device) -> None:
+    """Synchronises, reads the kernels' flags and raises KernelError if one was set."""
+    out = torch.zeros(1, dtype=torch.int32, device=device)
+    word = int(collect_status(out).item())
+    if word:
+        raise KernelError(status_message(device, word))
 
 
 def attention_libraries(head_dim: int, dtype: torch.dtype):

@@ -172,7 +172,8 @@ class Engine:
         if rows:
             ids = self.sampler.sample(logits, params, counters, keys=keys)
         else:
-            torch.cuda.current_stream().synchronize()
+            from ..csrc import ops
+            ops.raise_on_kernel_status(self.device)      # synchronises
             ids = []
         return out, None, ids, None
 
@@ -180,8 +181,7 @@ class Engine:
         out, _dev, ids, event = launched
         t0 = time.perf_counter()
         if event is not None:
-            event.synchronize()
-            ids = ids.tolist()
+            ids = self.sampler.read_async(ids, event)     # raises if a kernel's bounded wait ran out
         t1 = time.perf_counter()
         self.scheduler.process_outputs(out, ids)
         self.profile["sample"] += t1 - t0

@@ -35,6 +35,16 @@ def _bucket(n: int, cap: Optional[int] = None) -> int:
     return b if cap is None else min(b, max(cap, n))
 
 
+def splits_bound(longest: int, window: Optional[int], split_keys: int) -> int:
+    """The most key splits any request of at most ``longest`` tokens needs (see
+    ``DecodeGraphs._splits_needed``)."""
+    full = (longest + split_keys - 1) // split_keys
+    if not window:
+        return max(1, full)
+    span = min(longest, int(window))
+    return max(1, min(full, (span + split_keys - 2) // split_keys + 1))
+
+
 def _batch_bucket(n: int) -> int:
     """Rows of the captured step that takes n requests: powers of two, and from 24 on also the
     sizes half-way (24, 48, 96 ...), so that padding rows cost the projections at most a third
@@ -86,6 +96,10 @@ class DecodeStepContext(StepContext):
         self._ones = np.ones(B, dtype=np.int64)
         self.state_slots_host = np.zeros(0, dtype=np.int64)
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
+        # set after every copy of the pinned buffer: the next fill rewrites that buffer and must
+        # not start before the copy has read it (steps are launched ahead of one another)
+        self._copied = torch.cuda.Event() if torch.device(device).type == "cuda" else None
+        self._copy_pending = False
 
         def view(name):
             o, shape = lay[name]
@@ -124,6 +138,9 @@ class DecodeStepContext(StepContext):
         Rows keep their block tables between steps: when the same requests come back in the
         same order (the usual case while decoding), only newly added pages are written."""
         m, B, S, P = self.manager, self.batch, self.splits, self.page_tokens
+        if self._copy_pending:
+            self._copied.synchronize()        # almost always long satisfied
+            self._copy_pending = False
         R = len(entries)
         handles = [e.handle for e in entries]
         same = handles == self._handles
@@ -163,6 +180,9 @@ class DecodeStepContext(StepContext):
             self._h("seq_len")[:R] = ctx_before + 1
         self._handles = handles
         self.dev.copy_(self.host, non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._copy_pending = True
 
     def attention_work(self, group, group_size, tile_rows, window, num_heads, head_dim):
         w = self._work[(group, group_size, tile_rows, window)]
@@ -199,13 +219,17 @@ class DecodeGraphs:
         return all(gsize <= tile_rows for _, gsize, tile_rows, _ in self.runner._work_keys)
 
     def _splits_needed(self, entries, split_keys: int) -> int:
+        """Key splits a request of this step can need at most, from the longest request alone.
+        Without a window that is the longest request's own count.  Under a window W a request
+        of length n reads keys [max(0, n - W), n), and how many splits of ``split_keys`` that
+        range touches depends on where it lies: a shorter request can touch one more than the
+        longest.  A range of L keys touches at most (L + split_keys - 2) // split_keys + 1
+        splits wherever it lies, so that bound (capped by the unwindowed count) holds for
+        every request of the step and does not move as the requests grow."""
         m = self.runner.cache
         longest = m.max_reserved_len([e.handle for e in entries])
-        worst = 1
-        for _, _, _, window in self.runner._work_keys:
-            lo = max(0, longest - 1 - window + 1) if window else 0
-            worst = max(worst, (longest + split_keys - 1) // split_keys - lo // split_keys)
-        return worst
+        return max([1] + [splits_bound(longest, window, split_keys)
+                          for _, _, _, window in self.runner._work_keys])
 
     def run(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``device_tokens`` (int32 on the device, one per entry): the token ids of this step

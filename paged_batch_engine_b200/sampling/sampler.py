@@ -77,7 +77,8 @@ class Sampler:
                      keys=None):
         """Launches the sampling of every row and the copy of the ids to pinned host memory;
         returns (ids on the device, ids on the host, event): the host list is valid once the
-        event has completed.  ``keys``: the rows' request keys; a row with a repetition penalty
+        event has completed, and holds one element more than there are rows: the kernels' status
+        word (``ops.collect_status``), which ``read_async`` checks.  ``keys``: the rows' request keys; a row with a repetition penalty
         must belong to a tracked request (``track``).  Nothing here waits for the device: the
         rows' parameters go up from pinned memory (a copy from pageable memory would first wait
         for the stream, i.e. for the step that is still running).  Buffers rotate over four steps."""
@@ -86,7 +87,7 @@ class Sampler:
                for p, k in zip(params, keys if keys is not None else [None] * n)):
             raise ValueError("sample_async: a row with a repetition penalty needs a tracked request")
         slot = self._async_slots[self._async_next % len(self._async_slots)] if self._async_slots else None
-        if slot is None or slot[0].numel() < n:
+        if slot is None or slot[0].numel() < n + 1:
             cap = max(64, 2 * n)
             self._async_slots = [(torch.empty(cap, dtype=torch.int32, device=self.device),
                                   torch.empty(cap, dtype=torch.int32, pin_memory=True),
@@ -121,9 +122,19 @@ class Sampler:
             ops.sample(logits, fdev[0, :n], pdev[3, :n], fdev[1, :n], fdev[2, :n], out=dev[:n])
             if penalised:
                 ops.seen_mark(self._seen, dev[:n], pdev[4, :n])
-        host[:n].copy_(dev[:n], non_blocking=True)
+        ops.collect_status(dev[n:n + 1])
+        host[:n + 1].copy_(dev[:n + 1], non_blocking=True)
         event.record()
-        return dev[:n], host[:n], event
+        return dev[:n], host[:n + 1], event
+
+    def read_async(self, host: torch.Tensor, event) -> List[int]:
+        """Waits for a ``sample_async`` and returns its ids; raises ``ops.KernelError`` when a
+        kernel of the step reported a bounded wait that ran out (its ids are not valid)."""
+        event.synchronize()
+        vals = host.tolist()
+        if vals[-1]:
+            raise ops.KernelError(ops.status_message(self.device, vals[-1]))
+        return vals[:-1]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
                seen: Sequence[Sequence[int]] = (), keys=None) -> List[int]:
@@ -134,7 +145,7 @@ class Sampler:
         if n == 0:
             return []
         if all(p.is_greedy for p in params):
-            return ops.argmax(logits).cpu().tolist()
+            return self._checked(ops.argmax(logits))
         pen = self._penalty_rows(params, keys)
         if pen is not None:
             ops.penalty_seen(logits, self._seen, pen[0], pen[1])
@@ -159,4 +170,15 @@ class Sampler:
         out = ops.sample(logits, fdev[0].contiguous(), kdev, fdev[1].contiguous(), fdev[2].contiguous())
         if pen is not None:
             ops.seen_mark(self._seen, out, pen[0])
-        return out.cpu().tolist()
+        return self._checked(out)
+
+    def _checked(self, ids: torch.Tensor) -> List[int]:
+        """The ids on the host, with the kernels' status word read in the same transfer."""
+        n = ids.numel()
+        both = torch.empty(n + 1, dtype=torch.int32, device=ids.device)
+        both[:n].copy_(ids)
+        ops.collect_status(both[n:])
+        vals = both.cpu().tolist()
+        if vals[-1]:
+            raise ops.KernelError(ops.status_message(self.device, vals[-1]))
+        return vals[:-1]

@@ -33,3 +33,13 @@ def tiny_folders(tmp_path_factory):
         d = tmp_path_factory.mktemp(f"tiny_{name}")
         out[name] = make_model_folder(d, cfg, seed, sharpen)
     return out
+
+
+@pytest.fixture(autouse=True)
+def no_wait_ran_out(request):
+    """After every GPU test: no kernel of the package reported a bounded wait that ran out
+    (a result made by such a launch is not valid, whatever the tolerances said)."""
+    yield
+    if "gpu" in request.keywords and torch.cuda.is_available():
+        from paged_batch_engine_b200.csrc import ops
+        ops.raise_on_kernel_status(torch.device("cuda:0"))

@@ -83,11 +83,45 @@ def mixed(reqs: Dict[str, List[int]], max_live: int = 4, seed: int = 0, prefill_
     return recs
 
 
-def run_records(runner, records) -> Dict[str, Dict[int, torch.Tensor]]:
+def batch_decode(reqs: Dict[str, List[int]], decode_tokens: int, prefill_group: int = 4,
+                 portion: int = 24):
+    """All requests live at once: their heads go in as prompt portions, ``prefill_group``
+    requests a step, then the last ``decode_tokens`` tokens of every request one a step with
+    all requests in the same step (a decode step of len(reqs) rows)."""
+    recs, s = [], 0
+    ids = list(reqs)
+    heads = {r: max(1, len(reqs[r]) - decode_tokens) for r in ids}
+    for g in range(0, len(ids), prefill_group):
+        grp, done = ids[g:g + prefill_group], {}
+        while any(done.get(r, 0) < heads[r] for r in grp):
+            entries = []
+            for r in grp:
+                d = done.get(r, 0)
+                if d < heads[r]:
+                    n = min(portion, heads[r] - d)
+                    entries.append({"id": r, "tokens": reqs[r][d:d + n], "want": list(range(n))})
+                    done[r] = d + n
+            recs.append({"step": s, "entries": entries, "end": []})
+            s += 1
+    pos = dict(heads)
+    while any(pos[r] < len(reqs[r]) for r in ids):
+        entries, end = [], []
+        for r in ids:
+            if pos[r] < len(reqs[r]):
+                entries.append({"id": r, "tokens": [reqs[r][pos[r]]], "want": [0]})
+                pos[r] += 1
+                if pos[r] == len(reqs[r]):
+                    end.append(r)
+        recs.append({"step": s, "entries": entries, "end": end})
+        s += 1
+    return recs
+
+
+def run_records(runner, records, replayer=None, **replayer_args) -> Dict[str, Dict[int, torch.Tensor]]:
     """Runs records in-process through the replay code of the package; returns
     {request: {position: logits row (float32, CPU)}}."""
     from paged_batch_engine_b200.engine.replay import TraceReplayer
-    rp = TraceReplayer(runner)
+    rp = replayer if replayer is not None else TraceReplayer(runner, **replayer_args)
     progress: Dict[str, int] = {}
     out: Dict[str, Dict[int, torch.Tensor]] = {}
     for rec in records:

@@ -206,3 +206,33 @@ def test_state_slots_are_distinct_among_live_requests():
     m.free(hs[2])
     h = m.add_request()
     assert m.state_slot(h) == 2
+
+
+def test_captured_step_split_capacity_covers_every_request_of_the_step():
+    """The split capacity of a captured decode step is computed from the longest request
+    alone; under a window a shorter request can touch one more split than the longest
+    (window 512, splits of 256: 2,304 keys touch 2 splits, 1,704 keys touch 3).  The bound
+    must hold for every shorter request, and the work-list fill must accept them all."""
+    import numpy as np
+    from paged_batch_engine_b200.cache.manager import decode_work_fill
+    from paged_batch_engine_b200.engine.graphs import splits_bound
+    rng = random.Random(7)
+    cases = [(2304, 1704, 512, 256), (2304, 1704, 512, 512), (4096, 257, 300, 256), (1000, 999, None, 256)]
+    for _ in range(400):
+        sk = rng.choice([256, 512])
+        W = rng.choice([None, 1, 2, 24, 150, 255, 256, 257, 511, 512, 513, 1000, 4096])
+        longest = rng.randint(1, 6000)
+        cases.append((longest, rng.randint(1, longest), W, sk))
+    for longest, other, W, sk in cases:
+        S = splits_bound(longest, W, sk)
+        ctx = np.array([longest - 1, other - 1], dtype=np.int64)
+        work = np.zeros((2 * S, 4), dtype=np.int32)
+        counts = np.zeros(2, dtype=np.int32)
+        worst = decode_work_fill(2, 2, S, ctx, W, sk, work, counts, None, None, None, None, refresh=True)
+        assert 1 <= worst <= S, (longest, other, W, sk, S, worst)
+        for r, n in enumerate((longest, other)):
+            lo = max(0, n - W) if W else 0
+            assert counts[r] == (n + sk - 1) // sk - lo // sk
+    # the bound is tight somewhere: some shorter request does use all of it
+    S = splits_bound(2304, 512, 256)
+    assert S == 3

@@ -117,7 +117,7 @@ def test_bfloat16_greedy_tokens_are_plain_argmax_up_to_rounding(tiny_folders, na
         logits = plain.forward_logits(pcfg, w, seq[:-1])
         for i, tok in enumerate(r.output_tokens):
             row = logits[len(p) - 1 + i]
-            assert row.max() - row[tok] <= 0.04 * logits.abs().max(), (name, i)
+            assert row.max() - row[tok] <= 0.02 * logits.abs().max(), (name, i)
 
 
 @pytest.mark.parametrize("persistent", [False, True])
@@ -147,7 +147,7 @@ def test_many_requests_at_once(tiny_folders, monkeypatch, persistent):
                 logits = plain.forward_logits(pcfg, w, seq[:-1])
                 for i, tok in enumerate(r.output_tokens):
                     row = logits[len(p) - 1 + i]
-                    assert row.max() - row[tok] <= 0.04 * logits.abs().max()
+                    assert row.max() - row[tok] <= 0.02 * logits.abs().max()
 
 
 def test_temperature_sampling_follows_the_reference_algorithm(tiny_folders):
@@ -298,3 +298,56 @@ def test_command_line(tiny_folders, tmp_path):
     proc = subprocess.run([os.path.join(ROOT, "bin", "pbe-qwen"), "--write-random-model", str(out),
                            "--config", str(cfgfile), "--weights-seed", "4"], capture_output=True, text=True)
     assert proc.returncode == 0 and sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
+
+
+def test_all_layers_windowed_and_unequal_lengths_decode_together(tmp_path):
+    """Every layer under a window of 300 keys, five requests of unequal length decoding in one
+    captured step with key splits of 256: the request of 1,020 tokens touches two splits while
+    the one of 776 touches three, so the captured step's split capacity must follow from the
+    worst request, not from the longest."""
+    from paged_batch_engine_b200 import SamplingParams
+    from tests.helpers import TINY_C, make_model_folder
+    cfg = dict(TINY_C, sliding_window=300, max_window_layers=0, max_position_embeddings=2048)
+    folder = make_model_folder(tmp_path / "windowed", cfg, seed=8, sharpen=6.0)
+    pcfg, w = load_plain(folder)
+    prompts = prompts_for(cfg["vocab_size"], [1020, 776, 300, 50, 5], seed=13)
+    sp = SamplingParams(max_new_tokens=6, ignore_eos=True)
+    eng = engine(folder, "float32", 8, num_pages=400, max_num_batched_tokens=512, prefill_chunk_cap=256)
+    res = eng.generate(prompts, sp)
+    assert eng.runner.graphs.replays > 0
+    assert all(g.window == 300 for g in eng.runner.cache.groups)
+    for p, r in zip(prompts, res):
+        assert r.output_tokens == plain.greedy_generate(pcfg, w, p, 6), len(p)
+    eng.runner.cache.check_invariants()
+
+
+def test_a_wait_that_ran_out_stops_generation_with_an_error(tiny_folders):
+    """A kernel whose bounded wait ran out sets a flag on the device; the engine reads the flags
+    with the sampled ids and raises instead of handing out tokens made from invalid results.
+    The flag is set from the host here: nothing on the device waits, hangs or faults."""
+    from paged_batch_engine_b200 import SamplingParams
+    from paged_batch_engine_b200.csrc import ops as pbe_ops
+    cfg, _, page, _ = TINY["D"]
+    eng = engine(tiny_folders["D"], "bfloat16", page)
+    prompts = prompts_for(cfg["vocab_size"], [40, 9], seed=3)
+    sp = SamplingParams(max_new_tokens=6, ignore_eos=True)
+    good = eng.generate(prompts, sp)
+    dev = eng.device
+    for when in ("prompt", "decode"):
+        reqs = [eng.add_request(p, sp) for p in prompts]
+        if when == "decode":
+            while not all(r.outputs for r in reqs):
+                eng.step()
+        pbe_ops.tc5_attention_error_buffer(dev)[:1].fill_(1)
+        with pytest.raises(pbe_ops.KernelError, match="bounded wait ran out.*tcgen05 attention"):
+            for _ in range(4):
+                eng.step()
+            eng.drain()
+        assert pbe_ops.tc5_error_flag(dev) == 0             # the flags were cleared when they were read
+        for r in reqs:
+            eng.scheduler.cancel(r)
+        eng._pending = None
+        eng.drain()
+    # the engine is usable afterwards and gives the same tokens
+    again = eng.generate(prompts, sp)
+    assert [r.output_tokens for r in again] == [r.output_tokens for r in good]

@@ -85,3 +85,25 @@ def test_sampler_rules():
     assert plain.sample_row(logits, temperature=1e-3, repetition_penalty=4.0, seen_tokens=[1, 2], uniform=0.5) == 4
     lo, hi = plain.sample_cdf_interval(logits, 2, 1.0, top_k=3)
     assert 0 < lo < hi < 1
+
+
+def test_rotary_pairing_matches_the_reference_cpp_kernel():
+    """The reference's own C++ CPU rotary kernel in its Qwen2 branch (compiled unmodified by
+    tests/golden/make_reference_rope_golden.py) against the plain implementation: the pairing
+    (i, i + head_size/2), the direction of the rotation and every pair's frequency with
+    theta = 1e6, for query and key heads, at positions up to 4,095."""
+    from safetensors.torch import load_file
+    g = load_file(os.path.join(os.path.dirname(__file__), "golden", "reference_rope.safetensors"))
+    for tag in ("a", "b", "c"):
+        head_size, heads, kv_heads = g[f"{tag}.shape"].tolist()
+        pos = g[f"{tag}.positions"].long()
+        for name, n in (("q", heads), ("k", kv_heads)):
+            x = g[f"{tag}.{name}"].view(len(pos), n, head_size)
+            want = g[f"{tag}.{name}_rotated"].view(len(pos), n, head_size)
+            got = plain.rope_rotate_half(x, pos, theta=1000000.0)
+            # both take sine and cosine of the same float32 angle: a few units in the last place
+            assert (got - want).abs().max().item() <= 2e-6, (tag, name)
+            small = pos <= 64
+            assert not torch.allclose(got[1:], x[1:], atol=1e-3)                       # it did rotate
+            wrong = plain.rope_interleaved(x, pos, theta=1000000.0)
+            assert (wrong[small][1:] - want[small][1:]).abs().max().item() > 1e-2       # a mix-up shows

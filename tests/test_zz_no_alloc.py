@@ -43,20 +43,31 @@ def _noalloc(case):
     return out.float().cpu().view(-1, case.H, case.hd)
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2 ** -7)])
-def test_two_calls_in_a_row_match_the_regular_entry_points(dtype, tol):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_two_calls_in_a_row_match_the_regular_entry_points(dtype):
+    """The kernels are the regular entry points' own, so the results are equal bit for bit;
+    and the device's free memory does not move over the calls (a raw cudaMalloc inside the
+    library, which torch's allocator would not see, would show here)."""
     first, want1 = _case(1, [(700, 1), (300, 2), (0, 40), (513, 1)], dtype)
     second, want2 = _case(2, [(1200, 1), (40, 1), (257, 3)], dtype, window=None)
-    got1 = _noalloc(first)
+    got1 = _noalloc(first)                        # the first call on the device: looks up the array
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    # inputs and outputs of the next calls come from torch's cache, not from the device heap
     got2 = _noalloc(second)                       # reuses the array the first call wrote
     got1_again = _noalloc(first)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
     for got, want in ((got1, want1), (got2, want2), (got1_again, want1)):
         assert not torch.isnan(got).any()
-        assert (got - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+        assert torch.equal(got, want)
 
 
 def test_the_symbol_is_exported_and_refuses_what_does_not_fit():
-    from paged_batch_engine_b200.csrc.noalloc import SCRATCH_FLOATS, library
+    from paged_batch_engine_b200.csrc.noalloc import library, scratch_floats
+    SCRATCH_FLOATS = scratch_floats(48)
+    assert SCRATCH_FLOATS == 2 * 1024 * 1024             # the stated limit: 8 MiB
     from paged_batch_engine_b200.csrc.ops import AttnMergeParams, AttnParams
     lib = library(48)
     fn = lib.pbe_attn_simple_noalloc
@@ -66,7 +77,8 @@ def test_the_symbol_is_exported_and_refuses_what_does_not_fit():
     a = AttnParams(num_heads=32, num_kv_heads=8, max_splits=64, tile_rows=16, split_keys=256, page_tokens=16)
     m = AttnMergeParams(num_heads=32, head_dim=48, max_splits=64)
     rows = SCRATCH_FLOATS // (32 * 64 * 50) + 1
-    before = torch.cuda.memory_allocated()
-    assert fn(ctypes.byref(a), 1, ctypes.byref(m), rows, 0, None) == 1      # cudaErrorInvalidValue
-    assert torch.cuda.memory_allocated() == before
     torch.cuda.synchronize()
+    before = torch.cuda.mem_get_info()[0]
+    assert fn(ctypes.byref(a), 1, ctypes.byref(m), rows, 0, None) == 1      # cudaErrorInvalidValue
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == before
