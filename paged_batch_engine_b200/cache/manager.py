@@ -42,11 +42,21 @@ class CacheError(RuntimeError):
 
 @dataclass(frozen=True)
 class KVGroupSpec:
-    """Layers whose keys and values have the same geometry and the same lifetime."""
+    """Layers whose paged tensors have the same geometry and the same lifetime.  The manager
+    itself reads ``layers`` and ``window`` only; ``tensors`` (records with ``name``, ``heads``,
+    ``width``) says what the storage holds per token; without it the group is a key and a
+    value tensor of ``num_kv_heads`` x ``head_dim``."""
     layers: Tuple[int, ...]          # cache layer indices of the model's run order
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every key is kept; W: only the last W keys are read
+    tensors: Optional[Tuple[object, ...]] = None
+
+    def __post_init__(self):
+        if self.tensors is None:
+            from ..parts.base import CacheTensor
+            object.__setattr__(self, "tensors", (CacheTensor("k", self.num_kv_heads, self.head_dim),
+                                                 CacheTensor("v", self.num_kv_heads, self.head_dim)))
 
 
 _lib = None
@@ -85,6 +95,10 @@ def _host():
             "pbe_cm_decode_fill": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, vp, i32]),
             "pbe_cm_reserve_many": (None, [vp, i32, vp, i64, vp]),
             "pbe_cm_commit_many": (i32, [vp, i32, vp, vp]),
+            "pbe_cm_live_handles": (i32, [vp, vp, i32]),
+            "pbe_cm_share_page": (i32, [vp, i32, i32]),
+            "pbe_cm_unshare_page": (i32, [vp, i32, i32]),
+            "pbe_cm_page_owner": (i64, [vp, i32, i32]),
             "pbe_decode_work_fill": (i32, [i32, i32, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, i32]),
         }
         for name, (res, args) in sig.items():
@@ -322,6 +336,27 @@ class CacheManager:
     def page_generation(self, group: int, page: int) -> int:
         return _host().pbe_cm_page_generation(self._h, group, page)
 
+    def page_owner(self, group: int, page: int) -> Optional[int]:
+        """The handle of the request the page was handed to; None for a free page."""
+        v = int(_host().pbe_cm_page_owner(self._h, group, page))
+        if v == _ERR_BAD_ARG:
+            raise CacheError(f"page {page} lies outside the pool of group {group}")
+        return None if v < 0 else v
+
+    def share_page(self, group: int, page: int) -> None:
+        """One more hold on a page that is held (its reference count goes up): it stays out of
+        the free queue when its request gives it back, until ``unshare_page`` lets go as well.
+        Nothing in this engine shares pages yet (no prefix cache); the directory keeps the
+        count so that a page can be held more than once."""
+        rc = _host().pbe_cm_share_page(self._h, group, page)
+        if rc < 0:
+            self._raise(rc, None, f"page {page} of group {group} is not held: it cannot be shared")
+
+    def unshare_page(self, group: int, page: int) -> None:
+        rc = _host().pbe_cm_unshare_page(self._h, group, page)
+        if rc < 0:
+            self._raise(rc, None, f"page {page} of group {group} has no further hold to let go of")
+
     def set_free_order(self, group: int, pages: Sequence[int]) -> None:
         """Test hook: the order in which the free pages of a group will be handed out."""
         arr = np.asarray(list(pages), dtype=np.int32)
@@ -355,8 +390,18 @@ class CacheManager:
         if _host().pbe_cm_check(self._h, buf, 512) != 0:
             raise CacheError(buf.value.decode())
 
+    def live_handles(self) -> List[int]:
+        """Handles of all live requests."""
+        lib = _host()
+        out = np.empty(max(self.max_requests, 1), dtype=np.int64)
+        n = lib.pbe_cm_live_handles(self._h, out.ctypes.data, len(out))
+        return [int(h) for h in out[:n]]
+
     def reset(self) -> None:
-        raise CacheError("reset is not supported: free the requests you hold")
+        """Gives back everything every live request holds (a replay that starts over); handles
+        handed out before go stale.  Page generations and allocation counts go on counting."""
+        for h in self.live_handles():
+            self.free(h)
 
 
 def decode_work_fill(R: int, B: int, S: int, ctx_before: np.ndarray, window: Optional[int], split_keys: int,

@@ -31,22 +31,44 @@ struct Pool {
   int num_pages = 0;
   bool lifo = false;
   std::deque<int> free_q;
-  std::vector<int> refs, generation;
+  // The page directory: per page its reference count (the block table that holds it plus any
+  // further holds taken with share()), how often it has been handed out, the request that it
+  // was handed to (-1 while free) and how many further holds it has.  A page goes back to the
+  // free queue when its count reaches zero, whoever lets go last.  The reference keeps the same
+  // record in base::PageDirectory (page_directory.cpp:16-47) over BlockAllocator's counts
+  // (block_allocator.cpp:232-262).
+  std::vector<int> refs, generation, shares;
+  std::vector<int64_t> owner;
   int64_t allocations = 0;
-  int allocate() {
+  int allocate(int64_t handle) {
     if (free_q.empty()) return -1;
     int page;
     if (lifo) { page = free_q.back(); free_q.pop_back(); }
     else { page = free_q.front(); free_q.pop_front(); }
     refs[page] = 1;
+    owner[page] = handle;
     generation[page] += 1;
     allocations += 1;
     return page;
   }
   int release(int page) {
     if (page < 0 || page >= num_pages || refs[page] <= 0) return kFreedTwice;
-    if (--refs[page] == 0) free_q.push_back(page);
+    if (--refs[page] == 0) {
+      owner[page] = -1;
+      free_q.push_back(page);
+    }
     return kOk;
+  }
+  int share(int page) {            // one more hold on a page that is held
+    if (page < 0 || page >= num_pages || refs[page] <= 0) return kBadArg;
+    refs[page] += 1;
+    shares[page] += 1;
+    return kOk;
+  }
+  int unshare(int page) {
+    if (page < 0 || page >= num_pages || shares[page] <= 0) return kFreedTwice;
+    shares[page] -= 1;
+    return release(page);
   }
 };
 
@@ -97,6 +119,8 @@ API void* pbe_cm_new(int n_groups, const int* windows, int page_tokens, const in
     p.lifo = lifo != 0;
     p.refs.assign(p.num_pages, 0);
     p.generation.assign(p.num_pages, 0);
+    p.shares.assign(p.num_pages, 0);
+    p.owner.assign(p.num_pages, -1);
     for (int i = 0; i < p.num_pages; ++i) p.free_q.push_back(i);
   }
   m->slots.resize(max_requests);
@@ -186,7 +210,7 @@ API int pbe_cm_reserve(void* h, int64_t handle, int64_t n) {
   }
   for (size_t g = 0; g < m->pools.size(); ++g) {
     while ((int64_t)r->tables[g].size() < target) {
-      const int page = m->pools[g].allocate();
+      const int page = m->pools[g].allocate(handle);
       if (page < 0) return kCorrupt;
       r->tables[g].push_back(page);
     }
@@ -288,9 +312,10 @@ API int pbe_cm_check(void* h, char* buf, int cap) {
     for (int i = 0; i < p.num_pages && msg.empty(); ++i) {
       if (freec[i] > 1) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is in the free queue twice";
       else if (held[i] > 1) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is held by " + std::to_string(held[i]) + " block tables";
-      else if (held[i] == 1 && freec[i] == 1) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is both held and free";
-      else if (held[i] == 0 && freec[i] == 0) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is lost";
-      else if (held[i] == 1 && p.refs[i] != 1) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is held but its count is " + std::to_string(p.refs[i]);
+      else if (held[i] + p.shares[i] > 0 && freec[i] == 1) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is both held and free";
+      else if (held[i] + p.shares[i] == 0 && freec[i] == 0) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is lost";
+      else if (p.refs[i] != held[i] + p.shares[i]) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " is held " + std::to_string(held[i] + p.shares[i]) + " times but its count is " + std::to_string(p.refs[i]);
+      else if ((p.refs[i] == 0) != (p.owner[i] < 0)) msg = "group " + std::to_string(g) + ": page " + std::to_string(i) + " has an owner while free, or none while held";
     }
   }
   for (const Request& r : m->slots) {
@@ -305,6 +330,37 @@ API int pbe_cm_check(void* h, char* buf, int cap) {
     buf[cap - 1] = 0;
   }
   return 1;
+}
+
+// The page directory's further holds: share() pins a held page (its count goes up, it stays out
+// of the free queue when its request lets go of it), unshare() lets go of one such hold.
+API int pbe_cm_share_page(void* h, int group, int page) {
+  Manager* m = static_cast<Manager*>(h);
+  if (group < 0 || group >= (int)m->pools.size()) return kBadArg;
+  return m->pools[group].share(page);
+}
+API int pbe_cm_unshare_page(void* h, int group, int page) {
+  Manager* m = static_cast<Manager*>(h);
+  if (group < 0 || group >= (int)m->pools.size()) return kBadArg;
+  return m->pools[group].unshare(page);
+}
+// The handle of the request a page was handed to; -1 for a free page, kBadArg outside the pool.
+API int64_t pbe_cm_page_owner(void* h, int group, int page) {
+  Manager* m = static_cast<Manager*>(h);
+  if (group < 0 || group >= (int)m->pools.size() || page < 0 || page >= m->pools[group].num_pages) return kBadArg;
+  return m->pools[group].owner[page];
+}
+// Handles of all live requests into out[0..cap); returns how many there are.
+API int pbe_cm_live_handles(void* h, int64_t* out, int cap) {
+  Manager* m = static_cast<Manager*>(h);
+  int n = 0;
+  for (int slot = 0; slot < m->max_requests; ++slot) {
+    const Request& r = m->slots[slot];
+    if (!r.live) continue;
+    if (n < cap) out[n] = (r.generation << kSlotBits) | slot;
+    ++n;
+  }
+  return n;
 }
 
 // One decode step's integers for R requests, each bringing one token at its last reserved

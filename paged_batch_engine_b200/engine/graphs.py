@@ -57,8 +57,10 @@ class DecodeStepContext(StepContext):
     """A StepContext whose arrays are fixed views of one persistent buffer."""
     captured = True               # its launches are recorded once and replayed
 
-    def __init__(self, manager, device, work_keys, batch: int, splits: int, bt_strides: Sequence[int]):
+    def __init__(self, manager, device, work_keys, batch: int, splits: int, bt_strides: Sequence[int],
+                 state_pad_slot: int = 0):
         self.manager, self.device = manager, device
+        self.state_pad_slot = int(state_pad_slot)     # the state row that padding rows point at
         self.page_tokens = manager.page_tokens
         self.batch, self.splits = batch, splits
         self.split_keys = choose_split_keys(batch)
@@ -166,7 +168,7 @@ class DecodeStepContext(StepContext):
         self.context_before_host = ctx_before
         if not same:
             q = self._h("q_len"); q[:] = 0; q[:R] = 1
-            st = self._h("state"); st[:] = 0; st[:R] = self.state_slots_host
+            st = self._h("state"); st[:] = self.state_pad_slot; st[:R] = self.state_slots_host
         for i, key in enumerate(self.work_keys):
             # positions, lengths, tokens (once) and the work list of this key, in the host library
             first = i == 0
@@ -213,7 +215,9 @@ class DecodeGraphs:
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return False
-        if self.runner.storage.state:      # a mixer with state of its own runs host logic per step
+        # a captured step is recorded once: a mixer that runs host logic per step (loops over the
+        # requests, reads lengths on the host) cannot be in it; every mixer says which it is
+        if not self.runner.model.decode_capturable():
             return False
         # one row tile per request is what a fixed work list holds
         return all(gsize <= tile_rows for _, gsize, tile_rows, _ in self.runner._work_keys)
@@ -260,7 +264,8 @@ class DecodeGraphs:
                    for g in range(len(runner.cache.groups))) if runner.cache.groups else 1
         cap = max((self.max_context + P - 1) // P, need, 1)
         strides = [cap for _ in runner.cache.groups]
-        ctx = DecodeStepContext(runner.cache, runner.device, runner._work_keys, B, S, strides)
+        ctx = DecodeStepContext(runner.cache, runner.device, runner._work_keys, B, S, strides,
+                                state_pad_slot=runner.storage.state_pad_slot)
         ctx.fill(entries, runner.model.spec.vocab_size)
         # Warm up on a side stream (library handles, lazy kernel loading), then capture.  The
         # warm-up and the capture write this step's keys and values to the slots the step

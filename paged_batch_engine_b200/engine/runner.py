@@ -110,6 +110,11 @@ class ModelRunner:
         ``decode_graph``: replay a captured CUDA graph when every entry is a single token.
         ``device_tokens``: the step's token ids as an int32 device tensor (a step scheduled
         ahead of the one that samples them); captured decode steps only."""
+        if self.storage.state:
+            # a request whose first tokens run now finds its state rows zeroed (a new request, or
+            # one that starts over after a preemption); see parts.StateNeed
+            self.storage.zero_state([self.cache.state_slot(e.handle) for e in entries
+                                     if self.cache.context_len(e.handle) == 0])
         if decode_graph and self.graphs is not None and self.graphs.eligible(entries):
             logits = self.graphs.run(entries, device_tokens)
         elif device_tokens is not None:

@@ -76,6 +76,11 @@ class DecoderModel:
         """Compile, side by side, the kernels this model launches (no-op when built)."""
         compile_many(self.kernel_libraries())
 
+    def decode_capturable(self) -> bool:
+        """True when every mixer says it can step decoded tokens inside a captured CUDA graph
+        (``Mixer.decode_capturable``)."""
+        return all(getattr(b.mixer, "decode_capturable", False) for b in self.blocks)
+
     # ------------------------------------------------------------------ what a step needs
     def work_keys(self, storage):
         keys = []

@@ -1,4 +1,4 @@
-from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, StateNeed,
+from .base import (Block, CacheTensor, FeedForward, KVNeed, Mixer, Norm, PagedNeed, Part, PositionEncoding, StateNeed,
                    build_block, build_part, register_part)
 from .norm import RMSNorm
 from .rope import NoPositionEncoding, RotaryEncoding
@@ -6,6 +6,7 @@ from .attention import GQAttention
 from .mlp import SwiGLU
 from .block import PreNormBlock
 
-__all__ = ["Block", "FeedForward", "KVNeed", "Mixer", "Norm", "Part", "PositionEncoding", "StateNeed",
+__all__ = ["Block", "CacheTensor", "FeedForward", "KVNeed", "Mixer", "Norm", "PagedNeed", "Part", "PositionEncoding",
+           "StateNeed",
            "build_block", "build_part", "register_part", "RMSNorm", "NoPositionEncoding", "RotaryEncoding",
            "GQAttention", "SwiGLU", "PreNormBlock"]

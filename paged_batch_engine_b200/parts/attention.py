@@ -20,12 +20,21 @@ class GQAttention(Mixer):
     Reference: infMain/source/model/qwen2_batch.cpp:604-750 (three products, three bias
     launches, rope, scatter, decode and prefill attention kernels, output product).
     Checkpoint tensors: {q,k,v}_proj.weight [heads*head_dim, hidden] (+ .bias),
-    o_proj.weight [hidden, heads*head_dim] (+ .bias when o_bias)."""
+    o_proj.weight [hidden, heads*head_dim] (+ .bias when o_bias).  ``tensor_names`` renames
+    the four projections for checkpoints that call them otherwise, e.g.
+    ``dict(q="wq", k="wk", v="wv", o="wo")``; ``.weight`` / ``.bias`` are appended."""
+    TENSOR_NAMES = dict(q="q_proj", k="k_proj", v="v_proj", o="o_proj")
+    decode_capturable = True      # decoded tokens are stepped from the step's device arrays alone
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  dtype, device, qkv_bias: bool = True, o_bias: bool = False,
                  scale: Optional[float] = None, window: Optional[int] = None,
-                 position: Optional[PartSpec] = None, kernel: Optional[str] = None):
+                 position: Optional[PartSpec] = None, kernel: Optional[str] = None,
+                 tensor_names: Optional[dict] = None):
+        unknown = set(tensor_names or {}) - set(self.TENSOR_NAMES)
+        if unknown:
+            raise ValueError(f"tensor_names knows q, k, v and o; got {sorted(unknown)}")
+        self.names = dict(self.TENSOR_NAMES, **(tensor_names or {}))
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
@@ -52,30 +61,32 @@ class GQAttention(Mixer):
     # ---- tensors
     def param_specs(self, prefix):
         q_out, kv_out = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
-        specs = [ParamSpec(prefix + "q_proj.weight", (q_out, self.hidden_size)),
-                 ParamSpec(prefix + "k_proj.weight", (kv_out, self.hidden_size)),
-                 ParamSpec(prefix + "v_proj.weight", (kv_out, self.hidden_size)),
-                 ParamSpec(prefix + "o_proj.weight", (self.hidden_size, q_out))]
+        n = self.names
+        specs = [ParamSpec(prefix + n["q"] + ".weight", (q_out, self.hidden_size)),
+                 ParamSpec(prefix + n["k"] + ".weight", (kv_out, self.hidden_size)),
+                 ParamSpec(prefix + n["v"] + ".weight", (kv_out, self.hidden_size)),
+                 ParamSpec(prefix + n["o"] + ".weight", (self.hidden_size, q_out))]
         if self.qkv_bias:
-            specs += [ParamSpec(prefix + "q_proj.bias", (q_out,)),
-                      ParamSpec(prefix + "k_proj.bias", (kv_out,)),
-                      ParamSpec(prefix + "v_proj.bias", (kv_out,))]
+            specs += [ParamSpec(prefix + n["q"] + ".bias", (q_out,)),
+                      ParamSpec(prefix + n["k"] + ".bias", (kv_out,)),
+                      ParamSpec(prefix + n["v"] + ".bias", (kv_out,))]
         if self.o_bias:
-            specs.append(ParamSpec(prefix + "o_proj.bias", (self.hidden_size,)))
+            specs.append(ParamSpec(prefix + n["o"] + ".bias", (self.hidden_size,)))
         return specs + self.position.param_specs(prefix + "position.")
 
     def load(self, tensors, prefix):
-        ws = [tensors.pop(prefix + f"{n}_proj.weight") for n in "qkv"]
+        nm = self.names
+        ws = [tensors.pop(prefix + nm[n] + ".weight") for n in "qkv"]
         if len({w.dtype for w in ws}) != 1:
             ws = [w.to(torch.float32) for w in ws]
         self.w_qkv = torch.cat(ws, dim=0).contiguous()
         del ws
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors.pop(prefix + f"{n}_proj.bias").to(torch.float32)
+            self.b_qkv = torch.cat([tensors.pop(prefix + nm[n] + ".bias").to(torch.float32)
                                     for n in "qkv"]).contiguous()
-        self.w_o = tensors.pop(prefix + "o_proj.weight").contiguous()
+        self.w_o = tensors.pop(prefix + nm["o"] + ".weight").contiguous()
         if self.o_bias:
-            self.b_o = tensors.pop(prefix + "o_proj.bias").to(torch.float32).contiguous()
+            self.b_o = tensors.pop(prefix + nm["o"] + ".bias").to(torch.float32).contiguous()
         self.position.load(tensors, prefix + "position.")
 
     # ---- compute

@@ -15,7 +15,7 @@ PositionEncoding: ``kernel_args() -> (inv_freq | None, rotary_dim, interleaved)`
             mixer that applies it; one that brings its own code sets ``applies_itself`` and has
             ``apply(q, k, positions) -> (q, k)`` on float32 [rows, heads, head_dim] tensors
             (projection bias already added); its tensors live under the mixer's prefix + "position.".
-Mixer:      ``cache_need() -> KVNeed | StateNeed | None`` (what it keeps between steps) and
+Mixer:      ``cache_need() -> KVNeed | PagedNeed | StateNeed | None`` (what it keeps between steps) and
             ``forward(x, ctx, cache) -> y`` over all rows of the step.
 FeedForward: ``forward(x, ctx) -> y``.
 Block:      ``forward(residual, delta, ctx, cache) -> (residual, delta)``: the arrangement
@@ -34,16 +34,44 @@ from ..weights.loader import ParamSpec
 
 
 @dataclass(frozen=True)
-class KVNeed:
-    """Keys and values in pages: geometry and lifetime of one cache layer."""
-    num_kv_heads: int
-    head_dim: int
+class CacheTensor:
+    """One tensor of a paged cache layer: ``[page, heads, page_tokens, width]`` per layer."""
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
+class PagedNeed:
+    """What a mixer keeps per token, in pages: any number of named tensors, each with its own
+    heads and width (keys and values of different widths, one compressed latent, ...), and how
+    long a token is kept (``window`` None: for ever; W: while one of the last W).  Layers with
+    equal needs share a page pool and a block table."""
+    tensors: Tuple[CacheTensor, ...]
     window: Optional[int] = None
 
 
 @dataclass(frozen=True)
+class KVNeed:
+    """Keys and values of equal geometry in pages: the usual case of ``PagedNeed``."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+    @property
+    def tensors(self) -> Tuple[CacheTensor, ...]:
+        return (CacheTensor("k", self.num_kv_heads, self.head_dim),
+                CacheTensor("v", self.num_kv_heads, self.head_dim))
+
+
+@dataclass(frozen=True)
 class StateNeed:
-    """A fixed-size state per request (one row per request slot)."""
+    """A fixed-size state per request (one row per request slot).  The row of a request is
+    zeroed by the step function before the request's first tokens run (also when a preempted
+    request starts over), so a mixer finds zeros at ``context_before == 0``; it is never
+    cleared otherwise, and what a mixer leaves there is what it finds at the request's next
+    step.  One more row than there are request slots exists: the padding rows of a captured
+    decode step point at it."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
 
@@ -76,6 +104,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # Steps of single decoded tokens are captured once and replayed as CUDA graphs when every
+    # mixer of the model sets this: it then steps such tokens with device tensors only (the
+    # step's arrays, ``ctx.state_slots``), never with values read on the host, which a replay
+    # would not see change.  A mixer that loops over the requests on the host leaves it False.
+    decode_capturable = False
+
     def cache_need(self):
         return None
 

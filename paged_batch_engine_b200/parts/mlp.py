@@ -13,9 +13,14 @@ class SwiGLU(FeedForward):
     product.  Reference: infMain/source/model/qwen2_batch.cpp:762-777 and
     swiglu_kernel.cu:6-25 (g * 1/(1+exp(-g)) * u in float32).
     Checkpoint tensors: gate_proj.weight, up_proj.weight [inter, hidden]; down_proj.weight
-    [hidden, inter]."""
+    [hidden, inter]; ``tensor_names`` renames them, e.g. ``dict(gate="w1", down="w2", up="w3")``."""
+    TENSOR_NAMES = dict(gate="gate_proj", up="up_proj", down="down_proj")
 
-    def __init__(self, hidden_size: int, intermediate_size: int, dtype, device):
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype, device, tensor_names=None):
+        unknown = set(tensor_names or {}) - set(self.TENSOR_NAMES)
+        if unknown:
+            raise ValueError(f"tensor_names knows gate, up and down; got {sorted(unknown)}")
+        self.names = dict(self.TENSOR_NAMES, **(tensor_names or {}))
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.dtype, self.device = dtype, device
         self.w_gate_up = self.w_down = None
@@ -25,17 +30,19 @@ class SwiGLU(FeedForward):
 
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size
-        return [ParamSpec(prefix + "gate_proj.weight", (i, h)),
-                ParamSpec(prefix + "up_proj.weight", (i, h)),
-                ParamSpec(prefix + "down_proj.weight", (h, i))]
+        n = self.names
+        return [ParamSpec(prefix + n["gate"] + ".weight", (i, h)),
+                ParamSpec(prefix + n["up"] + ".weight", (i, h)),
+                ParamSpec(prefix + n["down"] + ".weight", (h, i))]
 
     def load(self, tensors, prefix):
-        g, u = tensors.pop(prefix + "gate_proj.weight"), tensors.pop(prefix + "up_proj.weight")
+        n = self.names
+        g, u = tensors.pop(prefix + n["gate"] + ".weight"), tensors.pop(prefix + n["up"] + ".weight")
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         del g, u
-        self.w_down = tensors.pop(prefix + "down_proj.weight").contiguous()
+        self.w_down = tensors.pop(prefix + n["down"] + ".weight").contiguous()
 
     def forward(self, x, ctx):
         if ops.skinny_applies(x, self.w_gate_up):

@@ -236,3 +236,46 @@ def test_captured_step_split_capacity_covers_every_request_of_the_step():
     # the bound is tight somewhere: some shorter request does use all of it
     S = splits_bound(2304, 512, 256)
     assert S == 3
+
+
+def test_page_directory_counts_owners_and_further_holds():
+    """A page knows who it was handed to; a further hold keeps it out of the free queue after
+    its request has given it back, and it returns when the last hold lets go."""
+    m = CacheManager([full()], page_tokens=4, num_pages=6)
+    a, b = m.add_request(), m.add_request()
+    assert m.reserve(a, 9) and m.reserve(b, 4)
+    ta, tb = m.block_table(a), m.block_table(b)
+    assert [m.page_owner(0, p) for p in ta] == [a] * 3 and m.page_owner(0, tb[0]) == b
+    free = [p for p in range(6) if p not in ta + tb]
+    assert all(m.page_owner(0, p) is None for p in free)
+    with pytest.raises(CacheError):
+        m.share_page(0, free[0])                      # a free page cannot be shared
+    m.share_page(0, ta[1])
+    m.share_page(0, ta[1])
+    assert m.pools[0].refcount(ta[1]) == 3
+    m.check_invariants()
+    m.free(a)
+    assert m.num_free_pages() == 6 - 1 - 1            # b's page and the shared one are still out
+    assert m.pools[0].refcount(ta[1]) == 2 and m.page_owner(0, ta[1]) == a
+    m.check_invariants()
+    m.unshare_page(0, ta[1])
+    m.unshare_page(0, ta[1])
+    assert m.num_free_pages() == 5 and m.page_owner(0, ta[1]) is None
+    with pytest.raises(CacheError):
+        m.unshare_page(0, ta[1])
+    m.check_invariants()
+
+
+def test_reset_gives_everything_back_and_stales_the_handles():
+    m = CacheManager([full((0,)), windowed(6, (1,))], page_tokens=4, num_pages=[8, 8])
+    hs = [m.add_request() for _ in range(3)]
+    for i, h in enumerate(hs):
+        assert m.reserve(h, 5 + 3 * i)
+        m.commit(h, 5 + 3 * i)
+    assert sorted(m.live_handles()) == sorted(hs)
+    m.reset()
+    assert m.num_live_requests == 0 and m.num_free_pages(0) == 8 and m.num_free_pages(1) == 8
+    assert not any(m.is_live(h) for h in hs)
+    m.check_invariants()
+    h = m.add_request()
+    assert m.reserve(h, 32) and h not in hs

@@ -506,3 +506,257 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(dtype):
         runner.cache.free(h)
         err = (torch.cat(got) - want).abs().max().item()
         assert err <= tol * max(1.0, want.abs().max().item()), (dtype, cuts, err)
+
+
+# ------------------------------------------------------------------ a compressed cache tensor, a capturable state, other tensor names
+def make_toy_latent_mixer_class():
+    from paged_batch_engine_b200.parts import CacheTensor, Mixer, PagedNeed
+    from paged_batch_engine_b200.weights import ParamSpec
+
+    class ToyLatentMixer(Mixer):
+        """One compressed tensor per token in the pages instead of keys and values: c_t = x_t C^T
+        (``rank`` numbers); y_t = (sum_j softmax_j(q_t . c_j) c_j) U^T over j <= t with q_t = x_t Q^T."""
+
+        def __init__(self, hidden_size, rank, dtype, device):
+            self.d, self.r, self.dtype, self.device = hidden_size, rank, dtype, device
+
+        def cache_need(self):
+            return PagedNeed((CacheTensor("latent", 1, self.r),))
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "C", (self.r, self.d)), ParamSpec(prefix + "Q", (self.r, self.d)),
+                    ParamSpec(prefix + "U", (self.d, self.r))]
+
+        def load(self, tensors, prefix):
+            self.C, self.Q, self.U = (tensors.pop(prefix + n).float() for n in "CQU")
+
+        def forward(self, x, ctx, cache):
+            pages = cache.tensors["latent"]                       # [page, 1, page_tokens, rank]
+            P = ctx.page_tokens
+            xf = x.float()
+            c, q = xf @ self.C.t(), xf @ self.Q.t()
+            slots = ctx.group(cache.group).slots.long()
+            pages.view(-1, self.r)[slots] = c.to(pages.dtype)     # heads = 1: slot = page * P + offset
+            y = torch.empty_like(xf)
+            table = ctx.group(cache.group).block_table
+            for r in range(ctx.num_requests):
+                lo, n, before = int(ctx.q_start_host[r]), int(ctx.q_len_host[r]), int(ctx.context_before_host[r])
+                total = before + n
+                ids = table[r, :(total + P - 1) // P].long()
+                lat = pages[ids, 0].reshape(-1, self.r)[:total].float()
+                s = q[lo:lo + n] @ lat.t()
+                keep = torch.arange(total, device=x.device)[None, :] <= (before + torch.arange(n, device=x.device))[:, None]
+                w = torch.softmax(s.masked_fill(~keep, float("-inf")), dim=-1)
+                y[lo:lo + n] = (w @ lat) @ self.U.t()
+            return y.to(x.dtype)
+
+    return ToyLatentMixer
+
+
+def make_toy_device_state_mixer_class():
+    from paged_batch_engine_b200.parts import Mixer, StateNeed
+    from paged_batch_engine_b200.weights import ParamSpec
+
+    class ToyDeviceStateMixer(Mixer):
+        """s_t = decay * s_{t-1} + x_t * w, y_t = s_t, with the state in the request's slot.  It
+        never zeroes its state (the step function does, before a request's first tokens) and it
+        steps decoded tokens with device tensors only, so it says it can be captured."""
+        decode_capturable = True
+
+        def __init__(self, hidden_size, dtype, device, decay=0.5):
+            self.d, self.decay = hidden_size, decay
+
+        def cache_need(self):
+            return StateNeed((self.d,), torch.float32)
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "mix", (self.d,))]
+
+        def load(self, tensors, prefix):
+            self.w = tensors.pop(prefix + "mix").float()
+
+        def forward(self, x, ctx, cache):
+            if getattr(ctx, "captured", False) or int(ctx.q_len_host.max()) == 1:
+                slots = ctx.state_slots[:x.shape[0]].long()       # padding rows point at the spare row
+                s = cache.state[slots] * self.decay + x.float() * self.w
+                cache.state.index_copy_(0, slots, s)
+                return s.to(x.dtype)
+            y = torch.empty_like(x)
+            for r in range(ctx.num_requests):
+                lo, n = int(ctx.q_start_host[r]), int(ctx.q_len_host[r])
+                s = cache.state[int(ctx.state_slots_host[r])]
+                for t in range(lo, lo + n):
+                    s.mul_(self.decay).add_(x[t].float() * self.w)
+                    y[t] = s.to(x.dtype)
+            return y
+
+    return ToyDeviceStateMixer
+
+
+def plain_toy_model_3(c, w, tokens):
+    T = len(tokens)
+    x = plain.embedding(tokens, w["emb"]) * c["embed_scale"]
+    # block A: the latent mixer, SwiGLU under other tensor names
+    if c["latent"]:
+        h = plain.rmsnorm(x, w["A.n1.weight"], c["eps"])
+        lat, q = h @ w["A.mx.C"].t(), h @ w["A.mx.Q"].t()
+        s = (q @ lat.t()).masked_fill(torch.arange(T)[None, :] > torch.arange(T)[:, None], float("-inf"))
+        x = x + (torch.softmax(s, dim=-1) @ lat) @ w["A.mx.U"].t()
+        f = plain.rmsnorm(x, w["A.n2.weight"], c["eps"])
+        x = x + plain.linear(plain.swiglu(plain.linear(f, w["A.ff.w1.weight"]), plain.linear(f, w["A.ff.w3.weight"])),
+                             w["A.ff.w2.weight"])
+    # block B: the state mixer
+    h = plain.rmsnorm(x, w["B.n1.weight"], c["eps"])
+    st, out = torch.zeros(c["d"]), []
+    for t in range(T):
+        st = c["decay"] * st + h[t] * w["B.mx.mix"]
+        out.append(st.clone())
+    x = x + torch.stack(out)
+    f = plain.rmsnorm(x, w["B.n2.weight"], c["eps"])
+    x = x + plain.linear(plain.swiglu(plain.linear(f, w["B.ff.w1.weight"]), plain.linear(f, w["B.ff.w3.weight"])),
+                         w["B.ff.w2.weight"])
+    # block C: attention under other tensor names
+    h = plain.rmsnorm(x, w["C.n1.weight"], c["eps"])
+    ww = {"q_proj": "wq", "k_proj": "wk", "v_proj": "wv", "o_proj": "wo"}
+    renamed = {f"C.at.{old}.{kind}": w[f"C.at.{new}.{kind}"] for old, new in ww.items() for kind in ("weight", "bias")
+               if f"C.at.{new}.{kind}" in w}
+    acfg = dict(num_attention_heads=c["heads"], num_key_value_heads=c["kv"], head_dim=c["hd"], hidden_size=c["d"],
+                rope_theta=c["theta"])
+    x = x + plain.attention_block(h, torch.arange(T), renamed, "C.at.", acfg, None)
+    f = plain.rmsnorm(x, w["C.n2.weight"], c["eps"])
+    x = x + plain.linear(plain.swiglu(plain.linear(f, w["C.ff.w1.weight"]), plain.linear(f, w["C.ff.w3.weight"])),
+                         w["C.ff.w2.weight"])
+    logits = plain.linear(plain.rmsnorm(x, w["fn.weight"], c["eps"]), w["head"])
+    return c["cap"] * torch.tanh(logits / c["cap"])
+
+
+@pytest.mark.parametrize("latent", [True, False], ids=["latent", "capturable"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_toy_compressed_cache_capturable_state_other_names_and_a_builder(dtype, latent):
+    """Defined here, with no change to the package: a mixer whose pages hold ONE compressed
+    tensor (no keys, no values; it runs host logic, so its model's decode steps stay eager); a
+    mixer with state that never zeroes it (the step function does) and that, with attention
+    alone beside it, keeps captured decode steps on for its model; attention and feed-forward
+    reading checkpoints with other tensor names; and an architecture with a builder of its own
+    (embedding scale and a cap on the logits around the generic decoder)."""
+    from paged_batch_engine_b200.config import (BlockSpec, ModelSpec, PartSpec, RunStep, load_config,
+                                                register_architecture)
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    from paged_batch_engine_b200.engine.runner import ModelRunner, build_model
+    from paged_batch_engine_b200.models.decoder import DecoderModel
+    from paged_batch_engine_b200.parts import register_part
+    from paged_batch_engine_b200.weights import random_state_dict
+
+    register_part("mixer", "toy_latent", make_toy_latent_mixer_class(), replace=True)
+    register_part("mixer", "toy_device_state", make_toy_device_state_mixer_class(), replace=True)
+
+    @dataclass
+    class Toy3Config:
+        d: int = 40
+        rank: int = 12
+        heads: int = 4
+        kv: int = 2
+        hd: int = 16
+        inter: int = 56
+        vocab: int = 89
+        eps: float = 1e-5
+        theta: float = 700.0
+        decay: float = 0.6
+        embed_scale: float = 3.0
+        cap: float = 4.0
+        latent: bool = True
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+        def model_spec(self):
+            norm = PartSpec("rmsnorm", dict(size=self.d, eps=self.eps))
+            ffn = PartSpec("swiglu", dict(hidden_size=self.d, intermediate_size=self.inter,
+                                          tensor_names=dict(gate="w1", down="w2", up="w3")))
+            attn = PartSpec("attention", dict(hidden_size=self.d, num_heads=self.heads, num_kv_heads=self.kv,
+                                              head_dim=self.hd, tensor_names=dict(q="wq", k="wk", v="wv", o="wo"),
+                                              position=PartSpec("rope", dict(theta=self.theta, head_dim=self.hd))))
+            names = dict(norm_mixer="n1.", norm_feed_forward="n2.", feed_forward="ff.", mixer="mx.")
+            blocks = (BlockSpec("prenorm", PartSpec("toy_latent", dict(hidden_size=self.d, rank=self.rank)), ffn, norm,
+                                norm, "A.", names),
+                      BlockSpec("prenorm", PartSpec("toy_device_state", dict(hidden_size=self.d, decay=self.decay)), ffn,
+                                norm, norm, "B.", names),
+                      BlockSpec("prenorm", attn, ffn, norm, norm, "C.", dict(names, mixer="at.")))
+            if not self.latent:
+                blocks = blocks[1:]
+            run = tuple(RunStep(i, i) for i in range(len(blocks)))
+            return ModelSpec("Toy3ForCausalLM", self.d, self.vocab, blocks, run, norm, "emb", "fn.", "head", 512)
+
+    conf = Toy3Config(latent=latent)
+
+    class ScaledCappedDecoder(DecoderModel):
+        """The generic decoder with the embedding table scaled at load and the logits capped."""
+
+        def load(self, tensors):
+            super().load(tensors)
+            self.embed = (self.embed.float() * conf.embed_scale).to(self.embed.dtype)
+
+        def forward(self, ctx, storage):
+            logits = super().forward(ctx, storage)
+            return conf.cap * torch.tanh(logits / conf.cap)
+
+    register_architecture("Toy3ForCausalLM", Toy3Config, builder=lambda spec, dt, dev: ScaledCappedDecoder(spec, dt, dev),
+                          replace=True)
+    model = build_model({"architectures": ["Toy3ForCausalLM"], "latent": latent}, dtype, torch.device(DEV))
+    assert type(model).__name__ == "ScaledCappedDecoder"
+    assert [type(n).__name__ for n in model.cache_needs] == (["PagedNeed"] if latent else []) + ["StateNeed", "KVNeed"]
+    names = [p.name for p in model.param_specs()]
+    assert "C.at.wq.weight" in names and "B.ff.w3.weight" in names and not any("q_proj" in n or "gate_proj" in n for n in names)
+    sd = random_state_dict(model.param_specs(), seed=9, dtype=torch.float32)
+    for k in sd:
+        if k.endswith(("mx.C", "mx.Q", "wq.weight", "wk.weight")):
+            sd[k] = sd[k] * 12
+        if k.endswith("mix"):
+            sd[k] = torch.linspace(0.5, 1.5, conf.d)
+    sd["head"] = sd["head"] * 8                                     # logits large enough for the cap to bend them
+    if dtype == torch.bfloat16:
+        sd = {k: (v.to(torch.bfloat16) if v.dim() > 1 else v) for k, v in sd.items()}
+    model.build_kernels()
+    model.load({k: v.to(DEV) for k, v in sd.items()})
+    runner = ModelRunner(model, page_tokens=8, num_pages=24, max_requests=4)
+    if latent:
+        assert len(runner.storage.groups) == 2                      # the latent pages and the keys/values
+        assert [t.name for t in runner.storage.groups[0].tensors] == ["latent"]
+        assert runner.storage.bytes_per_token() == (conf.rank + 2 * conf.kv * conf.hd) * (4 if dtype == torch.float32 else 2)
+    gen = torch.Generator().manual_seed(6)
+    toks = {r: torch.randint(0, conf.vocab, (n,), generator=gen).tolist() for r, n in (("a", 41), ("b", 19), ("c", 30))}
+    plain_w = {n: t.float() for n, t in sd.items()}
+    want = {r: plain_toy_model_3(conf.__dict__, plain_w, t) for r, t in toks.items()}
+    assert max(v.abs().max().item() for v in want.values()) > 0.6 * conf.cap
+    tol = 3e-5 if dtype == torch.float32 else 0.05
+    # the state rows start dirty: the step function must zero them for every new request
+    for t in runner.storage.state.values():
+        t.fill_(7.0)
+    for graphs in (False, True):
+        handles = {r: runner.cache.add_request() for r in toks}
+        got = {r: [] for r in toks}
+        heads = {"a": 30, "b": 9, "c": 21}
+        for r in toks:                                              # prompt portions, two steps each
+            done = 0
+            for n in (heads[r] - 4, 4):
+                assert runner.cache.reserve(handles[r], n)
+                got[r].append(runner.step([StepEntry(handles[r], toks[r][done:done + n], list(range(n)))]).float().cpu())
+                done += n
+        pos = dict(heads)
+        while any(pos[r] < len(toks[r]) for r in toks):             # all live requests decode together
+            live = [r for r in toks if pos[r] < len(toks[r])]
+            for r in live:
+                assert runner.cache.reserve(handles[r], 1)
+            out = runner.step([StepEntry(handles[r], [toks[r][pos[r]]], [0]) for r in live], decode_graph=graphs).float().cpu()
+            for i, r in enumerate(live):
+                got[r].append(out[i:i + 1])
+                pos[r] += 1
+        for r in toks:
+            runner.cache.free(handles[r])
+            err = (torch.cat(got[r]) - want[r]).abs().max().item()
+            assert err <= tol * max(1.0, want[r].abs().max().item()), (dtype, graphs, r, err)
+    # the state mixer and attention can be captured; the latent mixer's host logic cannot
+    assert runner.graphs.eligible([StepEntry(0, [1], [0])]) == (not latent)
+    assert (runner.graphs.replays > 0) == (not latent)
+    runner.cache.check_invariants()
