@@ -12,8 +12,12 @@ launches the next decode step before it reads this one's ids, feeding them on th
 wall clock between synchronisations.  ``prefill``: one step of a 2,048-token prompt.  ``roofline``: bytes a
 decode step has to read (every weight once, and the live requests' keys and values)
 divided by its time, against the measured copy bandwidth.  ``points``: decode at batch 1
-and 64.  Weights (15 GB) are far larger than L2 and are streamed once per step, so no L2
-flush is needed between steps.
+and 64; decode at batch 8 and 64 from 8,192-token contexts; the float32 path (decode at batch
+8, a 2,048-token prompt); and two whole workloads through the scheduler (the Qwen2.5-1.5B
+shape with 64 requests of 16 to 2,048 prompt tokens read in portions of 512 and 256 new
+tokens each; the Qwen2.5-14B shape with 8 prompts of 8,192 tokens and 512 new tokens each),
+each with its fraction of the measured peak where one applies.  Weights (15 GB) are far larger
+than L2 and are streamed once per step, so no L2 flush is needed between steps.
 """
 import argparse
 import json
@@ -213,6 +217,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-extended", action="store_true",
+                    help="skip the points at 8,192-token contexts, the float32 path and the scheduler workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -303,6 +309,56 @@ def main():
         flops = T * lin_flops + 2 * 2 * H * hd * L * (T * (T + 1) // 2) + 2 * V * d
         result["prefill"] = {"value": round(T * 1e3 / ms_p, 1), "tokens": T, "ms": round(ms_p, 3),
                              "frac": round(flops / (ms_p * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
+    if not args.no_points and not args.no_extended and args.dtype == "bfloat16" and not args.layers:
+        import gc
+        points = result["points"]
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        ext_steps = min(steps, 32)
+        # (1) long contexts: batch 8 and 64 from 8,192 tokens
+        long_ctx = 8192
+        new_tokens = 2 * (ext_steps + warmup) + 8 + 64
+        max_len = long_ctx + new_tokens + 64
+        engine = Engine(typed, dtype="bfloat16", seed=0, page_size=page, num_pages=64 * ((max_len + page - 1) // page) + 8,
+                        max_num_seqs=64, max_num_batched_tokens=8192, prefill_chunk_cap=2048, max_model_len=max_len)
+        for b in (8, 64):
+            reqs = prepare_decode(engine, b, long_ctx, new_tokens, seed=100 + b)
+            ms_b, _ = time_decode_device(engine, reqs, ext_steps, warmup)
+            finish(engine, reqs)
+            bytes_b = weight_bytes + b * (long_ctx + warmup + ext_steps / 2) * kv_per_token
+            points[f"decode_b{b}_ctx8192"] = round(b * 1e3 / ms_b, 2)
+            points[f"decode_b{b}_ctx8192_hbm_frac"] = round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        # (2) the float32 path of the same model: decode at batch 8, a 2,048-token prompt
+        f32_steps = min(steps, 16)
+        new_tokens = 2 * (f32_steps + warmup) + 16
+        max_len = args.context + new_tokens + 64
+        engine = Engine(typed, dtype="float32", seed=0, page_size=page,
+                        num_pages=8 * ((max_len + page - 1) // page) + 2 * (2048 // page) + 8, max_num_seqs=8,
+                        max_num_batched_tokens=4096, prefill_chunk_cap=2048, max_model_len=max_len)
+        reqs = prepare_decode(engine, 8, args.context, new_tokens, seed=7)
+        ms_b, _ = time_decode_device(engine, reqs, f32_steps, warmup)
+        finish(engine, reqs)
+        bytes_b = 2 * weight_bytes + 8 * (args.context + warmup + f32_steps / 2) * 2 * kv_per_token
+        points["decode_b8_fp32"] = round(8 * 1e3 / ms_b, 2)
+        points["decode_b8_fp32_hbm_frac"] = round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        ms_p = time_prefill(engine, 2048, repeats=1)
+        points["prefill_fp32_tok_s"] = round(2048 * 1e3 / ms_p, 1)
+        points["prefill_fp32_tflops"] = round(flops / (ms_p * 1e-3) / 1e12, 2)
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        # (3) whole workloads through the scheduler at two further model shapes
+        import bench_serving
+        for name, key in (("1.5b", "serve_1p5b_64req"), ("14b", "serve_14b_8x8192")):
+            line = bench_serving.run_workload(name)
+            points[f"{key}_tok_s"] = line["value"]
+            points[f"{key}_wall_s"] = line["wall_s"]
+            points[f"{key}_ttft_p50_ms"] = line["ttft_p50_ms"]
+            points[f"{key}_gap_p50_ms"] = line["token_gap_p50_ms"]
     print(json.dumps(result))
     return 0
 

@@ -2,7 +2,7 @@
 """Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
 each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
 
-    python bench_kernels.py [skinny|attn_decode|attn_fused|attn_prefill|tc5|sample|all] [--once]
+    python bench_kernels.py [skinny|sgemm|attn_decode|attn_fused|attn_prefill|tc5|sample|all] [--once]
 
 Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
 buffer is written between launches, so every launch starts with a cold L2)."""
@@ -97,6 +97,29 @@ def main():
             x = torch.randn(8, K, device=DEV).to(torch.bfloat16)
             t = timed(lambda: ops.gemm_skinny(x, w, None, torch.bfloat16, swiglu=sw), flush)
             print(f"gemm_skinny {name} M=8: {t * 1e3:.1f} us, {N * K * 2 / t / 1e6:.0f} GB/s")
+    if what in ("sgemm", "all"):
+        # the float32 path's own GEMM: few rows stream the weights (GB/s), many rows multiply (TFLOP/s)
+        for name, N, K in (("qkv", 4608, 3584), ("o", 3584, 3584), ("gate_up", 37888, 3584), ("down", 3584, 18944)):
+            w = torch.randn(N, K, device=DEV) * 0.02
+            for M in (1, 8, 16, 64, 2048):
+                if M == 2048 and name == "o":
+                    continue
+                x = torch.randn(M, K, device=DEV)
+                out = torch.empty(M, N, device=DEV)
+                t = timed(lambda: ops.sgemm_nt(x, w, None, out), flush, n=3)
+                print(f"sgemm {name} M={M}: {t * 1e3:.1f} us, {N * K * 4 / t / 1e6:.0f} GB/s of weights, "
+                      f"{2 * M * N * K / t / 1e9:.1f} TFLOP/s")
+            del w
+    if what == "sgemm_small":
+        # one launch each of the float32 kernels on a case small enough for a full ncu capture
+        # (the weights, 136 MB, still exceed the L2)
+        w = torch.randn(9472, 3584, device=DEV) * 0.02
+        for M in (8, 16, 512):
+            x = torch.randn(M, 3584, device=DEV)
+            out = torch.empty(M, 9472, device=DEV)
+            t = timed(lambda: ops.sgemm_nt(x, w, None, out), flush, n=3)
+            print(f"sgemm N=9472 K=3584 M={M}: {t * 1e3:.1f} us, {9472 * 3584 * 4 / t / 1e6:.0f} GB/s of weights, "
+                  f"{2 * M * 9472 * 3584 / t / 1e9:.1f} TFLOP/s")
     if what in ("attn_decode", "all"):
         for B in (8, 64):
             run, kv_bytes = attention_case([(2047, 1)] * B)

@@ -86,40 +86,30 @@ def prompt_sweep(layers):
                       "layers": L, "layers_full_model": layers_full, "dtype": "bf16", "rows": rows}))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="1.5b", choices=sorted(SHAPES) + ["prompt-sweep"])
-    ap.add_argument("--requests", type=int, default=0)
-    ap.add_argument("--new-tokens", type=int, default=0)
-    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (named in the line)")
-    ap.add_argument("--max-batched-tokens", type=int, default=0)
-    ap.add_argument("--prefill-chunk", type=int, default=0)
-    args = ap.parse_args()
-    if args.workload == "prompt-sweep":
-        return prompt_sweep(args.layers)
-
+def run_workload(workload, requests=0, new_tokens=0, layers=0, max_batched_tokens=0, prefill_chunk=0):
+    """One whole workload through ``Engine.generate``; returns its record (a dict)."""
     import torch
     from paged_batch_engine_b200 import Engine, SamplingParams
     from paged_batch_engine_b200.config import load_config
     from paged_batch_engine_b200.csrc import ops
 
-    cfg = dict(SHAPES[args.workload])
+    cfg = dict(SHAPES[workload])
     layers_full = cfg["num_hidden_layers"]
-    if args.layers:
-        cfg["num_hidden_layers"] = args.layers
+    if layers:
+        cfg["num_hidden_layers"] = layers
     _, typed = load_config(cfg)
     g = torch.Generator().manual_seed(2024)
-    if args.workload == "14b":
-        n = args.requests or 8
+    if workload == "14b":
+        n = requests or 8
         lengths = [8192] * n
-        new_tokens = args.new_tokens or 512
-        chunk = args.prefill_chunk or 2048
+        new_tokens = new_tokens or 512
+        chunk = prefill_chunk or 2048
     else:
-        n = args.requests or 64
+        n = requests or 64
         lengths = torch.randint(16, 2049, (n,), generator=g).tolist()
-        new_tokens = args.new_tokens or 256
-        chunk = args.prefill_chunk or 512
-    budget = args.max_batched_tokens or max(chunk, 2048)
+        new_tokens = new_tokens or 256
+        chunk = prefill_chunk or 512
+    budget = max_batched_tokens or max(chunk, 2048)
     vocab = cfg["vocab_size"]
     prompts = [torch.randint(0, vocab, (L,), generator=g).tolist() for L in lengths]
     page = 16
@@ -142,13 +132,16 @@ def main():
     wall = time.perf_counter() - t0
     generated = sum(len(r.output_tokens) for r in results)
     prof = engine.profile
+    summary = engine.summary([r.request for r in results], wall)
     line = {
-        "metric": f"generated tok/s, Qwen2.5-{args.workload.upper()} shape, {n} requests through the scheduler",
+        "metric": f"generated tok/s, Qwen2.5-{workload.upper()} shape, {n} requests through the scheduler",
         "value": round(generated / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3),
         "prompt_tokens": sum(lengths), "prompt_tok_per_s_overall": round(sum(lengths) / wall, 1),
         "generated_tokens": generated, "steps": prof["steps"],
         "host_ms_per_step": {k: round(1e3 * prof[k] / max(prof["steps"], 1), 3)
                              for k in ("schedule", "forward", "sample", "process")},
+        "ttft_p50_ms": round(summary["ttft_p50_ms"], 2), "ttft_p95_ms": round(summary["ttft_p95_ms"], 2),
+        "token_gap_p50_ms": round(summary["token_gap_p50_ms"], 3), "token_gap_p95_ms": round(summary["token_gap_p95_ms"], 3),
         "preemptions": sum(r.preemptions for r in results),
         "graph_captures": len(graphs.graphs) - captures0,
         "graph_capture_s": round(graphs.capture_seconds - capture_s0, 3),
@@ -159,7 +152,26 @@ def main():
                    "max_batched_tokens": budget, "prefill_chunk": chunk, "new_tokens": new_tokens,
                    "dtype": "bf16", "data": "synthetic tokens, random weights"},
     }
-    print(json.dumps(line))
+    del engine
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="1.5b", choices=sorted(SHAPES) + ["prompt-sweep"])
+    ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--new-tokens", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (named in the line)")
+    ap.add_argument("--max-batched-tokens", type=int, default=0)
+    ap.add_argument("--prefill-chunk", type=int, default=0)
+    args = ap.parse_args()
+    if args.workload == "prompt-sweep":
+        return prompt_sweep(args.layers)
+    print(json.dumps(run_workload(args.workload, args.requests, args.new_tokens, args.layers,
+                                  args.max_batched_tokens, args.prefill_chunk)))
 
 
 if __name__ == "__main__":

@@ -57,7 +57,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--no-cuda-graphs", action="store_true")
     ap.add_argument("--quiet", action="store_true")
     ap.add_argument("--step-profile", action="store_true")
-    ap.add_argument("--final-summary", action="store_true", default=True)
+    ap.add_argument("--request-metrics", action="store_true",
+                    help="print a REQUEST_METRIC line per request (time to first token, mean token gap, latency)")
+    ap.add_argument("--final-summary", action="store_true",
+                    help="print the run's FINAL_SUMMARY line (steps, tokens, scheduler counters, percentiles)")
     ap.add_argument("--write-random-model", metavar="DIR",
                     help="write config.json and model.safetensors with seeded random weights and exit")
     ap.add_argument("--config", help="config.json for --write-random-model")
@@ -133,6 +136,13 @@ def main(argv=None) -> int:
         n = max(1, p["steps"])
         print("STEP_PROFILE " + " ".join(f"{k}_ms={1e3 * p[k] / n:.3f}" for k in
                                           ("schedule", "forward", "sample", "process")) + f" steps={p['steps']}")
+    if args.request_metrics or args.final_summary:
+        from .engine.metrics import final_summary_line, request_metric_line
+        if args.request_metrics:
+            for r in results:
+                print(request_metric_line(r.request))
+        if args.final_summary:
+            print(final_summary_line(engine.summary([r.request for r in results], duration)))
     print(f"\nsteps:{steps}")
     print(f"\nduration:{duration:f}")
     print(f"\nsteps/s:{steps / duration if duration > 0 else 0.0:f}")

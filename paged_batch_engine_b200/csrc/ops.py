@@ -196,12 +196,28 @@ def sgemm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         raise KernelError("sgemm_nt: shapes or dtypes do not agree")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("sgemm_nt: bias must be float32 [N]")
+    need = _fn("sgemm", "pbe_sgemm_scratch_floats", [c_int, c_int, c_int, c_void_p])
+    need.restype = c_ll
+    n_tickets = c_int(0)
+    floats = int(need(M, N, K, ctypes.byref(n_tickets)))
+    scratch = tickets = None
+    if floats > 0:
+        # partial sums of the K slices, and the tickets by which the last block or warp of a group
+        # of outputs learns that it is the one to add them up (zeroed once, left at zero by every call)
+        scratch = torch.empty(floats, dtype=torch.float32, device=x.device)
+        tickets = _sgemm_tickets.get(x.device)
+        if tickets is None or tickets.numel() < n_tickets.value:
+            tickets = _sgemm_tickets[x.device] = torch.zeros(max(8192, 2 * n_tickets.value), dtype=torch.int32,
+                                                             device=x.device)
     fn = _fn("sgemm", "pbe_sgemm_nt",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-              c_void_p])
+              c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(x), _dtype_code(x), _ptr(w), _ptr(bias), _ptr(out), _dtype_code(out), M, N, K, K, N,
-              _stream()), "sgemm_nt")
+              _ptr(scratch), _ptr(tickets), _stream()), "sgemm_nt")
     return out
+
+
+_sgemm_tickets = {}      # per device: zeroed int32 tickets shared by the float32 products of the stream
 
 
 SKINNY_MAX_ROWS = 8      # batches of at most this many rows take the weight-streaming kernel (0: never); with 9 to

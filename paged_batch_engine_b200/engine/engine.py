@@ -21,6 +21,7 @@ import torch
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
+from .metrics import final_summary, nvtx_range
 from .runner import ModelRunner, _parse_dtype
 from .scheduler import Request, Scheduler, SchedulerConfig, SchedulerOutput
 
@@ -32,6 +33,7 @@ class GenerationResult:
     output_tokens: List[int]
     finish_reason: str
     preemptions: int = 0
+    request: Optional[Request] = None      # the scheduler's record (times, counters) behind this result
 
 
 class Engine:
@@ -105,6 +107,10 @@ class Engine:
         and only then reads the running step's tokens and does its bookkeeping, so the host's
         work hides behind the device's.  A request's tokens therefore become known one call
         later than they are computed; ``drain()`` brings the host up to date."""
+        with nvtx_range("engine.step"):
+            return self._step()
+
+    def _step(self) -> List[Request]:
         t0 = time.perf_counter()
         if self._pending is not None:
             prev, self._pending = self._pending, None
@@ -116,7 +122,8 @@ class Engine:
                 self.profile["steps"] += 1
                 return self._pop_finished()
             self._finish(prev)
-        out = self.scheduler.schedule_step()
+        with nvtx_range("schedule"):
+            out = self.scheduler.schedule_step()
         t1 = time.perf_counter()
         self.profile["schedule"] += t1 - t0
         self.profile["steps"] += 1
@@ -152,7 +159,8 @@ class Engine:
                    for e in out.entries]
         rows = [e for e in out.entries if e.samples]
         decode_only = self.use_cuda_graphs and len(rows) == len(entries) and all(len(e.tokens) == 1 for e in rows)
-        logits = self.runner.step(entries, commit=False, decode_graph=decode_only, device_tokens=device_tokens)
+        with nvtx_range("forward"):
+            logits = self.runner.step(entries, commit=False, decode_graph=decode_only, device_tokens=device_tokens)
         params = [e.request.params for e in rows]
         counters = [e.request.sampling_counter if e.counter is None else e.counter for e in rows]
         later = decode_only and self.decode_ahead and self.runner.graphs is not None and \
@@ -167,10 +175,12 @@ class Engine:
             if e.request.params.repetition_penalty != 1.0 and not self.sampler.tracked(e.request.request_id):
                 self.sampler.track(e.request.request_id, e.request.tokens, vocab)
         if later:
-            dev, host, event = self.sampler.sample_async(logits, params, counters, keys)
+            with nvtx_range("sample"):
+                dev, host, event = self.sampler.sample_async(logits, params, counters, keys)
             return out, dev, host, event
         if rows:
-            ids = self.sampler.sample(logits, params, counters, keys=keys)
+            with nvtx_range("sample"):
+                ids = self.sampler.sample(logits, params, counters, keys=keys)
         else:
             from ..csrc import ops
             ops.raise_on_kernel_status(self.device)      # synchronises
@@ -183,7 +193,8 @@ class Engine:
         if event is not None:
             ids = self.sampler.read_async(ids, event)     # raises if a kernel's bounded wait ran out
         t1 = time.perf_counter()
-        self.scheduler.process_outputs(out, ids)
+        with nvtx_range("process_outputs"):
+            self.scheduler.process_outputs(out, ids)
         self.profile["sample"] += t1 - t0
         self.profile["process"] += time.perf_counter() - t1
 
@@ -203,7 +214,11 @@ class Engine:
         for r in self.drain():
             finished[r.request_id] = r
         return [GenerationResult(r.request_id, list(r.prompt), list(r.outputs), r.finish_reason,
-                                 r.preemptions) for r in reqs]
+                                 r.preemptions, r) for r in reqs]
+
+    def summary(self, requests, wall_s: float) -> Dict[str, float]:
+        """The run's FINAL_SUMMARY record (see ``engine.metrics``) for these requests."""
+        return final_summary(requests, self.scheduler.metrics, self.profile, wall_s)
 
 
 def generate(model, prompts, sampling_params=None, **engine_args) -> List[List[int]]:

@@ -270,11 +270,16 @@ class DecodeGraphs:
         # Warm up on a side stream (library handles, lazy kernel loading), then capture.  The
         # warm-up and the capture write this step's keys and values to the slots the step
         # will write anyway, so the cache is not disturbed.
+        # A mixer's state rows are not: the warm-up would step them once more than the step
+        # itself (which runs when the captured graph is first replayed), so they are put back.
+        kept = {layer: t.clone() for layer, t in runner.storage.state.items()}
         side = torch.cuda.Stream(device=runner.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             runner.model.forward(ctx, runner.storage)
         torch.cuda.current_stream().wait_stream(side)
+        for layer, t in kept.items():
+            runner.storage.state[layer].copy_(t)
         torch.cuda.synchronize()
         from ..csrc import ops
         before = ops.launch_count()

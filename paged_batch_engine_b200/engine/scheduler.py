@@ -17,6 +17,7 @@ tested without a GPU by scripting the sampled tokens.
 """
 from __future__ import annotations
 
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
@@ -50,6 +51,19 @@ class Request:
     ready_step: int = 0
     finish_reason: str = ""
     preemptions: int = 0
+    # host clock (time.perf_counter) of arrival, of every token as the host learned of it, and
+    # of the end: what time to first token, token gaps and latency are made from
+    arrival_time: Optional[float] = None
+    token_times: List[float] = field(default_factory=list)
+    finished_time: Optional[float] = None
+
+    @property
+    def first_token_time(self) -> Optional[float]:
+        return self.token_times[0] if self.token_times else None
+
+    @property
+    def last_token_time(self) -> Optional[float]:
+        return self.token_times[-1] if self.token_times else None
 
     @property
     def tokens(self) -> List[int]:
@@ -114,11 +128,13 @@ class Scheduler:
         self.step_index = 0
         self._next_id = 0
         self.metrics = dict(steps=0, preemptions=0, decode_tokens=0, prefill_tokens=0, no_progress_steps=0,
-                            failed=0, ahead_steps=0, dropped_tokens=0)
+                            failed=0, ahead_steps=0, dropped_tokens=0, decode_only_steps=0,
+                            max_waiting_queue=0, max_running_queue=0)
 
     # ------------------------------------------------------------------ requests in and out
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
         req = Request(self._next_id, [int(t) for t in prompt], (params or SamplingParams()).normalized())
+        req.arrival_time = time.perf_counter()
         self._next_id += 1
         if not req.prompt:
             self._fail(req, "empty_prompt")
@@ -145,6 +161,7 @@ class Scheduler:
         if req in self.waiting:
             self.waiting.remove(req)
         req.status, req.finish_reason = "finished", "cancelled"
+        req.finished_time = time.perf_counter()
         self.finished.append(req)
 
     # ------------------------------------------------------------------ one step
@@ -162,6 +179,10 @@ class Scheduler:
             self._handle_no_progress()
         self.metrics["decode_tokens"] += out.num_decode
         self.metrics["prefill_tokens"] += out.total_tokens - out.num_decode
+        if out.entries and out.num_decode == len(out.entries):
+            self.metrics["decode_only_steps"] += 1
+        self.metrics["max_waiting_queue"] = max(self.metrics["max_waiting_queue"], len(self.waiting))
+        self.metrics["max_running_queue"] = max(self.metrics["max_running_queue"], len(self.running))
         return out
 
     def _schedule_decodes(self, out: SchedulerOutput, budget: int) -> int:
@@ -267,6 +288,7 @@ class Scheduler:
     def _fail(self, req: Request, reason: str) -> None:
         self._release(req)
         req.status, req.finish_reason = "failed", reason
+        req.finished_time = time.perf_counter()
         self.metrics["failed"] += 1
         self.finished.append(req)
 
@@ -317,6 +339,7 @@ class Scheduler:
         self.step_index += 1
         self.metrics["steps"] += 1
         self.metrics["ahead_steps"] += 1
+        self.metrics["decode_only_steps"] += 1
         out = SchedulerOutput()
         for e in prev.entries:
             out.entries.append(ScheduledEntry(e.request, [0], True, counter=e.request.sampling_counter + 1))
@@ -361,13 +384,15 @@ class Scheduler:
         not part of the output; the token budget stops it after max_new_tokens."""
         req.generated += 1
         req.sampling_counter += 1
+        now = time.perf_counter()
+        req.token_times.append(now)
         is_eos = token in self.eos
         p = req.params
         if is_eos and not p.ignore_eos and req.generated > p.min_new_tokens:
-            req.status, req.finish_reason = "finished", "stop"
+            req.status, req.finish_reason, req.finished_time = "finished", "stop", now
             return
         req.outputs.append(token)
         if req.generated >= p.max_new_tokens:
-            req.status, req.finish_reason = "finished", "length"
+            req.status, req.finish_reason, req.finished_time = "finished", "length", now
         elif self.config.max_model_len > 0 and req.target >= self.config.max_model_len:
-            req.status, req.finish_reason = "finished", "length"
+            req.status, req.finish_reason, req.finished_time = "finished", "length", now

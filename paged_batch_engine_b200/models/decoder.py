@@ -141,10 +141,16 @@ class DecoderModel:
         if native is not None:
             delta = self._forward_native(native, ctx, storage, residual)
         else:
-            for step in s.run_order:
+            from ..engine.metrics import nvtx_enabled, nvtx_range
+            traced = nvtx_enabled()
+            for i, step in enumerate(s.run_order):
                 block = self.blocks[step.block]
-                residual, delta = block.forward(residual, delta, ctx,
-                                                storage.layer(step.cache_layer, step.writes_cache))
+                cache = storage.layer(step.cache_layer, step.writes_cache)
+                if traced:
+                    with nvtx_range(f"layer.{i}"):
+                        residual, delta = block.forward(residual, delta, ctx, cache)
+                else:
+                    residual, delta = block.forward(residual, delta, ctx, cache)
         if ctx.num_wanted == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.add_norm(residual, delta, rows=ctx.want_rows)

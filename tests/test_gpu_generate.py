@@ -283,7 +283,7 @@ def test_command_line(tiny_folders, tmp_path):
     pcfg, w = load_plain(folder)
     prompts = prompts_for(cfg["vocab_size"], [6, 11], seed=2)
     cmd = [os.path.join(ROOT, "bin", "pbe-qwen"), folder, "--dtype", "float32", "--max-new-tokens=5",
-           "--ignore-eos", "--kv-cache-blocks-per-layer=32", "--step-profile"]
+           "--ignore-eos", "--kv-cache-blocks-per-layer=32", "--step-profile", "--request-metrics", "--final-summary"]
     for p in prompts:
         cmd += ["--prompt-ids", ",".join(map(str, p))]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
@@ -291,6 +291,10 @@ def test_command_line(tiny_folders, tmp_path):
     outs = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
     assert [o["output_ids"] for o in outs] == [plain.greedy_generate(pcfg, w, p, 5) for p in prompts]
     assert "steps:10" in proc.stdout and "steps/s:" in proc.stdout and "STEP_PROFILE" in proc.stdout
+    metric_lines = [l for l in proc.stdout.splitlines() if l.startswith("REQUEST_METRIC ")]
+    assert len(metric_lines) == 2 and all(" generated_tokens=5 " in l and " ttft_ms=" in l for l in metric_lines)
+    summary = [l for l in proc.stdout.splitlines() if l.startswith("FINAL_SUMMARY ")]
+    assert len(summary) == 1 and " completed_requests=2 " in summary[0] and " total_prefill_tokens=17 " in summary[0]
     # the random-weights mode writes a folder the engine can load
     cfgfile = tmp_path / "c.json"
     cfgfile.write_text(json.dumps(TINY["B"][0]))

@@ -158,14 +158,33 @@ def test_sgemm_true_float32(M, N, K):
 
 
 def test_sgemm_rows_do_not_depend_on_the_batch():
+    """One summation order for every output, whichever kernel computes it: the weight-streaming
+    kernel (up to 16 rows, 32 or 64 weight rows a task) and the tiled kernels (tiles of 32, 64
+    and 128 rows) give bitwise equal rows; K of 333 is no multiple of 4 (scalar copies), 1,100
+    spans three K slices with a ragged last one."""
     torch.manual_seed(4)
-    x, w = torch.randn(150, 333, device=DEV), torch.randn(77, 333, device=DEV)
-    full = torch.empty(150, 77, device=DEV)
-    ops().sgemm_nt(x, w, None, full)
-    for lo, hi in [(0, 1), (3, 10), (64, 129), (149, 150)]:
-        part = torch.empty(hi - lo, 77, device=DEV)
-        ops().sgemm_nt(x[lo:hi].contiguous(), w, None, part)
-        assert torch.equal(part, full[lo:hi])       # same summation order: bitwise equal
+    for K in (333, 1100):
+        x, w, b = torch.randn(150, K, device=DEV), torch.randn(77, K, device=DEV), torch.randn(77, device=DEV)
+        full = torch.empty(150, 77, device=DEV)
+        ops().sgemm_nt(x, w, b, full)
+        for lo, hi in [(0, 1), (3, 10), (20, 36), (64, 129), (100, 130), (90, 150), (149, 150)]:
+            part = torch.empty(hi - lo, 77, device=DEV)
+            ops().sgemm_nt(x[lo:hi].contiguous(), w, b, part)
+            assert torch.equal(part, full[lo:hi]), (K, lo, hi)       # same summation order: bitwise equal
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 17, 40, 200])
+def test_sgemm_sizes_that_divide_nothing(M):
+    """Rows, columns and depths that are multiples of no tile size, through both kernels; the
+    many-column case takes the weight-streaming kernel's 64-row tasks."""
+    torch.manual_seed(M)
+    big = [(19000, 4100)] if M <= 16 else [(300, 1030)] + ([(19000, 1100)] if M == 200 else [])
+    for N, K in [(1, 7), (33, 516), (130, 36)] + big:
+        x, w, b = torch.randn(M, K), torch.randn(N, K), torch.randn(N)
+        out = torch.full((M, N), float("nan"), device=DEV)
+        ops().sgemm_nt(x.to(DEV), w.to(DEV), b.to(DEV), out)
+        want = x.double() @ w.double().t() + b.double()
+        assert (out.cpu().double() - want).abs().max().item() <= 2e-6 * math.sqrt(K) * 4, (M, N, K)
 
 
 # ------------------------------------------------------------------ paged attention

@@ -297,3 +297,35 @@ def test_sizes_of_captured_decode_steps_and_key_splits():
         assert b >= n and (n < 16 or (b - n) * 3 <= b)
         assert choose_split_keys(n) == choose_split_keys(b)
     assert choose_split_keys(4) == 512 and choose_split_keys(5) == 256
+
+
+def test_request_metric_and_final_summary_records():
+    """Time to first token, the mean token gap and the latency as the reference defines them
+    (sequence_state.h:140-165), and the run's summary from the scheduler's counters."""
+    import time
+    from paged_batch_engine_b200.engine import metrics
+    m, s = make()
+    a = s.add_request(list(range(1, 12)), SamplingParams(max_new_tokens=4))
+    b = s.add_request([5, 6], SamplingParams(max_new_tokens=1))
+    c = s.add_request([], SamplingParams(max_new_tokens=1))              # fails at once: empty prompt
+    t0 = time.perf_counter()
+    drive(s, token_fn=lambda req: (time.sleep(0.002), 7)[1])
+    wall = time.perf_counter() - t0
+    assert a.arrival_time <= a.first_token_time <= a.last_token_time == a.finished_time
+    assert len(a.token_times) == a.generated == 4 and len(b.token_times) == 1
+    assert metrics.ttft_ms(a) > 0 and metrics.latency_ms(a) >= metrics.ttft_ms(a)
+    gap = (a.last_token_time - a.first_token_time) * 1e3 / 3
+    assert abs(metrics.itl_ms(a) - gap) < 1e-9 and metrics.itl_ms(b) == 0.0
+    line = metrics.request_metric_line(a)
+    assert line.startswith("REQUEST_METRIC client_request_id=0 status=ok prompt_tokens=11 generated_tokens=4 "
+                           "output_tokens=4 ttft_ms=") and " finish_reason=length" in line
+    assert "status=failed" in metrics.request_metric_line(c) and "finish_reason=empty_prompt" in metrics.request_metric_line(c)
+    summ = metrics.final_summary([a, b, c], s.metrics, dict(steps=s.metrics["steps"], schedule=0.01), wall)
+    assert summ["completed_requests"] == 2 and summ["failed_requests"] == 1
+    assert summ["total_prefill_tokens"] == 13 and summ["total_decode_tokens"] == 3
+    assert summ["total_steps"] == s.metrics["steps"] and summ["decode_only_steps"] == 3
+    assert summ["token_gap_count"] == 3 and summ["token_gap_p50_ms"] > 0
+    assert summ["ttft_p50_ms"] <= summ["ttft_p99_ms"] and summ["throughput_tps"] == pytest.approx(5 / wall)
+    text = metrics.final_summary_line(summ)
+    assert text.startswith("FINAL_SUMMARY total_steps=") and " itl_ms=" in text and " latency_p95_ms=" in text
+    assert metrics.percentile([1.0, 2.0, 3.0, 4.0], 0.5) == 2.5 and metrics.percentile([], 0.9) == 0.0
