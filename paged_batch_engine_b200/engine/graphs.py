@@ -211,6 +211,7 @@ class DecodeGraphs:
         self.launches_per_replay = 0      # this package's kernels inside one captured step
         self.last_h2d_bytes = 0           # size of the integer buffer copied before a replay
         self.capture_seconds = 0.0        # host time spent capturing (warm-up run included)
+        self._capture_stream = None
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
@@ -285,14 +286,27 @@ class DecodeGraphs:
         before = ops.launch_count()
         graph = torch.cuda.CUDAGraph()
         # Destroying another engine's captured graphs (or pinned buffers) while this capture is
-        # open would invalidate it: the collector stays off until the capture has ended.
+        # open would invalidate it: the collector stays off until the capture has ended.  The
+        # capture is begun and ended by hand on a side stream: the library's context manager
+        # would also run a full garbage collection and hand all cached device memory back to
+        # the driver first, after which every buffer of the next steps is allocated anew
+        # (a capture took 40 to 60 ms that way, most of it outside the capture itself).
         gc_was_on = gc.isenabled()
         gc.disable()
+        cap_stream = self._capture_stream
+        if cap_stream is None:
+            cap_stream = self._capture_stream = torch.cuda.Stream(device=runner.device)
+        cap_stream.wait_stream(torch.cuda.current_stream())
         try:
-            with torch.cuda.graph(graph):
-                logits = runner.model.forward(ctx, runner.storage)
+            with torch.cuda.stream(cap_stream):
+                graph.capture_begin()
+                try:
+                    logits = runner.model.forward(ctx, runner.storage)
+                finally:
+                    graph.capture_end()
         finally:
             if gc_was_on:
                 gc.enable()
+        torch.cuda.current_stream().wait_stream(cap_stream)
         self.launches_per_replay = ops.launch_count() - before
         return graph, ctx, logits
