@@ -2,7 +2,7 @@
 """Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
 each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
 
-    python bench_kernels.py [skinny|sgemm|attn_decode|attn_fused|attn_prefill|tc5|sample|all] [--once]
+    python bench_kernels.py [skinny|sgemm|attn_decode|attn_f32|attn_fused|attn_prefill|tc5|sample|all] [--once]
 
 Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
 buffer is written between launches, so every launch starts with a cold L2)."""
@@ -37,7 +37,7 @@ def timed(fn, flush, n=5):
     return sorted(ts)[len(ts) // 2]
 
 
-def attention_case(reqs, H=28, KV=4, hd=128, P=16, kind=None):
+def attention_case(reqs, H=28, KV=4, hd=128, P=16, kind=None, dtype=torch.bfloat16):
     from paged_batch_engine_b200.cache import CacheManager, KVGroupSpec
     from paged_batch_engine_b200.engine.batch import StepContext, StepEntry
     pages = sum((c + n + P - 1) // P for c, n in reqs) + 2
@@ -48,17 +48,17 @@ def attention_case(reqs, H=28, KV=4, hd=128, P=16, kind=None):
         m.reserve(h, c + n)
         m.commit(h, c)
         entries.append(StepEntry(h, [0] * n))
-    kind, tile_rows, _ = ops.attention_kernel_config(hd, torch.bfloat16, kind)
+    kind, tile_rows, _ = ops.attention_kernel_config(hd, dtype, kind)
     key = (0, H // KV, tile_rows, None)
     ctx = StepContext(m, entries, torch.device(DEV), [key])
     meta = ctx.attention_work(0, H // KV, tile_rows, None, H, hd)
     T = sum(n for _, n in reqs)
-    q = torch.randn(T, H * hd, device=DEV).to(torch.bfloat16)
-    k = torch.randn(pages, KV, P, hd, device=DEV).to(torch.bfloat16)
-    v = torch.randn(pages, KV, P, hd, device=DEV).to(torch.bfloat16)
+    q = torch.randn(T, H * hd, device=DEV).to(dtype)
+    k = torch.randn(pages, KV, P, hd, device=DEV).to(dtype)
+    v = torch.randn(pages, KV, P, hd, device=DEV).to(dtype)
     out = torch.empty_like(q)
     run = lambda: ops.paged_attention(q, k, v, out, meta, H, KV, hd, hd ** -0.5, None, P, kind=kind)
-    return run, sum(c + n for c, n in reqs) * KV * hd * 2 * 2
+    return run, sum(c + n for c, n in reqs) * KV * hd * 2 * q.element_size()
 
 
 def fused_decode_case(B, ctx_len, H=28, KV=4, hd=128, P=16):
@@ -125,6 +125,15 @@ def main():
             run, kv_bytes = attention_case([(2047, 1)] * B)
             t = timed(run, flush)
             print(f"attention decode B={B} ctx 2048: {t * 1e3:.1f} us, {kv_bytes / t / 1e6:.0f} GB/s")
+    if what in ("attn_f32", "all"):
+        # the float32 path's attention: decoded tokens of 8 requests, and a prompt of 2,048 tokens
+        run, kv_bytes = attention_case([(2047, 1)] * 8, kind="simple", dtype=torch.float32)
+        t = timed(run, flush)
+        print(f"float32 attention decode B=8 ctx 2048: {t * 1e3:.1f} us, {kv_bytes / t / 1e6:.0f} GB/s")
+        run, _ = attention_case([(0, 2048)], kind="simple", dtype=torch.float32)
+        t = timed(run, flush, n=3)
+        print(f"float32 attention prefill 2048 tokens: {t * 1e3:.1f} us, "
+              f"{2 * 2 * 28 * 128 * (2048 * 2049 // 2) / t / 1e9:.1f} TFLOP/s")
     if what in ("attn_fused", "all"):
         for B, ctx_len in ((1, 2048), (8, 2048), (8, 8192), (64, 2048)):
             run, kv_bytes, splits = fused_decode_case(B, ctx_len)
