@@ -23,7 +23,6 @@ constexpr int kBF16 = 1;                                 // dtype code of the ke
 constexpr int kOpN = 0, kOpT = 1;                        // cublasOperation_t
 constexpr int kR16BF = 14;                               // cudaDataType
 constexpr int kCompute32F = 68, kGemmDefaultTensorOp = 99;
-constexpr int kSkinnyMaxRows = 8;      // the same limit as the Python parts use
 }  // namespace
 
 struct PbeExecFns {
@@ -82,6 +81,7 @@ struct PbeStepDesc {
   int tc5_pages_ok;         // the page size suits the tcgen05 kernel
   int* tc5_err;
   void* cublas_handle;
+  int skinny_max_rows;      // steps of at most this many rows take the weight-streaming GEMM (the caller's rule)
 };
 
 namespace {
@@ -90,7 +90,7 @@ long long g_stage_calls[16];
 // y[T, N] = x[T, K] w[N, K]^T, bfloat16 in and out, float32 accumulation
 int linear(const PbeExecFns* fn, const PbeStepDesc* s, const void* x, const void* w, void* y, int T, int N, int K,
            stream_t stream) {
-  if (T <= kSkinnyMaxRows && (K & 7) == 0) return fn->gemm_skinny(x, w, nullptr, y, kBF16, T, N, K, 0, stream);
+  if (T <= s->skinny_max_rows && (K & 7) == 0) return fn->gemm_skinny(x, w, nullptr, y, kBF16, T, N, K, 0, stream);
   const float alpha = 1.0f, beta = 0.0f;
   // row-major y = x w^T is column-major y^T[N, T] = w^T-as-stored[K, N]^T x^T[K, T]
   const int rc = fn->cublas_gemm_ex(s->cublas_handle, kOpT, kOpN, N, T, K, &alpha, w, kR16BF, K, x, kR16BF, K, &beta, y,
@@ -163,7 +163,7 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
   // the output projection's result is what the second norm adds: it goes to delta_out first
   STAGE(6, linear(fn, s, s->attn, b->w_o, delta_out, T, d, H * hd, stream));
   STAGE(7, fn->add_rmsnorm(s->residual, delta_out, kBF16, b->norm2, s->x, kBF16, nullptr, T, d, b->eps2, stream));
-  if (T <= kSkinnyMaxRows && (d & 7) == 0) {
+  if (T <= s->skinny_max_rows && (d & 7) == 0) {
     STAGE(8, fn->gemm_skinny(s->x, b->w_gate_up, nullptr, s->act, kBF16, T, 2 * b->inter, d, 1, stream));
   } else {
     STAGE(8, linear(fn, s, s->x, b->w_gate_up, s->gate_up, T, 2 * b->inter, d, stream));

@@ -5,9 +5,11 @@
 // position p reads keys 0..p (or p-W+1..p under a window) from the pages its block table
 // names.  The rows of a request are packed with the query heads that share one key/value
 // head (row-major: packed = row * group + head_in_group), so the group's keys are read
-// once.  Long key ranges of short requests are cut into splits of a fixed number of keys;
-// the partial results are merged by attn_merge_kernel.  Split boundaries depend on the
-// request's own lengths only, never on what else is in the batch.
+// once.  Long key ranges of short requests are cut into splits of split_keys keys (the step
+// chooses 256 or 512 by its number of requests); the partial results are merged by
+// attn_merge_kernel.  Given the split size, the boundaries follow from the request's own
+// lengths; a request's result in steps of different sizes differs by the rounding of float32
+// sums taken in another order.
 //
 // It is the float32 path's attention and the checker for the tensor-core kernel.  It
 // stands where the reference runs paged_mha_kernel.cu:363-550 (decode) and

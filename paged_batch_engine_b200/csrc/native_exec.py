@@ -38,7 +38,8 @@ class StepDesc(ctypes.Structure):
                 ("slots", c_void_p), ("page_tokens", c_int), ("num_pages", c_int),
                 ("attn_params", ops.AttnParams), ("num_work", c_int), ("num_split_rows", c_int),
                 ("merge_params", ops.AttnMergeParams), ("fused_splits", c_int), ("decode_rows", c_int),
-                ("tc5_pages_ok", c_int), ("tc5_err", c_void_p), ("cublas_handle", c_void_p)]
+                ("tc5_pages_ok", c_int), ("tc5_err", c_void_p), ("cublas_handle", c_void_p),
+                ("skinny_max_rows", c_int)]
 
 
 def enabled() -> bool:
@@ -186,4 +187,5 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
         attn_params=ap, num_work=int(meta.num_work), num_split_rows=int(meta.num_split_rows), merge_params=mp,
         fused_splits=int(splits), decode_rows=int(meta.decode_rows),
         tc5_pages_ok=1 if use_tc5 and ops.tc5_attention_applies(hd, ctx.page_tokens) else 0,
-        tc5_err=err.data_ptr() if err is not None else None, cublas_handle=torch.cuda.current_blas_handle())
+        tc5_err=err.data_ptr() if err is not None else None, cublas_handle=torch.cuda.current_blas_handle(),
+        skinny_max_rows=int(ops.SKINNY_MAX_ROWS))

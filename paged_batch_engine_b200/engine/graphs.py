@@ -7,9 +7,11 @@ at fixed offsets, and replayed after a single host-to-device copy of that buffer
 beyond the live requests are padding: they write nothing to the cache, carry idle
 attention work items, and their logits are dropped.
 
-Split boundaries and the number of splits per request are the same as in eager steps (they
-follow from the request's own length), so a captured step returns what an eager step
-would.
+Split boundaries lie at multiples of the step's split size, which follows from the number of
+requests in the step (512 keys up to four requests, 256 beyond), and the fused decode kernel
+picks its cluster size from the step's size too: a request's logits therefore agree between
+a captured step, an eager step and steps of other sizes up to the rounding of float32 sums
+taken in another order, not bit for bit.
 """
 from __future__ import annotations
 
