@@ -97,6 +97,12 @@ def main():
             x = torch.randn(8, K, device=DEV).to(torch.bfloat16)
             t = timed(lambda: ops.gemm_skinny(x, w, None, torch.bfloat16, swiglu=sw), flush)
             print(f"gemm_skinny {name} M=8: {t * 1e3:.1f} us, {N * K * 2 / t / 1e6:.0f} GB/s")
+            for M in (1, 8, 16):        # the library GEMM and the kernel side by side, plain epilogue
+                xm = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+                tl = timed(lambda: torch.mm(xm, w.t()), flush)
+                ts = timed(lambda: ops.gemm_skinny(xm, w, None, torch.bfloat16), flush)
+                print(f"  {name} M={M}: library {tl * 1e3:.1f} us ({N * K * 2 / tl / 1e6:.0f} GB/s), "
+                      f"gemm_skinny {ts * 1e3:.1f} us ({N * K * 2 / ts / 1e6:.0f} GB/s)")
     if what in ("sgemm", "all"):
         # the float32 path's own GEMM: few rows stream the weights (GB/s), many rows multiply (TFLOP/s)
         for name, N, K in (("qkv", 4608, 3584), ("o", 3584, 3584), ("gate_up", 37888, 3584), ("down", 3584, 18944)):
