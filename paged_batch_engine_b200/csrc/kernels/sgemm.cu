@@ -449,8 +449,9 @@ int launch_skinny(const TX* X, const float* W, const float* bias, float* part, T
   return launch_status();
 }
 
-// 32 weight rows a task (four chunks in the ring); 64 (three chunks, half the activation reads per
-// product) is kept for matrices with very many tasks and is chosen by measurement, not by default
+// 32 weight rows a task.  (64 rows a task - two weight rows a lane, half the activation reads per
+// product, three chunks in the ring - measured no faster at any of the decode shapes and is not
+// instantiated; the kernel's NPER parameter is what it would take.)
 inline bool skinny_wide(int N, int K) {
   (void)N; (void)K;
   return false;
@@ -459,14 +460,9 @@ inline bool skinny_wide(int N, int K) {
 template <typename TX, typename TY>
 int skinny_dispatch(const TX* X, const float* W, const float* bias, float* part, TY* Y, int* tickets, int M, int N,
                     int K, int ldx, int ldy, bool vec, cudaStream_t stream) {
-  const bool wide = skinny_wide(N, K);
-#define SKINNY(MT)                                                                                                       \
-  do {                                                                                                                   \
-    if (wide) return vec ? launch_skinny<MT, 2, true, TX, TY>(X, W, bias, part, Y, tickets, M, N, K, ldx, ldy, stream)   \
-                         : launch_skinny<MT, 2, false, TX, TY>(X, W, bias, part, Y, tickets, M, N, K, ldx, ldy, stream); \
-    return vec ? launch_skinny<MT, 1, true, TX, TY>(X, W, bias, part, Y, tickets, M, N, K, ldx, ldy, stream)             \
-               : launch_skinny<MT, 1, false, TX, TY>(X, W, bias, part, Y, tickets, M, N, K, ldx, ldy, stream);           \
-  } while (0)
+#define SKINNY(MT)                                                                                             \
+  return vec ? launch_skinny<MT, 1, true, TX, TY>(X, W, bias, part, Y, tickets, M, N, K, ldx, ldy, stream)     \
+             : launch_skinny<MT, 1, false, TX, TY>(X, W, bias, part, Y, tickets, M, N, K, ldx, ldy, stream)
   if (M <= 4) SKINNY(4);
   if (M <= 8) SKINNY(8);
   SKINNY(16);
@@ -559,5 +555,5 @@ PBE_EXPORT int pbe_sgemm_nt(const void* X, int x_dtype, const float* W, const fl
     return sgemm_dispatch<bf16, bf16>((const bf16*)X, W, bias, (bf16*)Y, scratch, tickets, M, N, K, ldx, ldy, stream);
   if (x_dtype == PBE_BF16 && y_dtype == PBE_F32)
     return sgemm_dispatch<bf16, float>((const bf16*)X, W, bias, (float*)Y, scratch, tickets, M, N, K, ldx, ldy, stream);
-  return sgemm_dispatch<float, bf16>((const float*)X, W, bias, (bf16*)Y, scratch, tickets, M, N, K, ldx, ldy, stream);
+  return (int)cudaErrorInvalidValue;          // float32 rows in, bfloat16 rows out: nothing asks for it
 }

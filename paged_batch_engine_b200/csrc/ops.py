@@ -196,6 +196,8 @@ def sgemm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         raise KernelError("sgemm_nt: shapes or dtypes do not agree")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("sgemm_nt: bias must be float32 [N]")
+    if x.dtype == torch.float32 and out.dtype != torch.float32:
+        raise KernelError("sgemm_nt: float32 rows give float32 rows (bfloat16 rows give either)")
     need = _fn("sgemm", "pbe_sgemm_scratch_floats", [c_int, c_int, c_int, c_void_p])
     need.restype = c_ll
     n_tickets = c_int(0)

@@ -159,7 +159,7 @@ def test_sgemm_true_float32(M, N, K):
 
 def test_sgemm_rows_do_not_depend_on_the_batch():
     """One summation order for every output, whichever kernel computes it: the weight-streaming
-    kernel (up to 16 rows, 32 or 64 weight rows a task) and the tiled kernels (tiles of 32, 64
+    kernel (up to 16 rows) and the tiled kernels (tiles of 32, 64
     and 128 rows) give bitwise equal rows; K of 333 is no multiple of 4 (scalar copies), 1,100
     spans three K slices with a ragged last one."""
     torch.manual_seed(4)
@@ -176,7 +176,8 @@ def test_sgemm_rows_do_not_depend_on_the_batch():
 @pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 17, 40, 200])
 def test_sgemm_sizes_that_divide_nothing(M):
     """Rows, columns and depths that are multiples of no tile size, through both kernels; the
-    many-column case takes the weight-streaming kernel's 64-row tasks."""
+    large cases have many tasks a warp slot (weight-streaming kernel) and enough tiles for the
+    tiled kernel to keep its K slices in one block."""
     torch.manual_seed(M)
     big = [(19000, 4100)] if M <= 16 else [(300, 1030)] + ([(19000, 1100)] if M == 200 else [])
     for N, K in [(1, 7), (33, 516), (130, 36)] + big:
