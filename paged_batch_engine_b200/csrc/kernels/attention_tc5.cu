@@ -210,10 +210,14 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   unsigned char* Qs = base;                               // [KB][128 rows][128 B]
   unsigned char* Ks = Qs + Q_BYTES;                       // [NK stages][KB][128 keys][128 B]
   unsigned char* Vs = Ks + NK * KV_BYTES;                 // [NV stages][KB][128 keys][128 B]
-  __shared__ __align__(8) uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], p_full, o_ready;
+  __shared__ __align__(8) uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], p_full, o_ready, q_full;
   __shared__ uint32_t tmem_base_smem;
 
   pdl_wait();
+#ifdef PBE_TC5_SCHED   // a debugging build: every block records when it began, when its prologue ended and when it left
+  unsigned long long sched_t0 = 0;
+  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sched_t0));
+#endif
   const int KV = p.num_kv_heads;
   const int32_t* work = p.work + (size_t)(blockIdx.x / KV) * 4;
   const int r = work[0];
@@ -255,6 +259,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
     mbar_init(&p_full, 4);
     mbar_init(&o_ready, 1);
+    mbar_init(&q_full, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -263,6 +268,17 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                  ::"r"(smem_u32(&tmem_base_smem)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // Barriers and tensor memory are set up; the roles part here.  The key and value producers
+  // start fetching at once (they need the block table only), while the softmax warps copy the
+  // query tile; the MMA issuer waits for that copy (q_full) before its first product.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_smem;
+#ifdef PBE_TC5_SCHED
+  unsigned long long sched_t1 = 0;
+  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(sched_t1));
+#endif
   // the query tile: one packed row per softmax thread, into the swizzled K-major layout
   if (warp >= 2 && warp < 6) {
     const int row = (warp - 2) * 32 + lane;
@@ -272,17 +288,15 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       const int qrow = pr / G, hg = pr - qrow * G;
       src = (const bf16*)p.q + ((size_t)(qs + qrow) * H + kvh * G + hg) * HD;
     }
+    uint4 qv[HD / 8];
 #pragma unroll
-    for (int c = 0; c < HD / 8; ++c) {
-      const uint4 v = src ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(Qs + swz(row, c * 8, BM)) = v;
-    }
+    for (int c = 0; c < HD / 8; ++c) qv[c] = src ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) *reinterpret_cast<uint4*>(Qs + swz(row, c * 8, BM)) = qv[c];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the MMA's reads
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_full);
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_base_smem;
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------ TMA producers: keys (warp 0), values (warp 6)
@@ -342,6 +356,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         umma_commit(&k_empty[kst]);                           // the key tile is free once its scores exist
         umma_commit(&s_full[st]);
       };
+      ok = ok && mbar_wait(&q_full, 0, err);                  // the query tile is in shared memory
       // The S buffer of tile j holds P_j until its P V has read it; the scores of tile j + 2 go
       // to the same buffer and are issued after that P V: the tensor pipe runs them in order.
       issue_qk(0);
@@ -557,6 +572,20 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
+#ifdef PBE_TC5_SCHED
+  if (threadIdx.x == 0) {
+    unsigned long long t2;
+    unsigned smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    long long* rec = reinterpret_cast<long long*>(err + 1024) + (size_t)blockIdx.x * 5;
+    rec[0] = (long long)sched_t0;
+    rec[1] = (long long)sched_t1;
+    rec[2] = (long long)t2;
+    rec[3] = n_tiles;
+    rec[4] = smid;
+  }
+#endif
 }
 
 }  // namespace
