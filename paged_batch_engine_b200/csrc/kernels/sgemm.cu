@@ -222,12 +222,21 @@ sgemm_skinny_kernel(const TX* __restrict__ X, const float* __restrict__ W, const
     const int n = n0 + lane + 32 * j;
     if (n >= N) continue;
     const float b = bias ? bias[n] : 0.f;
-    for (int m = 0; m < M; ++m) {
-      float tot = __ldcg(&part[(size_t)m * N + n]);
-      for (int sl = 1; sl < num_slices; ++sl) tot += __ldcg(&part[((size_t)sl * M + m) * N + n]);
-      if (bias) tot += b;
-      Y[(size_t)m * ldy + n] = from_float<TY>(tot);
+    // every row's slices in slice order; the rows are independent chains, so a slice's loads for
+    // all rows are in flight together (one after the other they cost a memory latency each)
+    float tot[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) tot[m] = m < M ? __ldcg(&part[(size_t)m * N + n]) : 0.f;
+    for (int sl = 1; sl < num_slices; ++sl) {
+      float v[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) v[m] = m < M ? __ldcg(&part[((size_t)sl * M + m) * N + n]) : 0.f;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) tot[m] += v[m];
     }
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+      if (m < M) Y[(size_t)m * ldy + n] = from_float<TY>(bias ? tot[m] + b : tot[m]);
   }
 }
 
@@ -412,6 +421,29 @@ sgemm_tiled_kernel(const TX* __restrict__ X, const float* __restrict__ W, const 
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
+  // the slices in order; a thread's 64 outputs are independent chains, so a slice's loads are
+  // all in flight together
+  float tot[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) tot[i][j] = 0.f;
+  for (int s2 = 0; s2 < num_slices; ++s2) {
+    float v[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+      const int m = row_of(i);
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const int n = col_of(j);
+        v[i][j] = (m < M && n < N) ? __ldcg(&part[((size_t)s2 * M + m) * N + n]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) tot[i][j] = s2 == 0 ? v[i][j] : tot[i][j] + v[i][j];
+  }
 #pragma unroll
   for (int i = 0; i < TM; ++i) {
     const int m = row_of(i);
@@ -420,10 +452,9 @@ sgemm_tiled_kernel(const TX* __restrict__ X, const float* __restrict__ W, const 
     for (int j = 0; j < TN; ++j) {
       const int n = col_of(j);
       if (n >= N) continue;
-      float tot = __ldcg(&part[(size_t)m * N + n]);
-      for (int s2 = 1; s2 < num_slices; ++s2) tot += __ldcg(&part[((size_t)s2 * M + m) * N + n]);
-      if (bias) tot += bias[n];
-      Y[(size_t)m * ldy + n] = from_float<TY>(tot);
+      float out = tot[i][j];
+      if (bias) out += bias[n];
+      Y[(size_t)m * ldy + n] = from_float<TY>(out);
     }
   }
 }
