@@ -355,3 +355,26 @@ def test_a_wait_that_ran_out_stops_generation_with_an_error(tiny_folders):
     # the engine is usable afterwards and gives the same tokens
     again = eng.generate(prompts, sp)
     assert [r.output_tokens for r in again] == [r.output_tokens for r in good]
+
+
+def test_bfloat16_under_page_pressure_stays_plain_argmax(tiny_folders):
+    """bfloat16 with so few pages that requests are preempted and recomputed (through portions
+    of another size than the first time, beside other requests): every generated token is still
+    the plain implementation's greedy token up to rounding, and no page is lost."""
+    from paged_batch_engine_b200 import SamplingParams
+    cfg, _, page, _ = TINY["A"]
+    folder = tiny_folders["A"]
+    pcfg, w = load_plain(folder)
+    prompts = prompts_for(cfg["vocab_size"], [20, 25, 30, 18], seed=7)
+    eng = engine(folder, "bfloat16", page, num_pages=9)          # 144 tokens for 4 x (up to 70)
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=40, ignore_eos=True))
+    assert eng.scheduler.metrics["preemptions"] > 0 and any(r.preemptions for r in res)
+    for p, r in zip(prompts, res):
+        assert len(r.output_tokens) == 40 and r.finish_reason == "length"
+        seq = p + r.output_tokens
+        logits = plain.forward_logits(pcfg, w, seq[:-1])
+        for i, tok in enumerate(r.output_tokens):
+            row = logits[len(p) - 1 + i]
+            assert row.max() - row[tok] <= 0.02 * logits.abs().max(), (len(p), i)
+    eng.runner.cache.check_invariants()
+    assert eng.runner.cache.num_free_pages() == 9
