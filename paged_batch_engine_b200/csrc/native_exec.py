@@ -182,7 +182,7 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
         qkv=buf("qkv", (H + 2 * KV) * hd).data_ptr(), q=buf("q", H * hd).data_ptr(),
         attn=buf("attn", H * hd).data_ptr(),
         gate_up=buf("gate_up", 2 * f.intermediate_size).data_ptr() if big else None,
-        act=buf("act", f.intermediate_size).data_ptr(), positions=ctx.positions.data_ptr(),
+        act=buf("act", f.intermediate_size).data_ptr(), positions=ctx.position_ids.data_ptr(),
         slots=group.slots.data_ptr(), page_tokens=int(ctx.page_tokens), num_pages=int(cache.k.shape[0]),
         attn_params=ap, num_work=int(meta.num_work), num_split_rows=int(meta.num_split_rows), merge_params=mp,
         fused_splits=int(splits), decode_rows=int(meta.decode_rows),

@@ -48,6 +48,11 @@ class StepEntry:
     handle: int                 # the cache manager's request handle
     tokens: Sequence[int]       # the request's next tokens
     want: Sequence[int] = ()    # offsets among these tokens whose logits are wanted
+    # Position ids of these tokens for the position encoding, when they are not the tokens'
+    # places in the sequence: one integer per token, or a row of integers per token (an
+    # encoding with several axes).  None: the place in the sequence.  Where a token lies in the
+    # cache and what it may attend to always follow from its place in the sequence.
+    position_ids: Optional[Sequence] = None
 
 
 @dataclass
@@ -253,9 +258,20 @@ class StepContext:
                     raise ValueError(f"wanted place {w} is outside the entry's {int(q_len[r])} tokens")
                 want_rows.append(int(q_start[r]) + int(w))
         self.num_wanted = len(want_rows)
+        # explicit position ids (all entries or none): [T, axes]
+        given = [e.position_ids is not None for e in entries]
+        pos_ids = None
+        if any(given):
+            if not all(given):
+                raise ValueError("either every entry of a step brings position ids or none does")
+            rows_ = [np.asarray(e.position_ids, dtype=np.int64).reshape(len(e.tokens), -1) for e in entries]
+            if len({r_.shape[1] for r_ in rows_}) != 1:
+                raise ValueError("the entries' position ids differ in their number of axes")
+            pos_ids = np.concatenate(rows_, axis=0)
 
         pk = _Packer()
         i_tokens, i_pos = pk.add(tokens), pk.add(positions)
+        i_pos_ids = pk.add(pos_ids) if pos_ids is not None else None
         i_qs, i_ql, i_sl = pk.add(q_start), pk.add(q_len), pk.add(seq_len)
         i_want = pk.add(np.array(want_rows, dtype=np.int64))
         i_state = pk.add(self.state_slots_host)
@@ -284,6 +300,12 @@ class StepContext:
         self._packer = pk
         self.token_ids = pk.view(i_tokens)
         self.positions = pk.view(i_pos)
+        # what a position encoding is given: the explicit ids ([T] for one axis, [T, axes] for
+        # several), or the places in the sequence
+        self.position_ids = self.positions
+        if i_pos_ids is not None:
+            ids = pk.view(i_pos_ids)
+            self.position_ids = ids.reshape(-1) if ids.shape[1] == 1 else ids
         self.q_start, self.q_len, self.seq_len = pk.view(i_qs), pk.view(i_ql), pk.view(i_sl)
         self.want_rows = pk.view(i_want)
         self.state_slots = pk.view(i_state)

@@ -109,6 +109,7 @@ class DecodeStepContext(StepContext):
             o, shape = lay[name]
             return self.dev[o:o + int(np.prod(shape))].view(shape)
         self.token_ids, self.positions = view("tokens"), view("positions")
+        self.position_ids = self.positions          # captured steps take the places in the sequence
         self.q_start, self.q_len, self.seq_len = view("q_start"), view("q_len"), view("seq_len")
         self.want_rows, self.state_slots = view("want"), view("state")
         self._groups = [GroupArrays(view(f"bt{g}"), stride, view(f"slots{g}"))
@@ -216,7 +217,7 @@ class DecodeGraphs:
         self._capture_stream = None
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
-        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] and e.position_ids is None for e in entries):
             return False
         # a captured step is recorded once: a mixer that runs host logic per step (loops over the
         # requests, reads lengths on the host) cannot be in it; every mixer says which it is

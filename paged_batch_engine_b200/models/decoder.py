@@ -102,6 +102,8 @@ class DecoderModel:
         from ..csrc import native_exec
         if self.dtype != torch.bfloat16 or not native_exec.enabled() or getattr(ctx, "captured", False):
             return None
+        if ctx.position_ids.dim() != 1:        # several axes: only a position encoding of its own reads them
+            return None
         if self._native is None:
             descs = [native_exec.block_desc(b) for b in self.blocks]
             ok = all(d is not None for d in descs) and all(st.writes_cache for st in self.spec.run_order)

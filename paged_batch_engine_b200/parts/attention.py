@@ -117,10 +117,14 @@ class GQAttention(Mixer):
         if self.position.applies_itself:
             # a position encoding with code of its own: it gets q and k with the bias added and
             # the kernel below only copies (no rotation, no bias)
-            qkv, bias = self._apply_position(qkv, ctx.positions), None
+            qkv, bias = self._apply_position(qkv, ctx.position_ids), None
             inv_freq, rotary_dim, interleaved = None, 0, False
+            kernel_positions = ctx.positions          # the kernels below only copy
         else:
             inv_freq, rotary_dim, interleaved = self.position.kernel_args()
+            kernel_positions = ctx.position_ids
+        if ctx.position_ids.dim() != 1 and not self.position.applies_itself:
+            raise ValueError("position ids with several axes need a position encoding with code of its own")
         group = ctx.group(cache.group)
         k_pages, v_pages = cache.k, cache.v
         meta = ctx.attention_work(cache.group, H // KV, self.tile_rows, self.window, H, hd)
@@ -129,13 +133,13 @@ class GQAttention(Mixer):
             # decoded tokens only, every block of the step resident at once: position encoding, cache
             # write, attention and the merge of the key splits in one launch
             out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
-            ops.attention_decode_fused(qkv, bias, k_pages, v_pages, out, meta, ctx.positions, group.slots,
+            ops.attention_decode_fused(qkv, bias, k_pages, v_pages, out, meta, kernel_positions, group.slots,
                                        inv_freq, meta.decode_rows, H, KV, hd, self.scale, self.window,
                                        ctx.page_tokens, splits=splits)
             return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
         q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         ops.rope_kv_write(qkv, bias, q, k_pages if cache.writes else None,
-                          v_pages if cache.writes else None, ctx.positions, group.slots, inv_freq,
+                          v_pages if cache.writes else None, kernel_positions, group.slots, inv_freq,
                           H, KV, hd, rotary_dim, ctx.page_tokens, interleaved)
         out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         ops.paged_attention(q, k_pages, v_pages, out, meta, H, KV, hd, self.scale, self.window,

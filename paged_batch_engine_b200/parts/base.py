@@ -15,6 +15,9 @@ PositionEncoding: ``kernel_args() -> (inv_freq | None, rotary_dim, interleaved)`
             mixer that applies it; one that brings its own code sets ``applies_itself`` and has
             ``apply(q, k, positions) -> (q, k)`` on float32 [rows, heads, head_dim] tensors
             (projection bias already added); its tensors live under the mixer's prefix + "position.".
+            ``positions`` is int32 [rows]: the tokens' places in the sequence, or the position ids
+            the step's entries brought (``StepEntry.position_ids``), then [rows, axes] when they
+            have several axes.
 Mixer:      ``cache_need() -> KVNeed | PagedNeed | StateNeed | None`` (what it keeps between steps) and
             ``forward(x, ctx, cache) -> y`` over all rows of the step.
 FeedForward: ``forward(x, ctx) -> y``.

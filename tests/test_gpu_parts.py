@@ -760,3 +760,84 @@ def test_toy_compressed_cache_capturable_state_other_names_and_a_builder(dtype, 
     assert runner.graphs.eligible([StepEntry(0, [1], [0])]) == (not latent)
     assert (runner.graphs.replays > 0) == (not latent)
     runner.cache.check_invariants()
+
+
+# ------------------------------------------------------------------ position ids that are not the place in the sequence
+def make_toy_grid_position_class():
+    from paged_batch_engine_b200.parts import PositionEncoding
+    from paged_batch_engine_b200.weights import ParamSpec
+
+    class ToyGridPosition(PositionEncoding):
+        """Two axes of position ids (a row and a column, say): q and k get the learned vector of
+        each axis added.  The ids come with the step's entries, not from the place in the sequence."""
+        applies_itself = True
+
+        def __init__(self, head_dim, rows, cols, dtype, device):
+            self.hd, self.rows, self.cols = head_dim, rows, cols
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "row_table", (self.rows, self.hd)), ParamSpec(prefix + "col_table", (self.cols, self.hd))]
+
+        def load(self, tensors, prefix):
+            self.rt = tensors.pop(prefix + "row_table").float()
+            self.ct = tensors.pop(prefix + "col_table").float()
+
+        def apply(self, q, k, positions):
+            assert positions.dim() == 2 and positions.shape[1] == 2
+            add = (self.rt[positions[:, 0].long()] + self.ct[positions[:, 1].long()]).unsqueeze(1)
+            return q + add, k + add
+
+    return ToyGridPosition
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_position_ids_brought_by_the_entries(dtype):
+    """Position ids that a step's entries bring: two axes for a position encoding with code of
+    its own (defined here), and one axis for the rotary kernel (ids shifted against the place in
+    the sequence).  The cache and the causal mask still go by the place in the sequence."""
+    from paged_batch_engine_b200.config import PartSpec
+    from paged_batch_engine_b200.cache.storage import CacheStorage
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    from paged_batch_engine_b200.parts import build_part, register_part
+    register_part("position", "toy_grid", make_toy_grid_position_class(), replace=True)
+    torch.manual_seed(3)
+    d, H, KV, hd, T, P = 64, 4, 2, 32, 37, 8
+    cfg = dict(num_attention_heads=H, num_key_value_heads=KV, head_dim=hd, hidden_size=d, rope_theta=900.0)
+    tol = 3e-5 if dtype == torch.float32 else 0.04
+    x = torch.randn(T, d).to(dtype)
+    for kind in ("grid", "shifted"):
+        position = PartSpec("toy_grid", dict(head_dim=hd, rows=8, cols=5)) if kind == "grid" else \
+            PartSpec("rope", dict(theta=900.0, head_dim=hd))
+        att = build_part("mixer", PartSpec("attention", dict(hidden_size=d, num_heads=H, num_kv_heads=KV, head_dim=hd,
+                                                             position=position)), dtype, DEV)
+        w = {p.name: (torch.randn(p.shape) * (0.3 if len(p.shape) > 1 else 0.1)).to(dtype if len(p.shape) > 1 else torch.float32)
+             for p in att.param_specs("a.")}
+        att.load({k: v.to(DEV) for k, v in w.items()}, "a.")
+        wf = {k: v.float() for k, v in w.items()}
+        if kind == "grid":
+            ids = torch.stack([torch.arange(T) // 5, torch.arange(T) % 5], dim=1)
+            q = plain.linear(x.float(), wf["a.q_proj.weight"], wf["a.q_proj.bias"]).view(T, H, hd)
+            k = plain.linear(x.float(), wf["a.k_proj.weight"], wf["a.k_proj.bias"]).view(T, KV, hd)
+            v = plain.linear(x.float(), wf["a.v_proj.weight"], wf["a.v_proj.bias"]).view(T, KV, hd)
+            add = (wf["a.position.row_table"][ids[:, 0]] + wf["a.position.col_table"][ids[:, 1]]).unsqueeze(1)
+            o = plain.causal_attention(q + add, k + add, v, hd ** -0.5)
+            want = plain.linear(o.reshape(T, H * hd), wf["a.o_proj.weight"])
+        else:
+            ids = torch.arange(T) + 100 + (torch.arange(T) // 9) * 3          # neither the place nor a plain shift
+            want = plain.attention_block(x.float(), ids, wf, "a.", cfg, None)
+        storage = CacheStorage([att.cache_need()], P, 8, 2, dtype, torch.device(DEV), poison=True)
+        keys = [(0,) + kk for kk in att.work_keys()]
+        for cuts in ([T], [11, 2, 19] + [1] * 5):
+            hnd = storage.manager.add_request()
+            outs, i = [], 0
+            for n in cuts:
+                assert storage.manager.reserve(hnd, n)
+                ctx = _ctx(storage.manager, [StepEntry(hnd, [0] * n, position_ids=ids[i:i + n].tolist())], keys)
+                assert ctx.position_ids.shape == ((n, 2) if kind == "grid" else (n,))
+                assert ctx.positions.tolist() == list(range(i, i + n))
+                outs.append(att.forward(x[i:i + n].to(DEV), ctx, storage.layer(0)).float().cpu())
+                storage.manager.commit(hnd, n)
+                i += n
+            storage.manager.free(hnd)
+            got = torch.cat(outs)
+            assert (got - want).abs().max() <= tol * max(1.0, want.abs().max()), (kind, cuts)
