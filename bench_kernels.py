@@ -2,7 +2,7 @@
 """Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
 each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
 
-    python bench_kernels.py [skinny|sgemm|attn_decode|attn_f32|attn_fused|attn_prefill|tc5|sample|all] [--once]
+    python bench_kernels.py [skinny|sgemm|attn_decode|attn_f32|attn_fused|attn_prefill|tc5|tc5_shapes|sample|all] [--once]
 
 Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
 buffer is written between launches, so every launch starts with a cold L2)."""
@@ -160,6 +160,24 @@ def main():
         print(f"gemm_tc5 gate_up+SwiGLU M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
         t = timed(lambda: torch.mm(x, w.t()), flush)
         print(f"library GEMM gate_up M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
+        del w, x
+    if what == "tc5_shapes":
+        # gemm_tc5 beside the library over the prompt shapes of the 7B model; the fused SwiGLU
+        # epilogue against the library GEMM followed by the silu_mul kernel
+        for M in (256, 512, 1024, 2048, 4096, 8192):
+            for name, N, K, sw in (("qkv", 4608, 3584, False), ("o", 3584, 3584, False),
+                                   ("gate_up", 37888, 3584, True), ("down", 3584, 18944, False)):
+                w = (torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16)
+                x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+                t = timed(lambda: ops.gemm_tc5(x, w, torch.bfloat16, swiglu=sw), flush)
+                if sw:
+                    act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+                    tl = timed(lambda: ops.silu_mul(torch.mm(x, w.t()), act), flush)
+                else:
+                    tl = timed(lambda: torch.mm(x, w.t()), flush)
+                print(f"M={M} {name}: gemm_tc5 {t * 1e3:.1f} us, {2 * M * N * K / t / 1e9:.0f} TFLOP/s; "
+                      f"library{' + silu_mul' if sw else ''} {tl * 1e3:.1f} us")
+                del w
     if what in ("sample", "all"):
         V = 152064
         for B in (1, 8, 64, 256):

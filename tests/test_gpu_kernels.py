@@ -592,7 +592,9 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch():
 
 # ------------------------------------------------------------------ tcgen05 GEMM for many rows
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 256, 64), (300, 1000, 200), (2048, 4608, 3584),
-                                   (129, 520, 1000), (640, 3584, 18944)])
+                                   (129, 520, 1000), (640, 3584, 18944),
+                                   (8192, 4096, 64),      # seven tiles a pair of blocks: both accumulators reused
+                                   (4100, 2300, 136)])    # ragged in rows, columns and K with two-SM tiles
 def test_gemm_tc5(M, N, K):
     torch.manual_seed(M + N)
     x = torch.randn(M, K).to(torch.bfloat16).to(DEV)
