@@ -354,8 +354,11 @@ def main():
         # (3) whole workloads through the scheduler at two further model shapes
         import bench_serving
         for name, key in (("1.5b", "serve_1p5b_64req"), ("14b", "serve_14b_8x8192")):
-            line = bench_serving.run_workload(name)
+            # one untimed round first, as the reference's benchmark app runs with --warmup-rounds=1;
+            # that round's own rate (every decode graph captured inside it) is kept beside it
+            line = bench_serving.run_workload(name, warmup_rounds=1)
             points[f"{key}_tok_s"] = line["value"]
+            points[f"{key}_first_round_tok_s"] = line["first_round_value"]
             points[f"{key}_wall_s"] = line["wall_s"]
             points[f"{key}_ttft_p50_ms"] = line["ttft_p50_ms"]
             points[f"{key}_gap_p50_ms"] = line["token_gap_p50_ms"]
