@@ -297,7 +297,7 @@ def main():
     }
     if not args.no_points:
         points = {}
-        for b in (1, 64):
+        for b in (1, 16, 64):
             ms_b, ms_b_e2e, _ = decode_point(b)
             points[f"decode_b{b}"] = round(b * 1e3 / ms_b, 2)
             points[f"decode_b{b}_e2e"] = round(b * 1e3 / ms_b_e2e, 2)

@@ -2,7 +2,7 @@
 """Runs the engine's hot kernels alone on the shapes of the Qwen2.5-7B layer, a few launches
 each, so that one of them can be captured with ncu (`-k regex:<name>`) or timed.
 
-    python bench_kernels.py [skinny|sgemm|attn_decode|attn_f32|attn_fused|attn_prefill|tc5|tc5_shapes|sample|all] [--once]
+    python bench_kernels.py [skinny|sgemm|attn_decode|attn_f32|attn_fused|attn_prefill|tc5|tc5_shapes|stream|sample|all] [--once]
 
 Prints the median CUDA-event time and the achieved GB/s or TFLOP/s of each case (a 256 MiB
 buffer is written between launches, so every launch starts with a cold L2)."""
@@ -161,6 +161,27 @@ def main():
         t = timed(lambda: torch.mm(x, w.t()), flush)
         print(f"library GEMM gate_up M=2048: {t * 1e3:.1f} us, {2 * 2048 * 37888 * 3584 / t / 1e9:.0f} TFLOP/s")
         del w, x
+    if what in ("stream", "all"):
+        # gemm_stream (tcgen05, weights as the streamed operand) beside the library GEMM (followed by
+        # silu_mul for gate/up) and gemm_skinny, decode shapes of the 7B model, 8 to 64 rows
+        for name, N, K, sw in (("qkv", 4608, 3584, False), ("o", 3584, 3584, False), ("gate_up", 37888, 3584, True),
+                               ("down", 3584, 18944, False)):
+            w = (torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16)
+            for M in (8, 16, 32, 64):
+                x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+                t = timed(lambda: ops.gemm_stream(x, w, torch.bfloat16, swiglu=sw), flush)
+                if sw:
+                    act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+                    tl = timed(lambda: ops.silu_mul(torch.mm(x, w.t()), act), flush)
+                else:
+                    tl = timed(lambda: torch.mm(x, w.t()), flush)
+                row = f"gemm_stream {name} M={M}: {t * 1e3:.1f} us ({N * K * 2 / t / 1e6:.0f} GB/s); " \
+                      f"library{' + silu_mul' if sw else ''} {tl * 1e3:.1f} us"
+                if M <= 16:
+                    ts = timed(lambda: ops.gemm_skinny(x, w, None, torch.bfloat16, swiglu=sw), flush)
+                    row += f"; gemm_skinny {ts * 1e3:.1f} us"
+                print(row)
+            del w
     if what == "tc5_shapes":
         # gemm_tc5 beside the library over the prompt shapes of the 7B model; the fused SwiGLU
         # epilogue against the library GEMM followed by the silu_mul kernel

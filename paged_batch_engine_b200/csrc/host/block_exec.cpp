@@ -42,6 +42,8 @@ struct PbeExecFns {
   int (*cublas_gemm_ex)(void* handle, int transa, int transb, int m, int n, int k, const void* alpha, const void* A,
                         int a_type, int lda, const void* B, int b_type, int ldb, const void* beta, void* C, int c_type,
                         int ldc, int compute_type, int algo);
+  int (*gemm_stream)(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int mode, float* scratch,
+                     int* tickets, int* err, stream_t stream);
 };
 
 // What does not change from step to step: one per layer.
@@ -82,15 +84,26 @@ struct PbeStepDesc {
   int* tc5_err;
   void* cublas_handle;
   int skinny_max_rows;      // steps of at most this many rows take the weight-streaming GEMM (the caller's rule)
+  // steps of more rows than that and at most stream_max_rows take the tcgen05 weight-streaming
+  // GEMM for the projections whose bit is set (1 QKV, 2 output, 4 gate/up with SwiGLU, 8 down)
+  int stream_max_rows, stream_mask;
+  float* stream_scratch;
+  int* stream_tickets;
+  int* stream_err;
 };
 
 namespace {
 double g_stage_ns[16];        // host time spent in each stage's launcher (two clock reads a stage: tens of ns)
 long long g_stage_calls[16];
 // y[T, N] = x[T, K] w[N, K]^T, bfloat16 in and out, float32 accumulation
-int linear(const PbeExecFns* fn, const PbeStepDesc* s, const void* x, const void* w, void* y, int T, int N, int K,
-           stream_t stream) {
+bool streams(const PbeStepDesc* s, int bit, int T, int K) {
+  return T > s->skinny_max_rows && T <= s->stream_max_rows && (s->stream_mask & bit) != 0 && (K & 7) == 0;
+}
+int linear(const PbeExecFns* fn, const PbeStepDesc* s, int bit, const void* x, const void* w, void* y, int T, int N,
+           int K, stream_t stream) {
   if (T <= s->skinny_max_rows && (K & 7) == 0) return fn->gemm_skinny(x, w, nullptr, y, kBF16, T, N, K, 0, stream);
+  if (streams(s, bit, T, K))
+    return fn->gemm_stream(x, w, y, kBF16, T, N, K, 0, s->stream_scratch, s->stream_tickets, s->stream_err, stream);
   const float alpha = 1.0f, beta = 0.0f;
   // row-major y = x w^T is column-major y^T[N, T] = w^T-as-stored[K, N]^T x^T[K, T]
   const int rc = fn->cublas_gemm_ex(s->cublas_handle, kOpT, kOpN, N, T, K, &alpha, w, kR16BF, K, x, kR16BF, K, &beta, y,
@@ -119,7 +132,7 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
     ++launches;                                                                                     \
   } while (0)
   STAGE(1, fn->add_rmsnorm(s->residual, delta_in, kBF16, b->norm1, s->x, kBF16, nullptr, T, d, b->eps1, stream));
-  STAGE(2, linear(fn, s, s->x, b->w_qkv, s->qkv, T, (H + 2 * KV) * hd, d, stream));
+  STAGE(2, linear(fn, s, 1, s->x, b->w_qkv, s->qkv, T, (H + 2 * KV) * hd, d, stream));
   AttnParams ap = s->attn_params;
   ap.k_cache = k_cache;
   ap.v_cache = v_cache;
@@ -161,15 +174,18 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
     }
   }
   // the output projection's result is what the second norm adds: it goes to delta_out first
-  STAGE(6, linear(fn, s, s->attn, b->w_o, delta_out, T, d, H * hd, stream));
+  STAGE(6, linear(fn, s, 2, s->attn, b->w_o, delta_out, T, d, H * hd, stream));
   STAGE(7, fn->add_rmsnorm(s->residual, delta_out, kBF16, b->norm2, s->x, kBF16, nullptr, T, d, b->eps2, stream));
   if (T <= s->skinny_max_rows && (d & 7) == 0) {
     STAGE(8, fn->gemm_skinny(s->x, b->w_gate_up, nullptr, s->act, kBF16, T, 2 * b->inter, d, 1, stream));
+  } else if (streams(s, 4, T, d)) {
+    STAGE(8, fn->gemm_stream(s->x, b->w_gate_up, s->act, kBF16, T, 2 * b->inter, d, 1, s->stream_scratch,
+                             s->stream_tickets, s->stream_err, stream));
   } else {
-    STAGE(8, linear(fn, s, s->x, b->w_gate_up, s->gate_up, T, 2 * b->inter, d, stream));
+    STAGE(8, linear(fn, s, 0, s->x, b->w_gate_up, s->gate_up, T, 2 * b->inter, d, stream));
     STAGE(9, fn->silu_mul(s->gate_up, s->act, kBF16, T, b->inter, stream));
   }
-  STAGE(10, linear(fn, s, s->act, b->w_down, delta_out, T, d, b->inter, stream));
+  STAGE(10, linear(fn, s, 8, s->act, b->w_down, delta_out, T, d, b->inter, stream));
 #undef STAGE
   return launches;
 }

@@ -22,7 +22,8 @@ from .build import load_host_library, load_library
 
 class ExecFns(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in ("add_rmsnorm", "rope_kv_write", "gemm_skinny", "silu_mul", "attn_mma",
-                                        "attn_tc5", "attn_merge", "attn_decode_fused", "cublas_gemm_ex")]
+                                        "attn_tc5", "attn_merge", "attn_decode_fused", "cublas_gemm_ex",
+                                        "gemm_stream")]
 
 
 class BlockDesc(ctypes.Structure):
@@ -39,7 +40,8 @@ class StepDesc(ctypes.Structure):
                 ("attn_params", ops.AttnParams), ("num_work", c_int), ("num_split_rows", c_int),
                 ("merge_params", ops.AttnMergeParams), ("fused_splits", c_int), ("decode_rows", c_int),
                 ("tc5_pages_ok", c_int), ("tc5_err", c_void_p), ("cublas_handle", c_void_p),
-                ("skinny_max_rows", c_int)]
+                ("skinny_max_rows", c_int), ("stream_max_rows", c_int), ("stream_mask", c_int),
+                ("stream_scratch", c_void_p), ("stream_tickets", c_void_p), ("stream_err", c_void_p)]
 
 
 def enabled() -> bool:
@@ -71,7 +73,8 @@ def exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
                     attn_mma=_addr(mma.pbe_attn_mma),
                     attn_tc5=_addr(load_library("attention_tc5", defines).pbe_attn_tc5) if use_tc5 else None,
                     attn_merge=_addr(simple.pbe_attn_merge), attn_decode_fused=_addr(mma.pbe_attn_decode_fused),
-                    cublas_gemm_ex=_addr(cublas.cublasGemmEx))
+                    cublas_gemm_ex=_addr(cublas.cublasGemmEx),
+                    gemm_stream=_addr(load_library("gemm_stream").pbe_gemm_stream) if ops.STREAM_MASK else None)
         _fns[key] = f
     return f
 
@@ -144,6 +147,14 @@ def block_desc(block) -> Optional[BlockDesc]:
                      window=int(m.window or 0), use_tc5=1 if m.kernel_kind == "tc5" else 0)
 
 
+def _stream_fields(dev) -> dict:
+    if not ops.STREAM_MASK:
+        return dict(stream_max_rows=0, stream_mask=0, stream_scratch=None, stream_tickets=None, stream_err=None)
+    scratch, tickets, err = ops.gemm_stream_buffers(dev)
+    return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS if ops.STREAM_MASK else 0), stream_mask=int(ops.STREAM_MASK),
+                stream_scratch=scratch.data_ptr(), stream_tickets=tickets.data_ptr(), stream_err=err.data_ptr())
+
+
 def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepDesc:
     """A step's descriptor for the layers that share ``block``'s attention work list.  ``buffers``
     keeps the step's workspaces (allocated on first use, shared by all layers)."""
@@ -188,4 +199,4 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
         fused_splits=int(splits), decode_rows=int(meta.decode_rows),
         tc5_pages_ok=1 if use_tc5 and ops.tc5_attention_applies(hd, ctx.page_tokens) else 0,
         tc5_err=err.data_ptr() if err is not None else None, cublas_handle=torch.cuda.current_blas_handle(),
-        skinny_max_rows=int(ops.SKINNY_MAX_ROWS))
+        skinny_max_rows=int(ops.SKINNY_MAX_ROWS), **_stream_fields(dev))

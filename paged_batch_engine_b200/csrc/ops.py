@@ -222,7 +222,7 @@ def sgemm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
 _sgemm_tickets = {}      # per device: zeroed int32 tickets shared by the float32 products of the stream
 
 
-SKINNY_MAX_ROWS = 8      # batches of at most this many rows take the weight-streaming kernel (0: never); with 9 to
+SKINNY_MAX_ROWS = int(os.environ.get('PBE_SKINNY_ROWS', '8'))      # batches of at most this many rows take the weight-streaming kernel (0: never); with 9 to
                          # 16 rows its two-tile instance loses to the library GEMM (4.39 against 3.48 ms a step)
 
 
@@ -285,6 +285,71 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] 
     return out
 
 
+_stream_state = {}     # per device: (scratch floats, zeroed tickets) of the K-split products
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                swiglu: bool = False, check: bool = False) -> torch.Tensor:
+    """y = x w^T for up to 64 rows on the tcgen05 tensor cores with the weights as the streamed
+    operand (TMA-fed ring, accumulator in tensor memory, K split over blocks where the matrix has
+    few rows).  ``swiglu``: w is [gate; up] stacked and y = silu(x gate^T) * (x up^T), [M, N/2].
+    ``check`` synchronises and raises if a bounded wait inside the kernel ran out."""
+    _need_cuda(x, w)
+    _need_contiguous(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError("gemm_stream takes bfloat16 x [M, K] and w [N, K]")
+    if M > STREAM_KERNEL_ROWS or K % 8 != 0:
+        raise KernelError(f"gemm_stream takes at most {STREAM_KERNEL_ROWS} rows and K a multiple of 8 (got M={M}, K={K})")
+    out_dtype = out_dtype or torch.bfloat16
+    if swiglu and (N % 2 or out_dtype != torch.bfloat16):
+        raise KernelError("gemm_stream: the SwiGLU epilogue needs an even N and bfloat16 output")
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    scratch, tickets, err = gemm_stream_buffers(x.device)
+    fn = _fn("gemm_stream", "pbe_gemm_stream",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _ptr(out), _dtype_code(out), M, N, K, 1 if swiglu else 0, _ptr(scratch), _ptr(tickets),
+              _ptr(err), _stream()), "gemm_stream")
+    if check and int(err.item()) != 0:
+        err.zero_()
+        raise KernelError("gemm_stream: a wait inside the kernel ran out; the result is invalid")
+    return out
+
+
+def gemm_stream_buffers(device):
+    """(scratch, tickets, flag) of ``gemm_stream`` on this device, made on first use: partial tiles
+    of at most one block a multiprocessor (128 weight rows x 64 batch rows of float32, twice that
+    for gate and up), the tiles' tickets, zeroed once and left at zero by every launch, and the flag
+    that a bounded wait sets."""
+    device = torch.device(device)
+    st = _stream_state.get(device)
+    if st is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        st = _stream_state[device] = (torch.empty(sms * 128 * 128, dtype=torch.float32, device=device),
+                                      torch.zeros(1024, dtype=torch.int32, device=device))
+    err = _tc5_err.get(device)
+    if err is None:
+        err = _tc5_err[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return st[0], st[1], err
+
+
+# Steps of more rows than the skinny kernel takes and at most STREAM_MAX_ROWS send the projections
+# whose bit is set in STREAM_MASK through gemm_stream (1 QKV, 2 output, 4 gate/up with SwiGLU, 8
+# down, 16 LM head and others).  Measured in the captured decode step of the 7B shape against the
+# library GEMM (and silu_mul): 16 rows 3.52 -> 3.37 ms with gate/up and down, 3.40 with all four;
+# 24 and 32 rows level; 64 rows 4.58 -> 4.77 ms.  So: gate/up and down, up to 16 rows.  The kernel
+# itself takes up to 64; PBE_STREAM (mask, 0: never) and PBE_STREAM_ROWS override the choice.
+STREAM_KERNEL_ROWS = 64
+STREAM_MAX_ROWS = int(os.environ.get("PBE_STREAM_ROWS", "16"))
+STREAM_MASK = int(os.environ.get("PBE_STREAM", "12"))
+
+
+def stream_applies(x: torch.Tensor, w: torch.Tensor, bit: int) -> bool:
+    return (STREAM_MASK & bit != 0 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS and x.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0)
+
+
 # Projections of many rows: the vendor GEMM library by default (it runs two-SM tiles and is
 # the faster one); PBE_GEMM=tc5 in the environment sends them through gemm_tc5 instead.
 TC5_MIN_ROWS = 128 if os.environ.get("PBE_GEMM", "") == "tc5" else 0     # 0: never
@@ -299,7 +364,8 @@ def gemm_libraries(dtype: torch.dtype):
     """The matrix-product libraries a model of this dtype launches (for parallel builds)."""
     if dtype == torch.float32:
         return [("sgemm", None)]
-    return [("gemm_skinny", None)] + ([("gemm_tc5", None)] if TC5_MIN_ROWS > 0 else [])
+    return [("gemm_skinny", None)] + ([("gemm_stream", None)] if STREAM_MASK else []) + \
+        ([("gemm_tc5", None)] if TC5_MIN_ROWS > 0 else [])
 
 
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -308,10 +374,11 @@ def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, kind: int = 16) -> torch.Tensor:
     """y = x w^T (+ b).  A float32 weight takes the true-float32 kernel of this package; a
-    bfloat16 weight takes the vendor GEMM library with float32 accumulation, as the
-    reference does for every projection (matmul_kernel_batch.cu:39-208)."""
+    bfloat16 weight takes the package's weight-streaming kernels for few rows and otherwise the
+    vendor GEMM library with float32 accumulation, as the reference does for every projection
+    (matmul_kernel_batch.cu:39-208).  ``kind``: which projection this is, a bit of STREAM_MASK."""
     _need_cuda(x, w, bias)
     out_dtype = out_dtype or x.dtype
     if w.dtype == torch.float32:
@@ -321,6 +388,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         raise KernelError("a bfloat16 weight takes bfloat16 activations")
     if skinny_applies(x, w):
         return gemm_skinny(x, w, bias, out_dtype)
+    if bias is None and stream_applies(x, w, kind):
+        return gemm_stream(x, w, out_dtype)
     if tc5_applies(x, w) and bias is None:
         return gemm_tc5(x, w, out_dtype)
     if out_dtype == torch.float32:

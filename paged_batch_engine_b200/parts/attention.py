@@ -112,7 +112,7 @@ class GQAttention(Mixer):
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = ops.linear(x, self.w_qkv, None, out_dtype=self.dtype)
+        qkv = ops.linear(x, self.w_qkv, None, out_dtype=self.dtype, kind=1)
         bias = self.b_qkv
         if self.position.applies_itself:
             # a position encoding with code of its own: it gets q and k with the bias added and
@@ -136,7 +136,7 @@ class GQAttention(Mixer):
             ops.attention_decode_fused(qkv, bias, k_pages, v_pages, out, meta, kernel_positions, group.slots,
                                        inv_freq, meta.decode_rows, H, KV, hd, self.scale, self.window,
                                        ctx.page_tokens, splits=splits)
-            return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
+            return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype, kind=2)
         q = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         ops.rope_kv_write(qkv, bias, q, k_pages if cache.writes else None,
                           v_pages if cache.writes else None, kernel_positions, group.slots, inv_freq,
@@ -144,7 +144,7 @@ class GQAttention(Mixer):
         out = torch.empty((T, H * hd), dtype=self.dtype, device=x.device)
         ops.paged_attention(q, k_pages, v_pages, out, meta, H, KV, hd, self.scale, self.window,
                             ctx.page_tokens, kind=self.kernel_kind)
-        return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype)
+        return ops.linear(out, self.w_o, self.b_o, out_dtype=self.dtype, kind=2)
 
 
 register_part("mixer", "attention", GQAttention, replace=True)

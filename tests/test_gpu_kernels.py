@@ -613,6 +613,42 @@ def test_gemm_tc5(M, N, K):
         assert (act - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
 
 
+# ------------------------------------------------------------------ tcgen05 weight-streaming GEMM, up to 64 rows
+@pytest.mark.parametrize("M,N,K", [(64, 256, 128), (1, 128, 64), (9, 1000, 200), (16, 4608, 3584), (33, 3584, 18944),
+                                   (64, 37888, 3584),     # one tile a block, SwiGLU over 148 tiles
+                                   (48, 152064, 512),     # several tiles a block: both accumulators reused
+                                   (17, 520, 1000), (8, 1536, 8960)])
+def test_gemm_stream(M, N, K):
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).to(DEV)
+    want = (x.double() @ w.double().t())
+    scale = want.abs().max().item()
+    got = ops().gemm_stream(x, w, torch.float32, check=True).double()
+    assert got.shape == (M, N)
+    assert (got - want).abs().max().item() <= 2e-5 * scale * math.sqrt(K) / 8 + 1e-6     # float32 accumulation
+    again = ops().gemm_stream(x, w, torch.float32, check=True).double()
+    assert torch.equal(got, again)                       # the split sums are added in a fixed order
+    gotb = ops().gemm_stream(x, w, torch.bfloat16, check=True).double()
+    assert (gotb - want).abs().max().item() <= 2 ** -8 * scale
+    if N % 2 == 0:
+        act = ops().gemm_stream(x, w, torch.bfloat16, swiglu=True, check=True).float().cpu()
+        ref = plain.swiglu(want[:, :N // 2].float().cpu(), want[:, N // 2:].float().cpu())
+        assert act.shape == (M, N // 2)
+        assert (act - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
+
+
+def test_gemm_stream_rows_do_not_depend_on_the_batch():
+    """A row's outputs are the same bits whether it comes alone or among 63 others."""
+    torch.manual_seed(5)
+    x = torch.randn(64, 3584).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(3584, 3584) * 0.05).to(torch.bfloat16).to(DEV)
+    full = ops().gemm_stream(x, w, torch.float32, check=True)
+    for lo, hi in ((0, 1), (5, 14), (20, 53)):
+        part = ops().gemm_stream(x[lo:hi].contiguous(), w, torch.float32, check=True)
+        assert torch.equal(part, full[lo:hi])
+
+
 @pytest.mark.parametrize("H,KV,hd,P,window,ctxs", [
     (28, 4, 128, 16, None, [2047, 300, 0, 1, 255, 256, 257, 4000]),
     (6, 3, 48, 8, 40, [0, 5, 39, 40, 41, 100, 700]),

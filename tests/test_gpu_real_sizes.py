@@ -40,7 +40,8 @@ TOL_BF16_REL = 0.02
 def real_model(tmp_path_factory):
     folder = make_model_folder(tmp_path_factory.mktemp("real_sizes"), REAL, seed=11, sharpen=1.0)
     g = torch.Generator().manual_seed(17)
-    lens = {"main": 340, "s0": 21, "s1": 58, "s2": 45, "s3": 33}
+    lens = {"main": 340, "s0": 21, "s1": 58, "s2": 45, "s3": 33, "t0": 19, "t1": 27, "t2": 16, "t3": 30, "t4": 24,
+            "t5": 18}
     reqs = {k: torch.randint(0, REAL["vocab_size"], (n,), generator=g).tolist() for k, n in lens.items()}
     cfg, w = load_plain(folder)
     with torch.no_grad():
@@ -67,7 +68,7 @@ def test_layers_of_real_size_agree_with_plain(real_model, dtype):
     from paged_batch_engine_b200.engine.runner import ModelRunner
     folder, reqs, want = real_model
     runner = ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_tokens=PAGE,
-                                     max_cache_tokens=1024, max_requests=8, poison=True)
+                                     max_cache_tokens=2048, max_requests=16, poison=True)
     main = {"main": reqs["main"]}
     # whole; in portions of changing size with the last 40 tokens one by one, eagerly; the same
     # with the single tokens through captured steps
@@ -84,10 +85,19 @@ def test_layers_of_real_size_agree_with_plain(real_model, dtype):
         assert len(got["main"]) == 340 and rp.graph_steps == (40 if captured else 0)
         _check(got, want, dtype, "portions + 40 decoded" + (" (captured)" if captured else ""))
     # five requests decoding together (five rows in a captured step of eight)
-    recs = ru.batch_decode(reqs, decode_tokens=10, prefill_group=3, portion=200)
+    five = {k: reqs[k] for k in ("main", "s0", "s1", "s2", "s3")}
+    recs = ru.batch_decode(five, decode_tokens=10, prefill_group=3, portion=200)
     rp = TraceReplayer(runner, decode_graphs=True, device_tokens=True)
     got = ru.run_records(runner, recs, replayer=rp)
     assert rp.graph_steps == 10 and 8 in {b for b, _ in runner.graphs.graphs}
     _check(got, want, dtype, "five requests, captured")
+    # eleven together, eagerly and captured (a step of sixteen rows): in bfloat16 the gate/up and
+    # down projections of such a step are the tcgen05 weight-streaming kernel's
+    for captured in (False, True):
+        recs = ru.batch_decode(reqs, decode_tokens=6, prefill_group=4, portion=200)
+        rp = TraceReplayer(runner, decode_graphs=captured, device_tokens=captured)
+        got = ru.run_records(runner, recs, replayer=rp)
+        assert not captured or (rp.graph_steps == 6 and 16 in {b for b, _ in runner.graphs.graphs})
+        _check(got, want, dtype, "eleven requests" + (", captured" if captured else ""))
     runner.cache.check_invariants()
     assert runner.cache.num_live_requests == 0

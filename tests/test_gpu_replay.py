@@ -260,7 +260,7 @@ def test_captured_decode_steps_agree_with_plain(tiny_folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,count,rows", [("A", 5, 8), ("B", 20, 24), ("C", 33, 48), ("D", 3, 4)])
+@pytest.mark.parametrize("name,count,rows", [("A", 5, 8), ("B", 20, 24), ("C", 33, 48), ("D", 3, 4), ("B", 11, 16)])
 def test_captured_decode_steps_with_padding_rows(tiny_folders, name, count, rows, dtype):
     """Request counts that do not fill their captured step (5 of 8 rows, 20 of 24, 33 of 48,
     3 of 4): the padding rows write nothing, and as requests end the same requests move to
