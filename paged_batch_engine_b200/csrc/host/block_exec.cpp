@@ -43,7 +43,7 @@ struct PbeExecFns {
                         int a_type, int lda, const void* B, int b_type, int ldb, const void* beta, void* C, int c_type,
                         int ldc, int compute_type, int algo);
   int (*gemm_stream)(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int mode, float* scratch,
-                     int* tickets, int* err, stream_t stream);
+                     int* tickets, int* err, stream_t stream);                                    // may be null
 };
 
 // What does not change from step to step: one per layer.

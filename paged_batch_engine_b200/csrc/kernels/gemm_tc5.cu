@@ -17,7 +17,8 @@
 // From 256 rows on a pair of blocks (a cluster of two, tcgen05 cta_group::2) works on one
 // 256 x 256 tile: each block stages its 128 rows of X and its half of the weight tile, and the
 // leader's MMAs of M = 256 read both halves, so a weight tile crosses into shared memory once
-// for 256 rows (the second kernel below).  PBE_TC5_PAIR=0 keeps one block a tile.
+// for 256 rows (the second kernel below).  The caller asks for it (mode bit 2); one block a tile is
+// what runs otherwise.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets *err and the block goes on
 // to its end (wrong numbers, flagged), so that tensor memory is always released.  A waiting
@@ -454,10 +455,13 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 
 }  // namespace
 
-// mode 0: Y[M, N] = X W^T; mode 1: W is [gate; up] with N rows in total, Y[M, N/2] = silu(X gate^T) * (X up^T).
+// mode bit 1 clear: Y[M, N] = X W^T; set: W is [gate; up] with N rows in total, Y[M, N/2] = silu(X gate^T) * (X up^T).
+// mode bit 2: two-SM tiles from 256 rows on.
 // err: device int, set to 1 if a bounded wait ran out (the result is then invalid).
-PBE_EXPORT int pbe_gemm_tc5(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int mode,
+PBE_EXPORT int pbe_gemm_tc5(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int mode_bits,
                             int* err, cudaStream_t stream) {
+  const int mode = mode_bits & 1;
+  const bool pair = (mode_bits & 2) != 0;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) != 0) return (int)cudaErrorInvalidValue;          // TMA: row stride a multiple of 16 bytes
   if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
@@ -490,12 +494,8 @@ PBE_EXPORT int pbe_gemm_tc5(const void* X, const void* W, void* Y, int y_dtype, 
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (num_sms <= 0) num_sms = 148;
   }
-  // 256 rows and more: a pair of blocks a 256 x 256 tile (PBE_TC5_PAIR=0 keeps one block a tile)
-  static const bool pair_off = [] {
-    const char* e = getenv("PBE_TC5_PAIR");
-    return e != nullptr && e[0] == '0';
-  }();
-  if (M >= 256 && !pair_off && num_sms >= 2) {
+  // 256 rows and more, where the caller asked for it: a pair of blocks a 256 x 256 tile
+  if (M >= 256 && pair && num_sms >= 2) {
     p.tiles_n = mode == 1 ? (p.N_out + 127) / 128 : (N + BN - 1) / BN;
     p.tiles_m = (M + 255) / 256;
     const size_t smem2 = (size_t)STAGES2 * STAGE2_BYTES + 1024;

@@ -45,9 +45,9 @@ class StepDesc(ctypes.Structure):
 
 
 def enabled() -> bool:
-    """PBE_EXEC=python keeps every launch in the interpreter; the opt-in tcgen05 GEMM has no
-    place in the native block either."""
-    return os.environ.get("PBE_EXEC", "native").strip().lower() != "python" and ops.TC5_MIN_ROWS == 0
+    """PBE_EXEC=python keeps every launch in the interpreter; the opt-in tcgen05 GEMM for prompt
+    portions has no place in the native block either."""
+    return os.environ.get("PBE_EXEC", "native").strip().lower() != "python" and ops.TC5_MASK == 0
 
 
 _host = None
@@ -151,7 +151,7 @@ def _stream_fields(dev) -> dict:
     if not ops.STREAM_MASK:
         return dict(stream_max_rows=0, stream_mask=0, stream_scratch=None, stream_tickets=None, stream_err=None)
     scratch, tickets, err = ops.gemm_stream_buffers(dev)
-    return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS if ops.STREAM_MASK else 0), stream_mask=int(ops.STREAM_MASK),
+    return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS), stream_mask=int(ops.STREAM_MASK),
                 stream_scratch=scratch.data_ptr(), stream_tickets=tickets.data_ptr(), stream_err=err.data_ptr())
 
 
@@ -187,7 +187,10 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
                              num_heads=H, head_dim=hd, max_splits=int(meta.max_splits))
     use_tc5 = m.kernel_kind == "tc5"
     err = ops.tc5_attention_error_buffer(dev) if use_tc5 else None
-    big = T > ops.SKINNY_MAX_ROWS
+    # steps whose activation is the epilogue of the gate/up product need no [T, 2 inter] buffer
+    fused_act = m.hidden_size % 8 == 0 and (T <= ops.SKINNY_MAX_ROWS or
+                                            (ops.STREAM_MASK & 4 and T <= ops.STREAM_MAX_ROWS))
+    big = not fused_act
     return StepDesc(
         num_rows=T, residual=residual.data_ptr(), x=buf("x", m.hidden_size).data_ptr(),
         qkv=buf("qkv", (H + 2 * KV) * hd).data_ptr(), q=buf("q", H * hd).data_ptr(),

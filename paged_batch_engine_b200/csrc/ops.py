@@ -255,10 +255,15 @@ _tc5_err = {}        # per device: the GEMM's flag
 _tc5_attn_err = {}   # per device: the attention kernel's flag (element 0) and room for a debugging trace
 
 
+TC5_PAIR = os.environ.get("PBE_TC5_PAIR", "0") == "1"
+
+
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-             swiglu: bool = False, check: bool = False) -> torch.Tensor:
+             swiglu: bool = False, check: bool = False, pair: Optional[bool] = None) -> torch.Tensor:
     """y = x w^T for many rows on the tcgen05 tensor cores (TMA-fed, accumulator in tensor
     memory).  ``swiglu``: w is [gate; up] stacked and y = silu(x gate^T) * (x up^T), [M, N/2].
+    ``pair``: two-SM tiles (a cluster of two blocks a 256 x 256 tile) from 256 rows on; None
+    takes PBE_TC5_PAIR from the environment (off unless it is 1).
     ``check`` synchronises and raises if a bounded wait inside the kernel ran out."""
     _need_cuda(x, w)
     _need_contiguous(x, w)
@@ -277,8 +282,8 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] 
         err = _tc5_err[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
     fn = _fn("gemm_tc5", "pbe_gemm_tc5",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_ptr(x), _ptr(w), _ptr(out), _dtype_code(out), M, N, K, 1 if swiglu else 0, _ptr(err), _stream()),
-           "gemm_tc5")
+    mode = (1 if swiglu else 0) | (2 if (TC5_PAIR if pair is None else pair) else 0)
+    _check(fn(_ptr(x), _ptr(w), _ptr(out), _dtype_code(out), M, N, K, mode, _ptr(err), _stream()), "gemm_tc5")
     if check and int(err.item()) != 0:
         err.zero_()
         raise KernelError("gemm_tc5: a wait inside the kernel ran out; the result is invalid")
@@ -350,13 +355,25 @@ def stream_applies(x: torch.Tensor, w: torch.Tensor, bit: int) -> bool:
             and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0)
 
 
-# Projections of many rows: the vendor GEMM library by default (it runs two-SM tiles and is
-# the faster one); PBE_GEMM=tc5 in the environment sends them through gemm_tc5 instead.
-TC5_MIN_ROWS = 128 if os.environ.get("PBE_GEMM", "") == "tc5" else 0     # 0: never
+# Projections of many rows (prompt portions): which of them take gemm_tc5 instead of the vendor
+# GEMM library, as bits (1 QKV, 2 output, 4 gate/up with the SwiGLU epilogue, 8 down, 16 others).
+# PBE_GEMM in the environment: "tc5" all of them, "library" none, or the mask as a number.
+def _tc5_mask() -> int:
+    e = os.environ.get("PBE_GEMM", "").strip().lower()
+    if e == "tc5":
+        return 31
+    if e == "library":
+        return 0
+    return int(e) if e.isdigit() else TC5_DEFAULT_MASK
 
 
-def tc5_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (TC5_MIN_ROWS > 0 and x.shape[0] >= TC5_MIN_ROWS and x.dtype == torch.bfloat16
+TC5_DEFAULT_MASK = 0
+TC5_MIN_ROWS = 128
+TC5_MASK = _tc5_mask()
+
+
+def tc5_applies(x: torch.Tensor, w: torch.Tensor, bit: int = 16) -> bool:
+    return (TC5_MASK & bit != 0 and x.shape[0] >= TC5_MIN_ROWS and x.dtype == torch.bfloat16
             and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0)
 
 
@@ -365,7 +382,7 @@ def gemm_libraries(dtype: torch.dtype):
     if dtype == torch.float32:
         return [("sgemm", None)]
     return [("gemm_skinny", None)] + ([("gemm_stream", None)] if STREAM_MASK else []) + \
-        ([("gemm_tc5", None)] if TC5_MIN_ROWS > 0 else [])
+        ([("gemm_tc5", None)] if TC5_MASK else [])
 
 
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -390,7 +407,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return gemm_skinny(x, w, bias, out_dtype)
     if bias is None and stream_applies(x, w, kind):
         return gemm_stream(x, w, out_dtype)
-    if tc5_applies(x, w) and bias is None:
+    if tc5_applies(x, w, kind) and bias is None:
         return gemm_tc5(x, w, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(x, w.t(), out_dtype=torch.float32)

@@ -52,10 +52,10 @@ class SwiGLU(FeedForward):
         if ops.stream_applies(x, self.w_gate_up, 4):
             act = ops.gemm_stream(x, self.w_gate_up, self.dtype, swiglu=True)
             return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)
-        if ops.tc5_applies(x, self.w_gate_up):
+        if ops.tc5_applies(x, self.w_gate_up, 4):
             act = ops.gemm_tc5(x, self.w_gate_up, self.dtype, swiglu=True)
-            return ops.linear(act, self.w_down, None, out_dtype=self.dtype)
-        gu = ops.linear(x, self.w_gate_up, None, out_dtype=self.dtype)
+            return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)
+        gu = ops.linear(x, self.w_gate_up, None, out_dtype=self.dtype, kind=32)
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
         ops.silu_mul(gu, act)
         return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)

@@ -601,16 +601,17 @@ def test_gemm_tc5(M, N, K):
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).to(DEV)
     want = (x.double() @ w.double().t())
     scale = want.abs().max().item()
-    got = ops().gemm_tc5(x, w, torch.float32, check=True).double()
-    assert got.shape == (M, N)
-    assert (got - want).abs().max().item() <= 2e-5 * scale * math.sqrt(K) / 8 + 1e-6     # float32 accumulation
-    gotb = ops().gemm_tc5(x, w, torch.bfloat16, check=True).double()
-    assert (gotb - want).abs().max().item() <= 2 ** -8 * scale
-    if N % 2 == 0:
-        act = ops().gemm_tc5(x, w, torch.bfloat16, swiglu=True, check=True).float().cpu()
-        ref = plain.swiglu(want[:, :N // 2].float().cpu(), want[:, N // 2:].float().cpu())
-        assert act.shape == (M, N // 2)
-        assert (act - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
+    for pair in ((False, True) if M >= 256 else (False,)):      # one block a tile; two-SM tiles
+        got = ops().gemm_tc5(x, w, torch.float32, check=True, pair=pair).double()
+        assert got.shape == (M, N)
+        assert (got - want).abs().max().item() <= 2e-5 * scale * math.sqrt(K) / 8 + 1e-6     # float32 accumulation
+        gotb = ops().gemm_tc5(x, w, torch.bfloat16, check=True, pair=pair).double()
+        assert (gotb - want).abs().max().item() <= 2 ** -8 * scale
+        if N % 2 == 0:
+            act = ops().gemm_tc5(x, w, torch.bfloat16, swiglu=True, check=True, pair=pair).float().cpu()
+            ref = plain.swiglu(want[:, :N // 2].float().cpu(), want[:, N // 2:].float().cpu())
+            assert act.shape == (M, N // 2)
+            assert (act - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
 
 
 # ------------------------------------------------------------------ tcgen05 weight-streaming GEMM, up to 64 rows

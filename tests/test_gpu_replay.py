@@ -342,7 +342,7 @@ def _switch_runs(tiny_folders, name, switch, monkeypatch):
     elif switch == "rows":
         monkeypatch.setenv("PBE_DECODE_TILES", "rows")
     elif switch == "tc5gemm":
-        monkeypatch.setattr(pbe_ops, "TC5_MIN_ROWS", 128)
+        monkeypatch.setattr(pbe_ops, "TC5_MASK", 31)
     cfg, _, page, _ = TINY[name]
     reqs = requests_for(name, cfg["vocab_size"], extra=(12, 47, 29, 64, 140))
     runner = make_runner(tiny_folders[name], "bfloat16", page, pool_tokens=1024)
