@@ -311,9 +311,9 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     const int last_blk = n_tiles > 0 ? (k_end - 1) / P : 0;
     const int box_rows = min(P, BN);                       // a page, or the 64 keys of a larger page
     const int boxes_per_tile = BN / box_rows;
+    int go = 1;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j % ring;
-      int go = 1;
       if (lane == 0) {
         go = mbar_wait(&empty[st], ((j / ring) & 1) ^ 1, err) ? 1 : 0;
         if (go) mbar_expect_tx(&full[st], KV_BYTES);
@@ -333,6 +333,14 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           tma_load_2d(dst + kb * BN * 128 + pg * box_rows * 128, map, kb * 64, y, &full[st]);
       }
       __syncwarp();
+    }
+    // The commits that release the last tiles arrive on this block's barriers whenever the tensor
+    // core gets there: the block must not be gone by then, or they land in the shared memory of
+    // whatever runs next on this multiprocessor.  Wait for every one of them.
+    if (lane == 0) {
+      bool ok = go != 0;
+      for (int j = n_tiles > ring ? n_tiles - ring : 0; j < n_tiles && ok; ++j)
+        ok = mbar_wait(&empty[j % ring], (j / ring) & 1, err);
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {

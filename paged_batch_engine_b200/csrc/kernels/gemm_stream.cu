@@ -178,13 +178,19 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       pdl_wait();
       for (int s = 0; s < filled; ++s, cx.advance()) load_x(cx, s);
       bool ok = true;
-      for (int it = filled; !cw.done() && ok; ++it, cw.advance()) {
+      int it = filled;
+      for (; !cw.done() && ok; ++it, cw.advance()) {
         const int s = it % STAGES;
         ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, p.err);
         if (!ok) break;
         load_w(cw, s);
         load_x(cw, s);
       }
+      // The commits that release the last stages arrive on this block's barriers whenever the
+      // tensor core gets there: the block must not be gone by then, or they land in the shared
+      // memory of whatever runs next on this multiprocessor.  Wait for every one of them.
+      for (int q = it > STAGES ? it - STAGES : 0; q < it && ok; ++q)
+        ok = mbar_wait(&empty_bar[q % STAGES], (q / STAGES) & 1, p.err);
     } else {
       pdl_wait();
     }

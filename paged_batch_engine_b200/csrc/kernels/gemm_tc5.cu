@@ -160,6 +160,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           tma_load_2d(b + 128 * BK * 2, &map_w, kb * BK, wrow1, &full_bar[s]);
         }
       }
+      // The commits that release the last stages arrive on this block's barriers whenever the
+      // tensor core gets there: the block must not be gone by then, or they land in the shared
+      // memory of whatever runs next on this multiprocessor.  Wait for every one of them.
+      for (int q = it > STAGES ? it - STAGES : 0; q < it && ok; ++q)
+        ok = mbar_wait(&empty_bar[q % STAGES], (q / STAGES) & 1, p.err);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -368,6 +373,10 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           tma_load_2d_pair(b, &map_w, kb * BK, wrow, bar);
         }
       }
+      // As above, and here the commits come from the other block's tensor core as well: neither
+      // block leaves before the releases of its last stages have arrived.
+      for (int q = it > STAGES2 ? it - STAGES2 : 0; q < it && ok; ++q)
+        ok = mbar_wait(&empty_bar[q % STAGES2], (q / STAGES2) & 1, p.err);
     }
   } else if (warp == 1) {
     if (leader && lane == 0) {
@@ -395,6 +404,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         }
         umma_commit_pair(&acc_full[buf]);    // the accumulator is complete in both blocks
       }
+      // the other block's epilogue warps arrive on this block's acc_empty: all of it is in before this block leaves
+      for (int q = j > 2 ? j - 2 : 0; q < j && ok; ++q) ok = mbar_wait(&acc_empty[q & 1], (q >> 1) & 1, p.err);
     }
   } else {
     // -------------------------------------------------------------- epilogue warps 2..5 of each block
