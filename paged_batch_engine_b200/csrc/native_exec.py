@@ -40,7 +40,7 @@ class StepDesc(ctypes.Structure):
                 ("attn_params", ops.AttnParams), ("num_work", c_int), ("num_split_rows", c_int),
                 ("merge_params", ops.AttnMergeParams), ("fused_splits", c_int), ("decode_rows", c_int),
                 ("tc5_pages_ok", c_int), ("tc5_err", c_void_p), ("cublas_handle", c_void_p),
-                ("skinny_max_rows", c_int), ("stream_max_rows", c_int), ("stream_mask", c_int),
+                ("skinny_max_rows", c_int), ("stream_max_rows", c_int), ("stream_mask", c_int), ("stream_min_weight", ctypes.c_longlong),
                 ("stream_scratch", c_void_p), ("stream_tickets", c_void_p), ("stream_err", c_void_p)]
 
 
@@ -149,9 +149,11 @@ def block_desc(block) -> Optional[BlockDesc]:
 
 def _stream_fields(dev) -> dict:
     if not ops.STREAM_MASK:
-        return dict(stream_max_rows=0, stream_mask=0, stream_scratch=None, stream_tickets=None, stream_err=None)
+        return dict(stream_max_rows=0, stream_mask=0, stream_min_weight=0, stream_scratch=None, stream_tickets=None,
+                    stream_err=None)
     scratch, tickets, err = ops.gemm_stream_buffers(dev)
     return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS), stream_mask=int(ops.STREAM_MASK),
+                stream_min_weight=int(ops.STREAM_MIN_WEIGHT),
                 stream_scratch=scratch.data_ptr(), stream_tickets=tickets.data_ptr(), stream_err=err.data_ptr())
 
 
@@ -189,7 +191,8 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
     err = ops.tc5_attention_error_buffer(dev) if use_tc5 else None
     # steps whose activation is the epilogue of the gate/up product need no [T, 2 inter] buffer
     fused_act = m.hidden_size % 8 == 0 and (T <= ops.SKINNY_MAX_ROWS or
-                                            (ops.STREAM_MASK & 4 and T <= ops.STREAM_MAX_ROWS))
+                                            (ops.STREAM_MASK & 4 and T <= ops.STREAM_MAX_ROWS and
+                                             2 * f.intermediate_size * m.hidden_size >= ops.STREAM_MIN_WEIGHT))
     big = not fused_act
     return StepDesc(
         num_rows=T, residual=residual.data_ptr(), x=buf("x", m.hidden_size).data_ptr(),
