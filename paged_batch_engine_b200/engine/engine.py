@@ -116,12 +116,15 @@ class Engine:
             prev, self._pending = self._pending, None
             ahead = self.scheduler.schedule_ahead(prev[0]) if self.decode_ahead else None
             if ahead is not None:
+                t1 = time.perf_counter()
                 self._pending = self._launch(ahead, prev[1])
-                self._finish(prev)
-                self.profile["schedule"] += time.perf_counter() - t0
+                self.profile["schedule"] += t1 - t0
+                self.profile["forward"] += time.perf_counter() - t1
+                self._finish(prev)               # adds its own wait and bookkeeping to the profile
                 self.profile["steps"] += 1
                 return self._pop_finished()
             self._finish(prev)
+            t0 = time.perf_counter()
         with nvtx_range("schedule"):
             out = self.scheduler.schedule_step()
         t1 = time.perf_counter()
