@@ -84,9 +84,10 @@ struct PbeStepDesc {
   int* tc5_err;
   void* cublas_handle;
   int skinny_max_rows;      // steps of at most this many rows take the weight-streaming GEMM (the caller's rule)
-  // steps of more rows than that and at most stream_max_rows take the tcgen05 weight-streaming
-  // GEMM for the projections whose bit is set (1 QKV, 2 output, 4 gate/up with SwiGLU, 8 down)
-  int stream_max_rows, stream_mask;
+  // steps of at most stream_max_rows rows take the tcgen05 weight-streaming GEMM for the projections
+  // whose bit is set (1 QKV, 2 output, 4 gate/up with SwiGLU, 8 down): in stream_mask_few for steps
+  // that gemm_skinny takes otherwise, in stream_mask for larger ones
+  int stream_max_rows, stream_mask_few, stream_mask;
   long long stream_min_weight;   // and only matrices of at least this many elements (smaller ones: the library)
   float* stream_scratch;
   int* stream_tickets;
@@ -98,14 +99,15 @@ double g_stage_ns[16];        // host time spent in each stage's launcher (two c
 long long g_stage_calls[16];
 // y[T, N] = x[T, K] w[N, K]^T, bfloat16 in and out, float32 accumulation
 bool streams(const PbeStepDesc* s, int bit, int T, int N, int K) {
-  return T > s->skinny_max_rows && T <= s->stream_max_rows && (s->stream_mask & bit) != 0 && (K & 7) == 0 &&
+  const int mask = T <= s->skinny_max_rows ? s->stream_mask_few : s->stream_mask;
+  return T <= s->stream_max_rows && (mask & bit) != 0 && (K & 7) == 0 &&
          (long long)N * K >= s->stream_min_weight;
 }
 int linear(const PbeExecFns* fn, const PbeStepDesc* s, int bit, const void* x, const void* w, void* y, int T, int N,
            int K, stream_t stream) {
-  if (T <= s->skinny_max_rows && (K & 7) == 0) return fn->gemm_skinny(x, w, nullptr, y, kBF16, T, N, K, 0, stream);
   if (streams(s, bit, T, N, K))
     return fn->gemm_stream(x, w, y, kBF16, T, N, K, 0, s->stream_scratch, s->stream_tickets, s->stream_err, stream);
+  if (T <= s->skinny_max_rows && (K & 7) == 0) return fn->gemm_skinny(x, w, nullptr, y, kBF16, T, N, K, 0, stream);
   const float alpha = 1.0f, beta = 0.0f;
   // row-major y = x w^T is column-major y^T[N, T] = w^T-as-stored[K, N]^T x^T[K, T]
   const int rc = fn->cublas_gemm_ex(s->cublas_handle, kOpT, kOpN, N, T, K, &alpha, w, kR16BF, K, x, kR16BF, K, &beta, y,
@@ -178,11 +180,11 @@ API int pbe_exec_block(const PbeExecFns* fn, const PbeBlockDesc* b, const PbeSte
   // the output projection's result is what the second norm adds: it goes to delta_out first
   STAGE(6, linear(fn, s, 2, s->attn, b->w_o, delta_out, T, d, H * hd, stream));
   STAGE(7, fn->add_rmsnorm(s->residual, delta_out, kBF16, b->norm2, s->x, kBF16, nullptr, T, d, b->eps2, stream));
-  if (T <= s->skinny_max_rows && (d & 7) == 0) {
-    STAGE(8, fn->gemm_skinny(s->x, b->w_gate_up, nullptr, s->act, kBF16, T, 2 * b->inter, d, 1, stream));
-  } else if (streams(s, 4, T, 2 * b->inter, d)) {
+  if (streams(s, 4, T, 2 * b->inter, d)) {
     STAGE(8, fn->gemm_stream(s->x, b->w_gate_up, s->act, kBF16, T, 2 * b->inter, d, 1, s->stream_scratch,
                              s->stream_tickets, s->stream_err, stream));
+  } else if (T <= s->skinny_max_rows && (d & 7) == 0) {
+    STAGE(8, fn->gemm_skinny(s->x, b->w_gate_up, nullptr, s->act, kBF16, T, 2 * b->inter, d, 1, stream));
   } else {
     STAGE(8, linear(fn, s, 0, s->x, b->w_gate_up, s->gate_up, T, 2 * b->inter, d, stream));
     STAGE(9, fn->silu_mul(s->gate_up, s->act, kBF16, T, b->inter, stream));

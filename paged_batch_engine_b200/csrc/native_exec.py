@@ -40,7 +40,8 @@ class StepDesc(ctypes.Structure):
                 ("attn_params", ops.AttnParams), ("num_work", c_int), ("num_split_rows", c_int),
                 ("merge_params", ops.AttnMergeParams), ("fused_splits", c_int), ("decode_rows", c_int),
                 ("tc5_pages_ok", c_int), ("tc5_err", c_void_p), ("cublas_handle", c_void_p),
-                ("skinny_max_rows", c_int), ("stream_max_rows", c_int), ("stream_mask", c_int), ("stream_min_weight", ctypes.c_longlong),
+                ("skinny_max_rows", c_int), ("stream_max_rows", c_int), ("stream_mask_few", c_int), ("stream_mask", c_int),
+                ("stream_min_weight", ctypes.c_longlong),
                 ("stream_scratch", c_void_p), ("stream_tickets", c_void_p), ("stream_err", c_void_p)]
 
 
@@ -74,7 +75,8 @@ def exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
                     attn_tc5=_addr(load_library("attention_tc5", defines).pbe_attn_tc5) if use_tc5 else None,
                     attn_merge=_addr(simple.pbe_attn_merge), attn_decode_fused=_addr(mma.pbe_attn_decode_fused),
                     cublas_gemm_ex=_addr(cublas.cublasGemmEx),
-                    gemm_stream=_addr(load_library("gemm_stream").pbe_gemm_stream) if ops.STREAM_MASK else None)
+                    gemm_stream=_addr(load_library("gemm_stream").pbe_gemm_stream)
+                    if (ops.STREAM_MASK or ops.STREAM_MASK_FEW) else None)
         _fns[key] = f
     return f
 
@@ -148,11 +150,12 @@ def block_desc(block) -> Optional[BlockDesc]:
 
 
 def _stream_fields(dev) -> dict:
-    if not ops.STREAM_MASK:
-        return dict(stream_max_rows=0, stream_mask=0, stream_min_weight=0, stream_scratch=None, stream_tickets=None,
+    if not (ops.STREAM_MASK or ops.STREAM_MASK_FEW):
+        return dict(stream_max_rows=0, stream_mask_few=0, stream_mask=0, stream_min_weight=0, stream_scratch=None, stream_tickets=None,
                     stream_err=None)
     scratch, tickets, err = ops.gemm_stream_buffers(dev)
-    return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS), stream_mask=int(ops.STREAM_MASK),
+    return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS), stream_mask_few=int(ops.STREAM_MASK_FEW),
+                stream_mask=int(ops.STREAM_MASK),
                 stream_min_weight=int(ops.STREAM_MIN_WEIGHT),
                 stream_scratch=scratch.data_ptr(), stream_tickets=tickets.data_ptr(), stream_err=err.data_ptr())
 
@@ -191,7 +194,7 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
     err = ops.tc5_attention_error_buffer(dev) if use_tc5 else None
     # steps whose activation is the epilogue of the gate/up product need no [T, 2 inter] buffer
     fused_act = m.hidden_size % 8 == 0 and (T <= ops.SKINNY_MAX_ROWS or
-                                            (ops.STREAM_MASK & 4 and T <= ops.STREAM_MAX_ROWS and
+                                            (ops.stream_mask(T) & 4 and
                                              2 * f.intermediate_size * m.hidden_size >= ops.STREAM_MIN_WEIGHT))
     big = not fused_act
     return StepDesc(

@@ -339,22 +339,32 @@ def gemm_stream_buffers(device):
     return st[0], st[1], err
 
 
-# Steps of more rows than the skinny kernel takes and at most STREAM_MAX_ROWS send the projections
-# whose bit is set in STREAM_MASK through gemm_stream (1 QKV, 2 output, 4 gate/up with SwiGLU, 8
-# down, 16 LM head and others).  Measured in the captured decode step of the 7B shape against the
-# library GEMM (and silu_mul): 16 rows 3.52 -> 3.37 ms with gate/up and down, 3.40 with all four;
-# 24 and 32 rows level; 64 rows 4.58 -> 4.77 ms.  So: gate/up and down, up to 16 rows.  The kernel
-# itself takes up to 64; PBE_STREAM (mask, 0: never) and PBE_STREAM_ROWS override the choice.
+# Which projections of a decode step go through gemm_stream, as bits (1 QKV, 2 output, 4 gate/up
+# with SwiGLU, 8 down, 16 LM head and others): STREAM_MASK_FEW for steps of at most SKINNY_MAX_ROWS
+# rows (the rest of such a step is gemm_skinny's), STREAM_MASK for steps of more rows up to
+# STREAM_MAX_ROWS (the rest is the library's).  Measured in the captured decode step of the 7B
+# shape, ms a step: 1 / 2 / 4 / 8 rows with gate/up on it 2.91 / 2.93 / 2.98 / 3.12-3.14 against
+# 2.95 / 2.99 / 3.05 / 3.19 on gemm_skinny (down on it as well: 3.14 at 8 rows, down alone 3.22);
+# 16 rows 3.52 -> 3.37 with gate/up and down, 3.40 with all four; 24 and 32 rows level; 64 rows
+# 4.58 -> 4.77.  So: gate/up up to 8 rows, gate/up and down from 9 to 16.  The kernel itself takes
+# up to 64 rows; PBE_STREAM_FEW, PBE_STREAM (masks, 0: never) and PBE_STREAM_ROWS override the choice.
 STREAM_KERNEL_ROWS = 64
 STREAM_MAX_ROWS = int(os.environ.get("PBE_STREAM_ROWS", "16"))
+STREAM_MASK_FEW = int(os.environ.get("PBE_STREAM_FEW", "4"))
 STREAM_MASK = int(os.environ.get("PBE_STREAM", "12"))
 # ... and only matrices of at least this many elements: below it (the 1.5B shape's 27.5 M and 13.8 M)
 # the library's product is the shorter one (21.4 against 24.5 us, 19.5 against 20.5 us at 16 rows)
-STREAM_MIN_WEIGHT = 48 << 20
+STREAM_MIN_WEIGHT = int(os.environ.get("PBE_STREAM_MIN_WEIGHT", str(48 << 20)))
+
+
+def stream_mask(rows: int) -> int:
+    if rows <= SKINNY_MAX_ROWS:
+        return STREAM_MASK_FEW
+    return STREAM_MASK if rows <= STREAM_MAX_ROWS else 0
 
 
 def stream_applies(x: torch.Tensor, w: torch.Tensor, bit: int) -> bool:
-    return (STREAM_MASK & bit != 0 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS and x.dtype == torch.bfloat16
+    return (stream_mask(x.shape[0]) & bit != 0 and x.dtype == torch.bfloat16
             and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.numel() >= STREAM_MIN_WEIGHT)
 
 
@@ -384,7 +394,7 @@ def gemm_libraries(dtype: torch.dtype):
     """The matrix-product libraries a model of this dtype launches (for parallel builds)."""
     if dtype == torch.float32:
         return [("sgemm", None)]
-    return [("gemm_skinny", None)] + ([("gemm_stream", None)] if STREAM_MASK else []) + \
+    return [("gemm_skinny", None)] + ([("gemm_stream", None)] if (STREAM_MASK or STREAM_MASK_FEW) else []) + \
         ([("gemm_tc5", None)] if TC5_MASK else [])
 
 
@@ -406,10 +416,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return sgemm_nt(x, w, bias, out)
     if x.dtype != torch.bfloat16:
         raise KernelError("a bfloat16 weight takes bfloat16 activations")
-    if skinny_applies(x, w):
-        return gemm_skinny(x, w, bias, out_dtype)
     if bias is None and stream_applies(x, w, kind):
         return gemm_stream(x, w, out_dtype)
+    if skinny_applies(x, w):
+        return gemm_skinny(x, w, bias, out_dtype)
     if tc5_applies(x, w, kind) and bias is None:
         return gemm_tc5(x, w, out_dtype)
     if out_dtype == torch.float32:

@@ -45,12 +45,12 @@ class SwiGLU(FeedForward):
         self.w_down = tensors.pop(prefix + n["down"] + ".weight").contiguous()
 
     def forward(self, x, ctx):
-        if ops.skinny_applies(x, self.w_gate_up):
-            # few rows (decode): the activation is the epilogue of the weight-streaming product
-            act = ops.gemm_skinny(x, self.w_gate_up, None, self.dtype, swiglu=True)
-            return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)
+        # few rows (decode): the activation is the epilogue of a weight-streaming product
         if ops.stream_applies(x, self.w_gate_up, 4):
             act = ops.gemm_stream(x, self.w_gate_up, self.dtype, swiglu=True)
+            return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)
+        if ops.skinny_applies(x, self.w_gate_up):
+            act = ops.gemm_skinny(x, self.w_gate_up, None, self.dtype, swiglu=True)
             return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)
         if ops.tc5_applies(x, self.w_gate_up, 4):
             act = ops.gemm_tc5(x, self.w_gate_up, self.dtype, swiglu=True)
