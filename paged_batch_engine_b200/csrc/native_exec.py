@@ -59,9 +59,16 @@ def _addr(fn) -> int:
     return ctypes.cast(fn, c_void_p).value
 
 
-def exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
-    """The launchers' addresses for one head size (the attention libraries are built per head size)."""
-    key = (int(head_dim), bool(use_tc5))
+def block_streams(block) -> bool:
+    """True when one of the block's projections is large enough for gemm_stream."""
+    m, f = block.mixer, block.ffn
+    return ops.stream_wanted(max(t.numel() for t in (m.w_qkv, m.w_o, f.w_gate_up, f.w_down)))
+
+
+def exec_fns(head_dim: int, use_tc5: bool, stream: bool = False) -> ExecFns:
+    """The launchers' addresses for one head size (the attention libraries are built per head size);
+    ``stream``: with gemm_stream's (a model of small matrices never launches it)."""
+    key = (int(head_dim), bool(use_tc5), bool(stream))
     f = _fns.get(key)
     if f is None:
         defines = {"PBE_HEAD_DIM": int(head_dim)}
@@ -75,8 +82,7 @@ def exec_fns(head_dim: int, use_tc5: bool) -> ExecFns:
                     attn_tc5=_addr(load_library("attention_tc5", defines).pbe_attn_tc5) if use_tc5 else None,
                     attn_merge=_addr(simple.pbe_attn_merge), attn_decode_fused=_addr(mma.pbe_attn_decode_fused),
                     cublas_gemm_ex=_addr(cublas.cublasGemmEx),
-                    gemm_stream=_addr(load_library("gemm_stream").pbe_gemm_stream)
-                    if (ops.STREAM_MASK or ops.STREAM_MASK_FEW) else None)
+                    gemm_stream=_addr(load_library("gemm_stream").pbe_gemm_stream) if stream else None)
         _fns[key] = f
     return f
 
@@ -149,8 +155,8 @@ def block_desc(block) -> Optional[BlockDesc]:
                      window=int(m.window or 0), use_tc5=1 if m.kernel_kind == "tc5" else 0)
 
 
-def _stream_fields(dev) -> dict:
-    if not (ops.STREAM_MASK or ops.STREAM_MASK_FEW):
+def _stream_fields(dev, block) -> dict:
+    if not block_streams(block):
         return dict(stream_max_rows=0, stream_mask_few=0, stream_mask=0, stream_min_weight=0, stream_scratch=None, stream_tickets=None,
                     stream_err=None)
     scratch, tickets, err = ops.gemm_stream_buffers(dev)
@@ -208,4 +214,4 @@ def step_desc(block, ctx, cache, residual: torch.Tensor, buffers: dict) -> StepD
         fused_splits=int(splits), decode_rows=int(meta.decode_rows),
         tc5_pages_ok=1 if use_tc5 and ops.tc5_attention_applies(hd, ctx.page_tokens) else 0,
         tc5_err=err.data_ptr() if err is not None else None, cublas_handle=torch.cuda.current_blas_handle(),
-        skinny_max_rows=int(ops.SKINNY_MAX_ROWS), **_stream_fields(dev))
+        skinny_max_rows=int(ops.SKINNY_MAX_ROWS), **_stream_fields(dev, block))

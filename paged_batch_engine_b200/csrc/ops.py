@@ -390,11 +390,17 @@ def tc5_applies(x: torch.Tensor, w: torch.Tensor, bit: int = 16) -> bool:
             and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0)
 
 
-def gemm_libraries(dtype: torch.dtype):
-    """The matrix-product libraries a model of this dtype launches (for parallel builds)."""
+def stream_wanted(largest_weight: int) -> bool:
+    """True when a matrix of that many elements would go through gemm_stream at some step size."""
+    return bool(STREAM_MASK or STREAM_MASK_FEW) and largest_weight >= STREAM_MIN_WEIGHT
+
+
+def gemm_libraries(dtype: torch.dtype, largest_weight: int = 0):
+    """The matrix-product libraries a part of this dtype launches whose largest matrix has that
+    many elements (for parallel builds)."""
     if dtype == torch.float32:
         return [("sgemm", None)]
-    return [("gemm_skinny", None)] + ([("gemm_stream", None)] if (STREAM_MASK or STREAM_MASK_FEW) else []) + \
+    return [("gemm_skinny", None)] + ([("gemm_stream", None)] if stream_wanted(largest_weight) else []) + \
         ([("gemm_tc5", None)] if TC5_MASK else [])
 
 

@@ -125,7 +125,7 @@ class DecoderModel:
             sd = steps.get(key)
             if sd is None:
                 sd = steps[key] = native_exec.step_desc(block, ctx, cache, residual, buffers)
-            fns = native_exec.exec_fns(m.head_dim, m.kernel_kind == "tc5")
+            fns = native_exec.exec_fns(m.head_dim, m.kernel_kind == "tc5", native_exec.block_streams(block))
             delta_out = deltas[i & 1]
             native_exec.run_block(descs[step.block], fns, sd, delta_in, delta_out, cache.k, cache.v)
             delta_in = delta_out

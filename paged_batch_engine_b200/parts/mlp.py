@@ -26,7 +26,7 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self.w_down = None
 
     def kernel_libraries(self, dtype):
-        return [("elementwise", None)] + ops.gemm_libraries(dtype)
+        return [("elementwise", None)] + ops.gemm_libraries(dtype, 2 * self.intermediate_size * self.hidden_size)
 
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size
