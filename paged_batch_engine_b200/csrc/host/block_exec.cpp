@@ -86,8 +86,9 @@ struct PbeStepDesc {
   int skinny_max_rows;      // steps of at most this many rows take the weight-streaming GEMM (the caller's rule)
   // steps of at most stream_max_rows rows take the tcgen05 weight-streaming GEMM for the projections
   // whose bit is set (1 QKV, 2 output, 4 gate/up with SwiGLU, 8 down): in stream_mask_few for steps
-  // that gemm_skinny takes otherwise, in stream_mask for larger ones
-  int stream_max_rows, stream_mask_few, stream_mask;
+  // that gemm_skinny takes otherwise, in stream_mask for larger ones up to stream_mid_rows, in
+  // stream_mask_many beyond
+  int stream_mid_rows, stream_max_rows, stream_mask_few, stream_mask, stream_mask_many;
   long long stream_min_weight;   // and only matrices of at least this many elements (smaller ones: the library)
   float* stream_scratch;
   int* stream_tickets;
@@ -99,7 +100,8 @@ double g_stage_ns[16];        // host time spent in each stage's launcher (two c
 long long g_stage_calls[16];
 // y[T, N] = x[T, K] w[N, K]^T, bfloat16 in and out, float32 accumulation
 bool streams(const PbeStepDesc* s, int bit, int T, int N, int K) {
-  const int mask = T <= s->skinny_max_rows ? s->stream_mask_few : s->stream_mask;
+  const int mask = T <= s->skinny_max_rows ? s->stream_mask_few
+                   : T <= s->stream_mid_rows ? s->stream_mask : s->stream_mask_many;
   return T <= s->stream_max_rows && (mask & bit) != 0 && (K & 7) == 0 &&
          (long long)N * K >= s->stream_min_weight;
 }

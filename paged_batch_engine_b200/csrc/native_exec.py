@@ -40,7 +40,8 @@ class StepDesc(ctypes.Structure):
                 ("attn_params", ops.AttnParams), ("num_work", c_int), ("num_split_rows", c_int),
                 ("merge_params", ops.AttnMergeParams), ("fused_splits", c_int), ("decode_rows", c_int),
                 ("tc5_pages_ok", c_int), ("tc5_err", c_void_p), ("cublas_handle", c_void_p),
-                ("skinny_max_rows", c_int), ("stream_max_rows", c_int), ("stream_mask_few", c_int), ("stream_mask", c_int),
+                ("skinny_max_rows", c_int), ("stream_mid_rows", c_int), ("stream_max_rows", c_int), ("stream_mask_few", c_int), ("stream_mask", c_int),
+                ("stream_mask_many", c_int),
                 ("stream_min_weight", ctypes.c_longlong),
                 ("stream_scratch", c_void_p), ("stream_tickets", c_void_p), ("stream_err", c_void_p)]
 
@@ -157,11 +158,13 @@ def block_desc(block) -> Optional[BlockDesc]:
 
 def _stream_fields(dev, block) -> dict:
     if not block_streams(block):
-        return dict(stream_max_rows=0, stream_mask_few=0, stream_mask=0, stream_min_weight=0, stream_scratch=None, stream_tickets=None,
+        return dict(stream_mid_rows=0, stream_max_rows=0, stream_mask_few=0, stream_mask=0, stream_mask_many=0,
+                    stream_min_weight=0, stream_scratch=None, stream_tickets=None,
                     stream_err=None)
     scratch, tickets, err = ops.gemm_stream_buffers(dev)
-    return dict(stream_max_rows=int(ops.STREAM_MAX_ROWS), stream_mask_few=int(ops.STREAM_MASK_FEW),
-                stream_mask=int(ops.STREAM_MASK),
+    return dict(stream_mid_rows=int(ops.STREAM_MID_ROWS), stream_max_rows=int(ops.STREAM_MAX_ROWS),
+                stream_mask_few=int(ops.STREAM_MASK_FEW), stream_mask=int(ops.STREAM_MASK),
+                stream_mask_many=int(ops.STREAM_MASK_MANY),
                 stream_min_weight=int(ops.STREAM_MIN_WEIGHT),
                 stream_scratch=scratch.data_ptr(), stream_tickets=tickets.data_ptr(), stream_err=err.data_ptr())
 

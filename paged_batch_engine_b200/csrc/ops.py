@@ -342,16 +342,21 @@ def gemm_stream_buffers(device):
 # Which projections of a decode step go through gemm_stream, as bits (1 QKV, 2 output, 4 gate/up
 # with SwiGLU, 8 down, 16 LM head and others): STREAM_MASK_FEW for steps of at most SKINNY_MAX_ROWS
 # rows (the rest of such a step is gemm_skinny's), STREAM_MASK for steps of more rows up to
-# STREAM_MAX_ROWS (the rest is the library's).  Measured in the captured decode step of the 7B
-# shape, ms a step: 1 / 2 / 4 / 8 rows with gate/up on it 2.91 / 2.93 / 2.98 / 3.12-3.14 against
-# 2.95 / 2.99 / 3.05 / 3.19 on gemm_skinny (down on it as well: 3.14 at 8 rows, down alone 3.22);
-# 16 rows 3.52 -> 3.37 with gate/up and down, 3.40 with all four; 24 and 32 rows level; 64 rows
-# 4.58 -> 4.77.  So: gate/up up to 8 rows, gate/up and down from 9 to 16.  The kernel itself takes
-# up to 64 rows; PBE_STREAM_FEW, PBE_STREAM (masks, 0: never) and PBE_STREAM_ROWS override the choice.
+# STREAM_MID_ROWS and STREAM_MASK_MANY beyond that up to STREAM_MAX_ROWS (the rest is the
+# library's).  Measured in the captured decode step of the 7B shape, ms a step: 1 / 2 / 4 / 8 rows
+# with gate/up on it 2.91 / 2.93 / 2.98 / 3.12-3.14 against 2.95 / 2.99 / 3.05 / 3.19 on gemm_skinny
+# (down on it as well: 3.14 at 8 rows, down alone 3.22); 16 rows 3.52 -> 3.37 with gate/up and
+# down, 3.40 with all four; 24 / 32 / 48 / 64 rows with gate/up alone 3.67 / 3.76 / 4.18 / 4.52
+# against 3.75 / 3.84 / 4.26 / 4.58 on the library GEMM and silu_mul (with down as well: level at 24
+# and 32, 4.77 at 64).  So: gate/up everywhere up to 64 rows, down as well from 9 to 16.  The
+# PBE_STREAM_FEW, PBE_STREAM and PBE_STREAM_MANY masks (0: never) and PBE_STREAM_ROWS /
+# PBE_STREAM_MAX_ROWS override the choice.
 STREAM_KERNEL_ROWS = 64
-STREAM_MAX_ROWS = int(os.environ.get("PBE_STREAM_ROWS", "16"))
+STREAM_MID_ROWS = int(os.environ.get("PBE_STREAM_ROWS", "16"))
+STREAM_MAX_ROWS = min(STREAM_KERNEL_ROWS, int(os.environ.get("PBE_STREAM_MAX_ROWS", "64")))
 STREAM_MASK_FEW = int(os.environ.get("PBE_STREAM_FEW", "4"))
 STREAM_MASK = int(os.environ.get("PBE_STREAM", "12"))
+STREAM_MASK_MANY = int(os.environ.get("PBE_STREAM_MANY", "4"))
 # ... and only matrices of at least this many elements: below it (the 1.5B shape's 27.5 M and 13.8 M)
 # the library's product is the shorter one (21.4 against 24.5 us, 19.5 against 20.5 us at 16 rows)
 STREAM_MIN_WEIGHT = int(os.environ.get("PBE_STREAM_MIN_WEIGHT", str(48 << 20)))
@@ -360,7 +365,9 @@ STREAM_MIN_WEIGHT = int(os.environ.get("PBE_STREAM_MIN_WEIGHT", str(48 << 20)))
 def stream_mask(rows: int) -> int:
     if rows <= SKINNY_MAX_ROWS:
         return STREAM_MASK_FEW
-    return STREAM_MASK if rows <= STREAM_MAX_ROWS else 0
+    if rows <= STREAM_MID_ROWS:
+        return STREAM_MASK
+    return STREAM_MASK_MANY if rows <= STREAM_MAX_ROWS else 0
 
 
 def stream_applies(x: torch.Tensor, w: torch.Tensor, bit: int) -> bool:
@@ -392,7 +399,7 @@ def tc5_applies(x: torch.Tensor, w: torch.Tensor, bit: int = 16) -> bool:
 
 def stream_wanted(largest_weight: int) -> bool:
     """True when a matrix of that many elements would go through gemm_stream at some step size."""
-    return bool(STREAM_MASK or STREAM_MASK_FEW) and largest_weight >= STREAM_MIN_WEIGHT
+    return bool(STREAM_MASK or STREAM_MASK_FEW or STREAM_MASK_MANY) and largest_weight >= STREAM_MIN_WEIGHT
 
 
 def gemm_libraries(dtype: torch.dtype, largest_weight: int = 0):
