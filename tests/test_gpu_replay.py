@@ -341,12 +341,21 @@ def _switch_runs(tiny_folders, name, switch, monkeypatch):
         monkeypatch.setenv("PBE_DECODE_FUSED", "0")
     elif switch == "rows":
         monkeypatch.setenv("PBE_DECODE_TILES", "rows")
+    elif switch in ("stream", "stream-python"):
+        # the tcgen05 weight-streaming GEMM for every projection of every step of up to 64 rows,
+        # whatever the size of the matrix (by default only large matrices take it)
+        for mask in ("STREAM_MASK_FEW", "STREAM_MASK", "STREAM_MASK_MANY"):
+            monkeypatch.setattr(pbe_ops, mask, 15)
+        monkeypatch.setattr(pbe_ops, "STREAM_MIN_WEIGHT", 0)
+        native_exec._fns.clear()
+        if switch == "stream-python":
+            monkeypatch.setenv("PBE_EXEC", "python")
     elif switch == "tc5gemm":
         monkeypatch.setattr(pbe_ops, "TC5_MASK", 31)
     cfg, _, page, _ = TINY[name]
     reqs = requests_for(name, cfg["vocab_size"], extra=(12, 47, 29, 64, 140))
     runner = make_runner(tiny_folders[name], "bfloat16", page, pool_tokens=1024)
-    assert native_exec.enabled() == (switch not in ("python", "tc5gemm"))
+    assert native_exec.enabled() == (switch not in ("python", "tc5gemm", "stream-python"))
     out = {}
     for label, recs in (("whole", ru.whole(reqs)), ("tail32", ru.tail_decoded(reqs)),
                         ("mixed", ru.mixed(reqs, max_live=4, seed=4))):
@@ -354,23 +363,36 @@ def _switch_runs(tiny_folders, name, switch, monkeypatch):
     return reqs, out
 
 
-@pytest.mark.parametrize("switch", ["python", "mma", "unfused", "rows", "tc5gemm"])
+@pytest.mark.parametrize("switch", ["python", "mma", "unfused", "rows", "tc5gemm", "stream", "stream-python"])
 @pytest.mark.parametrize("name", ["B", "D"])
 def test_every_switch_of_the_step_agrees_with_plain(tiny_folders, name, switch, monkeypatch):
     """The ways through a bfloat16 step that are not the default: every launch from the
     interpreter instead of the host library's block (PBE_EXEC=python), the mma.sync prompt
     attention (PBE_ATTN=mma), separate rope / attention / merge launches for decoded tokens
     (PBE_DECODE_FUSED=0), key tiles copied row by row (PBE_DECODE_TILES=rows), the package's
-    tcgen05 GEMM for many rows (PBE_GEMM=tc5).  Each against the plain implementation; the
-    interpreter's way must equal the host library's bit for bit (same kernels, same order)."""
+    tcgen05 GEMM for many rows (PBE_GEMM=tc5), the tcgen05 weight-streaming GEMM for every projection
+    of steps of up to 64 rows (from the host library's block and from the interpreter).  Each against
+    the plain implementation; the interpreter's way must equal the host library's bit for bit (same
+    kernels, same order).  The launchers' table of the host library is made anew where a switch adds a
+    kernel to it."""
     cfg, _, page, _ = TINY[name]
     reqs, got = _switch_runs(tiny_folders, name, switch, monkeypatch)
     want = plain_logits(tiny_folders[name], reqs)
     for label, rows in got.items():
         check(rows, want, "bfloat16", f"{name}/{switch}/{label}")
-    if switch == "python":
+    from paged_batch_engine_b200.csrc import native_exec
+    native_exec._fns.clear()
+    if switch == "stream":
+        # the switch took: another kernel's sums are other bits somewhere
+        monkeypatch.undo()
+        _, base = _switch_runs(tiny_folders, name, "default", monkeypatch)
+        native_exec._fns.clear()
+        assert any(not torch.equal(row, base[label][rid][pos])
+                   for label in got for rid in got[label] for pos, row in got[label][rid].items())
+    if switch in ("python", "stream-python"):
         monkeypatch.delenv("PBE_EXEC")
-        _, native = _switch_runs(tiny_folders, name, "default", monkeypatch)
+        _, native = _switch_runs(tiny_folders, name, "default" if switch == "python" else "stream", monkeypatch)
+        native_exec._fns.clear()
         for label in got:
             for rid in got[label]:
                 for pos, row in got[label][rid].items():
