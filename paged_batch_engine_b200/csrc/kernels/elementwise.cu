@@ -72,6 +72,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    const int32_t* __restrict__ row_index, int d, float eps) {
   __shared__ float red[33];
   pdl_launch_dependents();   // the next kernel may fetch what does not depend on this one
+  // the gains are weights: a thread's first two vectors of them are fetched before the wait
+  constexpr int GAIN_AHEAD = 2;
+  float4 g_ahead[GAIN_AHEAD];
+  const bool vec = (d & 3) == 0;
+  if (vec) {
+#pragma unroll
+    for (int j = 0; j < GAIN_AHEAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      g_ahead[j] = i < d / 4 ? reinterpret_cast<const float4*>(gain)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   pdl_wait();
   const int r = blockIdx.x;
   const int src = row_index ? row_index[r] : r;
@@ -81,7 +92,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   extern __shared__ __align__(16) float row[];  // d floats: the summed row
   float ss = 0.f;
   const bool write_back = (row_index == nullptr) && (dl != nullptr);
-  if ((d & 3) == 0) {
+  if (vec) {
     // four elements a thread: 16-byte loads of the residual, 8- or 16-byte loads of the delta
     const float4* res4 = reinterpret_cast<const float4*>(res);
     float4* row4 = reinterpret_cast<float4*>(row);
@@ -98,13 +109,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     const float total = block_sum(ss, red);
     const float scale = rsqrtf(total / (float)d + eps);
     const float4* g4 = reinterpret_cast<const float4*>(gain);
-    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+    auto finish = [&](int i, const float4 g) {
       const float4 v = row4[i];
-      const float4 g = g4[i];
       if (write_back) reinterpret_cast<float4*>(res)[i] = v;
       const float y[4] = {(g.x * v.x) * scale, (g.y * v.y) * scale, (g.z * v.z) * scale, (g.w * v.w) * scale};
       store4(o + 4 * i, y);
+    };
+#pragma unroll
+    for (int j = 0; j < GAIN_AHEAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < d / 4) finish(i, g_ahead[j]);
     }
+    for (int i = threadIdx.x + GAIN_AHEAD * blockDim.x; i < d / 4; i += blockDim.x) finish(i, g4[i]);
     return;
   }
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
