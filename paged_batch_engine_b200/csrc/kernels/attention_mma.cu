@@ -607,10 +607,12 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     const bool owner = pos >= k_begin && pos < k_end;
     for (int i = 0; i < NST - 1; ++i)
       if (i < n_tiles) load_tile(tile0 + i * BN, i);
-    pdl_wait();
     // The new token's query heads (and, in the owner block, its key and value) from the fused
     // projection: bias, rotary position encoding (pairs i, i + hd/2; angle, sine, cosine and
-    // rotation in float32, one rounding), as rope_kv.cu does.
+    // rotation in float32, one rounding), as rope_kv.cu does.  What of that does not depend on
+    // the projection is done before the wait: the angles' sines and cosines (the position is the
+    // host's, the frequencies are weights) and the biases, which are laid where the projection's
+    // values are then added to them.
     constexpr int HALF = HD / 2;
     float* trig = reinterpret_cast<float*>(Ks + (NST - 1) * tile_elems);   // the last buffer: filled last
     float* qraw = trig + HD;                                          // [G][HD] biased query heads
@@ -619,9 +621,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     const int row_width = (H + 2 * KV) * HD;
     const bf16* in = (const bf16*)f.qkv + (size_t)qs * row_width;
     const int chunks_q = G * CPR, chunks_kv = owner ? 2 * CPR : 0;
-    for (int c = tid; c < chunks_q + chunks_kv; c += NTHREADS) {
-      int col;
-      float* dst;
+    auto chunk_of = [&](int c, int& col, float*& dst) {
       if (c < chunks_q) {
         col = kvh * G * HD + c * 8;
         dst = qraw + c * 8;
@@ -630,13 +630,33 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
         col = (H + which * KV + kvh) * HD + i8 * 8;
         dst = kvraw + which * HD + i8 * 8;
       }
+    };
+    for (int c = tid; c < chunks_q + chunks_kv; c += NTHREADS) {
+      int col;
+      float* dst;
+      chunk_of(c, col, dst);
+      if (f.bias) {
+        const float4 b0 = *reinterpret_cast<const float4*>(f.bias + col);
+        const float4 b1 = *reinterpret_cast<const float4*>(f.bias + col + 4);
+        *reinterpret_cast<float4*>(dst) = b0;
+        *reinterpret_cast<float4*>(dst + 4) = b1;
+      } else {
+        *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    pdl_wait();
+    for (int c = tid; c < chunks_q + chunks_kv; c += NTHREADS) {      // the same chunks, by the same threads
+      int col;
+      float* dst;
+      chunk_of(c, col, dst);
       const uint4 raw = *reinterpret_cast<const uint4*>(in + col);
       const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
-        dst[2 * e] = v.x + (f.bias ? f.bias[col + 2 * e] : 0.f);
-        dst[2 * e + 1] = v.y + (f.bias ? f.bias[col + 2 * e + 1] : 0.f);
+        dst[2 * e] = v.x + dst[2 * e];
+        dst[2 * e + 1] = v.y + dst[2 * e + 1];
       }
     }
     __syncthreads();
