@@ -441,6 +441,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
   int r, m_tile, split, nsplit, kvh;
   int fused_slot = 0;
   float fused_posf = 0.f;
+  constexpr int SPEC_PAGES = FUSED ? 4 * NTHREADS : NTHREADS;   // block-table entries read ahead (fused mode)
+  int spec[SPEC_PAGES / NTHREADS];
+  int spec_n = 0;
   if constexpr (FUSED) {
     // grid (CS, requests, kv heads), clusters along x: no work list
     r = blockIdx.y;
@@ -450,6 +453,18 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     kvh = blockIdx.z;
     fused_slot = f.slots[r];    // requested together with the lengths: one round of loads
     fused_posf = (float)f.positions[r];
+    // ... and with them the head of the request's block table, before the lengths say which part
+    // of it this block needs: a context of up to SPEC_PAGES pages then costs one round of loads
+    // before its first key tile can be asked for, not two
+    spec_n = min(SPEC_PAGES, p.bt_stride);
+    {
+      const int32_t* row = p.block_table + (size_t)r * p.bt_stride;
+#pragma unroll
+      for (int j = 0; j < SPEC_PAGES / NTHREADS; ++j) {
+        const int i = (int)threadIdx.x + j * NTHREADS;
+        spec[j] = i < spec_n ? row[i] : -1;
+      }
+    }
     if (p.q_len[r] != 1) {      // an idle row of a captured step: the whole cluster leaves
       pdl_wait();
       pdl_launch_dependents();
@@ -522,8 +537,18 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
   const int blk_count = n_tiles > 0 ? (k_end - 1) / P - blk_first + 1 : 0;
   const bool pages_in_smem = blk_count <= MAX_SMEM_PAGES;
   const int pshift = (P & (P - 1)) == 0 ? 31 - __clz(P) : -1;   // pages of a power of two: shifts, no division
-  if (pages_in_smem)
+  // fused mode: the entries read ahead cover this block's range: they are the staged ids, from block 0 on
+  const bool spec_ok = FUSED && blk_first + blk_count <= spec_n;
+  const int page_base = spec_ok ? 0 : blk_first;      // s_pages[i] is block page_base + i
+  if (spec_ok) {
+#pragma unroll
+    for (int j = 0; j < SPEC_PAGES / NTHREADS; ++j) {
+      const int i = tid + j * NTHREADS;
+      if (i < spec_n) s_pages[i] = spec[j];
+    }
+  } else if (pages_in_smem) {
     for (int i = tid; i < blk_count; i += NTHREADS) s_pages[i] = bt[blk_first + i];
+  }
   if (tid == 0) {
     // one arrival a row of keys and of values, or one for the whole tile when it comes by pages
     for (int i = 0; i < NST; ++i) mbar_init(&s_full[i], by_page ? 1 : 2 * BN);
@@ -565,7 +590,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
           const int key0 = ts + box_key;
           const int blk = pshift >= 0 ? key0 >> pshift : key0 / P;
           int page = 0;
-          if (key0 < k_end && blk >= blk_first) page = pages_in_smem ? s_pages[blk - blk_first] : bt[blk];
+          if (key0 < k_end && blk >= blk_first) page = pages_in_smem ? s_pages[blk - page_base] : bt[blk];
           if (page < 0) page = 0;
           const int y = (page * KV + kvh) * P + (key0 - blk * P);
           tma_box(reinterpret_cast<unsigned char*>(Ks) + box_dst + buf * (tile_elems * 2), box_map, box_x, y, bar);
@@ -582,7 +607,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
       bool valid = key >= k_begin && key < k_end && !(FUSED && key == sl - 1);
       if (valid) {
         const int blk = pshift >= 0 ? key >> pshift : key / P;
-        const int page = pages_in_smem ? s_pages[blk - blk_first] : bt[blk];
+        const int page = pages_in_smem ? s_pages[blk - page_base] : bt[blk];
         valid = page >= 0;
         if (valid) {
           // 32-bit row index (pages x heads x page tokens stays far below 2^31), one wide multiply
