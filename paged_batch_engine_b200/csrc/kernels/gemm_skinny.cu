@@ -75,9 +75,17 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 #ifndef PBE_SKINNY_STAGES_SMALL
 #define PBE_SKINNY_STAGES_SMALL 14
 #endif
-// ring depth: by batch tiles and by the number of warps of the arrangement (8: big matrices)
-template <int NT, int WARPS> struct Stages {
-  static constexpr int value = NT == 1 ? (WARPS >= 8 ? PBE_SKINNY_STAGES_BIG : PBE_SKINNY_STAGES_SMALL) : 6;
+// The QKV and output projections of a step of one row: 10 (2.84 -> 2.79 ms a step; with two rows
+// and more the 14 of the other small products are the better: 2.87 against 2.90 ms at two rows, 3.06
+// against 3.13 at eight).
+#ifndef PBE_SKINNY_STAGES_SHORT
+#define PBE_SKINNY_STAGES_SHORT 10
+#endif
+// ring depth: by batch tiles, by the number of warps of the arrangement (8: big matrices) and, for
+// the small arrangement, SHORT: a short K and a single row
+template <int NT, int WARPS, bool SHORT = false> struct Stages {
+  static constexpr int value = NT == 1 ? (WARPS >= 8 ? PBE_SKINNY_STAGES_BIG
+                                                     : (SHORT ? PBE_SKINNY_STAGES_SHORT : PBE_SKINNY_STAGES_SMALL)) : 6;
 };
 
 // NT: batch tiles of 8 rows (M <= 8 * NT).  A block has WN x WK warps: WN weight-row tiles by
@@ -90,10 +98,10 @@ template <int NT, int WARPS> struct Stages {
 // STAGES-1 blocks ahead; a thread only ever reads the slots it filled itself, so the main
 // loop needs no barrier.  The first STAGES-1 weight blocks are requested before the
 // programmatic dependency on the previous kernel is awaited: weights do not depend on it.
-template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY>
+template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY, bool SHORT = false>
 __global__ void __launch_bounds__(WN * WK * 32)
 gemm_skinny_kernel(SkinnyParams p) {
-  constexpr int STAGES = Stages<NT, WN * WK>::value;
+  constexpr int STAGES = Stages<NT, WN * WK, SHORT>::value;
   constexpr int SLOT = 2 + NT;                       // 16-byte chunks per thread and stage
   extern __shared__ __align__(16) uint4 ring[];      // [WN * WK][STAGES][SLOT][32]
   __shared__ float red[WK][WN][NT][32][4];
@@ -252,16 +260,16 @@ gemm_skinny_kernel(SkinnyParams p) {
   }
 }
 
-template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY>
+template <int NT, int WN, int WK, int CL, bool SWIGLU, typename TY, bool SHORT = false>
 int launch_cfg(const SkinnyParams& p, int row_blocks, cudaStream_t stream) {
-  constexpr size_t smem = sizeof(uint4) * WN * WK * Stages<NT, WN * WK>::value * (2 + NT) * 32;
+  constexpr size_t smem = sizeof(uint4) * WN * WK * Stages<NT, WN * WK, SHORT>::value * (2 + NT) * 32;
   static bool opted = false;
   if (!opted) {
-    cudaFuncSetAttribute(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY>,
+    cudaFuncSetAttribute(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY, SHORT>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     opted = true;
   }
-  launch_k_cluster(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY>, row_blocks * CL, WN * WK * 32, smem, stream,
+  launch_k_cluster(gemm_skinny_kernel<NT, WN, WK, CL, SWIGLU, TY, SHORT>, row_blocks * CL, WN * WK * 32, smem, stream,
                    CL, p);
   return launch_status();
 }
@@ -274,6 +282,7 @@ int launch(const SkinnyParams& p, cudaStream_t stream) {
   // that splits K eight ways was slower by 10 % alone and equal in the step).
   const int tiles = p.tiles;
   if (tiles >= 148 * 8) return launch_cfg<NT, 2, 4, 1, SWIGLU, TY>(p, (tiles + 1) / 2, stream);
+  if (NT == 1 && p.K <= 4096 && p.M == 1) return launch_cfg<NT, 1, 4, 1, SWIGLU, TY, true>(p, tiles, stream);
   return launch_cfg<NT, 1, 4, 1, SWIGLU, TY>(p, tiles, stream);
 }
 }  // namespace
