@@ -137,8 +137,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // clock stamps of thread 0 of block (0,0,0): [16 + 8 tile + k]
 __device__ long long g_trace[1024];
 #define TRACE(ptr, k) do { if (ptr) (ptr)[k] = clock64(); } while (0)
+// phases of the whole kernel, slots 1..15: thread 0 of block (0,0,0)
+#define PHASE(k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_trace[k] = clock64(); } while (0)
 #else
 #define TRACE(ptr, k) do { } while (0)
+#define PHASE(k) do { } while (0)
 #endif
 
 // Where the 16-byte chunk `chunk` of row `row` of a key or value tile lies.  Padded layout: rows
@@ -416,6 +419,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
                 const __grid_constant__ CUtensorMap map_v) {
   constexpr bool KEYS = MODE != 0;
   constexpr bool FUSED = MODE == 2;
+  PHASE(1);                                  // entry
   constexpr int QROWS = KEYS ? 16 : BM;
   constexpr int BN = KEYS ? BN_KEYS : BN_ROWS;
   // Keys modes, head sizes in steps of 64, page sizes that divide the key tile (or the other
@@ -630,8 +634,10 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     // first key tiles are requested before the wait.
     const int pos = sl - 1;
     const bool owner = pos >= k_begin && pos < k_end;
+    PHASE(2);                                // lengths and page ids are there
     for (int i = 0; i < NST - 1; ++i)
       if (i < n_tiles) load_tile(tile0 + i * BN, i);
+    PHASE(3);                                // first tiles asked for
     // The new token's query heads (and, in the owner block, its key and value) from the fused
     // projection: bias, rotary position encoding (pairs i, i + hd/2; angle, sine, cosine and
     // rotation in float32, one rounding), as rope_kv.cu does.  What of that does not depend on
@@ -670,7 +676,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
         *reinterpret_cast<float4*>(dst + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
+    PHASE(4);                                // sines, cosines, biases done
     pdl_wait();
+    PHASE(5);                                // the projection is complete
     for (int c = tid; c < chunks_q + chunks_kv; c += NTHREADS) {      // the same chunks, by the same threads
       int col;
       float* dst;
@@ -719,6 +727,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     }
     fence_proxy_async();        // the scratch was written here and a tile's copies land on it next
     __syncthreads();            // Q is complete, the scratch is free
+    PHASE(6);                                // the new token is rotated, stored, staged
   } else {
     cp_async_commit();          // the Q tile
     if (n_tiles > 0) load_tile(tile0, 0);
@@ -874,6 +883,7 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
     TRACE(tr, 6);
   }
   pdl_launch_dependents();      // the keys and values are read: the next kernel may start launching
+  PHASE(7);                                  // all key tiles done
 
   const float LN2 = 0.6931471805599453f;
   if constexpr (KEYS) {
@@ -957,7 +967,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
       cg::cluster_group cluster = cg::this_cluster();
       float* cl_o = reinterpret_cast<float*>(Vs) + 256;
       float* cl_ml = cl_o + 16 * HD;
+      PHASE(8);                              // the four warps' results merged
       if constexpr (CS > 1) cluster.sync(); else __syncthreads();
+      PHASE(9);                              // every block of the cluster is there
       constexpr int SLICE = HD / CS;                                    // columns a block merges (HD % 16 == 0)
       constexpr int VEC = (SLICE % 4 == 0) ? 4 : 2;
       const int d0 = split * SLICE;
@@ -998,7 +1010,9 @@ attn_mma_kernel(AttnParams p, AttnFusedParams f, const __grid_constant__ CUtenso
         for (int e = 0; e < VEC; e += 2)
           *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
       }
+      PHASE(10);                             // the cluster's results merged and written
       if constexpr (CS > 1) cluster.sync();   // nobody leaves while its shared memory may still be read
+      PHASE(11);
     }
     return;
   }
